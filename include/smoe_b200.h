@@ -1,0 +1,154 @@
+/* C ABI of libsmoe_b200.so: the sm_100a kernels of the MoE layer forward/backward hot path.
+ *
+ * Conventions (all entry points):
+ *   - plain pointers to DEVICE memory owned by the caller, 64-bit sizes, a
+ *     cudaStream_t passed as void*; nothing is allocated, nothing synchronises:
+ *     work is enqueued on `stream` and the call returns.
+ *   - return value 0 (SMOE_OK) or a SMOE_ERR_* code for argument / launch errors
+ *     detected on the host.  Failures detected on the device (a bounded wait
+ *     that ran out) are written to the caller's `status` word (0 = ok).
+ *   - "ISA-packed" scales: for a logical (rows, cols) operand with one ue8m0
+ *     byte per 1x32 group, byte(row, g) lives at
+ *       ((row/128)*ceil(cols/128) + g/4)*512 + (row%32)*16 + ((row%128)/32)*4 + g%4.
+ *
+ * Each declaration cites the reference interface it replaces (paths inside
+ * PFCCLab/supersonic-moe).
+ */
+#ifndef SMOE_B200_H_
+#define SMOE_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  SMOE_OK = 0,
+  SMOE_ERR_SHAPE = 1,   /* a size violates the documented divisibility / range rules */
+  SMOE_ERR_ALIGN = 2,   /* a pointer or row pitch is not 16-byte aligned */
+  SMOE_ERR_DRIVER = 3,  /* cuTensorMapEncodeTiled could not be resolved */
+  SMOE_ERR_TMAP = 4,    /* tensor-map encoding failed */
+  SMOE_ERR_LAUNCH = 5,  /* kernel launch failed */
+  SMOE_ERR_ARG = 6      /* null pointer / unsupported option */
+};
+
+/* ---- routing metadata ---------------------------------------------------- */
+
+/* count[e] = #(ids == e) and its inclusive cumsum, int32.
+ * Replaces count_cumsum (sonicmoe/count_cumsum/__init__.py:20-35, kernel.cu:154-218).
+ * ids_is_int64: 0 = int32 ids, 1 = int64 ids.  cumsum may be null. */
+int smoe_count_cumsum(const void* ids, int ids_is_int64, int64_t n, int64_t E, int32_t* count, int32_t* cumsum,
+                      void* stream);
+
+/* Bytes of scratch smoe_topk_metadata needs for N rows and E experts. */
+int64_t smoe_topk_metadata_workspace(int64_t N, int64_t E);
+
+/* top-k indices/probs -> padded routing metadata, replaces deepep_topk_to_sonic_metadata
+ * (sonicmoe/ernie_compat/deepep_metadata.py:180-358, deepep_topk_metadata_cuda/kernel.cu:829-1191).
+ *   idx [N,K] int32 (valid iff 0 <= e < E, a row's valid experts distinct), probs [N,K] f32
+ *   efo [E+1], x_gather_idx [TKp_alloc], s_scatter_idx [TKp_alloc], s_reverse_scatter_idx [TK_alloc],
+ *   naept [N+1], topk_scores [TKp_alloc] f32, score_src_idx [TK_alloc], counts [E]
+ *   lane_order: 0 = a token's lanes by ascending expert id (kernel.cu:567-578),
+ *               1 = by top-k slot (dense path, functional/triton_kernels/__init__.py:66-155)
+ *   pad_mode:   0 = pad rows scatter to real_TK (kernel.cu:611-650),
+ *               1 = i-th pad row scatters to real_TK + i (functional/__init__.py:226-234) */
+int smoe_topk_metadata(const int32_t* idx, const float* probs, int64_t N, int64_t K, int64_t E, int64_t alignment,
+                       int64_t TK_alloc, int64_t TKp_alloc, int lane_order, int pad_mode, int32_t* efo,
+                       int32_t* x_gather_idx, int32_t* s_scatter_idx, int32_t* s_reverse_scatter_idx, int32_t* naept,
+                       float* topk_scores, int32_t* score_src_idx, int32_t* counts, void* workspace, void* stream);
+
+/* ---- MXFP8 1x32 ue8m0 quantizers ------------------------------------------ */
+
+/* Row-wise: x bf16 [M,K] -> e4m3 [M,K] + raw scales [M,K/32] and/or ISA-packed scales
+ * (either scale pointer may be null).  Replaces quantize_and_pack_activation
+ * (sonicmoe/quack_utils/blockscaled_fp8_gemm.py:3214-3283) and
+ * quantize_activation_blockscaled_fast (:518-596).  K % 32 == 0. */
+int smoe_quant_rows(const void* x_bf16, int64_t M, int64_t K, void* q, void* raw_scales, void* isa_scales,
+                    void* stream);
+
+/* raw row scales [T, cols/32] gathered to `rows` rows by idx, ISA layout for (rows, cols).
+ * Replaces _gather_1x32_scales_to_isa (sonicmoe/quack_utils/sm100_funcs.py:148-180). */
+int smoe_gather_scales_isa(const void* raw_scales, const int32_t* idx, int64_t rows, int64_t cols, void* isa_scales,
+                           void* stream);
+
+/* Column-wise (groups of 32 consecutive rows) of src[idx] (idx may be null): src bf16 [T,dim] ->
+ *   q_t  e4m3 [dim, rows]  (TRANSPOSED: the reduction dimension of the weight-gradient GEMM is contiguous)
+ *   isa  ISA-packed scales for the logical (dim, rows) operand.
+ * Replaces colwise_quantize_and_pack (sonicmoe/quack_utils/blockscaled_fp8_gemm.py:1517-1592,1824-1847);
+ * same bytes and scale bytes, transposed storage.  rows % 128 == 0, dim % 64 == 0. */
+int smoe_quant_cols_t(const void* src_bf16, const int32_t* idx, int64_t rows, int64_t dim, void* q_t, void* isa,
+                      void* stream);
+
+/* 32x32 block ("iso32") quantizer: dz bf16 [rows, cols] -> q e4m3 [rows, cols] + row-ISA scales for (rows, cols),
+ * q_t e4m3 [cols, rows] + col-ISA scales for (cols, rows).  Replaces dual_quantize_varlen iso32
+ * (sonicmoe/quack_utils/blockscaled_fp8_gemm.py:2052-2198).  rows % 128 == 0, cols % 128 == 0. */
+int smoe_quant_iso32(const void* x_bf16, int64_t rows, int64_t cols, void* q, void* row_isa, void* q_t, void* col_isa,
+                     void* stream);
+
+/* ---- grouped GEMMs (tcgen05 block-scaled) --------------------------------- */
+
+/* C[p,:] = A[p,:] . B[e(p)]^T for rows grouped by expert (segments 128-aligned), bf16 out.
+ * A e4m3 [rows,K] + ISA scales (rows,K); B e4m3 [E,N,K] + ISA scales (E*N,K).
+ * Replaces fp8_kernels.gemm -> blockscaled_fp8_gemm_varlen
+ * (sonicmoe/quack_utils/sm100_funcs.py:784-807, blockscaled_fp8_gemm.py:4563-4748). */
+int smoe_gemm_varlen_m(const void* a_fp8, const void* a_sf, const void* b_fp8, const void* b_sf, const int32_t* efo,
+                       void* c_bf16, int64_t rows, int64_t N, int64_t K, int64_t E, int32_t* status, void* stream);
+
+/* Up-projection: z = x[a_idx] . W1[e]^T (N = 2I, K = H), y1 = swiglu(z) on interleaved gate/up columns;
+ * z -> e4m3 [rows,N] + raw scales [rows,N/32] (amax floor 1e-4), y1 -> bf16 RNE -> e4m3 [rows,N/2] + ISA scales.
+ * Replaces gemm_gated (sonicmoe/quack_utils/sm100_funcs.py:207-455, gemm_sm100_fp8_zeromat.py:379-406,
+ * _gated_epilogues.py:1331-1513).  N % 256 == 0. */
+int smoe_gemm_gated(const void* x_fp8, int64_t T, const int32_t* a_idx, const void* a_sf, const void* w1_fp8,
+                    const void* w1_sf, const int32_t* efo, void* z_fp8, void* z_scales, void* y1_fp8, void* y1_sf,
+                    int64_t rows, int64_t N, int64_t K, int64_t E, int32_t* status, void* stream);
+
+/* Backward of the activation: D = dout[a_idx] . W2T[e]^T (N = I, K = H) and, against the saved e4m3 z,
+ * dz (bf16 [rows,2N]), y1s = s*y (bf16 [rows,N]) and per-column-tile partial sums of ds ([partials, rows] f32).
+ * Replaces gemm_dgated (sonicmoe/quack_utils/sm100_funcs.py:824-885, _gated_epilogues.py:2772-3000). */
+int smoe_gemm_dgated(const void* dout_fp8, int64_t T, const int32_t* a_idx, const void* a_sf, const void* w2t_fp8,
+                     const void* w2t_sf, const int32_t* efo, const void* z_fp8, const void* z_scales, const float* s,
+                     void* dz_bf16, void* y1s_bf16, float* ds_partial, int64_t* ds_partial_tiles, int64_t rows,
+                     int64_t N, int64_t K, int64_t E, int32_t* status, void* stream);
+int64_t smoe_gemm_dgated_partials(int64_t N);
+
+/* Weight gradient: C[e] (M x N, f32) (+)= A_t[:, seg_e] . B_t[:, seg_e]^T with A_t e4m3 [M,TKp], B_t e4m3 [N,TKp]
+ * and ISA scales for (M,TKp) / (N,TKp).  Replaces wgrad_gemm_varlen_k
+ * (sonicmoe/quack_utils/sm100_funcs.py:947-976, blockscaled_fp8_gemm.py:2210-2687). */
+int smoe_gemm_wgrad(const void* a_t_fp8, const void* a_sf, const void* b_t_fp8, const void* b_sf, const int32_t* efo,
+                    float* c, int64_t M, int64_t N, int64_t TKp, int64_t E, int accumulate, int32_t* status,
+                    void* stream);
+
+/* Test hook: force the GEMM column tile (128 or 256; 0 = automatic). */
+int smoe_debug_force_bn(int bn);
+
+/* ---- combine / router ------------------------------------------------------ */
+
+/* o[t,:] = sum_j w * y[s_rev[naept[t]+j], :] in ascending j, f32 accumulate, bf16 store; w = scores[naept[t]+j]
+ * when scores != null else 1.  Replaces token_gather_and_sum_varlen_K_triton
+ * (sonicmoe/functional/reduction_over_k_gather.py:99-196,340-395). */
+int smoe_combine(const void* y_bf16, const int32_t* s_rev, const int32_t* naept, const float* scores, void* out_bf16,
+                 int64_t T, int64_t H, void* stream);
+
+/* s[p] = scores[s_scatter_idx[p]] for p < rows (replaces the score gather of
+ * sonicmoe/functional/__init__.py:2105). */
+int smoe_gather_scores(const float* scores, const int32_t* s_scatter_idx, int64_t rows, float* s, void* stream);
+
+/* ds_tm[i] = sum_t ds_partial[t][s_rev[i]] for i < TK (replaces the partial-sum + permutation of
+ * sonicmoe/quack_utils/sm100_funcs.py:885 and functional/__init__.py:2384). */
+int smoe_ds_finalize(const float* ds_partial, int64_t partials, int64_t rows, const int32_t* s_rev, int64_t TK,
+                     float* ds_tm, void* stream);
+
+/* top-K of each row of logits [T,E] (f32) and softmax over the K selected values.
+ * Replaces _softmax_topk_fwd (sonicmoe/functional/forward.py:217-236, topk_softmax.py). */
+int smoe_topk_softmax(const float* logits, int64_t T, int64_t E, int64_t K, float* scores, int32_t* idx, void* stream);
+
+/* dlogits[t, idx[t,k]] = s_k (g_k - sum_j g_j s_j), zero elsewhere.
+ * Replaces _softmax_topk_bwd (sonicmoe/functional/backward.py:572-641). */
+int smoe_topk_softmax_bwd(const float* scores, const int32_t* idx, const float* dscores, int64_t T, int64_t E, int64_t K,
+                          float* dlogits, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SMOE_B200_H_ */

@@ -1,0 +1,157 @@
+// Host side of the MXFP8 grouped GEMMs: tensor-map construction and launches.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cudaTypedefs.h>
+
+#include <mutex>
+
+#include "gemm.cuh"
+#include "smoe_b200.h"
+
+namespace smoe {
+
+static PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+static std::once_flag g_encode_once;
+
+static bool load_encode() {
+  std::call_once(g_encode_once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &fn, 12000, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+  });
+  return g_encode != nullptr;
+}
+
+// 2D row-major uint8 tensor [rows, cols], box {box_cols, box_rows}, 128-byte swizzle.
+static int make_tmap_u8(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols,
+                        uint32_t box_rows) {
+  if (!load_encode()) return SMOE_ERR_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (cols & 15)) return SMOE_ERR_ALIGN;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? SMOE_OK : SMOE_ERR_TMAP;
+}
+
+static int g_force_bn = 0;
+static int g_sm_count = 0;
+
+static int sm_count() {
+  if (g_sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return g_sm_count;
+}
+
+template <int BN, int MODE>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int max_tiles,
+                  cudaStream_t stream) {
+  using S = GemmSmem<BN>;
+  static bool attr_set = false;
+  auto kern = gemm_mxf8_kernel<BN, MODE>;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL) != cudaSuccess)
+      return SMOE_ERR_LAUNCH;
+    attr_set = true;
+  }
+  int grid = sm_count();
+  if (max_tiles < grid) grid = max_tiles;
+  if (grid <= 0) return SMOE_OK;
+  kern<<<grid, kThreads, S::TOTAL, stream>>>(ta, tb, p);
+  return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
+}
+
+static int pick_bn(int64_t N) {
+  if (g_force_bn == 128 || g_force_bn == 256) return (N % g_force_bn == 0) ? g_force_bn : 128;
+  return (N % 256 == 0) ? 256 : 128;
+}
+
+template <int MODE>
+static int run(const void* a, int64_t a_rows, int64_t a_cols, const void* b, int64_t b_rows, int64_t b_cols,
+               GemmParams& p, int max_tiles_128, cudaStream_t stream) {
+  if (p.E > kMaxExpertsSmem) return SMOE_ERR_SHAPE;
+  const int bn = pick_bn(p.N);
+  CUtensorMap ta, tb;
+  constexpr bool gather = (MODE == GATED || MODE == DGATED);
+  int rc = make_tmap_u8(&ta, a, a_rows, a_cols, BK, gather ? 1 : BM);
+  if (rc) return rc;
+  rc = make_tmap_u8(&tb, b, b_rows, b_cols, BK, bn);
+  if (rc) return rc;
+  if (bn == 256) return launch<256, MODE>(ta, tb, p, max_tiles_128 / 2, stream);
+  return launch<128, MODE>(ta, tb, p, max_tiles_128, stream);
+}
+
+}  // namespace smoe
+
+using namespace smoe;
+
+extern "C" {
+
+int smoe_debug_force_bn(int bn) {
+  g_force_bn = bn;
+  return SMOE_OK;
+}
+
+int smoe_gemm_varlen_m(const void* a_fp8, const void* a_sf, const void* b_fp8, const void* b_sf, const int* efo,
+                       void* c_bf16, int64_t rows, int64_t N, int64_t K, int64_t E, int* status, void* stream) {
+  if (rows % 128 || N % 128 || K % 128 || E <= 0) return SMOE_ERR_SHAPE;
+  GemmParams p{};
+  p.rows = (int)rows; p.N = (int)N; p.K = (int)K; p.E = (int)E;
+  p.efo = efo; p.sfa = (const uint8_t*)a_sf; p.sfb = (const uint8_t*)b_sf;
+  p.sfa_ktiles = (int)(K / 128); p.sfb_ktiles = (int)(K / 128);
+  p.c = c_bf16; p.status = status;
+  return run<PLAIN>(a_fp8, rows, K, b_fp8, E * N, K, p, (int)((rows / 128) * (N / 128)), (cudaStream_t)stream);
+}
+
+int smoe_gemm_gated(const void* x_fp8, int64_t T, const int* a_idx, const void* a_sf, const void* w1_fp8,
+                    const void* w1_sf, const int* efo, void* z_fp8, void* z_scales, void* y1_fp8, void* y1_sf,
+                    int64_t rows, int64_t N, int64_t K, int64_t E, int* status, void* stream) {
+  if (rows % 128 || N % 256 || K % 128 || E <= 0 || T <= 0) return SMOE_ERR_SHAPE;
+  GemmParams p{};
+  p.rows = (int)rows; p.N = (int)N; p.K = (int)K; p.E = (int)E;
+  p.efo = efo; p.a_idx = a_idx; p.sfa = (const uint8_t*)a_sf; p.sfb = (const uint8_t*)w1_sf;
+  p.sfa_ktiles = (int)(K / 128); p.sfb_ktiles = (int)(K / 128);
+  p.z_fp8 = (uint8_t*)z_fp8; p.z_sc = (uint8_t*)z_scales; p.y1_fp8 = (uint8_t*)y1_fp8; p.y1_sf = (uint8_t*)y1_sf;
+  p.status = status;
+  return run<GATED>(x_fp8, T, K, w1_fp8, E * N, K, p, (int)((rows / 128) * (N / 128)), (cudaStream_t)stream);
+}
+
+int smoe_gemm_dgated(const void* dout_fp8, int64_t T, const int* a_idx, const void* a_sf, const void* w2t_fp8,
+                     const void* w2t_sf, const int* efo, const void* z_fp8, const void* z_scales, const float* s,
+                     void* dz_bf16, void* y1s_bf16, float* ds_partial, int64_t* ds_partial_tiles, int64_t rows,
+                     int64_t N, int64_t K, int64_t E, int* status, void* stream) {
+  if (rows % 128 || N % 128 || K % 128 || E <= 0 || T <= 0) return SMOE_ERR_SHAPE;
+  GemmParams p{};
+  p.rows = (int)rows; p.N = (int)N; p.K = (int)K; p.E = (int)E;
+  p.efo = efo; p.a_idx = a_idx; p.sfa = (const uint8_t*)a_sf; p.sfb = (const uint8_t*)w2t_sf;
+  p.sfa_ktiles = (int)(K / 128); p.sfb_ktiles = (int)(K / 128);
+  p.z_fp8 = (uint8_t*)const_cast<void*>(z_fp8); p.z_sc = (uint8_t*)const_cast<void*>(z_scales);
+  p.s = s; p.dz = dz_bf16; p.y1s = y1s_bf16; p.ds_partial = ds_partial; p.status = status;
+  if (ds_partial_tiles) *ds_partial_tiles = N / pick_bn(N);
+  return run<DGATED>(dout_fp8, T, K, w2t_fp8, E * N, K, p, (int)((rows / 128) * (N / 128)), (cudaStream_t)stream);
+}
+
+int64_t smoe_gemm_dgated_partials(int64_t N) { return N / pick_bn(N); }
+
+int smoe_gemm_wgrad(const void* a_t_fp8, const void* a_sf, const void* b_t_fp8, const void* b_sf, const int* efo,
+                    float* c, int64_t M, int64_t N, int64_t TKp, int64_t E, int accumulate, int* status,
+                    void* stream) {
+  if (M % 128 || N % 128 || TKp % 128 || E <= 0) return SMOE_ERR_SHAPE;
+  GemmParams p{};
+  p.rows = (int)M; p.N = (int)N; p.K = (int)TKp; p.E = (int)E;
+  p.efo = efo; p.sfa = (const uint8_t*)a_sf; p.sfb = (const uint8_t*)b_sf;
+  p.sfa_ktiles = (int)(TKp / 128); p.sfb_ktiles = (int)(TKp / 128);
+  p.c = c; p.accumulate = accumulate; p.status = status;
+  return run<WGRAD>(a_t_fp8, M, TKp, b_t_fp8, N, TKp, p, (int)(E * (M / 128) * (N / 128)), (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,269 @@
+// MXFP8 1x32 ue8m0 block-scaled quantizers (HBM-bound; 128-bit global accesses,
+// warp-shuffle amax, 32-bit packed scale stores).
+//
+// Rule for one group of 32 values (amax = max |v|):
+//   e8m0 = max(bexp(amax) - 8 + (mantissa(amax) > 0x600000), 0), 0 for zero/denormal amax
+//   q    = cvt.rn.satfinite.e4m3( v * 2^(127 - e8m0) )
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "smoe_b200.h"
+
+namespace smoe {
+
+__device__ __forceinline__ int q_e8m0_of(float amax) {
+  const int bits = __float_as_int(amax);
+  const int bexp = (bits >> 23) & 0xFF;
+  const int e = bexp - 8 + ((bits & 0x7FFFFF) > 0x600000 ? 1 : 0);
+  return bexp > 0 ? max(e, 0) : 0;
+}
+__device__ __forceinline__ float q_scale_of(int e8m0) {
+  return __int_as_float(min(max(254 - e8m0, 1), 254) << 23);
+}
+__device__ __forceinline__ uint32_t q_pack4(float a, float b, float c, float d) {
+  uint16_t lo, hi;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
+  return (uint32_t)lo | ((uint32_t)hi << 16);
+}
+__device__ __forceinline__ void bf16x8_to_f32(const uint4& v, float (&f)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+__device__ __forceinline__ size_t isa_offset(size_t row, size_t g, size_t k_tiles) {
+  return ((row >> 7) * k_tiles + (g >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (g & 3);
+}
+
+// --------------------------------------------------------------------- rows
+// One warp per row; a lane owns 8 consecutive values, 4 lanes form a group.
+__global__ void __launch_bounds__(256)
+quant_rows_kernel(const uint4* __restrict__ x, int64_t M, int K, uint2* __restrict__ q, uint8_t* __restrict__ raw,
+                  uint8_t* __restrict__ isa) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = blockIdx.x * (int64_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const int groups = K / 32, k_tiles = (K + 127) / 128;
+  for (int64_t row = warp0; row < M; row += nwarps) {
+    for (int c0 = 0; c0 < K; c0 += 256) {
+      const int col = c0 + lane * 8;
+      const bool in = col < K;
+      float f[8];
+      if (in) {
+        bf16x8_to_f32(x[(row * K + col) >> 3], f);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = 0.f;
+      }
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffff, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffff, amax, 2));
+      const int e = q_e8m0_of(amax);
+      const float qs = q_scale_of(e);
+      if (in) {
+        uint2 o;
+        o.x = q_pack4(f[0] * qs, f[1] * qs, f[2] * qs, f[3] * qs);
+        o.y = q_pack4(f[4] * qs, f[5] * qs, f[6] * qs, f[7] * qs);
+        q[(row * K + col) >> 3] = o;
+      }
+      // gather the 4 group bytes of a 128-column tile into one word (lanes 0 and 16)
+      const uint32_t b1 = __shfl_down_sync(0xffffffff, (uint32_t)e, 4);
+      const uint32_t b2 = __shfl_down_sync(0xffffffff, (uint32_t)e, 8);
+      const uint32_t b3 = __shfl_down_sync(0xffffffff, (uint32_t)e, 12);
+      const int g = col >> 5;
+      if (in && (lane & 15) == 0) {
+        const uint32_t word = (uint32_t)e | (b1 << 8) | (b2 << 16) | (b3 << 24);
+        if (g + 3 < groups) {
+          if (raw) *reinterpret_cast<uint32_t*>(raw + row * groups + g) = word;
+          if (isa) *reinterpret_cast<uint32_t*>(isa + isa_offset(row, g, k_tiles)) = word;
+        } else {
+          for (int j = 0; g + j < groups; ++j) {
+            const uint8_t b = (uint8_t)(word >> (8 * j));
+            if (raw) raw[row * groups + g + j] = b;
+            if (isa) isa[isa_offset(row, g + j, k_tiles)] = b;
+          }
+        }
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------- scale gather
+__global__ void __launch_bounds__(256)
+gather_scales_isa_kernel(const uint8_t* __restrict__ raw, const int* __restrict__ idx, int64_t rows, int groups,
+                         int k_tiles, uint8_t* __restrict__ isa) {
+  const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i >= rows * k_tiles) return;
+  const int64_t row = i / k_tiles;
+  const int kt = (int)(i - row * k_tiles);
+  const int64_t src = idx ? idx[row] : row;
+  uint32_t word;
+  if (kt * 4 + 3 < groups && (groups & 3) == 0) {
+    word = *reinterpret_cast<const uint32_t*>(raw + src * groups + kt * 4);
+  } else {
+    word = 0x7F7F7F7Fu;
+    for (int j = 0; kt * 4 + j < groups && j < 4; ++j)
+      word = (word & ~(0xFFu << (8 * j))) | ((uint32_t)raw[src * groups + kt * 4 + j] << (8 * j));
+  }
+  *reinterpret_cast<uint32_t*>(isa + isa_offset(row, (size_t)kt * 4, k_tiles)) = word;
+}
+
+// ------------------------------------------------------------------ columns
+// Tile = 128 rows x 64 columns of src[idx].  Groups run down the rows; the
+// e4m3 bytes are written transposed ([dim, rows]) so that the reduction
+// dimension of the weight-gradient GEMM is contiguous.
+constexpr int CT_ROWS = 128, CT_COLS = 64, CT_PITCH = CT_COLS + 2;
+
+// ISO: one scale per 32x32 block (also emits the non-transposed bytes and the
+// row-direction scales); otherwise one scale per (column, 32 rows).
+template <bool ISO>
+__global__ void __launch_bounds__(256)
+quant_cols_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ idx, int64_t rows, int dim,
+                  uint8_t* __restrict__ q_t, uint8_t* __restrict__ col_isa, uint8_t* __restrict__ q,
+                  uint8_t* __restrict__ row_isa) {
+  __shared__ __nv_bfloat16 s_in[CT_ROWS][CT_PITCH];
+  __shared__ __align__(16) uint8_t s_out[CT_COLS][CT_ROWS + 16];
+  __shared__ uint32_t s_sc[CT_COLS];
+  const int tid = threadIdx.x;
+  const int64_t r0 = (int64_t)blockIdx.x * CT_ROWS;
+  const int c0 = blockIdx.y * CT_COLS;
+
+  // load: 8 threads x 16 bytes cover one 64-column row; 32 rows per pass
+  {
+    const int rr = tid >> 3, cc = (tid & 7) * 8;
+#pragma unroll
+    for (int pass = 0; pass < 4; ++pass) {
+      const int r = pass * 32 + rr;
+      const int64_t srow = idx ? idx[r0 + r] : (r0 + r);
+      const uint4 v = *reinterpret_cast<const uint4*>(src + srow * dim + c0 + cc);
+      uint32_t* d = reinterpret_cast<uint32_t*>(&s_in[r][cc]);
+      d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
+    }
+  }
+  __syncthreads();
+
+  const int c = tid & 63, g = tid >> 6;        // column, 32-row group
+  float v[32];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    v[i] = __bfloat162float(s_in[g * 32 + i][c]);
+    amax = fmaxf(amax, fabsf(v[i]));
+  }
+  if (ISO) {  // block amax over the 32 columns of this warp
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffff, amax, d));
+  }
+  const int e = q_e8m0_of(amax);
+  const float qs = q_scale_of(e);
+  uint32_t w[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) w[i] = q_pack4(v[4 * i] * qs, v[4 * i + 1] * qs, v[4 * i + 2] * qs, v[4 * i + 3] * qs);
+  uint4* so = reinterpret_cast<uint4*>(&s_out[c][g * 32]);
+  so[0] = make_uint4(w[0], w[1], w[2], w[3]);
+  so[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  if (g == 0) s_sc[c] = 0;
+  __syncthreads();
+  atomicOr(&s_sc[c], (uint32_t)e << (8 * g));   // distinct bits per thread: order-free
+  __syncthreads();
+
+  // transposed bytes: 8 threads x 16 bytes cover one 128-byte row of s_out
+  {
+    const int cc = tid >> 3, seg = (tid & 7) * 16;
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+      const int col = pass * 32 + cc;
+      *reinterpret_cast<uint4*>(q_t + (size_t)(c0 + col) * rows + r0 + seg) =
+          *reinterpret_cast<const uint4*>(&s_out[col][seg]);
+    }
+  }
+  // column scales: logical operand (dim, rows); one word = the 4 groups of this 128-row tile
+  if (tid < CT_COLS) {
+    const size_t col = c0 + tid;
+    *reinterpret_cast<uint32_t*>(col_isa + isa_offset(col, (size_t)(r0 >> 5), (size_t)(rows >> 7))) = s_sc[tid];
+  }
+  if (ISO) {
+    // non-transposed bytes: thread -> (row, 32-byte half of the 64 columns)
+    const int r = tid >> 1, h = tid & 1;
+    uint32_t o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int cc = h * 32 + i * 4;
+      o[i] = (uint32_t)s_out[cc][r] | ((uint32_t)s_out[cc + 1][r] << 8) | ((uint32_t)s_out[cc + 2][r] << 16) |
+             ((uint32_t)s_out[cc + 3][r] << 24);
+    }
+    uint4* dst = reinterpret_cast<uint4*>(q + (size_t)(r0 + r) * dim + c0 + h * 32);
+    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+    dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    // row scales: logical operand (rows, dim); this tile holds groups c0/32 and c0/32+1 of 128 rows
+    if (tid < CT_ROWS) {
+      const size_t row = r0 + tid;
+      const int gr = tid >> 5;
+      const int k_tiles = dim >> 7;
+      const int g0 = c0 >> 5;
+      const uint8_t b0 = (uint8_t)(s_sc[0] >> (8 * gr));
+      const uint8_t b1 = (uint8_t)(s_sc[32] >> (8 * gr));
+      *reinterpret_cast<uint16_t*>(row_isa + isa_offset(row, g0, k_tiles)) = (uint16_t)b0 | ((uint16_t)b1 << 8);
+    }
+  }
+}
+
+}  // namespace smoe
+
+using namespace smoe;
+
+extern "C" {
+
+int smoe_quant_rows(const void* x_bf16, int64_t M, int64_t K, void* q, void* raw_scales, void* isa_scales,
+                    void* stream) {
+  if (M < 0 || K <= 0 || K % 32) return SMOE_ERR_SHAPE;
+  if (isa_scales && K % 128) return SMOE_ERR_SHAPE;
+  if (K % 8 || ((uintptr_t)x_bf16 & 15) || ((uintptr_t)q & 7)) return SMOE_ERR_ALIGN;
+  if (M == 0) return SMOE_OK;
+  int64_t blocks = (M + 7) / 8;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  quant_rows_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>((const uint4*)x_bf16, M, (int)K, (uint2*)q,
+                                                                   (uint8_t*)raw_scales, (uint8_t*)isa_scales);
+  return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
+}
+
+int smoe_gather_scales_isa(const void* raw_scales, const int32_t* idx, int64_t rows, int64_t cols, void* isa_scales,
+                           void* stream) {
+  if (rows < 0 || cols <= 0 || cols % 32) return SMOE_ERR_SHAPE;
+  if (rows == 0) return SMOE_OK;
+  const int groups = (int)(cols / 32), k_tiles = (int)((cols + 127) / 128);
+  const int64_t n = rows * k_tiles;
+  gather_scales_isa_kernel<<<(int)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      (const uint8_t*)raw_scales, idx, rows, groups, k_tiles, (uint8_t*)isa_scales);
+  return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
+}
+
+int smoe_quant_cols_t(const void* src_bf16, const int32_t* idx, int64_t rows, int64_t dim, void* q_t, void* isa,
+                      void* stream) {
+  if (rows < 0 || rows % 128 || dim <= 0 || dim % 64) return SMOE_ERR_SHAPE;
+  if (rows == 0) return SMOE_OK;
+  dim3 grid((unsigned)(rows / CT_ROWS), (unsigned)(dim / CT_COLS));
+  quant_cols_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)src_bf16, idx, rows, (int)dim,
+                                                                   (uint8_t*)q_t, (uint8_t*)isa, nullptr, nullptr);
+  return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
+}
+
+int smoe_quant_iso32(const void* x_bf16, int64_t rows, int64_t cols, void* q, void* row_isa, void* q_t, void* col_isa,
+                     void* stream) {
+  if (rows < 0 || rows % 128 || cols <= 0 || cols % 128) return SMOE_ERR_SHAPE;
+  if (rows == 0) return SMOE_OK;
+  dim3 grid((unsigned)(rows / CT_ROWS), (unsigned)(cols / CT_COLS));
+  quant_cols_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x_bf16, nullptr, rows,
+                                                                  (int)cols, (uint8_t*)q_t, (uint8_t*)col_isa,
+                                                                  (uint8_t*)q, (uint8_t*)row_isa);
+  return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
+}
+
+}  // extern "C"

@@ -1,0 +1,234 @@
+"""Tensor-level wrappers over the C ABI: allocate outputs with the caching
+allocator, pass raw device pointers and the current stream.  CUDA tensors only;
+there is no CPU path.
+"""
+from __future__ import annotations
+
+import torch
+
+from ._lib import check, lib
+
+_U8 = torch.uint8
+_I32 = torch.int32
+
+
+def _p(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("sonicmoe kernels need CUDA tensors (no CPU fallback)")
+        if t is not None and not t.is_contiguous():
+            raise RuntimeError("sonicmoe kernels need contiguous tensors")
+
+
+def isa_bytes(rows: int, cols: int) -> int:
+    return -(-rows // 128) * -(-cols // 128) * 512
+
+
+_status = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device int32 word the GEMM kernels write a failure code into (0 = ok)."""
+    key = torch.device(device).index
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=_I32, device=device)
+    return _status[key]
+
+
+def check_status(device):
+    s = int(status_word(device).item())
+    if s != 0:
+        status_word(device).zero_()
+        raise RuntimeError(f"sonicmoe GEMM kernel reported device failure code {s} (a bounded wait ran out)")
+
+
+# ---------------------------------------------------------------- routing
+def count_cumsum(x: torch.Tensor, E: int, do_cumsum: bool = True):
+    _cuda(x)
+    if x.dtype not in (torch.int32, torch.int64):
+        raise ValueError(f"count_cumsum: expected int32/int64 ids, got {x.dtype}")
+    count = torch.empty(E, dtype=_I32, device=x.device)
+    cum = torch.empty(E, dtype=_I32, device=x.device) if do_cumsum else None
+    check(lib.smoe_count_cumsum(_p(x), int(x.dtype == torch.int64), x.numel(), E, _p(count), _p(cum), _stream()),
+          "count_cumsum")
+    return (count, cum) if do_cumsum else count
+
+
+def topk_metadata(idx, probs, E, alignment=128, TK_alloc=None, TKp_alloc=None, lane_order=0, pad_mode=0):
+    """Returns dict(efo, x_gather_idx, s_scatter_idx, s_reverse_scatter_idx, naept, topk_scores,
+    score_src_idx, counts).  Default sizing is the sync-free upper bound."""
+    _cuda(idx, probs)
+    if idx.dtype != _I32:
+        raise ValueError(f"dispatched_indices: expected int32, got {idx.dtype}")
+    if probs.dtype != torch.float32:
+        raise ValueError(f"dispatched_probs: expected float32, got {probs.dtype}")
+    if idx.ndim != 2 or probs.shape != idx.shape:
+        raise ValueError(f"shape mismatch: indices={tuple(idx.shape)} vs probs={tuple(probs.shape)}")
+    N, K = idx.shape
+    if TK_alloc is None:
+        TK_alloc = N * min(K, E)
+    if TKp_alloc is None:
+        TKp_alloc = -(-TK_alloc // alignment) * alignment + E * alignment
+    dev = idx.device
+    e = lambda n, dt=_I32: torch.empty(max(int(n), 0), dtype=dt, device=dev)
+    out = dict(efo=e(E + 1), x_gather_idx=e(TKp_alloc), s_scatter_idx=e(TKp_alloc),
+               s_reverse_scatter_idx=e(TK_alloc), naept=e(N + 1), topk_scores=e(TKp_alloc, torch.float32),
+               score_src_idx=e(TK_alloc), counts=e(E))
+    ws = e(lib.smoe_topk_metadata_workspace(N, E), _U8)
+    check(lib.smoe_topk_metadata(_p(idx), _p(probs), N, K, E, alignment, TK_alloc, TKp_alloc, lane_order, pad_mode,
+                                 _p(out["efo"]), _p(out["x_gather_idx"]), _p(out["s_scatter_idx"]),
+                                 _p(out["s_reverse_scatter_idx"]), _p(out["naept"]), _p(out["topk_scores"]),
+                                 _p(out["score_src_idx"]), _p(out["counts"]), _p(ws), _stream()), "topk_metadata")
+    out["TK_alloc"], out["TKp_alloc"] = TK_alloc, TKp_alloc
+    return out
+
+
+# ---------------------------------------------------------------- quantizers
+def quant_rows(x, raw=True, isa=False):
+    """bf16 [M,K] -> (e4m3 bytes [M,K] u8, raw scales [M,K/32] u8 | None, ISA scales u8 | None)."""
+    _cuda(x)
+    assert x.dtype == torch.bfloat16 and x.ndim == 2
+    M, K = x.shape
+    q = torch.empty(M, K, dtype=_U8, device=x.device)
+    r = torch.empty(M, K // 32, dtype=_U8, device=x.device) if raw else None
+    i = torch.empty(isa_bytes(M, K), dtype=_U8, device=x.device) if isa else None
+    check(lib.smoe_quant_rows(_p(x), M, K, _p(q), _p(r), _p(i), _stream()), "quant_rows")
+    return q, r, i
+
+
+def gather_scales_isa(raw, idx, rows, cols):
+    _cuda(raw, idx)
+    out = torch.empty(isa_bytes(rows, cols), dtype=_U8, device=raw.device)
+    check(lib.smoe_gather_scales_isa(_p(raw), _p(idx), rows, cols, _p(out), _stream()), "gather_scales_isa")
+    return out
+
+
+def quant_cols_t(src, idx, rows):
+    """bf16 [T,dim] (rows gathered by idx, or None) -> (e4m3 bytes [dim, rows], ISA scales for (dim, rows))."""
+    _cuda(src, idx)
+    assert src.dtype == torch.bfloat16
+    dim = src.shape[1]
+    q_t = torch.empty(dim, rows, dtype=_U8, device=src.device)
+    isa = torch.empty(isa_bytes(dim, rows), dtype=_U8, device=src.device)
+    check(lib.smoe_quant_cols_t(_p(src), _p(idx), rows, dim, _p(q_t), _p(isa), _stream()), "quant_cols_t")
+    return q_t, isa
+
+
+def quant_iso32(x):
+    """bf16 [rows, cols] -> (q [rows,cols], row ISA, q_t [cols,rows], col ISA)."""
+    _cuda(x)
+    assert x.dtype == torch.bfloat16
+    rows, cols = x.shape
+    dev = x.device
+    q = torch.empty(rows, cols, dtype=_U8, device=dev)
+    q_t = torch.empty(cols, rows, dtype=_U8, device=dev)
+    ri = torch.empty(isa_bytes(rows, cols), dtype=_U8, device=dev)
+    ci = torch.empty(isa_bytes(cols, rows), dtype=_U8, device=dev)
+    check(lib.smoe_quant_iso32(_p(x), rows, cols, _p(q), _p(ri), _p(q_t), _p(ci), _stream()), "quant_iso32")
+    return q, ri, q_t, ci
+
+
+# ---------------------------------------------------------------- GEMMs
+def gemm_varlen_m(a_q, a_sf, b_q, b_sf, efo):
+    """a_q u8 [rows,K], b_q u8 [E,N,K] -> bf16 [rows,N]."""
+    _cuda(a_q, a_sf, b_q, b_sf, efo)
+    rows, K = a_q.shape
+    E, N, _ = b_q.shape
+    c = torch.empty(rows, N, dtype=torch.bfloat16, device=a_q.device)
+    check(lib.smoe_gemm_varlen_m(_p(a_q), _p(a_sf), _p(b_q), _p(b_sf), _p(efo), _p(c), rows, N, K, E,
+                                 _p(status_word(a_q.device)), _stream()), "gemm_varlen_m")
+    return c
+
+
+def gemm_gated(x_q, a_idx, a_sf, w1_q, w1_sf, efo, rows):
+    """x_q u8 [T,H], w1_q u8 [E,2I,H] -> z_q [rows,2I], z_sc [rows,2I/32], y1_q [rows,I], y1_sf (ISA)."""
+    _cuda(x_q, a_idx, a_sf, w1_q, w1_sf, efo)
+    T, K = x_q.shape
+    E, N, _ = w1_q.shape
+    dev = x_q.device
+    z_q = torch.empty(rows, N, dtype=_U8, device=dev)
+    z_sc = torch.empty(rows, N // 32, dtype=_U8, device=dev)
+    y1_q = torch.empty(rows, N // 2, dtype=_U8, device=dev)
+    y1_sf = torch.empty(isa_bytes(rows, N // 2), dtype=_U8, device=dev)
+    check(lib.smoe_gemm_gated(_p(x_q), T, _p(a_idx), _p(a_sf), _p(w1_q), _p(w1_sf), _p(efo), _p(z_q), _p(z_sc),
+                              _p(y1_q), _p(y1_sf), rows, N, K, E, _p(status_word(dev)), _stream()), "gemm_gated")
+    return z_q, z_sc, y1_q, y1_sf
+
+
+def gemm_dgated(dout_q, a_idx, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, rows):
+    """dout_q u8 [T,H], w2t_q u8 [E,I,H] -> dz bf16 [rows,2I], y1s bf16 [rows,I], ds_partial f32 [parts, rows]."""
+    _cuda(dout_q, a_idx, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s)
+    T, K = dout_q.shape
+    E, N, _ = w2t_q.shape
+    dev = dout_q.device
+    parts = lib.smoe_gemm_dgated_partials(N)
+    dz = torch.empty(rows, 2 * N, dtype=torch.bfloat16, device=dev)
+    y1s = torch.empty(rows, N, dtype=torch.bfloat16, device=dev)
+    dsp = torch.zeros(parts, rows, dtype=torch.float32, device=dev)
+    check(lib.smoe_gemm_dgated(_p(dout_q), T, _p(a_idx), _p(a_sf), _p(w2t_q), _p(w2t_sf), _p(efo), _p(z_q), _p(z_sc),
+                               _p(s), _p(dz), _p(y1s), _p(dsp), None, rows, N, K, E, _p(status_word(dev)),
+                               _stream()), "gemm_dgated")
+    return dz, y1s, dsp
+
+
+def gemm_wgrad(a_t, a_sf, b_t, b_sf, efo, out, accumulate):
+    """a_t u8 [M,TKp], b_t u8 [N,TKp]; out f32 [E,M,N] (+)= per-expert products."""
+    _cuda(a_t, a_sf, b_t, b_sf, efo, out)
+    M, TKp = a_t.shape
+    N = b_t.shape[0]
+    E = out.shape[0]
+    assert out.dtype == torch.float32 and out.shape == (E, M, N)
+    check(lib.smoe_gemm_wgrad(_p(a_t), _p(a_sf), _p(b_t), _p(b_sf), _p(efo), _p(out), M, N, TKp, E, int(accumulate),
+                              _p(status_word(a_t.device)), _stream()), "gemm_wgrad")
+    return out
+
+
+# ---------------------------------------------------------------- token side
+def combine(y, s_rev, naept, scores, T):
+    _cuda(y, s_rev, naept, scores)
+    H = y.shape[1]
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=y.device)
+    check(lib.smoe_combine(_p(y), _p(s_rev), _p(naept), _p(scores), _p(out), T, H, _stream()), "combine")
+    return out
+
+
+def gather_scores(scores, s_scatter_idx):
+    _cuda(scores, s_scatter_idx)
+    rows = s_scatter_idx.numel()
+    s = torch.empty(rows, dtype=torch.float32, device=scores.device)
+    check(lib.smoe_gather_scores(_p(scores), _p(s_scatter_idx), rows, _p(s), _stream()), "gather_scores")
+    return s
+
+
+def ds_finalize(ds_partial, s_rev, TK):
+    _cuda(ds_partial, s_rev)
+    parts, rows = ds_partial.shape
+    out = torch.empty(TK, dtype=torch.float32, device=ds_partial.device)
+    check(lib.smoe_ds_finalize(_p(ds_partial), parts, rows, _p(s_rev), TK, _p(out), _stream()), "ds_finalize")
+    return out
+
+
+def topk_softmax(logits, K):
+    _cuda(logits)
+    assert logits.dtype == torch.float32 and logits.ndim == 2
+    T, E = logits.shape
+    scores = torch.empty(T, K, dtype=torch.float32, device=logits.device)
+    idx = torch.empty(T, K, dtype=_I32, device=logits.device)
+    check(lib.smoe_topk_softmax(_p(logits), T, E, K, _p(scores), _p(idx), _stream()), "topk_softmax")
+    return scores, idx
+
+
+def topk_softmax_bwd(scores, idx, dscores, E):
+    _cuda(scores, idx, dscores)
+    T, K = scores.shape
+    out = torch.empty(T, E, dtype=torch.float32, device=scores.device)
+    check(lib.smoe_topk_softmax_bwd(_p(scores), _p(idx), _p(dscores), T, E, K, _p(out), _stream()), "topk_softmax_bwd")
+    return out

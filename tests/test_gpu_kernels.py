@@ -1,0 +1,331 @@
+"""GPU parity tests of the individual kernels (through the C ABI) against the CPU oracle."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe as OM
+from oracle import quant as Q
+from oracle import routing as R
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from sonicmoe import ops as _ops
+    return _ops
+
+
+DEV = "cuda"
+
+
+def make_routing(N, K, E, p_mask=0.0, seed=0, skew=False):
+    g = torch.Generator().manual_seed(seed)
+    logits = torch.randn(N, E, generator=g)
+    if skew:
+        p = torch.arange(1, E + 1, dtype=torch.float32) ** -1.2
+        logits = logits + torch.log(p / p.sum())[torch.randperm(E, generator=g)]
+    idx = logits.topk(K, dim=-1).indices.to(torch.int32)
+    if p_mask > 0:
+        idx = torch.where(torch.rand(N, K, generator=g) < p_mask, torch.full_like(idx, -1), idx)
+    probs = torch.rand(N, K, generator=g, dtype=torch.float32)
+    return idx, probs
+
+
+MD_KEYS = ["efo", "x_gather_idx", "s_scatter_idx", "s_reverse_scatter_idx", "naept", "topk_scores", "score_src_idx",
+           "counts"]
+
+
+@pytest.mark.parametrize("N,K,E,p_mask,skew", [
+    (256, 2, 8, 0.0, False), (8192, 8, 8, 0.0, False), (4096, 8, 128, 0.0, True), (1000, 8, 64, 0.4, False),
+    (1, 8, 16, 0.0, False), (77, 6, 6, 1.0, False), (33, 4, 4, 0.9, False), (0, 4, 8, 0.0, False),
+    (2048, 16, 256, 0.2, True)])
+@pytest.mark.parametrize("lane_order,pad_mode", [(0, 0), (1, 1)])
+def test_topk_metadata_bit_exact(ops, N, K, E, p_mask, skew, lane_order, pad_mode):
+    idx, probs = make_routing(N, K, E, p_mask, seed=N + K + E, skew=skew)
+    got = ops.topk_metadata(idx.to(DEV), probs.to(DEV), E, 128, lane_order=lane_order, pad_mode=pad_mode)
+    ref = R.topk_metadata(idx, probs, E, 128, TK_alloc=got["TK_alloc"], TKp_alloc=got["TKp_alloc"],
+                          lane_order=["expert", "slot"][lane_order], pad_mode=["sentinel", "virtual"][pad_mode])
+    for k in MD_KEYS:
+        assert torch.equal(got[k].cpu(), ref[k]), k
+    # exact sizing too
+    got = ops.topk_metadata(idx.to(DEV), probs.to(DEV), E, 128, TK_alloc=ref["real_TK"], TKp_alloc=ref["real_TKp"],
+                            lane_order=lane_order, pad_mode=pad_mode)
+    ref = R.topk_metadata(idx, probs, E, 128, lane_order=["expert", "slot"][lane_order],
+                          pad_mode=["sentinel", "virtual"][pad_mode])
+    for k in MD_KEYS:
+        assert torch.equal(got[k].cpu(), ref[k]), k
+
+
+def test_topk_metadata_alignment_one(ops):
+    idx, probs = make_routing(500, 4, 16, 0.1, seed=9)
+    got = ops.topk_metadata(idx.to(DEV), probs.to(DEV), 16, 1)
+    ref = R.topk_metadata(idx, probs, 16, 1, TK_alloc=got["TK_alloc"], TKp_alloc=got["TKp_alloc"])
+    for k in MD_KEYS:
+        assert torch.equal(got[k].cpu(), ref[k]), k
+
+
+@pytest.mark.parametrize("n,E,dt", [(65536, 8, torch.int32), (1000, 128, torch.int64), (0, 4, torch.int32),
+                                    (131072, 50000, torch.int32)])
+def test_count_cumsum(ops, n, E, dt):
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, E, (n,), generator=g).to(dt)
+    c, cs = ops.count_cumsum(ids.to(DEV), E)
+    rc, rcs = R.count_cumsum(ids, E)
+    assert torch.equal(c.cpu(), rc) and torch.equal(cs.cpu(), rcs)
+
+
+def adversarial_rows(M, K, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, K, generator=g)
+    x[0] = 0.0                                     # all-zero groups -> scale byte 0
+    x[1, :32] = 0.0
+    x[1, 5] = 1.75 * 2.0 ** 3                      # exactly at the carry threshold
+    x[2, :32] = 0.0
+    x[2, 7] = 1.875 * 2.0 ** -5                    # just above it
+    x[3] *= 1e-30                                  # tiny
+    x[4] *= 1e30                                   # huge
+    x[5, 3] = 448.0 * 2.0 ** 4
+    x[6] *= 1e-3
+    x[7, ::3] = 0.0
+    return x.to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("M,K", [(256, 256), (8192, 3072), (100, 128), (64, 1536)])
+def test_quant_rows_bit_exact(ops, M, K):
+    x = adversarial_rows(M, K, M + K)
+    q, raw, isa = ops.quant_rows(x.to(DEV), raw=True, isa=True)
+    rq, rs = Q.row_quant(x)
+    assert torch.equal(q.cpu(), rq)
+    assert torch.equal(raw.cpu(), rs)
+    assert torch.equal(Q.unpack_isa(isa.cpu(), M, K), rs)
+
+
+def test_gather_scales_isa(ops):
+    T, K, rows = 300, 512, 1024
+    g = torch.Generator().manual_seed(3)
+    raw = torch.randint(0, 256, (T, K // 32), generator=g, dtype=torch.uint8)
+    idx = torch.randint(0, T, (rows,), generator=g, dtype=torch.int32)
+    got = ops.gather_scales_isa(raw.to(DEV), idx.to(DEV), rows, K)
+    assert torch.equal(got.cpu(), Q.gather_scales_to_isa(raw, idx, K))
+
+
+@pytest.mark.parametrize("T,dim,rows", [(256, 256, 512), (1000, 3072, 2048), (64, 64, 128)])
+def test_quant_cols_transposed_bit_exact(ops, T, dim, rows):
+    x = adversarial_rows(T, dim, T + dim)
+    g = torch.Generator().manual_seed(5)
+    idx = torch.randint(0, T, (rows,), generator=g, dtype=torch.int32)
+    q_t, isa = ops.quant_cols_t(x.to(DEV), idx.to(DEV), rows)
+    rq, rs = Q.col_quant(x, idx)
+    assert torch.equal(q_t.cpu(), rq.t().contiguous())
+    assert torch.equal(Q.unpack_isa(isa.cpu(), dim, rows), rs)
+    # without gather
+    x2 = adversarial_rows(rows, dim, 11)
+    q_t, isa = ops.quant_cols_t(x2.to(DEV), None, rows)
+    rq, rs = Q.col_quant(x2)
+    assert torch.equal(q_t.cpu(), rq.t().contiguous())
+    assert torch.equal(Q.unpack_isa(isa.cpu(), dim, rows), rs)
+
+
+@pytest.mark.parametrize("rows,cols", [(128, 128), (512, 3072), (1024, 256)])
+def test_quant_iso32_bit_exact(ops, rows, cols):
+    x = adversarial_rows(rows, cols, rows * 3 + cols)
+    q, ri, q_t, ci = ops.quant_iso32(x.to(DEV))
+    rq, bs = Q.iso32_quant(x)
+    assert torch.equal(q.cpu(), rq)
+    assert torch.equal(q_t.cpu(), rq.t().contiguous())
+    assert torch.equal(Q.unpack_isa(ri.cpu(), rows, cols), bs.repeat_interleave(32, dim=0))
+    assert torch.equal(Q.unpack_isa(ci.cpu(), cols, rows), bs.t().repeat_interleave(32, dim=0))
+
+
+def test_combine_matches_oracle_and_repeats(ops):
+    N, K, E, H = 512, 8, 16, 1024
+    idx, probs = make_routing(N, K, E, 0.2, seed=2)
+    md = R.topk_metadata(idx, probs, E, 128)
+    g = torch.Generator().manual_seed(4)
+    y2 = torch.randn(md["real_TKp"], H, generator=g).to(torch.bfloat16)
+    for weighted in (True, False):
+        ref = OM.combine(y2, md, N, weighted).to(torch.bfloat16)
+        got = ops.combine(y2.to(DEV), md["s_reverse_scatter_idx"].to(DEV), md["naept"].to(DEV),
+                          md["topk_scores"].to(DEV) if weighted else None, N)
+        got2 = ops.combine(y2.to(DEV), md["s_reverse_scatter_idx"].to(DEV), md["naept"].to(DEV),
+                           md["topk_scores"].to(DEV) if weighted else None, N)
+        assert torch.equal(got, got2)
+        # fp32 fma vs mul+add: at most 1 bf16 ulp apart
+        d = (got.cpu().float() - ref.float()).abs()
+        assert (d <= ref.float().abs() * 2 ** -7 + 1e-6).all()
+
+
+@pytest.mark.parametrize("T,E,K", [(1000, 8, 8), (512, 128, 8), (64, 64, 1), (300, 256, 16)])
+def test_topk_softmax_fwd_bwd(ops, T, E, K):
+    g = torch.Generator().manual_seed(T)
+    logits = torch.randn(T, E, generator=g)
+    s, i = ops.topk_softmax(logits.to(DEV), K)
+    rs, ri = OM.router_topk_softmax(logits, K)
+    assert torch.equal(i.cpu(), ri)
+    torch.testing.assert_close(s.cpu(), rs, rtol=1e-5, atol=1e-7)
+    dsc = torch.randn(T, K, generator=g)
+    dl = ops.topk_softmax_bwd(s, i, dsc.to(DEV), E)
+    torch.testing.assert_close(dl.cpu(), OM.router_backward(s.cpu(), ri, dsc, E), rtol=1e-5, atol=1e-6)
+
+
+# ------------------------------------------------------------------ GEMMs
+def rand_fp8(shape, g, lo_exp=118, hi_exp=126):
+    """Random e4m3 bytes (no NaN) and random ue8m0 scale bytes per 1x32 group."""
+    q = torch.randint(0, 256, shape, generator=g, dtype=torch.uint8)
+    q = torch.where((q & 0x7F) == 0x7F, q & 0xF0, q)
+    sc = torch.randint(lo_exp, hi_exp + 1, shape[:-1] + (shape[-1] // 32,), generator=g, dtype=torch.uint8)
+    return q, sc
+
+
+def deq(q, sc):
+    sh = q.shape
+    return Q.dequant_rows(q.reshape(-1, sh[-1]), sc.reshape(-1, sh[-1] // 32)).reshape(sh)
+
+
+def make_efo(counts128):
+    efo = torch.zeros(len(counts128) + 1, dtype=torch.int32)
+    efo[1:] = torch.cumsum(torch.tensor(counts128) * 128, 0)
+    return efo
+
+
+def stats(got, ref):
+    got, ref = got.float().flatten(), ref.float().flatten()
+    cos = float((got * ref).sum() / (got.norm() * ref.norm()).clamp(min=1e-30))
+    rr = float((got - ref).norm() / ref.norm().clamp(min=1e-30))
+    return cos, rr
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("tiles,N,K", [([1, 0, 2, 1], 256, 128), ([3, 2, 0, 0, 4, 1, 1, 2], 512, 1024),
+                                        ([40, 30, 50, 28], 1536, 768)])
+def test_gemm_varlen_m(ops, bn, tiles, N, K):
+    from sonicmoe._lib import lib
+    g = torch.Generator().manual_seed(sum(tiles) + N + K)
+    E = len(tiles)
+    efo = make_efo(tiles)
+    rows = int(efo[-1]) + 256                       # over-allocated tail must be ignored
+    a_q, a_sc = rand_fp8((rows, K), g)
+    b_q, b_sc = rand_fp8((E, N, K), g)
+    a_sf = Q.pack_isa(a_sc, rows, K)
+    b_sf = Q.pack_isa(b_sc.reshape(E * N, K // 32), E * N, K)
+    lib.smoe_debug_force_bn(bn)
+    try:
+        c = ops.gemm_varlen_m(a_q.to(DEV), a_sf.to(DEV), b_q.to(DEV), b_sf.to(DEV), efo.to(DEV))
+        torch.cuda.synchronize()
+        ops.check_status(DEV)
+    finally:
+        lib.smoe_debug_force_bn(0)
+    A, B = deq(a_q, a_sc).to(DEV), deq(b_q, b_sc).to(DEV)
+    for e in range(E):
+        a, b = int(efo[e]), int(efo[e + 1])
+        if b > a:
+            ref = (A[a:b] @ B[e].T)
+            cos, rr = stats(c[a:b], ref)
+            assert cos > 0.99999 and rr < 4e-3, (e, cos, rr)
+
+
+def gated_inputs(T, H, I, tiles, seed):
+    g = torch.Generator().manual_seed(seed)
+    E = len(tiles)
+    efo = make_efo(tiles)
+    rows = int(efo[-1])
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    w1 = (torch.randn(E, 2 * I, H, generator=g) * 0.05).to(torch.bfloat16)
+    a_idx = torch.randint(0, T, (rows,), generator=g, dtype=torch.int32)
+    return g, E, efo, rows, x, w1, a_idx
+
+
+@pytest.mark.parametrize("T,H,I,tiles", [(300, 256, 128, [1, 2, 0, 1]), (2000, 1024, 512, [5, 3, 9, 0, 0, 2, 1, 4])])
+def test_gemm_gated(ops, T, H, I, tiles):
+    g, E, efo, rows, x, w1, a_idx = gated_inputs(T, H, I, tiles, 7)
+    xq, xs = Q.row_quant(x)
+    wq, ws = Q.row_quant(w1.reshape(E * 2 * I, H))
+    a_sf = Q.gather_scales_to_isa(xs, a_idx, H)
+    w_sf = Q.pack_isa(ws, E * 2 * I, H)
+    z_q, z_sc, y1_q, y1_sf = ops.gemm_gated(xq.to(DEV), a_idx.to(DEV), a_sf.to(DEV), wq.reshape(E, 2 * I, H).to(DEV),
+                                            w_sf.to(DEV), efo.to(DEV), rows)
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    X = Q.dequant_rows(xq, xs)[a_idx.long()]
+    W = Q.dequant_rows(wq, ws).reshape(E, 2 * I, H)
+    z = torch.cat([X[int(efo[e]):int(efo[e + 1])] @ W[e].T for e in range(E)])
+    rz_q, rz_s = Q.row_quant(z, amax_floor=1e-4)
+    y1 = Q.bf16_rne(OM.swiglu(z))
+    ry_q, ry_s = Q.row_quant(y1)
+    # scale bytes agree except where the fp32 summation order moves amax across a rounding boundary
+    zs_mis = (z_sc.cpu() != rz_s).float().mean().item()
+    ys_mis = (Q.unpack_isa(y1_sf.cpu(), rows, I) != ry_s).float().mean().item()
+    assert zs_mis < 2e-3 and ys_mis < 2e-3, (zs_mis, ys_mis)
+    cos, rr = stats(Q.dequant_rows(z_q.cpu(), z_sc.cpu()), z)
+    assert cos > 0.999 and rr < 0.04, (cos, rr)
+    cos, rr = stats(Q.dequant_rows(y1_q.cpu(), Q.unpack_isa(y1_sf.cpu(), rows, I)), y1)
+    assert cos > 0.999 and rr < 0.04, (cos, rr)
+    # where scale bytes agree the payload bytes agree almost everywhere (1-ulp flips only)
+    same = (z_sc.cpu() == rz_s).repeat_interleave(32, dim=1)
+    byte_mis = ((z_q.cpu() != rz_q) & same).float().mean().item()
+    assert byte_mis < 0.02, byte_mis
+
+
+@pytest.mark.parametrize("T,H,I,tiles", [(300, 256, 128, [1, 2, 0, 1]), (2000, 1024, 512, [5, 3, 9, 0, 0, 2, 1, 4])])
+def test_gemm_dgated(ops, T, H, I, tiles):
+    g, E, efo, rows, dout, _, a_idx = gated_inputs(T, H, I, tiles, 13)
+    w2t = (torch.randn(E, I, H, generator=g) * 0.05).to(torch.bfloat16)
+    z = torch.randn(rows, 2 * I, generator=g)
+    zq, zs = Q.row_quant(z, amax_floor=1e-4)
+    s = torch.rand(rows, generator=g)
+    s[::7] = 0.0
+    dq, dsc = Q.row_quant(dout)
+    wq, ws = Q.row_quant(w2t.reshape(E * I, H))
+    a_sf = Q.gather_scales_to_isa(dsc, a_idx, H)
+    w_sf = Q.pack_isa(ws, E * I, H)
+    dz, y1s, dsp = ops.gemm_dgated(dq.to(DEV), a_idx.to(DEV), a_sf.to(DEV), wq.reshape(E, I, H).to(DEV), w_sf.to(DEV),
+                                   efo.to(DEV), zq.to(DEV), zs.to(DEV), s.to(DEV), rows)
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    Dm = Q.dequant_rows(dq, dsc)[a_idx.long()]
+    W = Q.dequant_rows(wq, ws).reshape(E, I, H)
+    D = torch.cat([Dm[int(efo[e]):int(efo[e + 1])] @ W[e].T for e in range(E)])
+    rdz, y = OM.dswiglu(Q.dequant_rows(zq, zs), s.unsqueeze(1) * D)
+    for got, ref in ((dz, rdz), (y1s, s.unsqueeze(1) * y), (dsp.sum(0), (y * D).sum(1))):
+        cos, rr = stats(got.cpu(), ref)
+        assert cos > 0.9999 and rr < 6e-3, (cos, rr)
+    assert (dz.cpu()[s == 0] == 0).all() and (y1s.cpu()[s == 0] == 0).all()
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("M,N,tiles", [(128, 256, [1, 0, 2, 1]), (512, 768, [3, 2, 0, 0, 4, 1, 1, 2])])
+def test_gemm_wgrad(ops, bn, M, N, tiles):
+    from sonicmoe._lib import lib
+    g = torch.Generator().manual_seed(M + N)
+    E = len(tiles)
+    efo = make_efo(tiles)
+    TKp = int(efo[-1]) + 128
+    a_q, a_sc = rand_fp8((M, TKp), g)
+    b_q, b_sc = rand_fp8((N, TKp), g)
+    a_sf, b_sf = Q.pack_isa(a_sc, M, TKp), Q.pack_isa(b_sc, N, TKp)
+    A, B = deq(a_q, a_sc).to(DEV), deq(b_q, b_sc).to(DEV)
+    init = torch.randn(E, M, N, generator=g)
+    lib.smoe_debug_force_bn(bn)
+    try:
+        out = init.clone().to(DEV)
+        ops.gemm_wgrad(a_q.to(DEV), a_sf.to(DEV), b_q.to(DEV), b_sf.to(DEV), efo.to(DEV), out, accumulate=True)
+        fresh = torch.full((E, M, N), 7.0, device=DEV)
+        ops.gemm_wgrad(a_q.to(DEV), a_sf.to(DEV), b_q.to(DEV), b_sf.to(DEV), efo.to(DEV), fresh, accumulate=False)
+        torch.cuda.synchronize()
+        ops.check_status(DEV)
+    finally:
+        lib.smoe_debug_force_bn(0)
+    for e in range(E):
+        a, b = int(efo[e]), int(efo[e + 1])
+        ref = A[:, a:b] @ B[:, a:b].T if b > a else torch.zeros(M, N, device=DEV)
+        if b > a:
+            cos, rr = stats(fresh[e], ref)
+            assert cos > 0.99999 and rr < 1e-4, (e, cos, rr)
+        else:
+            assert (fresh[e] == 0).all()
+        torch.testing.assert_close(out[e], init[e].to(DEV) + ref, rtol=1e-4, atol=1e-2 * ref.abs().max().item() + 1e-6)
