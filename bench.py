@@ -1,0 +1,372 @@
+"""Benchmark of the MoE layer forward+backward hot path (MXFP8, sm_100a).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config C2|C3|C4|C5]
+
+One "step" = one forward + backward of the expert compute on pre-routed inputs
+(routing metadata, quantizers, six grouped GEMMs, two combines, weight-gradient
+accumulation into an fp32 main_grad) - the region the reference's own benchmark
+times.  N=1 runs config C2 (T=8192 H=3072 I=1536 E=8 K=8); N>1 runs the
+expert-parallel step (experts sharded over ranks, NCCL all-to-all dispatch and
+combine) with a fixed number of tokens per rank (weak scaling).
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "supersonic-moe_b200"))
+
+import torch  # noqa: E402
+
+CONFIGS = {
+    "C1": dict(T=256, H=256, I=128, E=8, K=2, seed=0, skew=False),
+    "C2": dict(T=8192, H=3072, I=1536, E=8, K=8, seed=0, skew=False),
+    "C3": dict(T=8192, H=4096, I=4096, E=8, K=8, seed=1, skew=False),
+    "C4": dict(T=16384, H=2048, I=768, E=128, K=8, seed=2, skew=True),
+    "C5": dict(T=65536, H=6144, I=3072, E=64, K=8, seed=3, skew=False),
+}
+PUBLISHED_US = {"C2": 2659.8, "C3": 8521.7}       # reference README.md:28-38,348 (its own FP8 path, 1x SM100)
+FP8_PEAK_NOMINAL = 4.5e15
+# kernels launched per wrapper call (sonicmoe/ops.py)
+LAUNCHES = dict(topk_metadata=3, count_cumsum=3)
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm_gbs=d["hbm_gbs"], bf16=d["bf16_tflops"], bf16_sustained=d["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+def make_inputs(cfg, device, T=None):
+    """Seeded synthetic inputs with the shapes and distributions of the named config:
+    x, dy ~ N(0,1) bf16; weights ~ N(0,0.02) bf16; router logits ~ N(0,1) (+ log Zipf(1.2) bias over a seeded
+    expert permutation when skewed); top-K of the logits, softmax over the K selected."""
+    T = T or cfg["T"]
+    H, I, E, K = cfg["H"], cfg["I"], cfg["E"], cfg["K"]
+    g = torch.Generator().manual_seed(cfg["seed"])
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    dy = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    w1 = (torch.randn(E, 2 * I, H, generator=g) * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, generator=g) * 0.02).to(torch.bfloat16)
+    logits = torch.randn(T, E, generator=g)
+    if cfg["skew"]:
+        p = torch.arange(1, E + 1, dtype=torch.float32) ** -1.2
+        logits = logits + torch.log(p / p.sum())[torch.randperm(E, generator=g)]
+    vals, idx = logits.topk(K, dim=-1)
+    scores = torch.softmax(vals, dim=-1)
+    return dict(x=x, dy=dy, w1=w1, w2=w2, idx=idx.to(torch.int32), scores=scores.float())
+
+
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.idx)], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [t.strip() for t in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+def flops_of(cfg, T=None):
+    return 18.0 * (T or cfg["T"]) * cfg["K"] * cfg["H"] * cfg["I"]
+
+
+# ------------------------------------------------------------------ CPU reference arm
+def cpu_reference(cfg, budget_s=20.0):
+    """The reference's pure-PyTorch MoE path (restated in oracle/moe.py) timed on the host cores on a bounded
+    token sub-sample of the same config; reported scaled linearly in T to the full config."""
+    from oracle.moe import TorchMoEBaseline
+    torch.manual_seed(cfg["seed"])
+    H, I, E, K = cfg["H"], cfg["I"], cfg["E"], cfg["K"]
+    cores = torch.get_num_threads()
+    Ts = 256
+    model = TorchMoEBaseline(E, K, H, I, seed=cfg["seed"])
+    x = torch.randn(Ts, H).to(torch.bfloat16).requires_grad_(True)
+    dy = torch.randn(Ts, H).to(torch.bfloat16)
+
+    def step():
+        model.zero_grad(set_to_none=True)
+        out, _ = model(x)
+        out.backward(dy)
+
+    step()
+    t0 = time.perf_counter(); step(); t1 = time.perf_counter() - t0
+    iters = max(1, min(5, int(budget_s / max(t1, 1e-3))))
+    ts = []
+    for _ in range(iters):
+        t0 = time.perf_counter(); step(); ts.append(time.perf_counter() - t0)
+    med = statistics.median(ts)
+    us_full = med * 1e6 * cfg["T"] / Ts
+    return dict(value=us_full, unit="us/iter", cores=cores, kind="port",
+                sample=f"T={Ts} of {cfg['T']} tokens (same H,I,E,K; router+experts fwd+bwd, autograd, bf16 params), "
+                       f"median of {iters} iters = {med * 1e3:.1f} ms, scaled linearly in T; os.cpu_count()="
+                       f"{os.cpu_count()}")
+
+
+# ------------------------------------------------------------------ GPU arm
+def run_ours(args):
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    import sonicmoe
+    from sonicmoe import ops
+
+    cname = args.config or ("C2" if world == 1 else "C4")
+    cfg = CONFIGS[cname]
+    E, K, H, I, T = cfg["E"], cfg["K"], cfg["H"], cfg["I"], cfg["T"]
+    inp = make_inputs(cfg, dev)
+    pin = {k: inp[k].pin_memory() for k in ("x", "dy", "idx", "scores")}
+    if world > 1:
+        from sonicmoe.ep import ExpertParallelMoE
+        assert E % world == 0
+        El = E // world
+        w1 = torch.nn.Parameter(inp["w1"][rank * El:(rank + 1) * El].contiguous().to(dev))
+        w2 = torch.nn.Parameter(inp["w2"][rank * El:(rank + 1) * El].contiguous().to(dev))
+        ep = ExpertParallelMoE(E, K, dist.group.WORLD)
+    else:
+        El = E
+        w1 = torch.nn.Parameter(inp["w1"].to(dev))
+        w2 = torch.nn.Parameter(inp["w2"].to(dev))
+    w1.main_grad = torch.zeros(El, 2 * I, H, dtype=torch.float32, device=dev)
+    w2.main_grad = torch.zeros(El, I, H, dtype=torch.float32, device=dev)
+    sonicmoe.precompute_weight_fp8(w1, w2)          # once per optimizer step, outside the timed region
+    counts = torch.bincount(inp["idx"].flatten().long(), minlength=E).tolist()
+    d = {k: inp[k].to(dev) for k in ("x", "dy", "idx", "scores")}
+
+    def step(x, dy, idx, scores):
+        x = x.detach().requires_grad_(True)
+        if world > 1:
+            out = ep(x, idx, scores, w1, w2)
+        else:
+            out = sonicmoe.run_sonic_moe(x, idx, scores, K, E, w1, w2, fp8=True, tokens_per_expert=counts)
+        out.backward(dy)
+        return out, x.grad
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step(d["x"], d["dy"], d["idx"], d["scores"])
+    barrier()
+    ops.check_status(dev)
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    barrier()
+    ev[0].record()
+    for i in range(args.steps):
+        step(d["x"], d["dy"], d["idx"], d["scores"])
+        ev[i + 1].record()
+    barrier()
+    clocks = sampler.stop()
+    ops.check_status(dev)
+    total_ms = ev[0].elapsed_time(ev[-1])
+    per_step = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+    ms = total_ms / args.steps
+
+    # ---- end to end through the public API with host buffers
+    e2e_ev0, e2e_ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    out_h = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
+    dx_h = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
+    e2e_steps = max(3, min(args.steps, 6))
+
+    def e2e_step():
+        xd = pin["x"].to(dev, non_blocking=True)
+        dyd = pin["dy"].to(dev, non_blocking=True)
+        idxd = pin["idx"].to(dev, non_blocking=True)
+        scd = pin["scores"].to(dev, non_blocking=True)
+        out, dx = step(xd, dyd, idxd, scd)
+        out_h.copy_(out, non_blocking=True)
+        dx_h.copy_(dx, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e2e_ev0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e2e_ev1.record()
+    barrier()
+    e2e_ms = e2e_ev0.elapsed_time(e2e_ev1) / e2e_steps
+    h2d = sum(pin[k].numel() * pin[k].element_size() for k in pin)
+    d2h = 2 * T * H * 2
+
+    # ---- per-kernel breakdown with CUDA events on the launching stream (separate pass)
+    rec = []
+    ops.set_recorder(rec)
+    nprof = 3
+    for _ in range(nprof):
+        step(d["x"], d["dy"], d["idx"], d["scores"])
+    torch.cuda.synchronize()
+    ops.set_recorder(None)
+    agg, launches = {}, 0
+    order = []
+    for i, (name, e0, e1) in enumerate(rec):
+        key = f"{name}#{i % (len(rec) // nprof)}"
+        if key not in agg:
+            agg[key] = []
+            order.append(key)
+        agg[key].append(e0.elapsed_time(e1))
+    launches = sum(LAUNCHES.get(k.split("#")[0], 1) for k in order)
+    breakdown = {k: round(statistics.median(v) * 1e3, 1) for k, v in agg.items()}
+
+    # max over ranks
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = t.tolist()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    pk = peaks()
+    us = ms * 1e3
+    F = flops_of(cfg) * world
+    # dominant kernel = the op with the largest share; all six GEMMs are tensor-bound
+    tcost = dict(gemm_gated=4, gemm_varlen_m=None, gemm_dgated=2, gemm_wgrad=None)
+    gemm_keys = [k for k in order if k.startswith("gemm_")]
+    dom = max(gemm_keys, key=lambda k: breakdown[k])
+    per_gemm_flops = {}
+    TKH_I = T * K * H * I * (1.0 if world == 1 else 1.0)
+    seen = {"gemm_varlen_m": 0, "gemm_wgrad": 0}
+    for k in gemm_keys:
+        n = k.split("#")[0]
+        if n == "gemm_gated":
+            per_gemm_flops[k] = 4 * TKH_I
+        elif n == "gemm_dgated":
+            per_gemm_flops[k] = 2 * TKH_I
+        elif n == "gemm_varlen_m":      # first = down-proj (2), second = dgrad (4)
+            per_gemm_flops[k] = (2 if seen[n] == 0 else 4) * TKH_I
+            seen[n] += 1
+        else:                           # first = dw2 (2), second = dw1 (4)
+            per_gemm_flops[k] = (2 if seen[n] == 0 else 4) * TKH_I
+            seen[n] += 1
+    fp8_peak = 2.0 * pk["bf16_sustained"]
+    ach = per_gemm_flops[dom] / (breakdown[dom] * 1e-6) / 1e12
+    line = {
+        "metric": "MoE fwd+bwd us/iter (FP8 MXFP8 1x32, pre-routed expert compute incl. routing metadata, quant, "
+                  "6 GEMMs, combines, wgrad into fp32 main_grad)",
+        "value": round(us, 1), "unit": "us/iter", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": False, "scaling": "weak",
+        "vs_baseline": round(us / PUBLISHED_US[cname], 4) if (world == 1 and cname in PUBLISHED_US) else None,
+        "dtype": "fp8_e4m3 (ue8m0 1x32 scales), f32 accumulate", "data": "synthetic",
+        "config": {"workload": f"{cname}: T={T}{' per rank' if world > 1 else ''} H={H} I={I} E={E} K={K}, seed "
+                               f"{cfg['seed']}" + (", expert-parallel over %d ranks" % world if world > 1 else ""),
+                   "l2": "no flush: one step touches ~2.5 GB (> 126 MB L2)",
+                   "timed_region": "same as the reference's bench (router linear/top-k outside)"},
+        "mfu_fp8_of_4.5PF": round(F / (ms * 1e-3) / FP8_PEAK_NOMINAL / world, 4),
+        "tflops": round(F / (ms * 1e-3) / 1e12, 1),
+        "tokens_per_s": round(T * world / (ms * 1e-3), 1),
+        "per_step_ms": [round(v, 3) for v in per_step],
+        "clocks": clocks,
+        "e2e": {"value": round(e2e_ms * 1e3, 1), "unit": "us/iter", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "roofline": {"bound": "tensor", "kernel": dom, "achieved": round(ach, 1), "peak": round(fp8_peak, 1),
+                     "unit": "TFLOP/s", "frac": round(ach / fp8_peak, 4), "traffic": None,
+                     "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({pk['source']}); fp8 "
+                                    "tensor rate is twice the bf16 rate"},
+        "kernel_us": breakdown,
+    }
+    if world == 1 and not args.no_cpu:
+        line["cpu_baseline"] = cpu_reference(cfg)
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return
+    cname = args.config or ("C2" if world == 1 else "C4")
+    cfg = CONFIGS[cname]
+    cb = cpu_reference(cfg, budget_s=10.0 * max(1, min(args.steps, 6)))
+    T = cfg["T"] * world
+    us = cb["value"] * world      # one host runs the whole job's tokens
+    line = {
+        "impl": "reference",
+        "metric": "MoE fwd+bwd us/iter (FP8 MXFP8 1x32, pre-routed expert compute incl. routing metadata, quant, "
+                  "6 GEMMs, combines, wgrad into fp32 main_grad)",
+        "value": round(us, 1), "unit": "us/iter", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(us / 1e3, 3), "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 params, fp32 accumulate (reference CPU path)", "data": "synthetic",
+        "config": {"workload": f"{cname}: T={T} H={cfg['H']} I={cfg['I']} E={cfg['E']} K={cfg['K']}, seed {cfg['seed']}"},
+        "cpu_baseline": cb,
+        "e2e": {"value": round(us, 1), "unit": "us/iter", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=12)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default=None, choices=list(CONFIGS))
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

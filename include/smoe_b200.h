@@ -134,10 +134,12 @@ int smoe_combine(const void* y_bf16, const int32_t* s_rev, const int32_t* naept,
  * sonicmoe/functional/__init__.py:2105). */
 int smoe_gather_scores(const float* scores, const int32_t* s_scatter_idx, int64_t rows, float* s, void* stream);
 
-/* ds_tm[i] = sum_t ds_partial[t][s_rev[i]] for i < TK (replaces the partial-sum + permutation of
- * sonicmoe/quack_utils/sm100_funcs.py:885 and functional/__init__.py:2384). */
+/* ds_tm[i] = sum_t ds_partial[t][s_rev[i]] for i < min(TK, *real_tk), 0 beyond (real_tk may be null);
+ * optionally also scatter_out[src_idx[i]] = ds_tm[i] for the real entries (scatter_out must be pre-zeroed).
+ * Replaces the partial-sum + permutation of sonicmoe/quack_utils/sm100_funcs.py:885,
+ * sonicmoe/functional/__init__.py:2384 and the ds scatter of :2488-2500. */
 int smoe_ds_finalize(const float* ds_partial, int64_t partials, int64_t rows, const int32_t* s_rev, int64_t TK,
-                     float* ds_tm, void* stream);
+                     const int32_t* real_tk, float* ds_tm, const int32_t* src_idx, float* scatter_out, void* stream);
 
 /* top-K of each row of logits [T,E] (f32) and softmax over the K selected values.
  * Replaces _softmax_topk_fwd (sonicmoe/functional/forward.py:217-236, topk_softmax.py). */

@@ -57,14 +57,21 @@ __global__ void gather_scores_kernel(const float* __restrict__ scores, const int
   if (i < rows) s[i] = scores[s_scatter[i]];
 }
 
+// Entries at or beyond *real_tk (over-allocated tail) are written as 0 and never scattered.
 __global__ void ds_finalize_kernel(const float* __restrict__ part, int partials, int64_t rows,
-                                   const int* __restrict__ s_rev, int64_t TK, float* __restrict__ ds) {
+                                   const int* __restrict__ s_rev, int64_t TK, const int* __restrict__ real_tk,
+                                   float* __restrict__ ds, const int* __restrict__ src_idx,
+                                   float* __restrict__ scatter_out) {
   const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (i >= TK) return;
-  const int64_t p = s_rev[i];
   float a = 0.f;
-  for (int t = 0; t < partials; ++t) a += part[(int64_t)t * rows + p];
-  ds[i] = a;
+  const bool real = real_tk == nullptr || i < *real_tk;
+  if (real) {
+    const int64_t p = s_rev[i];
+    for (int t = 0; t < partials; ++t) a += part[(int64_t)t * rows + p];
+    if (scatter_out) scatter_out[src_idx[i]] = a;
+  }
+  if (ds) ds[i] = a;
 }
 
 // One warp per row: K rounds of arg-max (lowest index wins ties), then softmax
@@ -163,10 +170,11 @@ int smoe_gather_scores(const float* scores, const int32_t* s_scatter_idx, int64_
 }
 
 int smoe_ds_finalize(const float* ds_partial, int64_t partials, int64_t rows, const int32_t* s_rev, int64_t TK,
-                     float* ds_tm, void* stream) {
+                     const int32_t* real_tk, float* ds_tm, const int32_t* src_idx, float* scatter_out, void* stream) {
   if (TK <= 0) return TK == 0 ? SMOE_OK : SMOE_ERR_SHAPE;
-  ds_finalize_kernel<<<(unsigned)((TK + 255) / 256), 256, 0, (cudaStream_t)stream>>>(ds_partial, (int)partials, rows,
-                                                                                     s_rev, TK, ds_tm);
+  if (scatter_out && !src_idx) return SMOE_ERR_ARG;
+  ds_finalize_kernel<<<(unsigned)((TK + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      ds_partial, (int)partials, rows, s_rev, TK, real_tk, ds_tm, src_idx, scatter_out);
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }
 

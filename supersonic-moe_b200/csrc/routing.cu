@@ -193,7 +193,7 @@ scatter_fill_kernel(const int* __restrict__ idx, const float* __restrict__ probs
   for (int pos = gtid; pos < TKp_alloc; pos += nthreads) {
     if (pos >= real_TKp) {
       x_gather[pos] = 0;
-      s_scatter[pos] = real_TK;
+      s_scatter[pos] = pad_mode == 0 ? real_TK : pos;   // virtual numbering continues through the tail
       continue;
     }
     int lo = 0, hi = E;

@@ -31,7 +31,7 @@ SIGNATURES = {
     "smoe_debug_force_bn": (_I, [_I]),
     "smoe_combine": (_I, [_P, _P, _P, _P, _P, _L, _L, _P]),
     "smoe_gather_scores": (_I, [_P, _P, _L, _P, _P]),
-    "smoe_ds_finalize": (_I, [_P, _L, _L, _P, _L, _P, _P]),
+    "smoe_ds_finalize": (_I, [_P, _L, _L, _P, _L, _P, _P, _P, _P, _P]),
     "smoe_topk_softmax": (_I, [_P, _L, _L, _L, _P, _P, _P]),
     "smoe_topk_softmax_bwd": (_I, [_P, _P, _P, _L, _L, _L, _P, _P]),
 }

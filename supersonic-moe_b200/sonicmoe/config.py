@@ -1,0 +1,58 @@
+"""`SonicMoEConfig`: thread-local configuration object of the reference API
+(sonicmoe/config.py:149-300).  This build has one compute path - the MXFP8
+frontier path - so the flags that selected other backends are accepted and
+recorded but do not switch code paths."""
+from __future__ import annotations
+
+import threading
+from contextlib import contextmanager
+from dataclasses import dataclass
+from typing import Optional
+
+_tls = threading.local()
+
+
+def get_active_config() -> Optional["SonicMoEConfig"]:
+    return getattr(_tls, "config", None)
+
+
+def set_active_config(cfg: Optional["SonicMoEConfig"]) -> None:
+    _tls.config = cfg
+
+
+@dataclass
+class SonicMoEConfig:
+    use_fp8: Optional[bool] = None
+    use_quack_gemm: Optional[bool] = None
+    fp8_wgrad: Optional[bool] = None
+    save_z_fp8: Optional[bool] = None
+    recompute_z: Optional[bool] = None
+    epilogue_quant: Optional[bool] = None
+    fused_zy1_quant: Optional[bool] = None
+    fuse_y1_quant: Optional[bool] = None
+    fuse_y1_bf16_trunc: Optional[bool] = None
+    fused_weight_layout: Optional[bool] = None
+    assume_aligned: Optional[bool] = None
+    stagewise_memory: Optional[bool] = None
+    iso32_weight: Optional[bool] = None
+    swiglu_clamp_value: Optional[float] = None
+
+    def __post_init__(self) -> None:
+        if self.use_fp8 is True and self.use_quack_gemm is None:
+            self.use_quack_gemm = True
+        if self.recompute_z:
+            raise NotImplementedError("recompute_z is not built (z is saved as e4m3 + ue8m0 scales)")
+        if self.swiglu_clamp_value:
+            raise NotImplementedError("swiglu_clamp_value is not built")
+
+    def resolve_use_fp8(self) -> bool:
+        return bool(self.use_fp8)
+
+    @contextmanager
+    def activate(self):
+        prev = get_active_config()
+        set_active_config(self)
+        try:
+            yield self
+        finally:
+            set_active_config(prev)

@@ -1,0 +1,360 @@
+"""Autograd orchestration of the MoE layer on the sm_100a MXFP8 kernels.
+
+Mirrors the reference's functional layer (sonicmoe/functional/__init__.py):
+`_UpProjection` / `_DownProjection` autograd Functions with the reference's
+argument lists (:828-847, :1617-1640), the FP8 hand-off between them
+(:430-502), `main_grad` accumulation (:393-414), `enable_fp8` /
+`enable_quack_gemm` (functional/utils.py:15-76) and the dense entry point
+`moe_TC_softmax_topk_layer` (call sites sonicmoe/moe.py:604-616).
+
+Dataflow (one code path, MXFP8 1x32 ue8m0 everywhere a GEMM runs):
+  forward   x --row quant--> x_fp8 ; scales gathered to expert-sorted rows
+            up-proj GEMM (row gather by TMA) + SwiGLU + z/y1 re-quant in the epilogue
+            down-proj GEMM -> y2 bf16 ; top-k weighted combine -> o
+  backward  dout row quant ; GemmDGated (e4m3 z reload, dSwiGLU) -> dz, y1s, ds
+            column quantizers (transposed outputs) ; dw2, dw1 varlen-K GEMMs into fp32
+            dgrad GEMM -> dx_expanded ; unweighted combine -> dx
+"""
+from __future__ import annotations
+
+import os
+from contextlib import contextmanager
+
+import torch
+import torch.nn.functional as F
+
+from .. import ops
+from ..config import get_active_config
+from ..enums import ActivationType, require_swiglu
+
+# ----------------------------------------------------------------------------
+# flags (API kept; a single compute path sits behind them)
+# ----------------------------------------------------------------------------
+_IS_USING_QUACK_GEMM = os.getenv("USE_QUACK_GEMM", "1") == "1"
+_IS_FP8_ACTIVE = os.getenv("SONIC_MOE_FP8_MODE", "").strip().lower() in ("perf", "mem")
+
+
+@contextmanager
+def enable_quack_gemm(enable: bool = True):
+    global _IS_USING_QUACK_GEMM
+    prev = _IS_USING_QUACK_GEMM
+    _IS_USING_QUACK_GEMM = enable
+    try:
+        yield
+    finally:
+        _IS_USING_QUACK_GEMM = prev
+
+
+@contextmanager
+def enable_fp8(enable: bool = True):
+    global _IS_FP8_ACTIVE, _IS_USING_QUACK_GEMM
+    prev = (_IS_FP8_ACTIVE, _IS_USING_QUACK_GEMM)
+    _IS_FP8_ACTIVE = enable
+    if enable:
+        _IS_USING_QUACK_GEMM = True
+    try:
+        yield
+    finally:
+        _IS_FP8_ACTIVE, _IS_USING_QUACK_GEMM = prev
+
+
+def is_fp8_active() -> bool:
+    cfg = get_active_config()
+    if cfg is not None and cfg.use_fp8 is not None:
+        return cfg.use_fp8
+    return _IS_FP8_ACTIVE
+
+
+def is_using_quack_gemm() -> bool:
+    cfg = get_active_config()
+    if cfg is not None and cfg.use_quack_gemm is not None:
+        return cfg.use_quack_gemm
+    return _IS_USING_QUACK_GEMM
+
+
+def _require_fp8():
+    if not is_fp8_active():
+        raise NotImplementedError(
+            "this build implements the MXFP8 path of the MoE layer only: wrap the call in enable_fp8(), pass "
+            "use_fp8=True / fp8=True, or activate SonicMoEConfig(use_fp8=True) (the BF16 GEMM path is out of scope)")
+
+
+# ----------------------------------------------------------------------------
+# FP8 weight cache (four row-wise 1x32 layouts, refreshed when a weight's
+# version counter moves, i.e. once per optimizer step)
+# ----------------------------------------------------------------------------
+_WEIGHT_CACHE: dict = {}
+_WEIGHT_CACHE_MAX = 256
+
+
+def _base_of(w: torch.Tensor) -> torch.Tensor:
+    return w._base if w._base is not None else w
+
+
+def weight_fp8(w: torch.Tensor, transposed: bool):
+    """w [E,N,K] bf16 -> (e4m3 bytes [E,N,K], ISA scales) or, transposed, the same for w^T [E,K,N].
+    Replaces precompute_weight_fp8_warmup / the per-weight caches
+    (sonicmoe/quack_utils/blockscaled_fp8_gemm.py:299-345,4363-4406)."""
+    base = _base_of(w)
+    key = (w.data_ptr(), tuple(w.shape), tuple(w.stride()), transposed, w.device.index)
+    ver = base._version
+    hit = _WEIGHT_CACHE.get(key)
+    if hit is not None and hit[0] == ver:
+        return hit[1], hit[2]
+    with torch.no_grad():
+        src = w.detach().transpose(1, 2) if transposed else w.detach()
+        src = src.contiguous()
+        if src.dtype != torch.bfloat16:
+            src = src.to(torch.bfloat16)
+        E, N, K = src.shape
+        q, _, sf = ops.quant_rows(src.view(E * N, K), raw=False, isa=True)
+        q = q.view(E, N, K)
+    if len(_WEIGHT_CACHE) >= _WEIGHT_CACHE_MAX:
+        _WEIGHT_CACHE.pop(next(iter(_WEIGHT_CACHE)))
+    _WEIGHT_CACHE[key] = (ver, q, sf)
+    return q, sf
+
+
+def precompute_weight_fp8(w1: torch.Tensor, w2: torch.Tensor):
+    """Fill the four cached layouts: W1 (E,2I,H), W1^T (E,H,2I), W2 (E,H,I), W2^T (E,I,H)."""
+    for w in (w1, w2):
+        weight_fp8(w, False)
+        weight_fp8(w, True)
+
+
+def clear_weight_cache():
+    _WEIGHT_CACHE.clear()
+
+
+# ----------------------------------------------------------------------------
+# main_grad accumulation (sonicmoe/functional/__init__.py:393-414)
+# ----------------------------------------------------------------------------
+def _grad_target(w: torch.Tensor, shape):
+    """fp32 accumulator living on the parameter (`main_grad`), or None."""
+    base = _base_of(w)
+    mg = getattr(base, "main_grad", None)
+    if mg is None:
+        return None, base
+    if mg.dtype != torch.float32 or tuple(mg.shape) != tuple(shape) or not mg.is_contiguous():
+        raise ValueError(f"main_grad must be contiguous fp32 of shape {tuple(shape)}, got {mg.dtype} "
+                         f"{tuple(mg.shape)}")
+    return mg, base
+
+
+def _after_accumulate(base):
+    hook = getattr(base, "_apply_backward_hook", None)
+    if hook is not None:
+        hook()
+
+
+# hand-off of FP8 payloads from _UpProjection.forward to _DownProjection.forward
+# (the returned y1 / z tensors are zero-stride placeholders that only carry the
+# autograd edges)
+_HANDOFF: list = []
+
+
+def _placeholder(like: torch.Tensor, shape):
+    return torch.empty((), dtype=torch.bfloat16, device=like.device).expand(*shape)
+
+
+class _UpProjection(torch.autograd.Function):
+    @classmethod
+    def apply(cls, x, w1, b1, expert_frequency_offset, total_expert_freq, K, stream_id, x_gather_idx, s_scatter_idx,
+              s_reverse_scatter_idx, num_activated_expert_per_token_offset, is_varlen_K, activation_type,
+              is_inference_mode_enabled, use_low_precision_postact_buffer=False, prequant_activation_payload=None,
+              fp8_config=None):
+        return super().apply(x, w1, b1, expert_frequency_offset, total_expert_freq, K, stream_id, x_gather_idx,
+                             s_scatter_idx, s_reverse_scatter_idx, num_activated_expert_per_token_offset,
+                             is_varlen_K, activation_type, is_inference_mode_enabled,
+                             use_low_precision_postact_buffer, prequant_activation_payload, fp8_config)
+
+    @staticmethod
+    def forward(ctx, x, w1, b1, efo, TKp, K, stream_id, x_gather_idx, s_scatter_idx, s_rev, naept, is_varlen_K,
+                activation_type, is_inference, low_precision_postact, prequant_payload, fp8_config):
+        _require_fp8()
+        require_swiglu(activation_type)
+        if b1 is not None:
+            raise NotImplementedError("expert biases are not supported on the MXFP8 path")
+        E, N2, H = w1.shape
+        TKp = int(TKp)
+        if prequant_payload is not None:
+            # x arrives as e4m3 bytes + raw 1x32 ue8m0 scales (expert-parallel dispatch payload)
+            x_q, x_raw = prequant_payload[0], prequant_payload[1]
+            x_q = x_q.view(torch.uint8)
+        else:
+            x_q, x_raw, _ = ops.quant_rows(x.contiguous(), raw=True)
+        a_sf = ops.gather_scales_isa(x_raw, x_gather_idx, TKp, H)
+        w1_q, w1_sf = weight_fp8(w1, False)
+        z_q, z_sc, y1_q, y1_sf = ops.gemm_gated(x_q, x_gather_idx, a_sf, w1_q, w1_sf, efo, TKp)
+        link = {"y1": (y1_q, y1_sf), "z": (z_q, z_sc)}
+        _HANDOFF.append(link)
+        ctx.link = link
+        ctx.T = x.shape[0]
+        ctx.x_is_fp8 = prequant_payload is not None
+        ctx.x_dtype = x.dtype
+        ctx.save_for_backward(x if prequant_payload is None else x_q, x_raw if prequant_payload is not None else None,
+                              w1, efo, x_gather_idx, s_rev, naept)
+        y1 = _placeholder(x, (TKp, N2 // 2))
+        z = _placeholder(x, (TKp, N2))
+        ctx.mark_non_differentiable(y1)
+        return y1, z
+
+    @staticmethod
+    def backward(ctx, _dy1, _dz):
+        x, x_raw, w1, efo, x_gather_idx, s_rev, naept = ctx.saved_tensors
+        link = ctx.link
+        dz_q, dz_rsf, dz_t, dz_csf = link.pop("dz")
+        E, N2, H = w1.shape
+        TKp = dz_q.shape[0]
+        dw1 = None
+        if ctx.needs_input_grad[1]:
+            if ctx.x_is_fp8:
+                raise NotImplementedError("weight gradients from an FP8 x payload need the dequant-requant quantizer")
+            x_t, x_sf = ops.quant_cols_t(x, x_gather_idx, TKp)
+            mg, base = _grad_target(w1, (E, N2, H))
+            if mg is not None:
+                ops.gemm_wgrad(dz_t, dz_csf, x_t, x_sf, efo, mg, accumulate=True)
+                _after_accumulate(base)
+            else:
+                out = torch.empty(E, N2, H, dtype=torch.float32, device=dz_q.device)
+                ops.gemm_wgrad(dz_t, dz_csf, x_t, x_sf, efo, out, accumulate=False)
+                dw1 = out.to(w1.dtype)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            w1t_q, w1t_sf = weight_fp8(w1, True)
+            dx_exp = ops.gemm_varlen_m(dz_q, dz_rsf, w1t_q, w1t_sf, efo)
+            dx = ops.combine(dx_exp, s_rev, naept, None, ctx.T)
+            if dx.dtype != ctx.x_dtype:
+                dx = dx.to(ctx.x_dtype)
+        return (dx, dw1) + (None,) * 15
+
+
+class _DownProjection(torch.autograd.Function):
+    @classmethod
+    def apply(cls, y1, z, w2, b2, topk_scores, selected_experts, expert_frequency_offset, T, K, stream_id,
+              x_gather_idx, s_scatter_idx, s_reverse_scatter_idx, num_activated_expert_per_token_offset,
+              is_varlen_K, activation_type, fp8_protocol, fp8_combine_grad_handle=None, fp8_config=None,
+              router_score_source=None, router_score_src_idx=None):
+        return super().apply(y1, z, w2, b2, topk_scores, selected_experts, expert_frequency_offset, T, K, stream_id,
+                             x_gather_idx, s_scatter_idx, s_reverse_scatter_idx,
+                             num_activated_expert_per_token_offset, is_varlen_K, activation_type, fp8_protocol,
+                             fp8_combine_grad_handle, fp8_config, router_score_source, router_score_src_idx)
+
+    @staticmethod
+    def forward(ctx, y1, z, w2, b2, topk_scores, selected_experts, efo, T, K, stream_id, x_gather_idx, s_scatter_idx,
+                s_rev, naept, is_varlen_K, activation_type, fp8_protocol, fp8_combine_grad_handle, fp8_config,
+                router_score_source, router_score_src_idx):
+        _require_fp8()
+        if b2 is not None:
+            raise NotImplementedError("expert biases are not supported on the MXFP8 path")
+        if not _HANDOFF:
+            raise RuntimeError("_DownProjection must directly follow _UpProjection (FP8 hand-off is empty)")
+        link = _HANDOFF.pop()
+        y1_q, y1_sf = link.pop("y1")
+        w2_q, w2_sf = weight_fp8(w2, False)
+        y2 = ops.gemm_varlen_m(y1_q, y1_sf, w2_q, w2_sf, efo)
+        o = ops.combine(y2, s_rev, naept, topk_scores, int(T))
+        ctx.link = link
+        ctx.T = int(T)
+        ctx.score_source_shape = None if router_score_source is None else tuple(router_score_source.shape)
+        ctx.save_for_backward(w2, topk_scores, efo, x_gather_idx, s_scatter_idx, s_rev, naept, router_score_src_idx)
+        return o
+
+    @staticmethod
+    def backward(ctx, dout):
+        w2, topk_scores, efo, x_gather_idx, s_scatter_idx, s_rev, naept, src_idx = ctx.saved_tensors
+        link = ctx.link
+        z_q, z_sc = link.pop("z")
+        E, H, I = w2.shape
+        TKp = z_q.shape[0]
+        dout = dout.contiguous()
+        if dout.dtype != torch.bfloat16:
+            dout = dout.to(torch.bfloat16)
+        s = ops.gather_scores(topk_scores, s_scatter_idx)
+        dout_q, dout_raw, _ = ops.quant_rows(dout, raw=True)
+        a_sf = ops.gather_scales_isa(dout_raw, x_gather_idx, TKp, H)
+        w2t_q, w2t_sf = weight_fp8(w2, True)
+        dz, y1s, dsp = ops.gemm_dgated(dout_q, x_gather_idx, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, TKp)
+        del z_q, z_sc
+        dw2 = None
+        if ctx.needs_input_grad[2]:
+            y1s_t, y1s_sf = ops.quant_cols_t(y1s, None, TKp)
+            dout_t, dout_sf = ops.quant_cols_t(dout, x_gather_idx, TKp)
+            mg, base = _grad_target(w2, (E, I, H))
+            if mg is not None:
+                ops.gemm_wgrad(y1s_t, y1s_sf, dout_t, dout_sf, efo, mg, accumulate=True)
+                _after_accumulate(base)
+            else:
+                out = torch.empty(E, I, H, dtype=torch.float32, device=dout.device)
+                ops.gemm_wgrad(y1s_t, y1s_sf, dout_t, dout_sf, efo, out, accumulate=False)
+                dw2 = out.transpose(1, 2).to(w2.dtype)
+        link["dz"] = ops.quant_iso32(dz)
+        # ds: token-major (length of the score buffer) and, when asked, scattered to the [T,K] source
+        d_scores = d_source = None
+        want_flat = ctx.needs_input_grad[4]
+        want_src = ctx.needs_input_grad[19] and src_idx is not None
+        if want_flat or want_src:
+            TK = s_rev.numel()
+            numel = 1
+            if want_src:
+                for d in ctx.score_source_shape:
+                    numel *= d
+            ds_tm, ds_src = ops.ds_finalize(dsp, s_rev, TK, naept[-1:], src_idx if want_src else None, numel)
+            if want_flat:
+                d_scores = torch.zeros_like(topk_scores)
+                d_scores[:TK] = ds_tm
+            if want_src:
+                d_source = ds_src.view(ctx.score_source_shape)
+        grads = [None] * 21
+        grads[1] = dz
+        grads[2] = dw2
+        grads[4] = d_scores
+        grads[19] = d_source
+        return tuple(grads)
+
+
+# ----------------------------------------------------------------------------
+# router: top-k on logits, softmax over the K selected (forward.py:217-236,
+# backward.py:572-641)
+# ----------------------------------------------------------------------------
+class _TopKSoftmax(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, K):
+        scores, idx = ops.topk_softmax(logits.contiguous(), int(K))
+        ctx.save_for_backward(scores, idx)
+        ctx.E = logits.shape[1]
+        ctx.mark_non_differentiable(idx)
+        return scores, idx
+
+    @staticmethod
+    def backward(ctx, dscores, _didx):
+        scores, idx = ctx.saved_tensors
+        return ops.topk_softmax_bwd(scores, idx, dscores.contiguous().float(), ctx.E), None
+
+
+def _expert_major(w: torch.Tensor) -> torch.Tensor:
+    """[N,K,E] view (the layout the module passes) -> [E,N,K] contiguous."""
+    w = w.permute(2, 0, 1)
+    return w if w.is_contiguous() else w.contiguous()
+
+
+def moe_TC_softmax_topk_layer(x, router_w, w1, b1, w2, b2, K, stream_id, activation_type=ActivationType.SWIGLU,
+                              is_inference_mode_enabled=False, fp8_protocol=None):
+    """Dense top-k MoE layer.  x [T,H]; router_w [E,H]; w1 [2I,H,E] and w2 [H,I,E] views of the expert-major
+    parameters (rows of w1 interleaved gate0, up0, gate1, ...).  Returns (o [T,H], router_logits [T,E],
+    expert_frequency [E] int32); differentiable w.r.t. x, router_w, w1, w2."""
+    _require_fp8()
+    require_swiglu(activation_type)
+    T, H = x.shape
+    E = router_w.shape[0]
+    w1_e, w2_e = _expert_major(w1), _expert_major(w2)
+    logits = F.linear(x, router_w)
+    scores, idx = _TopKSoftmax.apply(logits.float(), K)
+    md = ops.topk_metadata(idx, scores.detach(), E, 128, TK_alloc=T * K, lane_order=1, pad_mode=1)
+    y1, z = _UpProjection.apply(x, w1_e, b1, md["efo"], md["TKp_alloc"], K, stream_id, md["x_gather_idx"],
+                                md["s_scatter_idx"], md["s_reverse_scatter_idx"], md["naept"], False,
+                                activation_type, is_inference_mode_enabled)
+    o = _DownProjection.apply(y1, z, w2_e, b2, md["topk_scores"], idx, md["efo"], T, K, stream_id,
+                              md["x_gather_idx"], md["s_scatter_idx"], md["s_reverse_scatter_idx"], md["naept"],
+                              False, activation_type, fp8_protocol, None, None, scores, md["score_src_idx"])
+    return o, logits, md["counts"]

@@ -1,0 +1,53 @@
+"""`run_sonic_moe`: expert compute on pre-routed (dispatched) tokens - the
+functional entry the host framework calls after its dispatch all-to-all
+(sonicmoe/interface.py:69-345)."""
+from __future__ import annotations
+
+import torch
+
+from . import ops
+from .enums import ActivationType
+from .functional import _DownProjection, _UpProjection, enable_fp8
+
+
+def run_sonic_moe(hidden_states, topk_indices, topk_scores, K, E, w1, w2, fp8=False, tokens_per_expert=None,
+                  fp8_scale=None, fp8_combine_grad_handle=None, fp8_config=None, release_fp8_weights=False,
+                  activation_type=ActivationType.SWIGLU, sync_free_sizing=False):
+    """hidden_states [N,H] bf16 (or e4m3 with `fp8_scale` = raw 1x32 ue8m0 bytes [N,H/32]);
+    topk_indices [N,K] with -1 for slots whose expert is not local (a row's valid experts distinct);
+    topk_scores [N,K] f32; w1 [E,2I,H]; w2 [E,H,I].  Returns [N,H] bf16.
+
+    `tokens_per_expert` (host list / tensor) sizes the expert-sorted buffers exactly; with
+    `sync_free_sizing` (or without counts) they are sized at the shape-only upper bound and no
+    device-to-host copy happens."""
+    if not fp8:
+        raise NotImplementedError("run_sonic_moe: only fp8=True (MXFP8) is built")
+    if fp8_combine_grad_handle is not None:
+        raise NotImplementedError("fp8_combine_grad_handle (FP8 dout payload) is not built")
+    N = hidden_states.shape[0]
+    idx = topk_indices if topk_indices.dtype == torch.int32 else topk_indices.to(torch.int32)
+    probs = topk_scores.detach()
+    if probs.dtype != torch.float32:
+        probs = probs.float()
+    TK = TKp = None
+    if tokens_per_expert is not None and not sync_free_sizing:
+        counts = tokens_per_expert.tolist() if isinstance(tokens_per_expert, torch.Tensor) else list(tokens_per_expert)
+        TK = int(sum(counts))
+        TKp = int(sum(-(-c // 128) * 128 for c in counts if c > 0))
+    md = ops.topk_metadata(idx.contiguous(), probs.contiguous(), E, 128, TK, TKp)
+    stream_id = torch.cuda.current_stream().cuda_stream
+    payload = None
+    if fp8_scale is not None:
+        payload = (hidden_states, fp8_scale)
+    need_router_grad = topk_scores.requires_grad
+    with enable_fp8(True):
+        y1, z = _UpProjection.apply(hidden_states, w1, None, md["efo"], md["TKp_alloc"], K, stream_id,
+                                    md["x_gather_idx"], md["s_scatter_idx"], md["s_reverse_scatter_idx"],
+                                    md["naept"], True, activation_type, False, False, payload, fp8_config)
+        out = _DownProjection.apply(y1, z, w2, None, md["topk_scores"], md["s_scatter_idx"], md["efo"], N, K,
+                                    stream_id, md["x_gather_idx"], md["s_scatter_idx"],
+                                    md["s_reverse_scatter_idx"], md["naept"], True, activation_type, None,
+                                    fp8_combine_grad_handle, fp8_config,
+                                    topk_scores if need_router_grad else None,
+                                    md["score_src_idx"] if need_router_grad else None)
+    return out

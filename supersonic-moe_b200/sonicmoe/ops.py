@@ -34,6 +34,31 @@ def isa_bytes(rows: int, cols: int) -> int:
 
 _status = {}
 
+# Optional per-op CUDA-event recorder (bench / profiling): a list that receives
+# (op name, start event, end event) for every kernel-launching wrapper below.
+_recorder = None
+
+
+def set_recorder(rec):
+    global _recorder
+    _recorder = rec
+
+
+def _timed(fn):
+    import functools
+
+    @functools.wraps(fn)
+    def wrapper(*a, **k):
+        if _recorder is None:
+            return fn(*a, **k)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        out = fn(*a, **k)
+        e1.record()
+        _recorder.append((fn.__name__, e0, e1))
+        return out
+    return wrapper
+
 
 def status_word(device) -> torch.Tensor:
     """Per-device int32 word the GEMM kernels write a failure code into (0 = ok)."""
@@ -51,6 +76,7 @@ def check_status(device):
 
 
 # ---------------------------------------------------------------- routing
+@_timed
 def count_cumsum(x: torch.Tensor, E: int, do_cumsum: bool = True):
     _cuda(x)
     if x.dtype not in (torch.int32, torch.int64):
@@ -62,6 +88,7 @@ def count_cumsum(x: torch.Tensor, E: int, do_cumsum: bool = True):
     return (count, cum) if do_cumsum else count
 
 
+@_timed
 def topk_metadata(idx, probs, E, alignment=128, TK_alloc=None, TKp_alloc=None, lane_order=0, pad_mode=0):
     """Returns dict(efo, x_gather_idx, s_scatter_idx, s_reverse_scatter_idx, naept, topk_scores,
     score_src_idx, counts).  Default sizing is the sync-free upper bound."""
@@ -92,6 +119,7 @@ def topk_metadata(idx, probs, E, alignment=128, TK_alloc=None, TKp_alloc=None, l
 
 
 # ---------------------------------------------------------------- quantizers
+@_timed
 def quant_rows(x, raw=True, isa=False):
     """bf16 [M,K] -> (e4m3 bytes [M,K] u8, raw scales [M,K/32] u8 | None, ISA scales u8 | None)."""
     _cuda(x)
@@ -104,6 +132,7 @@ def quant_rows(x, raw=True, isa=False):
     return q, r, i
 
 
+@_timed
 def gather_scales_isa(raw, idx, rows, cols):
     _cuda(raw, idx)
     out = torch.empty(isa_bytes(rows, cols), dtype=_U8, device=raw.device)
@@ -111,6 +140,7 @@ def gather_scales_isa(raw, idx, rows, cols):
     return out
 
 
+@_timed
 def quant_cols_t(src, idx, rows):
     """bf16 [T,dim] (rows gathered by idx, or None) -> (e4m3 bytes [dim, rows], ISA scales for (dim, rows))."""
     _cuda(src, idx)
@@ -122,6 +152,7 @@ def quant_cols_t(src, idx, rows):
     return q_t, isa
 
 
+@_timed
 def quant_iso32(x):
     """bf16 [rows, cols] -> (q [rows,cols], row ISA, q_t [cols,rows], col ISA)."""
     _cuda(x)
@@ -137,6 +168,7 @@ def quant_iso32(x):
 
 
 # ---------------------------------------------------------------- GEMMs
+@_timed
 def gemm_varlen_m(a_q, a_sf, b_q, b_sf, efo):
     """a_q u8 [rows,K], b_q u8 [E,N,K] -> bf16 [rows,N]."""
     _cuda(a_q, a_sf, b_q, b_sf, efo)
@@ -148,6 +180,7 @@ def gemm_varlen_m(a_q, a_sf, b_q, b_sf, efo):
     return c
 
 
+@_timed
 def gemm_gated(x_q, a_idx, a_sf, w1_q, w1_sf, efo, rows):
     """x_q u8 [T,H], w1_q u8 [E,2I,H] -> z_q [rows,2I], z_sc [rows,2I/32], y1_q [rows,I], y1_sf (ISA)."""
     _cuda(x_q, a_idx, a_sf, w1_q, w1_sf, efo)
@@ -163,6 +196,7 @@ def gemm_gated(x_q, a_idx, a_sf, w1_q, w1_sf, efo, rows):
     return z_q, z_sc, y1_q, y1_sf
 
 
+@_timed
 def gemm_dgated(dout_q, a_idx, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, rows):
     """dout_q u8 [T,H], w2t_q u8 [E,I,H] -> dz bf16 [rows,2I], y1s bf16 [rows,I], ds_partial f32 [parts, rows]."""
     _cuda(dout_q, a_idx, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s)
@@ -179,6 +213,7 @@ def gemm_dgated(dout_q, a_idx, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, rows):
     return dz, y1s, dsp
 
 
+@_timed
 def gemm_wgrad(a_t, a_sf, b_t, b_sf, efo, out, accumulate):
     """a_t u8 [M,TKp], b_t u8 [N,TKp]; out f32 [E,M,N] (+)= per-expert products."""
     _cuda(a_t, a_sf, b_t, b_sf, efo, out)
@@ -192,6 +227,7 @@ def gemm_wgrad(a_t, a_sf, b_t, b_sf, efo, out, accumulate):
 
 
 # ---------------------------------------------------------------- token side
+@_timed
 def combine(y, s_rev, naept, scores, T):
     _cuda(y, s_rev, naept, scores)
     H = y.shape[1]
@@ -200,6 +236,7 @@ def combine(y, s_rev, naept, scores, T):
     return out
 
 
+@_timed
 def gather_scores(scores, s_scatter_idx):
     _cuda(scores, s_scatter_idx)
     rows = s_scatter_idx.numel()
@@ -208,14 +245,19 @@ def gather_scores(scores, s_scatter_idx):
     return s
 
 
-def ds_finalize(ds_partial, s_rev, TK):
-    _cuda(ds_partial, s_rev)
+@_timed
+def ds_finalize(ds_partial, s_rev, TK, real_tk=None, src_idx=None, scatter_numel=0):
+    """Token-major ds [TK]; with src_idx also the scatter into a zeroed [scatter_numel] buffer."""
+    _cuda(ds_partial, s_rev, real_tk, src_idx)
     parts, rows = ds_partial.shape
     out = torch.empty(TK, dtype=torch.float32, device=ds_partial.device)
-    check(lib.smoe_ds_finalize(_p(ds_partial), parts, rows, _p(s_rev), TK, _p(out), _stream()), "ds_finalize")
-    return out
+    sc = torch.zeros(scatter_numel, dtype=torch.float32, device=ds_partial.device) if src_idx is not None else None
+    check(lib.smoe_ds_finalize(_p(ds_partial), parts, rows, _p(s_rev), TK, _p(real_tk), _p(out), _p(src_idx), _p(sc),
+                               _stream()), "ds_finalize")
+    return out, sc
 
 
+@_timed
 def topk_softmax(logits, K):
     _cuda(logits)
     assert logits.dtype == torch.float32 and logits.ndim == 2
@@ -226,6 +268,7 @@ def topk_softmax(logits, K):
     return scores, idx
 
 
+@_timed
 def topk_softmax_bwd(scores, idx, dscores, E):
     _cuda(scores, idx, dscores)
     T, K = scores.shape

@@ -1,0 +1,211 @@
+"""End-to-end parity of the MoE layer (module and functional API) on the GPU against the CPU oracle.
+
+Tolerances are the ones the reference publishes for its FP8 path against an fp32 gold
+(README.md:321-334): cosine >= 0.997 and RRMSE <= 7.6 % for out, dx, drouter, dw1, dw2."""
+import pytest
+import torch
+
+from oracle import moe as OM
+from oracle import routing as R
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+COS_MIN, RRMSE_MAX = 0.997, 0.076
+
+
+@pytest.fixture(scope="module")
+def sm():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import sonicmoe
+    return sonicmoe
+
+
+def stats(got, ref):
+    got, ref = got.detach().float().cpu().flatten(), ref.detach().float().cpu().flatten()
+    cos = float((got * ref).sum() / (got.norm() * ref.norm()).clamp(min=1e-30))
+    rr = float((got - ref).norm() / ref.norm().clamp(min=1e-30))
+    return cos, rr
+
+
+def check(name, got, ref, cos_min=COS_MIN, rr_max=RRMSE_MAX):
+    cos, rr = stats(got, ref)
+    assert cos >= cos_min and rr <= rr_max, f"{name}: cos {cos:.5f} rrmse {rr:.5f}"
+
+
+def make_layer(T, H, I, E, K, seed, skew=False):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    dy = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    w1 = (torch.randn(E, 2 * I, H, generator=g) * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, generator=g) * 0.02).to(torch.bfloat16)
+    # router weight scaled so that logits are ~N(0,1)
+    wr = (torch.randn(E, H, generator=g) / H ** 0.5).to(torch.bfloat16)
+    if skew:
+        p = torch.arange(1, E + 1, dtype=torch.float32) ** -1.2
+        bias = torch.log(p / p.sum())[torch.randperm(E, generator=g)]
+    else:
+        bias = None
+    return x, dy, w1, w2, wr, bias
+
+
+def oracle_dense(x, dy, w1, w2, wr, K):
+    """fp32 gold of the whole layer: router + experts, explicit backward."""
+    E = wr.shape[0]
+    xf, wrf = x.float(), wr.float()
+    logits = (x @ wr.T).float()                      # the module computes logits in bf16, then fp32 softmax
+    scores, idx = OM.router_topk_softmax(logits, K)
+    md = R.topk_metadata(idx, scores, E, 128, lane_order="slot", pad_mode="virtual")
+    r = OM.moe_fp32(x, w1, w2, md, dy)
+    dscores = r["ds"].view(-1, K)
+    dlogits = OM.router_backward(scores, idx, dscores, E)
+    r["dx_total"] = r["dx"] + dlogits @ wrf
+    r["dwr"] = dlogits.T @ xf
+    r["dlogits"] = dlogits
+    r["idx"], r["scores"], r["md"] = idx, scores, md
+    return r
+
+
+@pytest.mark.parametrize("T,H,I,E,K,seed", [(256, 256, 128, 8, 2, 0), (1024, 512, 256, 16, 4, 1),
+                                             (512, 1024, 384, 8, 8, 2)])
+def test_moe_module_fwd_bwd_vs_fp32_oracle(sm, T, H, I, E, K, seed):
+    x, dy, w1, w2, wr, _ = make_layer(T, H, I, E, K, seed)
+    moe = sm.MoE(E, K, H, I, sm.ActivationType.SWIGLU, add_bias=False, std=0.02).to(DEV).to(torch.bfloat16)
+    with torch.no_grad():
+        moe.router.weight.copy_(wr)
+        moe.c_fc.weight.copy_(w1)
+        moe.c_proj.weight.copy_(w2)
+    xd = x.to(DEV).requires_grad_(True)
+    out, aux = moe(xd, use_fp8=True)
+    out.backward(dy.to(DEV))
+    torch.cuda.synchronize()
+    sm.ops.check_status(DEV)
+    ref = oracle_dense(x, dy, w1, w2, wr, K)
+    check("out", out, ref["o"])
+    check("dx", xd.grad, ref["dx_total"])
+    check("dw1", moe.c_fc.weight.grad, ref["dw1"])
+    check("dw2", moe.c_proj.weight.grad, ref["dw2"])
+    check("drouter", moe.router.weight.grad, ref["dwr"])
+    assert aux is not None and torch.isfinite(aux)
+    # aux loss = E * sum(normalize1(sum_t softmax(logits)) * normalize1(freq))
+    logits = (x @ wr.T).float()
+    freq = torch.bincount(ref["idx"].flatten().long(), minlength=E).float()
+    exp = E * (torch.nn.functional.normalize(torch.softmax(logits, -1).sum(0), p=1, dim=0) *
+               torch.nn.functional.normalize(freq, p=1, dim=0)).sum()
+    assert abs(float(aux) - float(exp)) < 2e-2 * abs(float(exp))
+
+
+def test_module_rejects_non_fp8_and_other_backends(sm):
+    moe = sm.MoE(8, 2, 256, 128, sm.ActivationType.SWIGLU, add_bias=False, std=0.02).to(DEV).to(torch.bfloat16)
+    x = torch.randn(64, 256, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(NotImplementedError):
+        moe(x)
+    with pytest.raises(NotImplementedError):
+        moe(x, kernel_backend_moe=sm.KernelBackendMoE.torch, use_fp8=True)
+
+
+def masked_routing(T, E, K, E_local, seed, bias=None):
+    """Global top-k routing; experts >= E_local are 'not local' (-1), as an EP rank sees it."""
+    g = torch.Generator().manual_seed(seed)
+    logits = torch.randn(T, E, generator=g)
+    if bias is not None:
+        logits = logits + bias
+    scores, idx = OM.router_topk_softmax(logits, K)
+    idx = torch.where(idx < E_local, idx, torch.full_like(idx, -1))
+    return idx, scores
+
+
+@pytest.mark.parametrize("sizing", ["exact", "sync_free"])
+def test_run_sonic_moe_masked_skewed_vs_oracles(sm, sizing):
+    T, H, I, E, K = 2048, 512, 256, 32, 8
+    x, dy, w1, w2, _, bias = make_layer(T, H, I, E, K, 5, skew=True)
+    E_local = 24                                       # 8 experts "remote"; Zipf skew leaves some local ones empty
+    idx, scores = masked_routing(T, E, K, E_local, 6, bias * 3)
+    w1, w2 = w1[:E_local].contiguous(), w2[:E_local].contiguous()
+    counts = torch.bincount(idx[idx >= 0].long(), minlength=E_local)
+    assert (counts == 0).any(), "test wants at least one empty expert"
+    md = R.topk_metadata(idx, scores, E_local, 128)
+    gold = OM.moe_fp32(x, w1, w2, md, dy)
+    emu = OM.moe_fp8_emulated(x, w1, w2, md, dy)
+
+    xd = x.to(DEV).requires_grad_(True)
+    w1d = w1.to(DEV).requires_grad_(True)
+    w2d = w2.to(DEV).requires_grad_(True)
+    sd = scores.to(DEV).requires_grad_(True)
+    kw = dict(tokens_per_expert=counts.tolist()) if sizing == "exact" else dict(sync_free_sizing=True)
+    out = sm.run_sonic_moe(xd, idx.to(DEV), sd, K, E_local, w1d, w2d, fp8=True, **kw)
+    out.backward(dy.to(DEV))
+    torch.cuda.synchronize()
+    sm.ops.check_status(DEV)
+    ds_ref = torch.zeros(T * K)
+    ds_ref[md["score_src_idx"][:md["real_TK"]].long()] = gold["ds"][:md["real_TK"]]
+    for name, got, ref in [("out", out, gold["o"]), ("dx", xd.grad, gold["dx"]), ("dw1", w1d.grad, gold["dw1"]),
+                           ("dw2", w2d.grad, gold["dw2"]), ("ds", sd.grad.flatten(), ds_ref)]:
+        check(name, got, ref)
+    # against the FP8-emulating oracle the agreement is far tighter (same quantisation points)
+    ds_emu = torch.zeros(T * K)
+    ds_emu[md["score_src_idx"][:md["real_TK"]].long()] = emu["ds"][:md["real_TK"]]
+    for name, got, ref in [("out", out, emu["o"]), ("dx", xd.grad, emu["dx"]), ("dw1", w1d.grad, emu["dw1"]),
+                           ("dw2", w2d.grad, emu["dw2_IH"].transpose(1, 2)), ("ds", sd.grad.flatten(), ds_emu)]:
+        check(name + " (fp8 emu)", got, ref, cos_min=0.9995, rr_max=0.03)
+    # empty experts: exactly-zero weight gradients; masked slots: exactly-zero score gradients
+    empty = (counts == 0).nonzero().flatten()
+    assert (w1d.grad[empty.to(DEV)] == 0).all() and (w2d.grad[empty.to(DEV)] == 0).all()
+    assert (sd.grad.cpu()[idx < 0] == 0).all()
+
+
+def test_main_grad_accumulation_and_bit_exact_repeat(sm):
+    T, H, I, E, K = 1024, 512, 256, 8, 4
+    x, dy, w1, w2, _, _ = make_layer(T, H, I, E, K, 9)
+    idx, scores = masked_routing(T, E, K, E, 10)
+    w1d = torch.nn.Parameter(w1.to(DEV))
+    w2d = torch.nn.Parameter(w2.to(DEV))
+    hooks = []
+    for w, shape in ((w1d, (E, 2 * I, H)), (w2d, (E, I, H))):
+        w.main_grad = torch.zeros(shape, dtype=torch.float32, device=DEV)
+        w._apply_backward_hook = lambda: hooks.append(1)
+
+    def step():
+        xd = x.to(DEV).requires_grad_(True)
+        sd = scores.to(DEV).requires_grad_(True)
+        out = sm.run_sonic_moe(xd, idx.to(DEV), sd, K, E, w1d, w2d, fp8=True)
+        out.backward(dy.to(DEV))
+        return out.detach().clone(), xd.grad.clone(), sd.grad.clone()
+
+    o1, dx1, ds1 = step()
+    g1 = (w1d.main_grad.clone(), w2d.main_grad.clone())
+    assert w1d.grad is None and w2d.grad is None and len(hooks) == 2
+    o2, dx2, ds2 = step()
+    torch.cuda.synchronize()
+    sm.ops.check_status(DEV)
+    assert torch.equal(o1, o2) and torch.equal(dx1, dx2) and torch.equal(ds1, ds2)
+    # second step added exactly the same increment
+    assert torch.equal(w1d.main_grad - g1[0], g1[0]) and torch.equal(w2d.main_grad - g1[1], g1[1])
+    md = R.topk_metadata(idx, scores, E, 128)
+    gold = OM.moe_fp32(x, w1, w2, md, dy)
+    check("main_grad w1", g1[0], gold["dw1"])
+    check("main_grad w2 [E,I,H]", g1[1], gold["dw2_IH"])
+
+
+def test_all_masked_and_single_token(sm):
+    H, I, E, K = 256, 128, 8, 2
+    x, dy, w1, w2, _, _ = make_layer(64, H, I, E, K, 3)
+    idx = torch.full((64, K), -1, dtype=torch.int32)
+    scores = torch.rand(64, K)
+    xd = x.to(DEV).requires_grad_(True)
+    w1d, w2d = w1.to(DEV).requires_grad_(True), w2.to(DEV).requires_grad_(True)
+    out = sm.run_sonic_moe(xd, idx.to(DEV), scores.to(DEV), K, E, w1d, w2d, fp8=True)
+    out.backward(dy.to(DEV))
+    assert (out == 0).all() and (xd.grad == 0).all() and (w1d.grad == 0).all() and (w2d.grad == 0).all()
+    # one token
+    idx = torch.tensor([[3, 5]], dtype=torch.int32)
+    scores = torch.tensor([[0.7, 0.3]])
+    md = R.topk_metadata(idx, scores, E, 128)
+    gold = OM.moe_fp32(x[:1], w1, w2, md, dy[:1])
+    xd = x[:1].to(DEV).requires_grad_(True)
+    out = sm.run_sonic_moe(xd, idx.to(DEV), scores.to(DEV), K, E, w1d, w2d, fp8=True)
+    out.backward(dy[:1].to(DEV))
+    torch.cuda.synchronize()
+    sm.ops.check_status(DEV)
+    check("out", out, gold["o"])
+    check("dx", xd.grad, gold["dx"])
