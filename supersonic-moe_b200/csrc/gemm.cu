@@ -6,6 +6,7 @@
 #include <mutex>
 
 #include "gemm.cuh"
+#include "gemm2.cuh"
 #include "smoe_b200.h"
 
 namespace smoe {
@@ -40,7 +41,23 @@ static int make_tmap_u8(CUtensorMap* m, const void* base, uint64_t rows, uint64_
   return r == CUDA_SUCCESS ? SMOE_OK : SMOE_ERR_TMAP;
 }
 
+// General 2D row-major tensor map.
+static int make_tmap(CUtensorMap* m, CUtensorMapDataType dt, int esize, const void* base, uint64_t rows,
+                     uint64_t cols, uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle sw) {
+  if (!load_encode()) return SMOE_ERR_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((cols * esize) & 15)) return SMOE_ERR_ALIGN;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * esize};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? SMOE_OK : SMOE_ERR_TMAP;
+}
+
 static int g_force_bn = 0;
+static int g_skip_store = 0;
+static int g_force_v1 = 0;
 static int g_sm_count = 0;
 
 static int sm_count() {
@@ -75,10 +92,94 @@ static int pick_bn(int64_t N) {
   return (N % 256 == 0) ? 256 : 128;
 }
 
+// ---- two-CTA kernel -----------------------------------------------------------
+struct OutMaps {
+  CUtensorMap c, c2;
+};
+
+template <int BN, int MODE>
+static int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa, const CUtensorMap& tsb,
+                   const OutMaps& om, const GemmParams& p, int64_t max_pair_tiles, cudaStream_t stream) {
+  using S = Gemm2Smem<BN>;
+  static bool attr_set = false;
+  auto kern = gemm2_mxf8_kernel<BN, MODE>;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL) != cudaSuccess)
+      return SMOE_ERR_LAUNCH;
+    attr_set = true;
+  }
+  int64_t pairs = sm_count() / 2;
+  if (max_pair_tiles < pairs) pairs = max_pair_tiles;
+  if (pairs <= 0) return SMOE_OK;
+  kern<<<(unsigned)(2 * pairs), kThreads2, S::TOTAL, stream>>>(ta, tb, tsa, tsb, om.c, om.c2, p);
+  return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
+}
+
+// Column tile of the two-CTA kernel for a mode and N; 0 = not applicable.
+template <int MODE>
+static int pick_bn2(int64_t N) {
+  if (g_force_v1) return 0;
+  if (MODE == GATED) return 128;
+  if (g_force_bn == 128) return 128;
+  if (g_force_bn == 192) return (N % 192 == 0) ? 192 : 128;
+  return (N % 192 == 0) ? 192 : 128;
+}
+
+template <int MODE>
+static int run2(const void* a, int64_t a_rows, int64_t a_cols, const void* b, int64_t b_rows, int64_t b_cols,
+                GemmParams& p, const OutMaps& om, int bn, int64_t sfa_tiles, int64_t sfb_tiles, cudaStream_t stream) {
+  CUtensorMap ta, tb, tsa, tsb;
+  constexpr bool gather = (MODE == GATED || MODE == DGATED);
+  int rc = make_tmap_u8(&ta, a, a_rows, a_cols, BK, gather ? 1 : BM);
+  if (rc) return rc;
+  rc = make_tmap_u8(&tb, b, b_rows, b_cols, BK, bn / 2);
+  if (rc) return rc;
+  rc = make_tmap(&tsa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, p.sfa, sfa_tiles, 128, 128, 1, CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc) return rc;
+  rc = make_tmap(&tsb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, p.sfb, sfb_tiles, 128, 128, 1, CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc) return rc;
+  // upper bound of pair tiles: varlen-M: every expert may add one half-empty pair
+  int64_t pair_tiles;
+  if (MODE == WGRAD) pair_tiles = (int64_t)p.E * (p.rows / 256) * (p.N / bn);
+  else pair_tiles = ((int64_t)p.rows / 256 + p.E) * (p.N / bn);
+  if (bn == 192) return launch2<192, MODE == GATED ? PLAIN : MODE>(ta, tb, tsa, tsb, om, p, pair_tiles, stream);
+  return launch2<128, MODE>(ta, tb, tsa, tsb, om, p, pair_tiles, stream);
+}
+
 template <int MODE>
 static int run(const void* a, int64_t a_rows, int64_t a_cols, const void* b, int64_t b_rows, int64_t b_cols,
                GemmParams& p, int max_tiles_128, cudaStream_t stream) {
   if (p.E > kMaxExpertsSmem) return SMOE_ERR_SHAPE;
+  {
+    const int bn2 = pick_bn2<MODE>(p.N);
+    const bool ok2 = bn2 != 0 && (MODE != WGRAD || p.rows % 256 == 0);
+    if (ok2) {
+      OutMaps om{};
+      int rc = SMOE_OK;
+      const int64_t sfa_tiles = (MODE == WGRAD) ? (int64_t)(p.rows / 128) * p.sfa_ktiles
+                                                : (int64_t)(p.rows / 128) * p.sfa_ktiles;
+      const int64_t sfb_tiles = (b_rows / 128) * p.sfb_ktiles;
+      if (MODE == PLAIN) {
+        rc = make_tmap(&om.c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.c, p.rows, p.N, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B);
+        om.c2 = om.c;
+      } else if (MODE == WGRAD) {
+        rc = make_tmap(&om.c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.c, (uint64_t)p.E * p.rows, p.N, 32, 32,
+                       CU_TENSOR_MAP_SWIZZLE_128B);
+        om.c2 = om.c;
+      } else if (MODE == DGATED) {
+        rc = make_tmap(&om.c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.dz, p.rows, 2 * (uint64_t)p.N, 64, 32,
+                       CU_TENSOR_MAP_SWIZZLE_128B);
+        if (!rc)
+          rc = make_tmap(&om.c2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.y1s, p.rows, p.N, 32, 32,
+                         CU_TENSOR_MAP_SWIZZLE_64B);
+      } else {  // GATED stores straight from registers; the output maps are unused
+        rc = make_tmap_u8(&om.c, p.z_fp8, p.rows, p.N, 32, 32);
+        om.c2 = om.c;
+      }
+      if (rc) return rc;
+      return run2<MODE>(a, a_rows, a_cols, b, b_rows, b_cols, p, om, bn2, sfa_tiles, sfb_tiles, stream);
+    }
+  }
   const int bn = pick_bn(p.N);
   CUtensorMap ta, tb;
   constexpr bool gather = (MODE == GATED || MODE == DGATED);
@@ -97,7 +198,9 @@ using namespace smoe;
 extern "C" {
 
 int smoe_debug_force_bn(int bn) {
-  g_force_bn = bn;
+  g_force_bn = bn & 0xFFFF;
+  g_skip_store = (bn >> 16) & 1;
+  g_force_v1 = (bn >> 17) & 1;
   return SMOE_OK;
 }
 
@@ -108,7 +211,7 @@ int smoe_gemm_varlen_m(const void* a_fp8, const void* a_sf, const void* b_fp8, c
   p.rows = (int)rows; p.N = (int)N; p.K = (int)K; p.E = (int)E;
   p.efo = efo; p.sfa = (const uint8_t*)a_sf; p.sfb = (const uint8_t*)b_sf;
   p.sfa_ktiles = (int)(K / 128); p.sfb_ktiles = (int)(K / 128);
-  p.c = c_bf16; p.status = status;
+  p.c = c_bf16; p.status = status; p.debug_skip_store = g_skip_store;
   return run<PLAIN>(a_fp8, rows, K, b_fp8, E * N, K, p, (int)((rows / 128) * (N / 128)), (cudaStream_t)stream);
 }
 
@@ -125,6 +228,8 @@ int smoe_gemm_gated(const void* x_fp8, int64_t T, const int* a_idx, const void* 
   return run<GATED>(x_fp8, T, K, w1_fp8, E * N, K, p, (int)((rows / 128) * (N / 128)), (cudaStream_t)stream);
 }
 
+int64_t smoe_gemm_dgated_partials(int64_t N);
+
 int smoe_gemm_dgated(const void* dout_fp8, int64_t T, const int* a_idx, const void* a_sf, const void* w2t_fp8,
                      const void* w2t_sf, const int* efo, const void* z_fp8, const void* z_scales, const float* s,
                      void* dz_bf16, void* y1s_bf16, float* ds_partial, int64_t* ds_partial_tiles, int64_t rows,
@@ -136,11 +241,14 @@ int smoe_gemm_dgated(const void* dout_fp8, int64_t T, const int* a_idx, const vo
   p.sfa_ktiles = (int)(K / 128); p.sfb_ktiles = (int)(K / 128);
   p.z_fp8 = (uint8_t*)const_cast<void*>(z_fp8); p.z_sc = (uint8_t*)const_cast<void*>(z_scales);
   p.s = s; p.dz = dz_bf16; p.y1s = y1s_bf16; p.ds_partial = ds_partial; p.status = status;
-  if (ds_partial_tiles) *ds_partial_tiles = N / pick_bn(N);
+  if (ds_partial_tiles) *ds_partial_tiles = smoe_gemm_dgated_partials(N);
   return run<DGATED>(dout_fp8, T, K, w2t_fp8, E * N, K, p, (int)((rows / 128) * (N / 128)), (cudaStream_t)stream);
 }
 
-int64_t smoe_gemm_dgated_partials(int64_t N) { return N / pick_bn(N); }
+int64_t smoe_gemm_dgated_partials(int64_t N) {
+  const int bn2 = pick_bn2<DGATED>(N);
+  return bn2 ? 2 * (N / bn2) : N / pick_bn(N);
+}
 
 int smoe_gemm_wgrad(const void* a_t_fp8, const void* a_sf, const void* b_t_fp8, const void* b_sf, const int* efo,
                     float* c, int64_t M, int64_t N, int64_t TKp, int64_t E, int accumulate, int* status,

@@ -1,0 +1,538 @@
+// Two-CTA (cta_group::2) variant of the MXFP8 grouped GEMM: a pair of CTAs on
+// neighbouring SMs computes one 256 x BN tile.  Each CTA stages its own 128 rows
+// of A and its own half of the B tile (no multicast loads anywhere); the leader
+// CTA issues tcgen05.mma for both, each CTA keeps its 128 x BN accumulator in
+// its own TMEM (two stages, so the epilogue of tile i overlaps the main loop of
+// tile i+1) and drains it with eight epilogue warps.  Outputs go through a
+// swizzled shared-memory staging buffer and TMA stores / TMA reduce-adds.
+#pragma once
+#include "gemm.cuh"
+
+namespace smoe {
+
+constexpr int kEpiWarps2 = 8;
+constexpr int kThreads2 = 32 * (2 + kEpiWarps2);
+
+// ---- cluster helpers -------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cta address of this CTA -> shared::cluster address of the same offset in CTA `rank`
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Loads of a CTA pair: data lands in the issuing CTA, the byte count is
+// credited to the barrier named by a shared::cluster address (the leader's).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap, uint32_t bar_cluster, int c0,
+                                                 int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(tmap), "r"(bar_cluster), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_gather4_pair(uint32_t dst, const void* tmap, uint32_t bar_cluster, int c0, int r0,
+                                                 int r1, int r2, int r3) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(dst), "l"(tmap), "r"(bar_cluster), "r"(c0), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void mma_mxf8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+// completion of all MMAs issued so far -> one arrival on the barrier at this
+// offset in every CTA of `mask`
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar, uint16_t mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(bar), "h"(mask)
+      : "memory");
+}
+__device__ __forceinline__ void tc_cp_sf_pair(uint32_t dst_tmem, uint64_t src_desc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(dst_tmem), "l"(src_desc) : "memory");
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+// sigmoid with two MUFU ops (ex2 + rcp); relative error ~1e-7, far below the
+// bf16 / e4m3 resolution of everything it feeds
+__device__ __forceinline__ float fast_sigmoid(float x) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * x));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return r;
+}
+
+template <int BN>
+struct Gemm2Smem {
+  static constexpr int A_BYTES = BM * BK;                 // this CTA's 128 rows
+  static constexpr int B_BYTES = (BN / 2) * BK;           // this CTA's half of the B tile
+  static constexpr int SF_BYTES = 2048;                   // SFA 512 + SFB 2 x 512, padded
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SF_BYTES;
+  static constexpr int EPI_BYTES_PER_WARP = 8192;
+  static constexpr int EPI_BYTES = kEpiWarps2 * EPI_BYTES_PER_WARP;
+  static constexpr int AUX_BYTES = 1024 + 2 * (kMaxExpertsSmem + 1) * 4;
+  static constexpr int STAGES_RAW = (227 * 1024 - 1024 - AUX_BYTES - EPI_BYTES) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 6 ? 6 : STAGES_RAW;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + EPI_BYTES + AUX_BYTES + 1024;
+  static constexpr int SFB_TILES = (BN == 128) ? 1 : 2;   // 128-row scale tiles covering the BN window
+  static constexpr int SF_COLS = 4 + 4 * SFB_TILES;
+  static constexpr int SF_COL0 = 2 * BN;
+  static_assert(SF_COL0 + STAGES * SF_COLS <= 512, "TMEM budget");
+  static constexpr uint32_t TX_BYTES = 2u * (A_BYTES + B_BYTES + 512 + 512 * SFB_TILES);
+};
+
+struct PairTile {
+  int m0;       // first row of this CTA's 128 rows (A' / C rows; WGRAD: output rows)
+  int n0;       // first output column
+  int e;        // expert
+  int kt0, nkt; // K-tile range
+  int valid;    // 0: this CTA's half lies beyond its expert's rows - compute, store nothing
+};
+
+// varlen-M: experts own ceil(n_e / 2) row pairs; s_pairs = exclusive prefix of that.
+template <int BN, int MODE>
+__device__ __forceinline__ PairTile pair_tile(int tile, int rank, const GemmParams& p, const int* s_efo,
+                                              const int* s_pairs) {
+  PairTile t;
+  const int n_tiles = p.N / BN;
+  if (MODE == WGRAD) {
+    const int m_pairs = p.rows / (2 * BM);
+    const int per_e = m_pairs * n_tiles;
+    t.e = tile / per_e;
+    const int r = tile - t.e * per_e;
+    t.m0 = (r / n_tiles) * 2 * BM + rank * BM;
+    t.n0 = (r % n_tiles) * BN;
+    t.kt0 = s_efo[t.e] / BK;
+    t.nkt = (s_efo[t.e + 1] - s_efo[t.e]) / BK;
+    t.valid = 1;
+  } else {
+    const int pr = tile / n_tiles;
+    t.n0 = (tile - pr * n_tiles) * BN;
+    int lo = 0, hi = p.E;
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (s_pairs[mid + 1] <= pr) lo = mid + 1; else hi = mid;
+    }
+    t.e = lo;
+    const int j = pr - s_pairs[lo];
+    t.m0 = s_efo[lo] + (2 * j + rank) * BM;
+    t.valid = t.m0 < s_efo[lo + 1];
+    t.kt0 = 0;
+    t.nkt = p.K / BK;
+  }
+  return t;
+}
+
+template <int BN, int MODE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
+gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                  const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
+                  const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_c2,
+                  const GemmParams p) {
+  using S = Gemm2Smem<BN>;
+  constexpr bool GATHER = (MODE == GATED || MODE == DGATED);
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* epi = smem + S::STAGES * S::STAGE_BYTES;
+  uint8_t* aux = epi + S::EPI_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aux);     // full[S], empty[S], tfull[2], tempty[2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux + 512);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(aux + 516);
+  int* s_efo = reinterpret_cast<int*>(aux + 1024);
+  int* s_pairs = s_efo + (kMaxExpertsSmem + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair_id = blockIdx.x >> 1;
+  const int n_pairs_grid = gridDim.x >> 1;
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = bar_full + 8 * S::STAGES;
+  const uint32_t bar_tfull = bar_empty + 8 * S::STAGES;
+  const uint32_t bar_tempty = bar_tfull + 8 * 2;
+
+  for (int i = threadIdx.x; i <= p.E; i += blockDim.x) s_efo[i] = p.efo[i];
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < p.E; ++e) {
+      s_pairs[e] = acc;
+      acc += ((s_efo[e + 1] - s_efo[e]) / BM + 1) >> 1;
+    }
+    s_pairs[p.E] = acc;
+    for (int s = 0; s < S::STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);        // leader's: its own producer arms it; both CTAs' copies credit it
+      mbar_init(bar_empty + 8 * s, 1);       // one commit arrival per use, in each CTA
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_tfull + 8 * s, 1);                   // commit arrival, in each CTA
+      mbar_init(bar_tempty + 8 * s, 2 * kEpiWarps2);     // leader's: the epilogue warps of both CTAs
+    }
+    *s_abort = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc2(smem_u32(tmem_slot), 512);
+    tmem_relinquish2();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t smem_base = smem_u32(smem);
+  const int n_total = (MODE == WGRAD) ? p.E * (p.rows / (2 * BM)) * (p.N / BN) : s_pairs[p.E] * (p.N / BN);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer (both CTAs)
+    if (lane == 0) {
+      prefetch_tmap(&tmap_a); prefetch_tmap(&tmap_b); prefetch_tmap(&tmap_sfa); prefetch_tmap(&tmap_sfb);
+    }
+    const uint32_t full0 = map_to_cta(bar_full, 0);      // the leader's full barriers
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = pair_id; tile < n_total && ok; tile += n_pairs_grid) {
+      const PairTile t = pair_tile<BN, MODE>(tile, rank, p, s_efo, s_pairs);
+      if (t.nkt == 0) continue;
+      int4 rows4 = make_int4(0, 0, 0, 0);
+      if (GATHER && t.valid) rows4 = *reinterpret_cast<const int4*>(p.a_idx + t.m0 + 4 * lane);
+      const int b_base = (MODE == WGRAD) ? t.n0 : t.e * p.N + t.n0;
+      const int b_row = b_base + rank * (BN / 2);
+      // rows of the A-scale tensor are 512-byte tiles: (row tile, k tile)
+      int sfa_tile = t.m0 / 128;
+      if (!t.valid) sfa_tile = 0;                        // phantom half: any in-range tile will do
+      const int sfb_tile = b_base / 128;                 // first 128-row scale tile touching the BN window
+      for (int kt = t.kt0; kt < t.kt0 + t.nkt; ++kt) {
+        if (lane == 0) ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1);
+        ok = __shfl_sync(0xffffffff, ok, 0);
+        if (!ok) break;
+        const uint32_t full = full0 + 8 * stage;
+        const uint32_t a_dst = smem_base + stage * S::STAGE_BYTES;
+        const uint32_t b_dst = a_dst + S::A_BYTES;
+        const uint32_t sf_dst = b_dst + S::B_BYTES;
+        if (lane == 0) {
+          if (rank == 0) mbar_expect_tx(bar_full + 8 * stage, S::TX_BYTES);
+          if (!GATHER) tma_load_2d_pair(a_dst, &tmap_a, full, kt * BK, t.valid ? t.m0 : 0);
+          tma_load_2d_pair(b_dst, &tmap_b, full, kt * BK, b_row);
+          tma_load_2d_pair(sf_dst, &tmap_sfa, full, 0, sfa_tile * p.sfa_ktiles + kt);
+#pragma unroll
+          for (int j = 0; j < S::SFB_TILES; ++j)
+            tma_load_2d_pair(sf_dst + 512 + 512 * j, &tmap_sfb, full, 0, (sfb_tile + j) * p.sfb_ktiles + kt);
+        }
+        if (GATHER) {
+          __syncwarp();
+          tma_gather4_pair(a_dst + lane * 4 * BK, &tmap_a, full, kt * BK, rows4.x, rows4.y, rows4.z, rows4.w);
+        }
+        if (++stage == S::STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+    if (!ok && lane == 0) { *s_abort = 1; atomicCAS(p.status, 0, 201); }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (rank == 0 && elect_one()) {
+      constexpr uint32_t idesc = make_idesc_mxf8(2 * BM, BN);
+      int stage = 0, as = 0;
+      uint32_t phase = 0, aphase = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < n_total && ok; tile += n_pairs_grid) {
+        const PairTile t = pair_tile<BN, MODE>(tile, 0, p, s_efo, s_pairs);
+        if (t.nkt == 0) continue;
+        ok = mbar_wait(bar_tempty + 8 * as, aphase ^ 1);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + as * BN;
+        // BN = 192: an odd column tile starts 64 rows into its first 128-row scale tile
+        const uint32_t sfb_shift = (BN == 192) ? (((t.n0 / BN) & 1) ? 2u : 0u) : 0u;
+        for (int k = 0; k < t.nkt; ++k) {
+          ok = mbar_wait(bar_full + 8 * stage, phase);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_src = smem_base + stage * S::STAGE_BYTES;
+          const uint32_t b_src = a_src + S::A_BYTES;
+          const uint32_t sf_src = b_src + S::B_BYTES;
+          const uint32_t sfa_t = tmem_base + S::SF_COL0 + stage * S::SF_COLS;
+          const uint32_t sfb_t = sfa_t + 4;
+          tc_cp_sf_pair(sfa_t, make_desc_sf(sf_src));
+#pragma unroll
+          for (int j = 0; j < S::SFB_TILES; ++j) tc_cp_sf_pair(sfb_t + 4 * j, make_desc_sf(sf_src + 512 + 512 * j));
+          const uint64_t a_desc = make_desc_kmajor_sw128(a_src);
+          const uint64_t b_desc = make_desc_kmajor_sw128(b_src);
+#pragma unroll
+          for (int kb = 0; kb < BK / 32; ++kb) {
+            mma_mxf8_pair(d_tmem, a_desc + 2 * kb, b_desc + 2 * kb, idesc_with_sf_ids(idesc, kb, kb), sfa_t,
+                          sfb_t + sfb_shift, (k | kb) != 0);
+          }
+          tc_commit_pair(bar_empty + 8 * stage, 3);
+          if (++stage == S::STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        tc_commit_pair(bar_tfull + 8 * as, 3);
+        if (++as == 2) { as = 0; aphase ^= 1; }
+      }
+      if (!ok) { *s_abort = 1; atomicCAS(p.status, 0, 202); }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ epilogue (8 warps per CTA)
+    const int q = warp & 3;                       // TMEM lane quadrant of this warp
+    const int half = (warp - 2) >> 2;             // which half of the tile's columns
+    const int row_in_tile = q * 32 + lane;
+    constexpr int COLS_PER_WARP = BN / 2;
+    const uint32_t stg = smem_u32(epi + (warp - 2) * S::EPI_BYTES_PER_WARP);
+    const uint32_t tempty0 = map_to_cta(bar_tempty, 0);
+    int as = 0;
+    uint32_t aphase = 0;
+    bool ok = true;
+    int buf = 0;
+    for (int tile = pair_id; tile < n_total && ok; tile += n_pairs_grid) {
+      const PairTile t = pair_tile<BN, MODE>(tile, rank, p, s_efo, s_pairs);
+      const size_t grow = (size_t)t.m0 + row_in_tile;
+      const int c_base = t.n0 + half * COLS_PER_WARP;
+      if (t.nkt == 0) {
+        if (MODE == WGRAD && !p.accumulate) {
+          float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.c) +
+                                                  ((size_t)t.e * p.rows + grow) * p.N + c_base);
+          for (int i = 0; i < COLS_PER_WARP / 4; ++i) dst[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        continue;
+      }
+      if (lane == 0) ok = mbar_wait(bar_tfull + 8 * as, aphase);
+      ok = __shfl_sync(0xffffffff, ok, 0);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + as * BN + half * COLS_PER_WARP;
+
+      if (MODE == PLAIN) {
+        // 32 columns of bf16 = 64-byte rows, SWIZZLE_64B staging, two buffers of 2 KB
+#pragma unroll 1
+        for (int c = 0; c < COLS_PER_WARP / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(t_row + c * 32, r);
+          tmem_ld_wait();
+          const uint32_t sb = stg + buf * 2048;
+          if (lane == 0) bulk_wait_group_read<1>();
+          __syncwarp();
+          if (t.valid) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t a = sb + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4);
+              st_shared_v4(a, pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1])),
+                           pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3])),
+                           pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5])),
+                           pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7])));
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmap_c, sb, c_base + c * 32, t.m0 + q * 32);
+              bulk_commit_group();
+            }
+          }
+          buf ^= 1;
+        }
+      } else if (MODE == WGRAD) {
+        // 32 columns of f32 = 128-byte rows, SWIZZLE_128B staging, two buffers of 4 KB
+#pragma unroll 1
+        for (int c = 0; c < COLS_PER_WARP / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(t_row + c * 32, r);
+          tmem_ld_wait();
+          const uint32_t sb = stg + buf * 4096;
+          if (lane == 0) bulk_wait_group_read<1>();
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            st_shared_v4(sb + lane * 128 + ((j ^ (lane & 7)) << 4), r[4 * j], r[4 * j + 1], r[4 * j + 2],
+                         r[4 * j + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const int crow = t.e * p.rows + t.m0 + q * 32;
+            if (p.accumulate) tma_reduce_add_2d(&tmap_c, sb, c_base + c * 32, crow);
+            else tma_store_2d(&tmap_c, sb, c_base + c * 32, crow);
+            bulk_commit_group();
+          }
+          buf ^= 1;
+        }
+      } else if (MODE == GATED) {
+        // this warp: z columns [c_base, c_base + 64) -> y1 columns [c_base/2, c_base/2 + 32): one y1 scale group
+        static_assert(MODE != GATED || BN == 128, "GATED uses BN = 128 so that a warp owns whole y1 scale groups");
+        const int Nz = p.N, Ny = p.N / 2;
+        float y[32];
+        uint8_t zs[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t r[32];
+          tmem_ld32(t_row + h * 32, r);
+          tmem_ld_wait();
+          float amax = 0.f;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(__uint_as_float(r[i])));
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float g = __uint_as_float(r[2 * i]), u = __uint_as_float(r[2 * i + 1]);
+            y[h * 16 + i] = bf16_rne((g * fast_sigmoid(g)) * u);
+          }
+          const int e = e8m0_of(fmaxf(amax, 1e-4f));
+          const float qs = qscale_of(e);
+          zs[h] = (uint8_t)e;
+          if (t.valid) {
+            uint4* zd = reinterpret_cast<uint4*>(p.z_fp8 + grow * Nz + c_base + h * 32);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              uint4 v;
+              v.x = pack_e4m3x4(__uint_as_float(r[16 * i + 0]) * qs, __uint_as_float(r[16 * i + 1]) * qs,
+                                __uint_as_float(r[16 * i + 2]) * qs, __uint_as_float(r[16 * i + 3]) * qs);
+              v.y = pack_e4m3x4(__uint_as_float(r[16 * i + 4]) * qs, __uint_as_float(r[16 * i + 5]) * qs,
+                                __uint_as_float(r[16 * i + 6]) * qs, __uint_as_float(r[16 * i + 7]) * qs);
+              v.z = pack_e4m3x4(__uint_as_float(r[16 * i + 8]) * qs, __uint_as_float(r[16 * i + 9]) * qs,
+                                __uint_as_float(r[16 * i + 10]) * qs, __uint_as_float(r[16 * i + 11]) * qs);
+              v.w = pack_e4m3x4(__uint_as_float(r[16 * i + 12]) * qs, __uint_as_float(r[16 * i + 13]) * qs,
+                                __uint_as_float(r[16 * i + 14]) * qs, __uint_as_float(r[16 * i + 15]) * qs);
+              zd[i] = v;
+            }
+          }
+        }
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(y[i]));
+        const int e = e8m0_of(amax);
+        const float qs = qscale_of(e);
+        if (t.valid) {
+          *reinterpret_cast<uint16_t*>(p.z_sc + grow * (Nz / 32) + c_base / 32) = (uint16_t)zs[0] | ((uint16_t)zs[1] << 8);
+          uint4* yd = reinterpret_cast<uint4*>(p.y1_fp8 + grow * Ny + c_base / 2);
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            uint4 v;
+            v.x = pack_e4m3x4(y[16 * i + 0] * qs, y[16 * i + 1] * qs, y[16 * i + 2] * qs, y[16 * i + 3] * qs);
+            v.y = pack_e4m3x4(y[16 * i + 4] * qs, y[16 * i + 5] * qs, y[16 * i + 6] * qs, y[16 * i + 7] * qs);
+            v.z = pack_e4m3x4(y[16 * i + 8] * qs, y[16 * i + 9] * qs, y[16 * i + 10] * qs, y[16 * i + 11] * qs);
+            v.w = pack_e4m3x4(y[16 * i + 12] * qs, y[16 * i + 13] * qs, y[16 * i + 14] * qs, y[16 * i + 15] * qs);
+            yd[i] = v;
+          }
+          const int g = (c_base / 2) / 32;
+          p.y1_sf[((grow / 128) * (size_t)(Ny / 128) + g / 4) * 512 + (grow % 32) * 16 + ((grow % 128) / 32) * 4 +
+                  (g % 4)] = (uint8_t)e;
+        }
+      } else {  // DGATED
+        // this warp: D columns [c_base, c_base + BN/2) of I in chunks of 32 -> dz 64 bf16 (128-byte rows,
+        // SWIZZLE_128B, 4 KB) and y1s 32 bf16 (64-byte rows, SWIZZLE_64B, 2 KB)
+        const int Nz = 2 * p.N;
+        const float s = t.valid ? p.s[grow] : 0.f;
+        float ds_acc = 0.f;
+#pragma unroll 1
+        for (int c = 0; c < COLS_PER_WARP / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(t_row + c * 32, r);
+          uint4 zb[4];
+          float sc0 = 0.f, sc1 = 0.f;
+          if (t.valid) {
+            const uint8_t* zrow = p.z_fp8 + grow * Nz + 2 * (c_base + c * 32);
+            const uint8_t* zsc = p.z_sc + grow * (Nz / 32) + (2 * (c_base + c * 32)) / 32;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) zb[i] = reinterpret_cast<const uint4*>(zrow)[i];
+            const uint32_t sc = *reinterpret_cast<const uint16_t*>(zsc);
+            sc0 = __int_as_float((int)(sc & 0xFF) << 23);
+            sc1 = __int_as_float((int)(sc >> 8) << 23);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) zb[i] = make_uint4(0, 0, 0, 0);
+          }
+          tmem_ld_wait();
+          const uint32_t* zw = reinterpret_cast<const uint32_t*>(zb);
+          uint32_t dzp[32];
+          uint32_t ysp[16];
+          float yprev = 0.f;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const uint32_t pair = (zw[i >> 1] >> (16 * (i & 1))) & 0xFFFF;
+            const float scale = (i < 16) ? sc0 : sc1;
+            const float2 gu = e4m3x2_to_f32(pair);
+            const float g = gu.x * scale, u = gu.y * scale;
+            const float D = __uint_as_float(r[i]);
+            const float dout = s * D;
+            const float sig = fast_sigmoid(g);
+            const float silu = g * sig;
+            const float sd = silu * dout;
+            const float dg = ((sig - silu * sig) * dout + sd) * u;
+            const float yv = silu * u;
+            ds_acc = fmaf(yv, D, ds_acc);
+            dzp[i] = pack_bf16x2(dg, sd);
+            const float ys = s * yv;
+            if (i & 1) ysp[i >> 1] = pack_bf16x2(yprev, ys); else yprev = ys;
+          }
+          if (lane == 0) bulk_wait_group_read<0>();
+          __syncwarp();
+          if (t.valid) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              st_shared_v4(stg + lane * 128 + ((j ^ (lane & 7)) << 4), dzp[4 * j], dzp[4 * j + 1], dzp[4 * j + 2],
+                           dzp[4 * j + 3]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              st_shared_v4(stg + 4096 + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4), ysp[4 * j], ysp[4 * j + 1],
+                           ysp[4 * j + 2], ysp[4 * j + 3]);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmap_c, stg, 2 * (c_base + c * 32), t.m0 + q * 32);
+              tma_store_2d(&tmap_c2, stg + 4096, c_base + c * 32, t.m0 + q * 32);
+              bulk_commit_group();
+            }
+          }
+        }
+        if (t.valid) p.ds_partial[(size_t)((t.n0 / BN) * 2 + half) * p.rows + grow] = ds_acc;
+      }
+
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * as);
+      if (++as == 2) { as = 0; aphase ^= 1; }
+    }
+    if (lane == 0) bulk_wait_group<0>();      // all staged stores have left shared memory and are visible
+    if (!ok && lane == 0) { *s_abort = 1; atomicCAS(p.status, 0, 203); }
+  }
+
+  // common exit: everyone arrives here, also after a failed wait
+  __syncthreads();
+  if (*s_abort) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  cluster_sync_all();                         // the peer may still be signalling this CTA's barriers
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc2(tmem_base, 512);
+}
+
+}  // namespace smoe

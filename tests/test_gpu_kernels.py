@@ -200,9 +200,9 @@ def stats(got, ref):
     return cos, rr
 
 
-@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("bn", [128, 192, 128 | (1 << 17), 256 | (1 << 17)])
 @pytest.mark.parametrize("tiles,N,K", [([1, 0, 2, 1], 256, 128), ([3, 2, 0, 0, 4, 1, 1, 2], 512, 1024),
-                                        ([40, 30, 50, 28], 1536, 768)])
+                                        ([40, 30, 50, 28], 1536, 768), ([5, 4, 0, 7], 768, 256)])
 def test_gemm_varlen_m(ops, bn, tiles, N, K):
     from sonicmoe._lib import lib
     g = torch.Generator().manual_seed(sum(tiles) + N + K)
@@ -297,8 +297,8 @@ def test_gemm_dgated(ops, T, H, I, tiles):
     assert (dz.cpu()[s == 0] == 0).all() and (y1s.cpu()[s == 0] == 0).all()
 
 
-@pytest.mark.parametrize("bn", [128, 256])
-@pytest.mark.parametrize("M,N,tiles", [(128, 256, [1, 0, 2, 1]), (512, 768, [3, 2, 0, 0, 4, 1, 1, 2])])
+@pytest.mark.parametrize("bn", [128, 192, 128 | (1 << 17), 256 | (1 << 17)])
+@pytest.mark.parametrize("M,N,tiles", [(128, 256, [1, 0, 2, 1]), (512, 768, [3, 2, 0, 0, 4, 1, 1, 2]), (768, 384, [2, 1, 3])])
 def test_gemm_wgrad(ops, bn, M, N, tiles):
     from sonicmoe._lib import lib
     g = torch.Generator().manual_seed(M + N)
