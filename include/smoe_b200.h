@@ -72,6 +72,14 @@ int smoe_quant_rows(const void* x_bf16, int64_t M, int64_t K, void* q, void* raw
 int smoe_gather_scales_isa(const void* raw_scales, const int32_t* idx, int64_t rows, int64_t cols, void* isa_scales,
                            void* stream);
 
+/* Rows of an already quantised activation gathered into expert-sorted order: q_out[r,:] = q[idx[r],:] and the
+ * rows' raw scales [T,K/32] written in the ISA layout of (rows, K).  Rows >= *valid_rows (device int, may be null)
+ * are left untouched.  Materialises the A operand of the up-projection / GemmDGated for the tiled-TMA load path;
+ * the reference gathers inside its GEMM (sonicmoe/quack_utils/gemm_sm100_fp8_zeromat.py:65-67) and packs the scales
+ * with _gather_1x32_scales_to_isa (sm100_funcs.py:148-180).  K % 128 == 0. */
+int smoe_gather_rows_fp8(const void* q, const void* raw_scales, const int32_t* idx, const int32_t* valid_rows,
+                         int64_t rows, int64_t K, void* q_out, void* isa_out, void* stream);
+
 /* Column-wise (groups of 32 consecutive rows) of src[idx] (idx may be null): src bf16 [T,dim] ->
  *   q_t  e4m3 [dim, rows]  (TRANSPOSED: the reduction dimension of the weight-gradient GEMM is contiguous)
  *   isa  ISA-packed scales for the logical (dim, rows) operand.
@@ -97,6 +105,8 @@ int smoe_gemm_varlen_m(const void* a_fp8, const void* a_sf, const void* b_fp8, c
 
 /* Up-projection: z = x[a_idx] . W1[e]^T (N = 2I, K = H), y1 = swiglu(z) on interleaved gate/up columns;
  * z -> e4m3 [rows,N] + raw scales [rows,N/32] (amax floor 1e-4), y1 -> bf16 RNE -> e4m3 [rows,N/2] + ISA scales.
+ * a_idx == NULL: x_fp8 is already in expert-sorted row order ([rows,K]) and is loaded as plain TMA tiles;
+ * a_idx != NULL: rows are fetched by index with TMA gather4 and no gathered copy exists.
  * Replaces gemm_gated (sonicmoe/quack_utils/sm100_funcs.py:207-455, gemm_sm100_fp8_zeromat.py:379-406,
  * _gated_epilogues.py:1331-1513).  N % 256 == 0. */
 int smoe_gemm_gated(const void* x_fp8, int64_t T, const int32_t* a_idx, const void* a_sf, const void* w1_fp8,

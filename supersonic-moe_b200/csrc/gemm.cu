@@ -100,7 +100,7 @@ struct OutMaps {
 template <int BN, int MODE>
 static int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa, const CUtensorMap& tsb,
                    const OutMaps& om, const GemmParams& p, int64_t max_pair_tiles, cudaStream_t stream) {
-  using S = Gemm2Smem<BN>;
+  using S = Gemm2Smem<BN, MODE>;
   static bool attr_set = false;
   auto kern = gemm2_mxf8_kernel<BN, MODE>;
   if (!attr_set) {
@@ -119,9 +119,11 @@ static int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
 template <int MODE>
 static int pick_bn2(int64_t N) {
   if (g_force_v1) return 0;
-  if (MODE == GATED) return 128;
+  const bool wide = (MODE == PLAIN || MODE == WGRAD);      // single-stage 256-column tiles
   if (g_force_bn == 128) return 128;
   if (g_force_bn == 192) return (N % 192 == 0) ? 192 : 128;
+  if (g_force_bn == 256) return (wide && N % 256 == 0) ? 256 : 128;
+  if (wide && N % 256 == 0) return 256;
   return (N % 192 == 0) ? 192 : 128;
 }
 
@@ -129,7 +131,7 @@ template <int MODE>
 static int run2(const void* a, int64_t a_rows, int64_t a_cols, const void* b, int64_t b_rows, int64_t b_cols,
                 GemmParams& p, const OutMaps& om, int bn, int64_t sfa_tiles, int64_t sfb_tiles, cudaStream_t stream) {
   CUtensorMap ta, tb, tsa, tsb;
-  constexpr bool gather = (MODE == GATED || MODE == DGATED);
+  const bool gather = p.a_idx != nullptr;
   int rc = make_tmap_u8(&ta, a, a_rows, a_cols, BK, gather ? 1 : BM);
   if (rc) return rc;
   rc = make_tmap_u8(&tb, b, b_rows, b_cols, BK, bn / 2);
@@ -142,7 +144,11 @@ static int run2(const void* a, int64_t a_rows, int64_t a_cols, const void* b, in
   int64_t pair_tiles;
   if (MODE == WGRAD) pair_tiles = (int64_t)p.E * (p.rows / 256) * (p.N / bn);
   else pair_tiles = ((int64_t)p.rows / 256 + p.E) * (p.N / bn);
-  if (bn == 192) return launch2<192, MODE == GATED ? PLAIN : MODE>(ta, tb, tsa, tsb, om, p, pair_tiles, stream);
+  if (bn == 256) {
+    constexpr int M256 = (MODE == PLAIN || MODE == WGRAD) ? MODE : PLAIN;   // only the wide modes reach here
+    return launch2<256, M256>(ta, tb, tsa, tsb, om, p, pair_tiles, stream);
+  }
+  if (bn == 192) return launch2<192, MODE>(ta, tb, tsa, tsb, om, p, pair_tiles, stream);
   return launch2<128, MODE>(ta, tb, tsa, tsb, om, p, pair_tiles, stream);
 }
 
@@ -182,7 +188,7 @@ static int run(const void* a, int64_t a_rows, int64_t a_cols, const void* b, int
   }
   const int bn = pick_bn(p.N);
   CUtensorMap ta, tb;
-  constexpr bool gather = (MODE == GATED || MODE == DGATED);
+  const bool gather = p.a_idx != nullptr;
   int rc = make_tmap_u8(&ta, a, a_rows, a_cols, BK, gather ? 1 : BM);
   if (rc) return rc;
   rc = make_tmap_u8(&tb, b, b_rows, b_cols, BK, bn);

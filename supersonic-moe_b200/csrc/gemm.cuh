@@ -144,7 +144,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const GemmParams p) {
   using S = GemmSmem<BN>;
-  constexpr bool GATHER = (MODE == GATED || MODE == DGATED);
+  const bool GATHER = p.a_idx != nullptr;   // rows of A fetched by index (TMA gather4) vs. a plain tile
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* aux = smem + S::STAGES * S::STAGE_BYTES;

@@ -90,21 +90,24 @@ __device__ __forceinline__ float fast_sigmoid(float x) {
   return r;
 }
 
-template <int BN>
+template <int BN, int MODE>
 struct Gemm2Smem {
   static constexpr int A_BYTES = BM * BK;                 // this CTA's 128 rows
   static constexpr int B_BYTES = (BN / 2) * BK;           // this CTA's half of the B tile
   static constexpr int SF_BYTES = 2048;                   // SFA 512 + SFB 2 x 512, padded
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SF_BYTES;
-  static constexpr int EPI_BYTES_PER_WARP = 8192;
+  // output staging per epilogue warp: PLAIN 2 x 2 KB (bf16 32x32), WGRAD 2 x 4 KB (f32 32x32),
+  // DGATED 4 KB (dz) + 2 KB (y1s) (+2 KB so that buffers stay 1 KB aligned), GATED none
+  static constexpr int EPI_BYTES_PER_WARP = MODE == PLAIN ? 4096 : (MODE == GATED ? 0 : 8192);
   static constexpr int EPI_BYTES = kEpiWarps2 * EPI_BYTES_PER_WARP;
   static constexpr int AUX_BYTES = 1024 + 2 * (kMaxExpertsSmem + 1) * 4;
   static constexpr int STAGES_RAW = (227 * 1024 - 1024 - AUX_BYTES - EPI_BYTES) / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_RAW > 6 ? 6 : STAGES_RAW;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int TOTAL = STAGES * STAGE_BYTES + EPI_BYTES + AUX_BYTES + 1024;
+  static constexpr int ACC_STAGES = (BN == 256) ? 1 : 2;  // TMEM: 512 columns
   static constexpr int SFB_TILES = (BN == 128) ? 1 : 2;   // 128-row scale tiles covering the BN window
   static constexpr int SF_COLS = 4 + 4 * SFB_TILES;
-  static constexpr int SF_COL0 = 2 * BN;
+  static constexpr int SF_COL0 = ACC_STAGES * BN;
   static_assert(SF_COL0 + STAGES * SF_COLS <= 512, "TMEM budget");
   static constexpr uint32_t TX_BYTES = 2u * (A_BYTES + B_BYTES + 512 + 512 * SFB_TILES);
 };
@@ -157,8 +160,8 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                   const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                   const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_c2,
                   const GemmParams p) {
-  using S = Gemm2Smem<BN>;
-  constexpr bool GATHER = (MODE == GATED || MODE == DGATED);
+  using S = Gemm2Smem<BN, MODE>;
+  const bool GATHER = p.a_idx != nullptr;   // rows of A fetched by index (TMA gather4) vs. a plain tile
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi = smem + S::STAGES * S::STAGE_BYTES;
@@ -241,13 +244,18 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const uint32_t b_dst = a_dst + S::A_BYTES;
         const uint32_t sf_dst = b_dst + S::B_BYTES;
         if (lane == 0) {
-          if (rank == 0) mbar_expect_tx(bar_full + 8 * stage, S::TX_BYTES);
+          const bool skip_sf = p.debug_skip_store != 0;   // timing experiment: no scale loads (stale scales)
+          if (rank == 0)
+            mbar_expect_tx(bar_full + 8 * stage,
+                           skip_sf ? 2u * (S::A_BYTES + S::B_BYTES) : S::TX_BYTES);
           if (!GATHER) tma_load_2d_pair(a_dst, &tmap_a, full, kt * BK, t.valid ? t.m0 : 0);
           tma_load_2d_pair(b_dst, &tmap_b, full, kt * BK, b_row);
-          tma_load_2d_pair(sf_dst, &tmap_sfa, full, 0, sfa_tile * p.sfa_ktiles + kt);
+          if (!skip_sf) {
+            tma_load_2d_pair(sf_dst, &tmap_sfa, full, 0, sfa_tile * p.sfa_ktiles + kt);
 #pragma unroll
-          for (int j = 0; j < S::SFB_TILES; ++j)
-            tma_load_2d_pair(sf_dst + 512 + 512 * j, &tmap_sfb, full, 0, (sfb_tile + j) * p.sfb_ktiles + kt);
+            for (int j = 0; j < S::SFB_TILES; ++j)
+              tma_load_2d_pair(sf_dst + 512 + 512 * j, &tmap_sfb, full, 0, (sfb_tile + j) * p.sfb_ktiles + kt);
+          }
         }
         if (GATHER) {
           __syncwarp();
@@ -297,7 +305,7 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         }
         if (!ok) break;
         tc_commit_pair(bar_tfull + 8 * as, 3);
-        if (++as == 2) { as = 0; aphase ^= 1; }
+        if (++as == S::ACC_STAGES) { as = 0; aphase ^= 1; }
       }
       if (!ok) { *s_abort = 1; atomicCAS(p.status, 0, 202); }
     }
@@ -332,25 +340,35 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + as * BN + half * COLS_PER_WARP;
 
+      bool released = false;
       if (MODE == PLAIN) {
-        // 32 columns of bf16 = 64-byte rows, SWIZZLE_64B staging, two buffers of 2 KB
-#pragma unroll 1
-        for (int c = 0; c < COLS_PER_WARP / 32; ++c) {
+        // Drain the whole row segment into registers (bf16-packed), hand the accumulator back to the
+        // MMA warp, then stage and store.  32 columns of bf16 = 64-byte rows, SWIZZLE_64B, 2 x 2 KB.
+        constexpr int NC = COLS_PER_WARP / 32;
+        uint32_t pk[NC][16];
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
           uint32_t r[32];
           tmem_ld32(t_row + c * 32, r);
           tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            pk[c][i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * as);
+        released = true;
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
           const uint32_t sb = stg + buf * 2048;
           if (lane == 0) bulk_wait_group_read<1>();
           __syncwarp();
           if (t.valid) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint32_t a = sb + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4);
-              st_shared_v4(a, pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1])),
-                           pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3])),
-                           pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5])),
-                           pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7])));
-            }
+            for (int j = 0; j < 4; ++j)
+              st_shared_v4(sb + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4), pk[c][4 * j], pk[c][4 * j + 1],
+                           pk[c][4 * j + 2], pk[c][4 * j + 3]);
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
@@ -361,19 +379,26 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           buf ^= 1;
         }
       } else if (MODE == WGRAD) {
-        // 32 columns of f32 = 128-byte rows, SWIZZLE_128B staging, two buffers of 4 KB
-#pragma unroll 1
-        for (int c = 0; c < COLS_PER_WARP / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32(t_row + c * 32, r);
-          tmem_ld_wait();
+        // Same scheme with f32: 32 columns = 128-byte rows, SWIZZLE_128B, 2 x 4 KB; TMA reduce-add
+        // when accumulating into an existing gradient.
+        constexpr int NC = COLS_PER_WARP / 32;
+        uint32_t acc[NC][32];
+#pragma unroll
+        for (int c = 0; c < NC; ++c) tmem_ld32(t_row + c * 32, acc[c]);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * as);
+        released = true;
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
           const uint32_t sb = stg + buf * 4096;
           if (lane == 0) bulk_wait_group_read<1>();
           __syncwarp();
 #pragma unroll
           for (int j = 0; j < 8; ++j)
-            st_shared_v4(sb + lane * 128 + ((j ^ (lane & 7)) << 4), r[4 * j], r[4 * j + 1], r[4 * j + 2],
-                         r[4 * j + 3]);
+            st_shared_v4(sb + lane * 128 + ((j ^ (lane & 7)) << 4), acc[c][4 * j], acc[c][4 * j + 1],
+                         acc[c][4 * j + 2], acc[c][4 * j + 3]);
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
@@ -385,64 +410,72 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           buf ^= 1;
         }
       } else if (MODE == GATED) {
-        // this warp: z columns [c_base, c_base + 64) -> y1 columns [c_base/2, c_base/2 + 32): one y1 scale group
-        static_assert(MODE != GATED || BN == 128, "GATED uses BN = 128 so that a warp owns whole y1 scale groups");
+        // 64-column chunks of z (= 32 columns of y1 = one y1 scale group).  BN = 128: one chunk per warp;
+        // BN = 192: the first warp of a quadrant takes chunks 0 and 1, the second takes chunk 2.
+        static_assert(MODE != GATED || BN == 128 || BN == 192, "GATED column tiles");
         const int Nz = p.N, Ny = p.N / 2;
-        float y[32];
-        uint8_t zs[2];
+        const int ch0 = (BN == 128) ? half : (half == 0 ? 0 : 2);
+        const int nch = (BN == 128) ? 1 : (half == 0 ? 2 : 1);
+        const uint32_t t_tile = tmem_base + ((uint32_t)(q * 32) << 16) + as * BN;
+#pragma unroll 1
+        for (int ci = 0; ci < nch; ++ci) {
+          const int zc = t.n0 + (ch0 + ci) * 64;           // first z column of the chunk
+          float y[32];
+          uint32_t zs = 0;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t r[32];
-          tmem_ld32(t_row + h * 32, r);
-          tmem_ld_wait();
+          for (int h = 0; h < 2; ++h) {
+            uint32_t r[32];
+            tmem_ld32(t_tile + (ch0 + ci) * 64 + h * 32, r);
+            tmem_ld_wait();
+            float amax = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(__uint_as_float(r[i])));
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float g = __uint_as_float(r[2 * i]), u = __uint_as_float(r[2 * i + 1]);
+              y[h * 16 + i] = bf16_rne((g * fast_sigmoid(g)) * u);
+            }
+            const int e = e8m0_of(fmaxf(amax, 1e-4f));
+            const float qs = qscale_of(e);
+            zs |= (uint32_t)e << (8 * h);
+            if (t.valid) {
+              uint4* zd = reinterpret_cast<uint4*>(p.z_fp8 + grow * Nz + zc + h * 32);
+#pragma unroll
+              for (int i = 0; i < 2; ++i) {
+                uint4 v;
+                v.x = pack_e4m3x4(__uint_as_float(r[16 * i + 0]) * qs, __uint_as_float(r[16 * i + 1]) * qs,
+                                  __uint_as_float(r[16 * i + 2]) * qs, __uint_as_float(r[16 * i + 3]) * qs);
+                v.y = pack_e4m3x4(__uint_as_float(r[16 * i + 4]) * qs, __uint_as_float(r[16 * i + 5]) * qs,
+                                  __uint_as_float(r[16 * i + 6]) * qs, __uint_as_float(r[16 * i + 7]) * qs);
+                v.z = pack_e4m3x4(__uint_as_float(r[16 * i + 8]) * qs, __uint_as_float(r[16 * i + 9]) * qs,
+                                  __uint_as_float(r[16 * i + 10]) * qs, __uint_as_float(r[16 * i + 11]) * qs);
+                v.w = pack_e4m3x4(__uint_as_float(r[16 * i + 12]) * qs, __uint_as_float(r[16 * i + 13]) * qs,
+                                  __uint_as_float(r[16 * i + 14]) * qs, __uint_as_float(r[16 * i + 15]) * qs);
+                zd[i] = v;
+              }
+            }
+          }
           float amax = 0.f;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(__uint_as_float(r[i])));
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float g = __uint_as_float(r[2 * i]), u = __uint_as_float(r[2 * i + 1]);
-            y[h * 16 + i] = bf16_rne((g * fast_sigmoid(g)) * u);
-          }
-          const int e = e8m0_of(fmaxf(amax, 1e-4f));
+          for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(y[i]));
+          const int e = e8m0_of(amax);
           const float qs = qscale_of(e);
-          zs[h] = (uint8_t)e;
           if (t.valid) {
-            uint4* zd = reinterpret_cast<uint4*>(p.z_fp8 + grow * Nz + c_base + h * 32);
+            *reinterpret_cast<uint16_t*>(p.z_sc + grow * (Nz / 32) + zc / 32) = (uint16_t)zs;
+            uint4* yd = reinterpret_cast<uint4*>(p.y1_fp8 + grow * Ny + zc / 2);
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
               uint4 v;
-              v.x = pack_e4m3x4(__uint_as_float(r[16 * i + 0]) * qs, __uint_as_float(r[16 * i + 1]) * qs,
-                                __uint_as_float(r[16 * i + 2]) * qs, __uint_as_float(r[16 * i + 3]) * qs);
-              v.y = pack_e4m3x4(__uint_as_float(r[16 * i + 4]) * qs, __uint_as_float(r[16 * i + 5]) * qs,
-                                __uint_as_float(r[16 * i + 6]) * qs, __uint_as_float(r[16 * i + 7]) * qs);
-              v.z = pack_e4m3x4(__uint_as_float(r[16 * i + 8]) * qs, __uint_as_float(r[16 * i + 9]) * qs,
-                                __uint_as_float(r[16 * i + 10]) * qs, __uint_as_float(r[16 * i + 11]) * qs);
-              v.w = pack_e4m3x4(__uint_as_float(r[16 * i + 12]) * qs, __uint_as_float(r[16 * i + 13]) * qs,
-                                __uint_as_float(r[16 * i + 14]) * qs, __uint_as_float(r[16 * i + 15]) * qs);
-              zd[i] = v;
+              v.x = pack_e4m3x4(y[16 * i + 0] * qs, y[16 * i + 1] * qs, y[16 * i + 2] * qs, y[16 * i + 3] * qs);
+              v.y = pack_e4m3x4(y[16 * i + 4] * qs, y[16 * i + 5] * qs, y[16 * i + 6] * qs, y[16 * i + 7] * qs);
+              v.z = pack_e4m3x4(y[16 * i + 8] * qs, y[16 * i + 9] * qs, y[16 * i + 10] * qs, y[16 * i + 11] * qs);
+              v.w = pack_e4m3x4(y[16 * i + 12] * qs, y[16 * i + 13] * qs, y[16 * i + 14] * qs, y[16 * i + 15] * qs);
+              yd[i] = v;
             }
+            const int g = zc / 64;
+            p.y1_sf[((grow / 128) * (size_t)(Ny / 128) + g / 4) * 512 + (grow % 32) * 16 + ((grow % 128) / 32) * 4 +
+                    (g % 4)] = (uint8_t)e;
           }
-        }
-        float amax = 0.f;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(y[i]));
-        const int e = e8m0_of(amax);
-        const float qs = qscale_of(e);
-        if (t.valid) {
-          *reinterpret_cast<uint16_t*>(p.z_sc + grow * (Nz / 32) + c_base / 32) = (uint16_t)zs[0] | ((uint16_t)zs[1] << 8);
-          uint4* yd = reinterpret_cast<uint4*>(p.y1_fp8 + grow * Ny + c_base / 2);
-#pragma unroll
-          for (int i = 0; i < 2; ++i) {
-            uint4 v;
-            v.x = pack_e4m3x4(y[16 * i + 0] * qs, y[16 * i + 1] * qs, y[16 * i + 2] * qs, y[16 * i + 3] * qs);
-            v.y = pack_e4m3x4(y[16 * i + 4] * qs, y[16 * i + 5] * qs, y[16 * i + 6] * qs, y[16 * i + 7] * qs);
-            v.z = pack_e4m3x4(y[16 * i + 8] * qs, y[16 * i + 9] * qs, y[16 * i + 10] * qs, y[16 * i + 11] * qs);
-            v.w = pack_e4m3x4(y[16 * i + 12] * qs, y[16 * i + 13] * qs, y[16 * i + 14] * qs, y[16 * i + 15] * qs);
-            yd[i] = v;
-          }
-          const int g = (c_base / 2) / 32;
-          p.y1_sf[((grow / 128) * (size_t)(Ny / 128) + g / 4) * 512 + (grow % 32) * 16 + ((grow % 128) / 32) * 4 +
-                  (g % 4)] = (uint8_t)e;
         }
       } else {  // DGATED
         // this warp: D columns [c_base, c_base + BN/2) of I in chunks of 32 -> dz 64 bf16 (128-byte rows,
@@ -514,10 +547,12 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         if (t.valid) p.ds_partial[(size_t)((t.n0 / BN) * 2 + half) * p.rows + grow] = ds_acc;
       }
 
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * as);
-      if (++as == 2) { as = 0; aphase ^= 1; }
+      if (!released) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * as);
+      }
+      if (++as == S::ACC_STAGES) { as = 0; aphase ^= 1; }
     }
     if (lane == 0) bulk_wait_group<0>();      // all staged stores have left shared memory and are visible
     if (!ok && lane == 0) { *s_abort = 1; atomicCAS(p.status, 0, 203); }

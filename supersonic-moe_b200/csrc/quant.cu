@@ -115,6 +115,22 @@ gather_scales_isa_kernel(const uint8_t* __restrict__ raw, const int* __restrict_
   *reinterpret_cast<uint32_t*>(isa + isa_offset(row, (size_t)kt * 4, k_tiles)) = word;
 }
 
+// ------------------------------------------------------------- row gather
+// out[r, :] = q[idx[r], :] (e4m3 bytes) and the row's scales into the ISA layout of (rows, K).
+// One block per output row; rows at or beyond *valid_rows (over-allocated tail) are skipped.
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const uint4* __restrict__ q, const uint8_t* __restrict__ raw, const int* __restrict__ idx,
+                   const int* __restrict__ valid_rows, int K, uint4* __restrict__ out, uint8_t* __restrict__ isa) {
+  const int64_t row = blockIdx.x;
+  if (valid_rows && row >= *valid_rows) return;
+  const int64_t src = idx[row];
+  const int k16 = K >> 4, groups = K >> 5, k_tiles = K >> 7;
+  for (int c = threadIdx.x; c < k16; c += blockDim.x) out[row * k16 + c] = q[src * k16 + c];
+  for (int kt = threadIdx.x; kt < k_tiles; kt += blockDim.x)
+    *reinterpret_cast<uint32_t*>(isa + isa_offset(row, (size_t)kt * 4, k_tiles)) =
+        *reinterpret_cast<const uint32_t*>(raw + src * groups + kt * 4);
+}
+
 // ------------------------------------------------------------------ columns
 // Tile = 128 rows x 64 columns of src[idx].  Groups run down the rows; the
 // e4m3 bytes are written transposed ([dim, rows]) so that the reduction
@@ -242,6 +258,17 @@ int smoe_gather_scales_isa(const void* raw_scales, const int32_t* idx, int64_t r
   const int64_t n = rows * k_tiles;
   gather_scales_isa_kernel<<<(int)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
       (const uint8_t*)raw_scales, idx, rows, groups, k_tiles, (uint8_t*)isa_scales);
+  return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
+}
+
+int smoe_gather_rows_fp8(const void* q, const void* raw_scales, const int32_t* idx, const int32_t* valid_rows,
+                         int64_t rows, int64_t K, void* q_out, void* isa_out, void* stream) {
+  if (rows < 0 || K <= 0 || K % 128) return SMOE_ERR_SHAPE;
+  if (((uintptr_t)q & 15) || ((uintptr_t)q_out & 15) || ((uintptr_t)raw_scales & 3)) return SMOE_ERR_ALIGN;
+  if (rows == 0) return SMOE_OK;
+  const int threads = K / 16 >= 256 ? 256 : (int)((K / 16 + 31) / 32 * 32);
+  gather_rows_kernel<<<(unsigned)rows, threads, 0, (cudaStream_t)stream>>>(
+      (const uint4*)q, (const uint8_t*)raw_scales, idx, valid_rows, (int)K, (uint4*)q_out, (uint8_t*)isa_out);
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }
 

@@ -141,6 +141,18 @@ def gather_scales_isa(raw, idx, rows, cols):
 
 
 @_timed
+def gather_rows_fp8(q, raw, idx, rows, valid_rows=None):
+    """q u8 [T,K], raw scales u8 [T,K/32] -> (q[idx] [rows,K], ISA scales of (rows,K))."""
+    _cuda(q, raw, idx, valid_rows)
+    K = q.shape[1]
+    out = torch.empty(rows, K, dtype=_U8, device=q.device)
+    isa = torch.empty(isa_bytes(rows, K), dtype=_U8, device=q.device)
+    check(lib.smoe_gather_rows_fp8(_p(q), _p(raw), _p(idx), _p(valid_rows), rows, K, _p(out), _p(isa), _stream()),
+          "gather_rows_fp8")
+    return out, isa
+
+
+@_timed
 def quant_cols_t(src, idx, rows):
     """bf16 [T,dim] (rows gathered by idx, or None) -> (e4m3 bytes [dim, rows], ISA scales for (dim, rows))."""
     _cuda(src, idx)
@@ -184,6 +196,8 @@ def gemm_varlen_m(a_q, a_sf, b_q, b_sf, efo):
 def gemm_gated(x_q, a_idx, a_sf, w1_q, w1_sf, efo, rows):
     """x_q u8 [T,H], w1_q u8 [E,2I,H] -> z_q [rows,2I], z_sc [rows,2I/32], y1_q [rows,I], y1_sf (ISA)."""
     _cuda(x_q, a_idx, a_sf, w1_q, w1_sf, efo)
+    if a_idx is None and x_q.shape[0] != rows:
+        raise ValueError("gemm_gated without a_idx needs x_q in expert-sorted order [rows, K]")
     T, K = x_q.shape
     E, N, _ = w1_q.shape
     dev = x_q.device
@@ -200,6 +214,8 @@ def gemm_gated(x_q, a_idx, a_sf, w1_q, w1_sf, efo, rows):
 def gemm_dgated(dout_q, a_idx, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, rows):
     """dout_q u8 [T,H], w2t_q u8 [E,I,H] -> dz bf16 [rows,2I], y1s bf16 [rows,I], ds_partial f32 [parts, rows]."""
     _cuda(dout_q, a_idx, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s)
+    if a_idx is None and dout_q.shape[0] != rows:
+        raise ValueError("gemm_dgated without a_idx needs dout_q in expert-sorted order [rows, K]")
     T, K = dout_q.shape
     E, N, _ = w2t_q.shape
     dev = dout_q.device

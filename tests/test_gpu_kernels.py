@@ -114,6 +114,18 @@ def test_gather_scales_isa(ops):
     assert torch.equal(got.cpu(), Q.gather_scales_to_isa(raw, idx, K))
 
 
+def test_gather_rows_fp8(ops):
+    T, K, rows, valid = 300, 512, 1024, 896
+    g = torch.Generator().manual_seed(8)
+    q = torch.randint(0, 256, (T, K), generator=g, dtype=torch.uint8)
+    raw = torch.randint(0, 256, (T, K // 32), generator=g, dtype=torch.uint8)
+    idx = torch.randint(0, T, (rows,), generator=g, dtype=torch.int32)
+    vr = torch.tensor([valid], dtype=torch.int32)
+    out, isa = ops.gather_rows_fp8(q.to(DEV), raw.to(DEV), idx.to(DEV), rows, vr.to(DEV))
+    assert torch.equal(out.cpu()[:valid], q[idx.long()][:valid])
+    assert torch.equal(Q.unpack_isa(isa.cpu(), rows, K)[:valid], raw[idx.long()][:valid])
+
+
 @pytest.mark.parametrize("T,dim,rows", [(256, 256, 512), (1000, 3072, 2048), (64, 64, 128)])
 def test_quant_cols_transposed_bit_exact(ops, T, dim, rows):
     x = adversarial_rows(T, dim, T + dim)
@@ -200,7 +212,7 @@ def stats(got, ref):
     return cos, rr
 
 
-@pytest.mark.parametrize("bn", [128, 192, 128 | (1 << 17), 256 | (1 << 17)])
+@pytest.mark.parametrize("bn", [128, 192, 256, 128 | (1 << 17), 256 | (1 << 17)])
 @pytest.mark.parametrize("tiles,N,K", [([1, 0, 2, 1], 256, 128), ([3, 2, 0, 0, 4, 1, 1, 2], 512, 1024),
                                         ([40, 30, 50, 28], 1536, 768), ([5, 4, 0, 7], 768, 256)])
 def test_gemm_varlen_m(ops, bn, tiles, N, K):
@@ -240,15 +252,36 @@ def gated_inputs(T, H, I, tiles, seed):
     return g, E, efo, rows, x, w1, a_idx
 
 
-@pytest.mark.parametrize("T,H,I,tiles", [(300, 256, 128, [1, 2, 0, 1]), (2000, 1024, 512, [5, 3, 9, 0, 0, 2, 1, 4])])
-def test_gemm_gated(ops, T, H, I, tiles):
+GATED_SHAPES = [(300, 256, 128, [1, 2, 0, 1]), (2000, 1024, 512, [5, 3, 9, 0, 0, 2, 1, 4]),
+                (1000, 512, 768, [3, 1, 2])]
+# A rows: "tma_gather" = fetched by index inside the GEMM (TMA gather4); "gathered" = expert-sorted copy, tiled TMA;
+# the "_1cta" variants run the single-CTA kernel
+GATHER_MODES = ["tma_gather", "gathered", "tma_gather_1cta", "gathered_1cta"]
+
+
+def _force(mode):
+    from sonicmoe._lib import lib
+    lib.smoe_debug_force_bn((1 << 17) if mode.endswith("_1cta") else 0)
+
+
+@pytest.mark.parametrize("mode", GATHER_MODES)
+@pytest.mark.parametrize("T,H,I,tiles", GATED_SHAPES)
+def test_gemm_gated(ops, T, H, I, tiles, mode):
     g, E, efo, rows, x, w1, a_idx = gated_inputs(T, H, I, tiles, 7)
     xq, xs = Q.row_quant(x)
     wq, ws = Q.row_quant(w1.reshape(E * 2 * I, H))
     a_sf = Q.gather_scales_to_isa(xs, a_idx, H)
     w_sf = Q.pack_isa(ws, E * 2 * I, H)
-    z_q, z_sc, y1_q, y1_sf = ops.gemm_gated(xq.to(DEV), a_idx.to(DEV), a_sf.to(DEV), wq.reshape(E, 2 * I, H).to(DEV),
-                                            w_sf.to(DEV), efo.to(DEV), rows)
+    _force(mode)
+    try:
+        if mode.startswith("tma_gather"):
+            a_in, idx_in = xq.to(DEV), a_idx.to(DEV)
+        else:
+            a_in, idx_in = xq[a_idx.long()].contiguous().to(DEV), None
+        z_q, z_sc, y1_q, y1_sf = ops.gemm_gated(a_in, idx_in, a_sf.to(DEV), wq.reshape(E, 2 * I, H).to(DEV),
+                                                w_sf.to(DEV), efo.to(DEV), rows)
+    finally:
+        _force("")
     torch.cuda.synchronize()
     ops.check_status(DEV)
     X = Q.dequant_rows(xq, xs)[a_idx.long()]
@@ -271,8 +304,9 @@ def test_gemm_gated(ops, T, H, I, tiles):
     assert byte_mis < 0.02, byte_mis
 
 
-@pytest.mark.parametrize("T,H,I,tiles", [(300, 256, 128, [1, 2, 0, 1]), (2000, 1024, 512, [5, 3, 9, 0, 0, 2, 1, 4])])
-def test_gemm_dgated(ops, T, H, I, tiles):
+@pytest.mark.parametrize("mode", GATHER_MODES)
+@pytest.mark.parametrize("T,H,I,tiles", GATED_SHAPES)
+def test_gemm_dgated(ops, T, H, I, tiles, mode):
     g, E, efo, rows, dout, _, a_idx = gated_inputs(T, H, I, tiles, 13)
     w2t = (torch.randn(E, I, H, generator=g) * 0.05).to(torch.bfloat16)
     z = torch.randn(rows, 2 * I, generator=g)
@@ -283,8 +317,16 @@ def test_gemm_dgated(ops, T, H, I, tiles):
     wq, ws = Q.row_quant(w2t.reshape(E * I, H))
     a_sf = Q.gather_scales_to_isa(dsc, a_idx, H)
     w_sf = Q.pack_isa(ws, E * I, H)
-    dz, y1s, dsp = ops.gemm_dgated(dq.to(DEV), a_idx.to(DEV), a_sf.to(DEV), wq.reshape(E, I, H).to(DEV), w_sf.to(DEV),
-                                   efo.to(DEV), zq.to(DEV), zs.to(DEV), s.to(DEV), rows)
+    _force(mode)
+    try:
+        if mode.startswith("tma_gather"):
+            a_in, idx_in = dq.to(DEV), a_idx.to(DEV)
+        else:
+            a_in, idx_in = dq[a_idx.long()].contiguous().to(DEV), None
+        dz, y1s, dsp = ops.gemm_dgated(a_in, idx_in, a_sf.to(DEV), wq.reshape(E, I, H).to(DEV), w_sf.to(DEV),
+                                       efo.to(DEV), zq.to(DEV), zs.to(DEV), s.to(DEV), rows)
+    finally:
+        _force("")
     torch.cuda.synchronize()
     ops.check_status(DEV)
     Dm = Q.dequant_rows(dq, dsc)[a_idx.long()]
@@ -297,7 +339,7 @@ def test_gemm_dgated(ops, T, H, I, tiles):
     assert (dz.cpu()[s == 0] == 0).all() and (y1s.cpu()[s == 0] == 0).all()
 
 
-@pytest.mark.parametrize("bn", [128, 192, 128 | (1 << 17), 256 | (1 << 17)])
+@pytest.mark.parametrize("bn", [128, 192, 256, 128 | (1 << 17), 256 | (1 << 17)])
 @pytest.mark.parametrize("M,N,tiles", [(128, 256, [1, 0, 2, 1]), (512, 768, [3, 2, 0, 0, 4, 1, 1, 2]), (768, 384, [2, 1, 3])])
 def test_gemm_wgrad(ops, bn, M, N, tiles):
     from sonicmoe._lib import lib
