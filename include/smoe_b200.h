@@ -88,6 +88,12 @@ int smoe_gather_rows_fp8(const void* q, const void* raw_scales, const int32_t* i
 int smoe_quant_cols_t(const void* src_bf16, const int32_t* idx, int64_t rows, int64_t dim, void* q_t, void* isa,
                       void* stream);
 
+/* Same, for a source that is already e4m3 with raw row-wise 1x32 scales [T,dim/32] (an FP8 dispatch payload):
+ * dequantise, then column-wise re-quantise.  Replaces _dequant_colwise_quantize_and_pack_from_isa_kernel
+ * (sonicmoe/quack_utils/blockscaled_fp8_gemm.py:5206-5359). */
+int smoe_requant_cols_t(const void* src_fp8, const void* src_scales, const int32_t* idx, int64_t rows, int64_t dim,
+                        void* q_t, void* isa, void* stream);
+
 /* 32x32 block ("iso32") quantizer: dz bf16 [rows, cols] -> q e4m3 [rows, cols] + row-ISA scales for (rows, cols),
  * q_t e4m3 [cols, rows] + col-ISA scales for (cols, rows).  Replaces dual_quantize_varlen iso32
  * (sonicmoe/quack_utils/blockscaled_fp8_gemm.py:2052-2198).  rows % 128 == 0, cols % 128 == 0. */

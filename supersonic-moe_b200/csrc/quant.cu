@@ -139,20 +139,42 @@ constexpr int CT_ROWS = 128, CT_COLS = 64, CT_PITCH = CT_COLS + 2;
 
 // ISO: one scale per 32x32 block (also emits the non-transposed bytes and the
 // row-direction scales); otherwise one scale per (column, 32 rows).
-template <bool ISO>
+// SRC_FP8: the source is e4m3 bytes with raw row-wise 1x32 scales (`src_scales`, [T, dim/32]); it is
+// dequantised exactly (an e4m3 value times a power of two fits bf16) and re-quantised column-wise.
+template <bool ISO, bool SRC_FP8>
 __global__ void __launch_bounds__(256)
-quant_cols_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ idx, int64_t rows, int dim,
-                  uint8_t* __restrict__ q_t, uint8_t* __restrict__ col_isa, uint8_t* __restrict__ q,
-                  uint8_t* __restrict__ row_isa) {
+quant_cols_kernel(const void* __restrict__ src_, const uint8_t* __restrict__ src_scales,
+                  const int* __restrict__ idx, int64_t rows, int dim, uint8_t* __restrict__ q_t,
+                  uint8_t* __restrict__ col_isa, uint8_t* __restrict__ q, uint8_t* __restrict__ row_isa) {
   __shared__ __nv_bfloat16 s_in[CT_ROWS][CT_PITCH];
   __shared__ __align__(16) uint8_t s_out[CT_COLS][CT_ROWS + 16];
   __shared__ uint32_t s_sc[CT_COLS];
   const int tid = threadIdx.x;
   const int64_t r0 = (int64_t)blockIdx.x * CT_ROWS;
   const int c0 = blockIdx.y * CT_COLS;
+  const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(src_);
 
-  // load: 8 threads x 16 bytes cover one 64-column row; 32 rows per pass
-  {
+  if (SRC_FP8) {
+    // 4 threads x 16 bytes cover one 64-column row; 64 rows per pass
+    const uint8_t* src8 = reinterpret_cast<const uint8_t*>(src_);
+    const int rr = tid >> 2, cc = (tid & 3) * 16;
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+      const int r = pass * 64 + rr;
+      const int64_t srow = idx ? idx[r0 + r] : (r0 + r);
+      const uint4 v = *reinterpret_cast<const uint4*>(src8 + srow * dim + c0 + cc);
+      const float sc = __int_as_float((int)src_scales[srow * (dim >> 5) + ((c0 + cc) >> 5)] << 23);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        uint32_t h2;
+        asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"((uint16_t)(w[i >> 1] >> (16 * (i & 1)))));
+        s_in[r][cc + 2 * i] = __float2bfloat16_rn(__half2float(__ushort_as_half((unsigned short)(h2 & 0xFFFF))) * sc);
+        s_in[r][cc + 2 * i + 1] = __float2bfloat16_rn(__half2float(__ushort_as_half((unsigned short)(h2 >> 16))) * sc);
+      }
+    }
+  } else {
+    // load: 8 threads x 16 bytes cover one 64-column row; 32 rows per pass
     const int rr = tid >> 3, cc = (tid & 7) * 8;
 #pragma unroll
     for (int pass = 0; pass < 4; ++pass) {
@@ -277,8 +299,19 @@ int smoe_quant_cols_t(const void* src_bf16, const int32_t* idx, int64_t rows, in
   if (rows < 0 || rows % 128 || dim <= 0 || dim % 64) return SMOE_ERR_SHAPE;
   if (rows == 0) return SMOE_OK;
   dim3 grid((unsigned)(rows / CT_ROWS), (unsigned)(dim / CT_COLS));
-  quant_cols_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)src_bf16, idx, rows, (int)dim,
-                                                                   (uint8_t*)q_t, (uint8_t*)isa, nullptr, nullptr);
+  quant_cols_kernel<false, false><<<grid, 256, 0, (cudaStream_t)stream>>>(src_bf16, nullptr, idx, rows, (int)dim,
+                                                                          (uint8_t*)q_t, (uint8_t*)isa, nullptr, nullptr);
+  return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
+}
+
+int smoe_requant_cols_t(const void* src_fp8, const void* src_scales, const int32_t* idx, int64_t rows, int64_t dim,
+                        void* q_t, void* isa, void* stream) {
+  if (rows < 0 || rows % 128 || dim <= 0 || dim % 64) return SMOE_ERR_SHAPE;
+  if (!src_scales) return SMOE_ERR_ARG;
+  if (rows == 0) return SMOE_OK;
+  dim3 grid((unsigned)(rows / CT_ROWS), (unsigned)(dim / CT_COLS));
+  quant_cols_kernel<false, true><<<grid, 256, 0, (cudaStream_t)stream>>>(
+      src_fp8, (const uint8_t*)src_scales, idx, rows, (int)dim, (uint8_t*)q_t, (uint8_t*)isa, nullptr, nullptr);
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }
 
@@ -287,9 +320,9 @@ int smoe_quant_iso32(const void* x_bf16, int64_t rows, int64_t cols, void* q, vo
   if (rows < 0 || rows % 128 || cols <= 0 || cols % 128) return SMOE_ERR_SHAPE;
   if (rows == 0) return SMOE_OK;
   dim3 grid((unsigned)(rows / CT_ROWS), (unsigned)(cols / CT_COLS));
-  quant_cols_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x_bf16, nullptr, rows,
-                                                                  (int)cols, (uint8_t*)q_t, (uint8_t*)col_isa,
-                                                                  (uint8_t*)q, (uint8_t*)row_isa);
+  quant_cols_kernel<true, false><<<grid, 256, 0, (cudaStream_t)stream>>>(x_bf16, nullptr, nullptr, rows, (int)cols,
+                                                                         (uint8_t*)q_t, (uint8_t*)col_isa, (uint8_t*)q,
+                                                                         (uint8_t*)row_isa);
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }
 

@@ -1,0 +1,170 @@
+"""Expert-parallel MoE step: experts are sharded over the ranks of a process
+group, tokens travel to the ranks that own their experts and back.
+
+The reference ships no communication code (its host framework calls DeepEP
+around `run_sonic_moe`); this module supplies the two exchanges as NCCL
+all-to-alls (`torch.distributed.all_to_all_single`, NVLink / NVSwitch on one
+node) with the payload formats the reference's entry points accept:
+
+  dispatch  a token is sent ONCE to every rank that owns at least one of its
+            top-k experts, as e4m3 bytes + raw 1x32 ue8m0 scales (quantise before
+            the wire: half the bytes of bf16), with its K local expert ids
+            (-1 = not on that rank) and K probabilities
+            -> `run_sonic_moe(hidden_states=e4m3, fp8_scale=scales, topk_indices with -1)`
+  combine   each rank returns one bf16 row per received token (the weighted sum
+            over ITS experts); the source adds the copies in ascending rank order
+  backward  mirrors them: dout is dispatched as e4m3 + scales and handed to the
+            down-projection backward through `Fp8CombineGradHandle`; dx and the
+            score gradients return with the reverse all-to-all.
+
+Every reduction has a fixed order, so results do not depend on timing.
+The planning and exchange code is device-agnostic (CPU tensors + gloo work);
+only the FP8 payload and the expert compute need the CUDA kernels.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+class DispatchPlan:
+    """Who goes where, built from the top-k indices of this rank's tokens.
+
+    send_tok   [n_send]  token of each outgoing row, grouped by destination rank, ascending token inside
+    send_idx   [n_send,K] local expert id on the destination (-1 where the slot lives elsewhere)
+    send_counts / recv_counts  rows per peer (host lists)
+    copy_pos / copy_off  for the source-side reductions: the outgoing rows of token t are
+                         copy_pos[copy_off[t]:copy_off[t+1]], ascending destination rank
+    """
+
+    def __init__(self, idx: torch.Tensor, E: int, group):
+        world = dist.get_world_size(group)
+        assert E % world == 0
+        El = E // world
+        T, K = idx.shape
+        dest = torch.div(idx, El, rounding_mode="floor")                     # [T,K] owning rank
+        ranks = torch.arange(world, device=idx.device).view(world, 1, 1)
+        hit = (dest.unsqueeze(0) == ranks) & (idx.unsqueeze(0) >= 0)          # [P,T,K]
+        goes = hit.any(dim=2)                                                 # [P,T]
+        pt = goes.nonzero()                                                   # rank-major, token ascending
+        self.send_rank, self.send_tok = pt[:, 0], pt[:, 1]
+        local = idx.unsqueeze(0) - ranks * El
+        local = torch.where(hit, local, torch.full_like(local, -1))          # [P,T,K]
+        self.send_idx = local[self.send_rank, self.send_tok].to(torch.int32).contiguous()
+        counts = goes.sum(dim=1).to(torch.int64)
+        recv = torch.empty_like(counts)
+        dist.all_to_all_single(recv, counts, group=group)
+        self.send_counts = counts.tolist()
+        self.recv_counts = recv.tolist()
+        self.n_send, self.n_recv = sum(self.send_counts), sum(self.recv_counts)
+        # copies of a token, ascending rank: stable sort of the outgoing rows by token
+        order = torch.sort(self.send_tok, stable=True).indices
+        self.copy_pos = order.to(torch.int32).contiguous()
+        off = torch.zeros(T + 1, dtype=torch.int64, device=idx.device)
+        off[1:] = goes.sum(dim=0).cumsum(0)
+        self.copy_off = off.to(torch.int32).contiguous()
+        self.T, self.K, self.El, self.group = T, K, El, group
+
+    def a2a(self, send: torch.Tensor, reverse: bool = False) -> torch.Tensor:
+        """Rows travel to their destination (or, reversed, back to their source)."""
+        s, r = (self.recv_counts, self.send_counts) if reverse else (self.send_counts, self.recv_counts)
+        out = send.new_empty((sum(r),) + tuple(send.shape[1:]))
+        dist.all_to_all_single(out, send.contiguous(), output_split_sizes=r, input_split_sizes=s, group=self.group)
+        return out
+
+    def sum_copies(self, rows: torch.Tensor) -> torch.Tensor:
+        """[n_send, C] -> [T, C]: add a token's copies in ascending rank order (fp32 accumulate)."""
+        if rows.is_cuda and rows.dtype == torch.bfloat16 and rows.shape[1] % 8 == 0:
+            from . import ops
+            return ops.combine(rows.contiguous(), self.copy_pos, self.copy_off, None, self.T)
+        out = torch.zeros(self.T, rows.shape[1], dtype=torch.float32, device=rows.device)
+        n = (self.copy_off[1:] - self.copy_off[:-1]).long()
+        for j in range(int(n.max()) if self.T else 0):
+            has = n > j
+            out[has] += rows[self.copy_pos[(self.copy_off[:-1].long() + j)[has]].long()].float()
+        return out.to(rows.dtype)
+
+
+class _Dispatch(torch.autograd.Function):
+    """x [T,H], probs [T,K] -> rows received by this rank.  FP8 payload: outputs (placeholder [N,H] carrying
+    the graph, probs [N,K], e4m3 bytes [N,H], raw scales [N,H/32]); bf16 payload: (x rows, probs, None, None)."""
+
+    @staticmethod
+    def forward(ctx, x, probs, plan: DispatchPlan, fp8: bool):
+        ctx.plan, ctx.x_dtype = plan, x.dtype
+        tok = plan.send_tok
+        p_recv = plan.a2a(probs.float()[tok])
+        if fp8:
+            from . import ops
+            q, raw, _ = ops.quant_rows(x.contiguous(), raw=True)
+            q_recv, raw_recv = plan.a2a(q[tok]), plan.a2a(raw[tok])
+            holder = torch.empty((), dtype=x.dtype, device=x.device).expand(plan.n_recv, x.shape[1])
+            ctx.mark_non_differentiable(q_recv, raw_recv)
+            return holder, p_recv, q_recv, raw_recv
+        return plan.a2a(x[tok]), p_recv, None, None
+
+    @staticmethod
+    def backward(ctx, dx_recv, dp_recv, _dq, _draw):
+        plan = ctx.plan
+        dx = dp = None
+        if ctx.needs_input_grad[0]:
+            dx = plan.sum_copies(plan.a2a(dx_recv.contiguous(), reverse=True)).to(ctx.x_dtype)
+        if ctx.needs_input_grad[1] and dp_recv is not None:
+            back = plan.a2a(dp_recv.contiguous().float(), reverse=True)
+            # a slot lives on exactly one rank: every other copy contributes an exact zero
+            dp = torch.zeros(plan.T, plan.K, dtype=torch.float32, device=back.device).index_add_(0, plan.send_tok, back)
+        return dx, dp, None, None
+
+
+class _Combine(torch.autograd.Function):
+    """Per-rank partial outputs [N,H] -> out [T,H] at the source.  In backward the gradient is dispatched
+    (as e4m3 + scales into `handle` when given, else as bf16 rows)."""
+
+    @staticmethod
+    def forward(ctx, o_recv, plan: DispatchPlan, handle):
+        ctx.plan, ctx.handle = plan, handle
+        return plan.sum_copies(plan.a2a(o_recv.contiguous(), reverse=True))
+
+    @staticmethod
+    def backward(ctx, dout):
+        plan, tok = ctx.plan, ctx.plan.send_tok
+        dout = dout.contiguous()
+        if ctx.handle is not None:
+            from . import ops
+            q, raw, _ = ops.quant_rows(dout.to(torch.bfloat16), raw=True)
+            ctx.handle.put(plan.a2a(q[tok]), plan.a2a(raw[tok]))
+            return torch.empty((), dtype=dout.dtype, device=dout.device).expand(plan.n_recv, dout.shape[1]), None, None
+        return plan.a2a(dout[tok]), None, None
+
+
+class ExpertParallelMoE:
+    """out = EP(x, topk_idx, topk_scores, w1_local, w2_local).
+
+    `expert_fn(rows, local_idx, probs, w1, w2, fp8_scale, handle) -> [N,H]` is the per-rank expert compute; the
+    default runs `run_sonic_moe` on the FP8 payload.  Tests on CPU pass `payload="bf16"` and an fp32 stand-in."""
+
+    def __init__(self, num_experts: int, top_k: int, group=None, payload: str = "fp8", expert_fn=None):
+        self.E, self.K, self.group, self.payload = num_experts, top_k, group, payload
+        self.expert_fn = expert_fn or self._sonic_experts
+
+    def _sonic_experts(self, rows, local_idx, probs, w1, w2, fp8_scale, handle):
+        from .interface import run_sonic_moe
+        if fp8_scale is not None:
+            holder, qbytes = rows
+            return run_sonic_moe(qbytes, local_idx, probs, self.K, self.El, w1, w2, fp8=True, fp8_scale=fp8_scale,
+                                 fp8_combine_grad_handle=handle, sync_free_sizing=True, grad_holder=holder)
+        return run_sonic_moe(rows, local_idx, probs, self.K, self.El, w1, w2, fp8=True, sync_free_sizing=True)
+
+    def __call__(self, x, topk_idx, topk_scores, w1, w2):
+        plan = DispatchPlan(topk_idx, self.E, self.group)
+        self.El = plan.El
+        fp8 = self.payload == "fp8"
+        rows, probs, q, raw = _Dispatch.apply(x, topk_scores, plan, fp8)
+        handle = None
+        if fp8:
+            from .functional import Fp8CombineGradHandle
+            handle = Fp8CombineGradHandle()
+            rows = (rows, q)
+        local_idx = plan.a2a(plan.send_idx)
+        o_recv = self.expert_fn(rows, local_idx, probs, w1, w2, raw, handle)
+        return _Combine.apply(o_recv, plan, handle)

@@ -164,6 +164,23 @@ def _placeholder(like: torch.Tensor, shape):
     return torch.empty((), dtype=torch.bfloat16, device=like.device).expand(*shape)
 
 
+class Fp8CombineGradHandle:
+    """Carrier for an FP8 `dout` payload: the backward of an FP8 combine all-to-all `put`s the received
+    (e4m3 bytes [N,H], raw 1x32 ue8m0 scales [N,H/32]); `_DownProjection.backward` `take`s it instead of
+    quantising the gradient tensor it is handed (reference: fp8_combine_grad_handle,
+    sonicmoe/functional/__init__.py:2130-2157)."""
+
+    def __init__(self):
+        self._payload = None
+
+    def put(self, q, raw):
+        self._payload = (q, raw)
+
+    def take(self):
+        p, self._payload = self._payload, None
+        return p
+
+
 class _UpProjection(torch.autograd.Function):
     @classmethod
     def apply(cls, x, w1, b1, expert_frequency_offset, total_expert_freq, K, stream_id, x_gather_idx, s_scatter_idx,
@@ -220,9 +237,10 @@ class _UpProjection(torch.autograd.Function):
         TKp = dz_q.shape[0]
         dw1 = None
         if ctx.needs_input_grad[1]:
-            if ctx.x_is_fp8:
-                raise NotImplementedError("weight gradients from an FP8 x payload need the dequant-requant quantizer")
-            x_t, x_sf = ops.quant_cols_t(x, x_gather_idx, TKp)
+            if ctx.x_is_fp8:     # x is e4m3 + raw scales: dequantise, then column-wise re-quantise
+                x_t, x_sf = ops.requant_cols_t(x, x_raw, x_gather_idx, TKp)
+            else:
+                x_t, x_sf = ops.quant_cols_t(x, x_gather_idx, TKp)
             mg, base = _grad_target(w1, (E, N2, H))
             if mg is not None:
                 ops.gemm_wgrad(dz_t, dz_csf, x_t, x_sf, efo, mg, accumulate=True)
@@ -268,6 +286,7 @@ class _DownProjection(torch.autograd.Function):
         o = ops.combine(y2, s_rev, naept, topk_scores, int(T))
         ctx.link = link
         ctx.T = int(T)
+        ctx.grad_handle = fp8_combine_grad_handle
         ctx.score_source_shape = None if router_score_source is None else tuple(router_score_source.shape)
         ctx.save_for_backward(w2, topk_scores, efo, x_gather_idx, s_scatter_idx, s_rev, naept, router_score_src_idx)
         return o
@@ -279,11 +298,18 @@ class _DownProjection(torch.autograd.Function):
         z_q, z_sc = link.pop("z")
         E, H, I = w2.shape
         TKp = z_q.shape[0]
-        dout = dout.contiguous()
-        if dout.dtype != torch.bfloat16:
-            dout = dout.to(torch.bfloat16)
         s = ops.gather_scores(topk_scores, s_scatter_idx)
-        dout_q, dout_raw, _ = ops.quant_rows(dout, raw=True)
+        payload = ctx.grad_handle.take() if ctx.grad_handle is not None else None
+        if payload is not None:
+            # dout arrives already as e4m3 + raw 1x32 scales (backward of an FP8 combine all-to-all);
+            # the `dout` argument is then only a placeholder carrying the autograd edge
+            dout_q, dout_raw = payload
+            dout = None
+        else:
+            dout = dout.contiguous()
+            if dout.dtype != torch.bfloat16:
+                dout = dout.to(torch.bfloat16)
+            dout_q, dout_raw, _ = ops.quant_rows(dout, raw=True)
         w2t_q, w2t_sf = weight_fp8(w2, True)
         if USE_TMA_GATHER:
             a_sf = ops.gather_scales_isa(dout_raw, x_gather_idx, TKp, H)
@@ -296,13 +322,16 @@ class _DownProjection(torch.autograd.Function):
         dw2 = None
         if ctx.needs_input_grad[2]:
             y1s_t, y1s_sf = ops.quant_cols_t(y1s, None, TKp)
-            dout_t, dout_sf = ops.quant_cols_t(dout, x_gather_idx, TKp)
+            if dout is None:
+                dout_t, dout_sf = ops.requant_cols_t(dout_q, dout_raw, x_gather_idx, TKp)
+            else:
+                dout_t, dout_sf = ops.quant_cols_t(dout, x_gather_idx, TKp)
             mg, base = _grad_target(w2, (E, I, H))
             if mg is not None:
                 ops.gemm_wgrad(y1s_t, y1s_sf, dout_t, dout_sf, efo, mg, accumulate=True)
                 _after_accumulate(base)
             else:
-                out = torch.empty(E, I, H, dtype=torch.float32, device=dout.device)
+                out = torch.empty(E, I, H, dtype=torch.float32, device=y1s.device)
                 ops.gemm_wgrad(y1s_t, y1s_sf, dout_t, dout_sf, efo, out, accumulate=False)
                 dw2 = out.transpose(1, 2).to(w2.dtype)
         link["dz"] = ops.quant_iso32(dz)

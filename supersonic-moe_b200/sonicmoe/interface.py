@@ -12,18 +12,20 @@ from .functional import _DownProjection, _UpProjection, enable_fp8
 
 def run_sonic_moe(hidden_states, topk_indices, topk_scores, K, E, w1, w2, fp8=False, tokens_per_expert=None,
                   fp8_scale=None, fp8_combine_grad_handle=None, fp8_config=None, release_fp8_weights=False,
-                  activation_type=ActivationType.SWIGLU, sync_free_sizing=False):
+                  activation_type=ActivationType.SWIGLU, sync_free_sizing=False, grad_holder=None):
     """hidden_states [N,H] bf16 (or e4m3 with `fp8_scale` = raw 1x32 ue8m0 bytes [N,H/32]);
     topk_indices [N,K] with -1 for slots whose expert is not local (a row's valid experts distinct);
     topk_scores [N,K] f32; w1 [E,2I,H]; w2 [E,H,I].  Returns [N,H] bf16.
+
+    With an e4m3 `hidden_states` no gradient can flow to it (torch has no differentiable 8-bit tensors);
+    `grad_holder` - a bf16 [N,H] tensor that requires grad, contents ignored - then receives dx in its place
+    (the expert-parallel dispatch passes its placeholder here; not part of the reference signature).
 
     `tokens_per_expert` (host list / tensor) sizes the expert-sorted buffers exactly; with
     `sync_free_sizing` (or without counts) they are sized at the shape-only upper bound and no
     device-to-host copy happens."""
     if not fp8:
         raise NotImplementedError("run_sonic_moe: only fp8=True (MXFP8) is built")
-    if fp8_combine_grad_handle is not None:
-        raise NotImplementedError("fp8_combine_grad_handle (FP8 dout payload) is not built")
     N = hidden_states.shape[0]
     idx = topk_indices if topk_indices.dtype == torch.int32 else topk_indices.to(torch.int32)
     probs = topk_scores.detach()
@@ -38,7 +40,9 @@ def run_sonic_moe(hidden_states, topk_indices, topk_scores, K, E, w1, w2, fp8=Fa
     stream_id = torch.cuda.current_stream().cuda_stream
     payload = None
     if fp8_scale is not None:
-        payload = (hidden_states, fp8_scale)
+        payload = (hidden_states.view(torch.uint8), fp8_scale)
+        hidden_states = grad_holder if grad_holder is not None else torch.empty(
+            (), dtype=torch.bfloat16, device=hidden_states.device).expand(N, hidden_states.shape[1])
     need_router_grad = topk_scores.requires_grad
     with enable_fp8(True):
         y1, z = _UpProjection.apply(hidden_states, w1, None, md["efo"], md["TKp_alloc"], K, stream_id,

@@ -165,6 +165,18 @@ def quant_cols_t(src, idx, rows):
 
 
 @_timed
+def requant_cols_t(src_q, src_raw, idx, rows):
+    """e4m3 bytes [T,dim] + raw row scales [T,dim/32] -> (e4m3 [dim, rows], ISA scales for (dim, rows))."""
+    _cuda(src_q, src_raw, idx)
+    dim = src_q.shape[1]
+    q_t = torch.empty(dim, rows, dtype=_U8, device=src_q.device)
+    isa = torch.empty(isa_bytes(dim, rows), dtype=_U8, device=src_q.device)
+    check(lib.smoe_requant_cols_t(_p(src_q), _p(src_raw), _p(idx), rows, dim, _p(q_t), _p(isa), _stream()),
+          "requant_cols_t")
+    return q_t, isa
+
+
+@_timed
 def quant_iso32(x):
     """bf16 [rows, cols] -> (q [rows,cols], row ISA, q_t [cols,rows], col ISA)."""
     _cuda(x)

@@ -19,3 +19,19 @@ def pytest_configure(config):
 @pytest.fixture(scope="session")
 def golden_dir():
     return GOLDEN
+
+
+@pytest.fixture(scope="session")
+def built_library():
+    """Path of libsmoe_b200.so; compiled with nvcc (no GPU needed) when it is not there yet."""
+    so = os.path.join(PKG, "sonicmoe", "libsmoe_b200.so")
+    if not os.path.exists(so):
+        sys.path.insert(0, ROOT)
+        import __graft_entry__
+        __graft_entry__.build()
+    return so
+
+
+@pytest.fixture(scope="session", autouse=True)
+def _library_present(built_library):
+    return built_library

@@ -1,0 +1,120 @@
+"""Expert-parallel dispatch / combine on CPU: two gloo ranks, bf16 payload, an fp32 stand-in for the
+per-rank expert compute.  Checks the plan, the exchanges and their backward against a single-process
+oracle of the whole problem, and the host-side failure handling (a rank with inconsistent sizes)."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import moe as OM
+from oracle import routing as R
+
+T, H, I, E, K = 96, 64, 32, 8, 4
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _inputs(rank, world):
+    g = torch.Generator().manual_seed(100 + rank)
+    x = torch.randn(T, H, generator=g)
+    dy = torch.randn(T, H, generator=g)
+    logits = torch.randn(T, E, generator=g)
+    scores, idx = OM.router_topk_softmax(logits, K)
+    gw = torch.Generator().manual_seed(7)
+    w1 = torch.randn(E, 2 * I, H, generator=gw) * 0.1
+    w2 = torch.randn(E, H, I, generator=gw) * 0.1
+    return x, dy, scores, idx, w1, w2
+
+
+def _expert_fn_fp32(rows, local_idx, probs, w1, w2, fp8_scale, handle):
+    """Differentiable fp32 stand-in of run_sonic_moe on (rows, masked local indices, probs)."""
+    El = w1.shape[0]
+    out = torch.zeros(rows.shape[0], rows.shape[1])
+    for k in range(local_idx.shape[1]):
+        for e in range(El):
+            sel = (local_idx[:, k] == e).nonzero().flatten()
+            if sel.numel():
+                z = rows[sel] @ w1[e].T
+                y = (z[:, 0::2] * torch.sigmoid(z[:, 0::2])) * z[:, 1::2]
+                out = out.index_add(0, sel, probs[sel, k:k + 1] * (y @ w2[e].T))
+    return out
+
+
+def _worker(rank, world, port, out_q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from sonicmoe.ep import DispatchPlan, ExpertParallelMoE
+    x, dy, scores, idx, w1, w2 = _inputs(rank, world)
+    El = E // world
+    x = x.requires_grad_(True)
+    scores = scores.requires_grad_(True)
+    w1l = w1[rank * El:(rank + 1) * El].clone().requires_grad_(True)
+    w2l = w2[rank * El:(rank + 1) * El].clone().requires_grad_(True)
+    ep = ExpertParallelMoE(E, K, dist.group.WORLD, payload="bf16", expert_fn=_expert_fn_fp32)
+    out = ep(x, idx, scores, w1l, w2l)
+    out.backward(dy)
+    plan = DispatchPlan(idx, E, dist.group.WORLD)
+    res = dict(out=out.detach(), dx=x.grad, ds=scores.grad, dw1=w1l.grad, dw2=w2l.grad,
+               n_send=plan.n_send, n_recv=plan.n_recv, send_counts=plan.send_counts,
+               copies=(plan.copy_off[1:] - plan.copy_off[:-1]).clone())
+    # host-side failure: an exchange whose split sizes disagree with the buffer is refused before any data moves
+    try:
+        plan.send_counts = [c + 1 for c in plan.send_counts]
+        plan.a2a(torch.zeros(plan.n_send, 4))
+        res["bad_split_raises"] = False
+    except Exception:
+        res["bad_split_raises"] = True
+    out_q.put((rank, res))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_ep_two_ranks_matches_single_process_oracle():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=180) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    El = E // world
+    dw1_tot = [torch.zeros(El, 2 * I, H) for _ in range(world)]
+    dw2_tot = [torch.zeros(El, H, I) for _ in range(world)]
+    for rank in range(world):
+        x, dy, scores, idx, w1, w2 = _inputs(rank, world)
+        md = R.topk_metadata(idx, scores, E, 1)
+        gold = OM.moe_fp32(x, w1, w2, md, dy)
+        r = results[rank]
+        torch.testing.assert_close(r["out"], gold["o"], rtol=1e-4, atol=1e-4)
+        torch.testing.assert_close(r["dx"], gold["dx"], rtol=1e-4, atol=1e-4)
+        ds = torch.zeros(T * K)
+        ds[md["score_src_idx"].long()] = gold["ds"]
+        torch.testing.assert_close(r["ds"].flatten(), ds, rtol=1e-4, atol=1e-4)
+        # plan: one copy of a token per destination rank
+        dest = torch.div(idx, El, rounding_mode="floor")
+        n_dest = torch.tensor([len(set(row.tolist())) for row in dest])
+        assert torch.equal(r["copies"].long(), n_dest)
+        assert r["n_send"] == int(n_dest.sum()) and sum(r["send_counts"]) == r["n_send"]
+        assert r["bad_split_raises"]
+        # this rank's tokens contribute to every rank's expert gradients
+        for o in range(world):
+            dw1_tot[o] += gold["dw1"][o * El:(o + 1) * El]
+            dw2_tot[o] += gold["dw2"][o * El:(o + 1) * El]
+    for o in range(world):
+        torch.testing.assert_close(results[o]["dw1"], dw1_tot[o], rtol=1e-4, atol=1e-4)
+        torch.testing.assert_close(results[o]["dw2"], dw2_tot[o], rtol=1e-4, atol=1e-4)
+    assert results[0]["n_recv"] == results[0]["send_counts"][0] + results[1]["send_counts"][0]
