@@ -149,11 +149,14 @@ class ExpertParallelMoE:
 
     def _sonic_experts(self, rows, local_idx, probs, w1, w2, fp8_scale, handle):
         from .interface import run_sonic_moe
+        # the exchange already synchronised with the host for its split sizes; one more small read-back
+        # sizes the expert-sorted buffers exactly instead of at the N*K upper bound
+        counts = torch.bincount(local_idx.flatten().clamp(min=-1) + 1, minlength=self.El + 1)[1:].tolist()
         if fp8_scale is not None:
             holder, qbytes = rows
             return run_sonic_moe(qbytes, local_idx, probs, self.K, self.El, w1, w2, fp8=True, fp8_scale=fp8_scale,
-                                 fp8_combine_grad_handle=handle, sync_free_sizing=True, grad_holder=holder)
-        return run_sonic_moe(rows, local_idx, probs, self.K, self.El, w1, w2, fp8=True, sync_free_sizing=True)
+                                 fp8_combine_grad_handle=handle, tokens_per_expert=counts, grad_holder=holder)
+        return run_sonic_moe(rows, local_idx, probs, self.K, self.El, w1, w2, fp8=True, tokens_per_expert=counts)
 
     def __call__(self, x, topk_idx, topk_scores, w1, w2):
         plan = DispatchPlan(topk_idx, self.E, self.group)
