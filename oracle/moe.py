@@ -34,8 +34,11 @@ from . import quant as Q
 # router
 # ----------------------------------------------------------------------------
 def router_topk_softmax(logits: torch.Tensor, K: int):
-    """top-K on logits (descending), softmax over the K values in fp32."""
-    vals, idx = logits.float().topk(K, dim=-1)
+    """top-K on logits (descending), softmax over the K values in fp32.  Ties (frequent when the logits
+    come out of a bf16 linear) go to the lower expert index - torch.topk leaves that unspecified, a stable
+    descending sort pins it."""
+    vals, idx = torch.sort(logits.float(), dim=-1, descending=True, stable=True)
+    vals, idx = vals[:, :K], idx[:, :K]
     return F.softmax(vals, dim=-1, dtype=torch.float32), idx.to(torch.int32)
 
 

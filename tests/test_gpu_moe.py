@@ -63,11 +63,12 @@ def make_layer(T, H, I, E, K, seed, skew=False):
     return x, dy, w1, w2, wr, bias
 
 
-def oracle_dense(x, dy, w1, w2, wr, K):
-    """fp32 gold of the whole layer: router + experts, explicit backward."""
+def oracle_dense(x, dy, w1, w2, wr, K, logits):
+    """fp32 gold of the whole layer: router + experts, explicit backward.  `logits` are the router logits as the
+    module computes them (bf16 linear on the GPU): a CPU matmul rounds differently and would flip the top-k choice
+    of tokens whose K-th and (K+1)-th logits nearly tie, which is a property of the test, not of the layer."""
     E = wr.shape[0]
     xf, wrf = x.float(), wr.float()
-    logits = (x @ wr.T).float()                      # the module computes logits in bf16, then fp32 softmax
     scores, idx = OM.router_topk_softmax(logits, K)
     md = R.topk_metadata(idx, scores, E, 128, lane_order="slot", pad_mode="virtual")
     r = OM.moe_fp32(x, w1, w2, md, dy)
@@ -99,7 +100,9 @@ def test_moe_module_fwd_bwd_vs_fp32_oracle(sm, T, H, I, E, K, seed):
     out.backward(dy.to(DEV))
     torch.cuda.synchronize()
     sm.ops.check_status(DEV)
-    ref = oracle_dense(x, dy, w1, w2, wr, K)
+    with torch.no_grad():
+        logits = torch.nn.functional.linear(x.to(DEV), moe.router.weight).float().cpu()
+    ref = oracle_dense(x, dy, w1, w2, wr, K, logits)
     emu = ref["emu"]
     check("out", out, ref["o"], emu=emu["o"])
     check("dx", xd.grad, ref["dx_total"], emu=emu["dx_total"])
@@ -108,11 +111,10 @@ def test_moe_module_fwd_bwd_vs_fp32_oracle(sm, T, H, I, E, K, seed):
     check("drouter", moe.router.weight.grad, ref["dwr"], emu=emu["dwr"])
     assert aux is not None and torch.isfinite(aux)
     # aux loss = E * sum(normalize1(sum_t softmax(logits)) * normalize1(freq))
-    logits = (x @ wr.T).float()
     freq = torch.bincount(ref["idx"].flatten().long(), minlength=E).float()
     exp = E * (torch.nn.functional.normalize(torch.softmax(logits, -1).sum(0), p=1, dim=0) *
                torch.nn.functional.normalize(freq, p=1, dim=0)).sum()
-    assert abs(float(aux) - float(exp)) < 2e-2 * abs(float(exp))
+    assert abs(float(aux.detach()) - float(exp)) < 1e-3 * abs(float(exp))
 
 
 def test_module_rejects_non_fp8_and_other_backends(sm):
