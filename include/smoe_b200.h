@@ -58,6 +58,25 @@ int smoe_topk_metadata(const int32_t* idx, const float* probs, int64_t N, int64_
                        int32_t* x_gather_idx, int32_t* s_scatter_idx, int32_t* s_reverse_scatter_idx, int32_t* naept,
                        float* topk_scores, int32_t* score_src_idx, int32_t* counts, void* workspace, void* stream);
 
+/* smoe_topk_metadata for callers that cannot allocate device memory (no counterpart in the reference, whose
+ * launcher allocates its scratch and outputs itself): work captured into a CUDA graph or run from a stream
+ * callback, a serving process that bans cudaMalloc after start-up, a host framework whose allocator this
+ * library has no handle to.  The scratch is a fixed 1 MiB array inside the library (every GPU that loads the
+ * library holds it until the process exits); the caller still passes inputs and outputs.
+ *   - sizes whose scratch need, smoe_topk_metadata_workspace(N, E), exceeds
+ *     smoe_topk_metadata_static_capacity() are refused with SMOE_ERR_SHAPE (e.g. 16384 rows x 128 experts fit);
+ *   - the first call on a device looks the array's device address up (once per device, with that device
+ *     current); make that first call before any stream capture begins;
+ *   - all calls share the one array, which keeps the previous call's contents: nothing in it needs clearing
+ *     between calls, but two calls whose kernels can overlap on the GPU (different streams) race on it;
+ *   - calls no cudaMalloc / cudaFree and no allocating library routine. */
+int smoe_topk_metadata_static(const int32_t* idx, const float* probs, int64_t N, int64_t K, int64_t E,
+                              int64_t alignment, int64_t TK_alloc, int64_t TKp_alloc, int lane_order, int pad_mode,
+                              int32_t* efo, int32_t* x_gather_idx, int32_t* s_scatter_idx,
+                              int32_t* s_reverse_scatter_idx, int32_t* naept, float* topk_scores,
+                              int32_t* score_src_idx, int32_t* counts, void* stream);
+int64_t smoe_topk_metadata_static_capacity(void);
+
 /* ---- MXFP8 1x32 ue8m0 quantizers ------------------------------------------ */
 
 /* Row-wise: x bf16 [M,K] -> e4m3 [M,K] + raw scales [M,K/32] and/or ISA-packed scales

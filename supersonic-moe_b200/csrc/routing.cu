@@ -302,3 +302,59 @@ int smoe_topk_metadata(const int32_t* idx, const float* probs, int64_t N, int64_
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// smoe_topk_metadata_static: the same routing-metadata computation for callers
+// that must not allocate - code running inside a CUDA-graph capture or a stream
+// callback, a serving loop that forbids cudaMalloc after start-up, a host
+// framework whose allocator this library cannot reach.  The scratch that
+// smoe_topk_metadata takes from its caller lives here in a fixed device array
+// that every GPU loading the library holds until the process exits.
+// ---------------------------------------------------------------------------
+namespace smoe {
+
+constexpr size_t kStaticScratchBytes = 1u << 20;   // 1 MiB: e.g. 16384 rows x 128 experts, or 65536 rows x 32
+static __device__ __align__(256) unsigned char g_topk_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static void* g_scratch_addr[kMaxDevices] = {nullptr};   // device address of g_topk_scratch, per device
+
+// In host code the array's name is only a handle; the address a kernel can use
+// comes from cudaGetSymbolAddress, asked once per device with that device current.
+static int static_scratch(void** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return SMOE_ERR_ARG;
+  if (g_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_topk_scratch) != cudaSuccess || p == nullptr) return SMOE_ERR_DRIVER;
+    g_scratch_addr[dev] = p;
+  }
+  *out = g_scratch_addr[dev];
+  return SMOE_OK;
+}
+
+}  // namespace smoe
+
+extern "C" {
+
+int64_t smoe_topk_metadata_static_capacity(void) { return (int64_t)smoe::kStaticScratchBytes; }
+
+int smoe_topk_metadata_static(const int32_t* idx, const float* probs, int64_t N, int64_t K, int64_t E,
+                              int64_t alignment, int64_t TK_alloc, int64_t TKp_alloc, int lane_order, int pad_mode,
+                              int32_t* efo, int32_t* x_gather_idx, int32_t* s_scatter_idx,
+                              int32_t* s_reverse_scatter_idx, int32_t* naept, float* topk_scores,
+                              int32_t* score_src_idx, int32_t* counts, void* stream) {
+  if (N < 0 || E <= 0) return SMOE_ERR_SHAPE;
+  // the scratch need grows with rows x experts; anything beyond the fixed array is refused, never truncated
+  if (smoe_topk_metadata_workspace(N, E) > (int64_t)smoe::kStaticScratchBytes) return SMOE_ERR_SHAPE;
+  void* scratch = nullptr;
+  const int rc = smoe::static_scratch(&scratch);
+  if (rc != SMOE_OK) return rc;
+  // nothing in the scratch has to start at zero: the first kernel clears the bit masks it builds on, and every
+  // other word is written before it is read, so the previous call's contents are harmless
+  return smoe_topk_metadata(idx, probs, N, K, E, alignment, TK_alloc, TKp_alloc, lane_order, pad_mode, efo,
+                            x_gather_idx, s_scatter_idx, s_reverse_scatter_idx, naept, topk_scores, score_src_idx,
+                            counts, scratch, stream);
+}
+
+}  // extern "C"

@@ -19,6 +19,8 @@ SIGNATURES = {
     "smoe_count_cumsum": (_I, [_P, _I, _L, _L, _P, _P, _P]),
     "smoe_topk_metadata_workspace": (_L, [_L, _L]),
     "smoe_topk_metadata": (_I, [_P, _P, _L, _L, _L, _L, _L, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "smoe_topk_metadata_static": (_I, [_P, _P, _L, _L, _L, _L, _L, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "smoe_topk_metadata_static_capacity": (_L, []),
     "smoe_quant_rows": (_I, [_P, _L, _L, _P, _P, _P, _P]),
     "smoe_gather_scales_isa": (_I, [_P, _P, _L, _L, _P, _P]),
     "smoe_gather_rows_fp8": (_I, [_P, _P, _P, _P, _L, _L, _P, _P, _P]),
