@@ -86,6 +86,12 @@ int64_t smoe_topk_metadata_static_capacity(void);
 int smoe_quant_rows(const void* x_bf16, int64_t M, int64_t K, void* q, void* raw_scales, void* isa_scales,
                     void* stream);
 
+/* Row quantizer with the expert-sorted gather fused in: q[r,:] = quant(x[idx[r],:]) for r < min(rows, *valid_rows),
+ * ISA scales for (rows, K).  One pass instead of quantise + gather (sonicmoe/quack_utils/sm100_funcs.py:248-283 does
+ * quantize_and_pack_activation followed by _gather_1x32_scales_to_isa and gathers rows inside its GEMM). */
+int smoe_quant_rows_gather(const void* x_bf16, const int32_t* idx, const int32_t* valid_rows, int64_t rows, int64_t K,
+                           void* q, void* isa_scales, void* stream);
+
 /* raw row scales [T, cols/32] gathered to `rows` rows by idx, ISA layout for (rows, cols).
  * Replaces _gather_1x32_scales_to_isa (sonicmoe/quack_utils/sm100_funcs.py:148-180). */
 int smoe_gather_scales_isa(const void* raw_scales, const int32_t* idx, int64_t rows, int64_t cols, void* isa_scales,

@@ -44,18 +44,22 @@ __device__ __forceinline__ size_t isa_offset(size_t row, size_t g, size_t k_tile
 // One warp per row; a lane owns 8 consecutive values, 4 lanes form a group.
 __global__ void __launch_bounds__(256)
 quant_rows_kernel(const uint4* __restrict__ x, int64_t M, int K, uint2* __restrict__ q, uint8_t* __restrict__ raw,
-                  uint8_t* __restrict__ isa) {
+                  uint8_t* __restrict__ isa, const int* __restrict__ idx, const int* __restrict__ valid_rows) {
   const int lane = threadIdx.x & 31;
   const int64_t warp0 = blockIdx.x * (int64_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
   const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
   const int groups = K / 32, k_tiles = (K + 127) / 128;
-  for (int64_t row = warp0; row < M; row += nwarps) {
+  // with idx: output row `row` is the quantised source row idx[row] (gather fused into the quantizer);
+  // rows at or beyond *valid_rows (over-allocated tail) are skipped
+  const int64_t m_end = valid_rows ? min((int64_t)*valid_rows, M) : M;
+  for (int64_t row = warp0; row < m_end; row += nwarps) {
+    const int64_t srow = idx ? idx[row] : row;
     for (int c0 = 0; c0 < K; c0 += 256) {
       const int col = c0 + lane * 8;
       const bool in = col < K;
       float f[8];
       if (in) {
-        bf16x8_to_f32(x[(row * K + col) >> 3], f);
+        bf16x8_to_f32(x[(srow * K + col) >> 3], f);
       } else {
 #pragma unroll
         for (int i = 0; i < 8; ++i) f[i] = 0.f;
@@ -268,7 +272,21 @@ int smoe_quant_rows(const void* x_bf16, int64_t M, int64_t K, void* q, void* raw
   int64_t blocks = (M + 7) / 8;
   if (blocks > 148 * 16) blocks = 148 * 16;
   quant_rows_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>((const uint4*)x_bf16, M, (int)K, (uint2*)q,
-                                                                   (uint8_t*)raw_scales, (uint8_t*)isa_scales);
+                                                                   (uint8_t*)raw_scales, (uint8_t*)isa_scales, nullptr,
+                                                                   nullptr);
+  return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
+}
+
+int smoe_quant_rows_gather(const void* x_bf16, const int32_t* idx, const int32_t* valid_rows, int64_t rows, int64_t K,
+                           void* q, void* isa_scales, void* stream) {
+  if (rows < 0 || K <= 0 || K % 128) return SMOE_ERR_SHAPE;
+  if (!idx || !isa_scales) return SMOE_ERR_ARG;
+  if (((uintptr_t)x_bf16 & 15) || ((uintptr_t)q & 7)) return SMOE_ERR_ALIGN;
+  if (rows == 0) return SMOE_OK;
+  int64_t blocks = (rows + 7) / 8;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  quant_rows_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>((const uint4*)x_bf16, rows, (int)K, (uint2*)q,
+                                                                   nullptr, (uint8_t*)isa_scales, idx, valid_rows);
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }
 

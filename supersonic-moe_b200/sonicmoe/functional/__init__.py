@@ -195,24 +195,29 @@ class _UpProjection(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w1, b1, efo, TKp, K, stream_id, x_gather_idx, s_scatter_idx, s_rev, naept, is_varlen_K,
                 activation_type, is_inference, low_precision_postact, prequant_payload, fp8_config):
+        ctx.set_materialize_grads(False)   # an unused output must not be handed a zero-filled [TKp, I] gradient
         _require_fp8()
         require_swiglu(activation_type)
         if b1 is not None:
             raise NotImplementedError("expert biases are not supported on the MXFP8 path")
         E, N2, H = w1.shape
         TKp = int(TKp)
+        x_q = x_raw = None
         if prequant_payload is not None:
             # x arrives as e4m3 bytes + raw 1x32 ue8m0 scales (expert-parallel dispatch payload)
             x_q, x_raw = prequant_payload[0], prequant_payload[1]
             x_q = x_q.view(torch.uint8)
-        else:
+        elif USE_TMA_GATHER:
             x_q, x_raw, _ = ops.quant_rows(x.contiguous(), raw=True)
         w1_q, w1_sf = weight_fp8(w1, False)
         if USE_TMA_GATHER:
             a_sf = ops.gather_scales_isa(x_raw, x_gather_idx, TKp, H)
             z_q, z_sc, y1_q, y1_sf = ops.gemm_gated(x_q, x_gather_idx, a_sf, w1_q, w1_sf, efo, TKp)
         else:
-            xg_q, a_sf = ops.gather_rows_fp8(x_q, x_raw, x_gather_idx, TKp, efo[-1:])
+            if x_q is not None:
+                xg_q, a_sf = ops.gather_rows_fp8(x_q, x_raw, x_gather_idx, TKp, efo[-1:])
+            else:      # quantise straight into expert-sorted order
+                xg_q, a_sf = ops.quant_rows_gather(x.contiguous(), x_gather_idx, TKp, efo[-1:])
             z_q, z_sc, y1_q, y1_sf = ops.gemm_gated(xg_q, None, a_sf, w1_q, w1_sf, efo, TKp)
             del xg_q
         link = {"y1": (y1_q, y1_sf), "z": (z_q, z_sc)}
@@ -274,6 +279,7 @@ class _DownProjection(torch.autograd.Function):
     def forward(ctx, y1, z, w2, b2, topk_scores, selected_experts, efo, T, K, stream_id, x_gather_idx, s_scatter_idx,
                 s_rev, naept, is_varlen_K, activation_type, fp8_protocol, fp8_combine_grad_handle, fp8_config,
                 router_score_source, router_score_src_idx):
+        ctx.set_materialize_grads(False)
         _require_fp8()
         if b2 is not None:
             raise NotImplementedError("expert biases are not supported on the MXFP8 path")
@@ -309,13 +315,18 @@ class _DownProjection(torch.autograd.Function):
             dout = dout.contiguous()
             if dout.dtype != torch.bfloat16:
                 dout = dout.to(torch.bfloat16)
-            dout_q, dout_raw, _ = ops.quant_rows(dout, raw=True)
+            dout_q = dout_raw = None
+            if USE_TMA_GATHER:
+                dout_q, dout_raw, _ = ops.quant_rows(dout, raw=True)
         w2t_q, w2t_sf = weight_fp8(w2, True)
         if USE_TMA_GATHER:
             a_sf = ops.gather_scales_isa(dout_raw, x_gather_idx, TKp, H)
             dz, y1s, dsp = ops.gemm_dgated(dout_q, x_gather_idx, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, TKp)
         else:
-            dg_q, a_sf = ops.gather_rows_fp8(dout_q, dout_raw, x_gather_idx, TKp, efo[-1:])
+            if dout_q is not None:
+                dg_q, a_sf = ops.gather_rows_fp8(dout_q, dout_raw, x_gather_idx, TKp, efo[-1:])
+            else:
+                dg_q, a_sf = ops.quant_rows_gather(dout, x_gather_idx, TKp, efo[-1:])
             dz, y1s, dsp = ops.gemm_dgated(dg_q, None, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, TKp)
             del dg_q
         del z_q, z_sc

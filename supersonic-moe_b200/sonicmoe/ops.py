@@ -133,6 +133,19 @@ def quant_rows(x, raw=True, isa=False):
 
 
 @_timed
+def quant_rows_gather(x, idx, rows, valid_rows=None):
+    """bf16 [T,K] -> (e4m3 of x[idx] [rows,K], ISA scales of (rows,K)) in one pass."""
+    _cuda(x, idx, valid_rows)
+    assert x.dtype == torch.bfloat16 and x.ndim == 2
+    K = x.shape[1]
+    q = torch.empty(rows, K, dtype=_U8, device=x.device)
+    isa = torch.empty(isa_bytes(rows, K), dtype=_U8, device=x.device)
+    check(lib.smoe_quant_rows_gather(_p(x), _p(idx), _p(valid_rows), rows, K, _p(q), _p(isa), _stream()),
+          "quant_rows_gather")
+    return q, isa
+
+
+@_timed
 def gather_scales_isa(raw, idx, rows, cols):
     _cuda(raw, idx)
     out = torch.empty(isa_bytes(rows, cols), dtype=_U8, device=raw.device)

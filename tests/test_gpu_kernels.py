@@ -114,6 +114,17 @@ def test_gather_scales_isa(ops):
     assert torch.equal(got.cpu(), Q.gather_scales_to_isa(raw, idx, K))
 
 
+def test_quant_rows_gather_bit_exact(ops):
+    T, K, rows, valid = 300, 1536, 1024, 900
+    x = adversarial_rows(T, K, 21)
+    g = torch.Generator().manual_seed(22)
+    idx = torch.randint(0, T, (rows,), generator=g, dtype=torch.int32)
+    q, isa = ops.quant_rows_gather(x.to(DEV), idx.to(DEV), rows, torch.tensor([valid], dtype=torch.int32).to(DEV))
+    rq, rs = Q.row_quant(x)
+    assert torch.equal(q.cpu()[:valid], rq[idx.long()][:valid])
+    assert torch.equal(Q.unpack_isa(isa.cpu(), rows, K)[:valid], rs[idx.long()][:valid])
+
+
 def test_gather_rows_fp8(ops):
     T, K, rows, valid = 300, 512, 1024, 896
     g = torch.Generator().manual_seed(8)
