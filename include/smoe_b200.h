@@ -92,6 +92,14 @@ int smoe_quant_rows(const void* x_bf16, int64_t M, int64_t K, void* q, void* raw
 int smoe_quant_rows_gather(const void* x_bf16, const int32_t* idx, const int32_t* valid_rows, int64_t rows, int64_t K,
                            void* q, void* isa_scales, void* stream);
 
+/* Same result in scatter form: every token row of x [T,K] is read and quantised once and written to each
+ * expert-sorted position it occupies, s_rev[naept[t] .. naept[t+1]); pad rows (s_scatter_idx[row] >= naept[T]) are
+ * zero-filled (the gather form copies token 0 there; either way they are multiplied by a zero score downstream).
+ * K % 128 == 0, K <= 16384. */
+int smoe_quant_rows_scatter(const void* x_bf16, int64_t T, int64_t K, const int32_t* naept, const int32_t* s_rev,
+                            const int32_t* s_scatter_idx, const int32_t* valid_rows, int64_t rows, void* q,
+                            void* isa_scales, void* stream);
+
 /* raw row scales [T, cols/32] gathered to `rows` rows by idx, ISA layout for (rows, cols).
  * Replaces _gather_1x32_scales_to_isa (sonicmoe/quack_utils/sm100_funcs.py:148-180). */
 int smoe_gather_scales_isa(const void* raw_scales, const int32_t* idx, int64_t rows, int64_t cols, void* isa_scales,

@@ -99,6 +99,76 @@ quant_rows_kernel(const uint4* __restrict__ x, int64_t M, int K, uint2* __restri
   }
 }
 
+// ------------------------------------------------------------- rows, scatter form
+// Each token row is read and quantised ONCE and written to every expert-sorted position it occupies
+// (positions s_rev[naept[t] .. naept[t+1])): HBM traffic = one read of x + the gathered output, instead of
+// re-reading a token once per selected expert.  Pad rows (s_scatter[row] >= real_TK) are zero-filled so that
+// the GEMM consuming the buffer only ever sees finite values.
+// Blocks [0, token_blocks): one warp per token, row staged in shared memory; the remaining blocks clear pad rows.
+__global__ void __launch_bounds__(256)
+quant_rows_scatter_kernel(const uint4* __restrict__ x, int64_t T, int K, const int* __restrict__ naept,
+                          const int* __restrict__ s_rev, const int* __restrict__ s_scatter,
+                          const int* __restrict__ valid_rows, int64_t rows, uint4* __restrict__ q,
+                          uint8_t* __restrict__ isa, int token_blocks) {
+  extern __shared__ __align__(16) uint8_t s_rowbuf[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int k_tiles = K >> 7, k16 = K >> 4;
+  if ((int)blockIdx.x < token_blocks) {
+    const int64_t t = (int64_t)blockIdx.x * nw + warp;
+    if (t >= T) return;
+    const int beg = naept[t], end = naept[t + 1];
+    if (beg == end) return;
+    uint8_t* sq = s_rowbuf + (size_t)warp * (K + 4 * k_tiles);
+    uint32_t* ssc = reinterpret_cast<uint32_t*>(sq + K);
+    for (int c0 = 0; c0 < K; c0 += 256) {
+      const int col = c0 + lane * 8;
+      const bool in = col < K;
+      float f[8];
+      if (in) {
+        bf16x8_to_f32(x[(t * K + col) >> 3], f);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = 0.f;
+      }
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffff, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffff, amax, 2));
+      const int e = q_e8m0_of(amax);
+      const float qs = q_scale_of(e);
+      const uint32_t b1 = __shfl_down_sync(0xffffffff, (uint32_t)e, 4);
+      const uint32_t b2 = __shfl_down_sync(0xffffffff, (uint32_t)e, 8);
+      const uint32_t b3 = __shfl_down_sync(0xffffffff, (uint32_t)e, 12);
+      if (in) {
+        uint2 o;
+        o.x = q_pack4(f[0] * qs, f[1] * qs, f[2] * qs, f[3] * qs);
+        o.y = q_pack4(f[4] * qs, f[5] * qs, f[6] * qs, f[7] * qs);
+        *reinterpret_cast<uint2*>(sq + col) = o;
+        if ((lane & 15) == 0) ssc[col >> 7] = (uint32_t)e | (b1 << 8) | (b2 << 16) | (b3 << 24);
+      }
+    }
+    __syncwarp();
+    for (int j = beg; j < end; ++j) {
+      const int64_t pos = s_rev[j];
+      for (int c = lane; c < k16; c += 32) q[pos * k16 + c] = reinterpret_cast<const uint4*>(sq)[c];
+      for (int kt = lane; kt < k_tiles; kt += 32)
+        *reinterpret_cast<uint32_t*>(isa + isa_offset(pos, (size_t)kt * 4, k_tiles)) = ssc[kt];
+    }
+  } else {
+    const int real_tk = naept[T];
+    const int64_t m_end = valid_rows ? min((int64_t)*valid_rows, rows) : rows;
+    const int64_t w0 = (int64_t)(blockIdx.x - token_blocks) * nw + warp;
+    const int64_t nwarps = (int64_t)(gridDim.x - token_blocks) * nw;
+    for (int64_t row = w0; row < m_end; row += nwarps) {
+      if (s_scatter[row] < real_tk) continue;
+      for (int c = lane; c < k16; c += 32) q[row * k16 + c] = make_uint4(0, 0, 0, 0);
+      for (int kt = lane; kt < k_tiles; kt += 32)
+        *reinterpret_cast<uint32_t*>(isa + isa_offset(row, (size_t)kt * 4, k_tiles)) = 0u;
+    }
+  }
+}
+
 // ------------------------------------------------------------- scale gather
 __global__ void __launch_bounds__(256)
 gather_scales_isa_kernel(const uint8_t* __restrict__ raw, const int* __restrict__ idx, int64_t rows, int groups,
@@ -274,6 +344,24 @@ int smoe_quant_rows(const void* x_bf16, int64_t M, int64_t K, void* q, void* raw
   quant_rows_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>((const uint4*)x_bf16, M, (int)K, (uint2*)q,
                                                                    (uint8_t*)raw_scales, (uint8_t*)isa_scales, nullptr,
                                                                    nullptr);
+  return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
+}
+
+int smoe_quant_rows_scatter(const void* x_bf16, int64_t T, int64_t K, const int32_t* naept, const int32_t* s_rev,
+                            const int32_t* s_scatter_idx, const int32_t* valid_rows, int64_t rows, void* q,
+                            void* isa_scales, void* stream) {
+  if (T < 0 || rows < 0 || K <= 0 || K % 128 || K > 16384) return SMOE_ERR_SHAPE;
+  if (!naept || !s_rev || !s_scatter_idx || !isa_scales) return SMOE_ERR_ARG;
+  if (((uintptr_t)x_bf16 & 15) || ((uintptr_t)q & 15)) return SMOE_ERR_ALIGN;
+  if (rows == 0) return SMOE_OK;
+  const int row_bytes = (int)(K + 4 * (K / 128));
+  const int warps = row_bytes * 8 <= 48 * 1024 ? 8 : (row_bytes * 4 <= 48 * 1024 ? 4 : 2);
+  const int token_blocks = (int)((T + warps - 1) / warps);
+  int pad_blocks = (int)((rows + 63) / 64);
+  if (pad_blocks > 296) pad_blocks = 296;
+  quant_rows_scatter_kernel<<<token_blocks + pad_blocks, warps * 32, (size_t)warps * row_bytes,
+                              (cudaStream_t)stream>>>((const uint4*)x_bf16, T, (int)K, naept, s_rev, s_scatter_idx,
+                                                      valid_rows, rows, (uint4*)q, (uint8_t*)isa_scales, token_blocks);
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }
 

@@ -217,7 +217,7 @@ class _UpProjection(torch.autograd.Function):
             if x_q is not None:
                 xg_q, a_sf = ops.gather_rows_fp8(x_q, x_raw, x_gather_idx, TKp, efo[-1:])
             else:      # quantise straight into expert-sorted order
-                xg_q, a_sf = ops.quant_rows_gather(x.contiguous(), x_gather_idx, TKp, efo[-1:])
+                xg_q, a_sf = ops.quant_rows_scatter(x.contiguous(), naept, s_rev, s_scatter_idx, TKp, efo[-1:])
             z_q, z_sc, y1_q, y1_sf = ops.gemm_gated(xg_q, None, a_sf, w1_q, w1_sf, efo, TKp)
             del xg_q
         link = {"y1": (y1_q, y1_sf), "z": (z_q, z_sc)}
@@ -326,7 +326,7 @@ class _DownProjection(torch.autograd.Function):
             if dout_q is not None:
                 dg_q, a_sf = ops.gather_rows_fp8(dout_q, dout_raw, x_gather_idx, TKp, efo[-1:])
             else:
-                dg_q, a_sf = ops.quant_rows_gather(dout, x_gather_idx, TKp, efo[-1:])
+                dg_q, a_sf = ops.quant_rows_scatter(dout, naept, s_rev, s_scatter_idx, TKp, efo[-1:])
             dz, y1s, dsp = ops.gemm_dgated(dg_q, None, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, TKp)
             del dg_q
         del z_q, z_sc

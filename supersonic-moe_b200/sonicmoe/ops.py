@@ -146,6 +146,20 @@ def quant_rows_gather(x, idx, rows, valid_rows=None):
 
 
 @_timed
+def quant_rows_scatter(x, naept, s_rev, s_scatter_idx, rows, valid_rows=None):
+    """bf16 [T,K] -> (e4m3 rows in expert-sorted order [rows,K], ISA scales of (rows,K)); each token is
+    quantised once and written to all its positions; pad rows are zero."""
+    _cuda(x, naept, s_rev, s_scatter_idx, valid_rows)
+    assert x.dtype == torch.bfloat16 and x.ndim == 2
+    T, K = x.shape
+    q = torch.empty(rows, K, dtype=_U8, device=x.device)
+    isa = torch.empty(isa_bytes(rows, K), dtype=_U8, device=x.device)
+    check(lib.smoe_quant_rows_scatter(_p(x), T, K, _p(naept), _p(s_rev), _p(s_scatter_idx), _p(valid_rows), rows,
+                                      _p(q), _p(isa), _stream()), "quant_rows_scatter")
+    return q, isa
+
+
+@_timed
 def gather_scales_isa(raw, idx, rows, cols):
     _cuda(raw, idx)
     out = torch.empty(isa_bytes(rows, cols), dtype=_U8, device=raw.device)

@@ -125,6 +125,24 @@ def test_quant_rows_gather_bit_exact(ops):
     assert torch.equal(Q.unpack_isa(isa.cpu(), rows, K)[:valid], rs[idx.long()][:valid])
 
 
+@pytest.mark.parametrize("N,K,E,H,p_mask", [(500, 4, 8, 512, 0.3), (2048, 8, 16, 3072, 0.0), (64, 2, 4, 6144, 0.5)])
+def test_quant_rows_scatter_bit_exact(ops, N, K, E, H, p_mask):
+    idx, probs = make_routing(N, K, E, p_mask, seed=N)
+    md = R.topk_metadata(idx, probs, E, 128)
+    x = adversarial_rows(N, H, N + 1)
+    rows = md["real_TKp"] + 128                     # over-allocated tail stays untouched
+    dev = lambda k: md[k].to(DEV)
+    sscat = torch.cat([md["s_scatter_idx"], torch.full((128,), md["real_TK"], dtype=torch.int32)]).to(DEV)
+    q, isa = ops.quant_rows_scatter(x.to(DEV), dev("naept"), dev("s_reverse_scatter_idx"), sscat, rows,
+                                    dev("efo")[-1:])
+    rq, rs = Q.row_quant(x)
+    real = md["s_scatter_idx"] < md["real_TK"]
+    xg = md["x_gather_idx"].long()
+    got_q, got_s = q.cpu()[:md["real_TKp"]], Q.unpack_isa(isa.cpu(), rows, H)[:md["real_TKp"]]
+    assert torch.equal(got_q[real], rq[xg][real]) and torch.equal(got_s[real], rs[xg][real])
+    assert (got_q[~real] == 0).all() and (got_s[~real] == 0).all()
+
+
 def test_gather_rows_fp8(ops):
     T, K, rows, valid = 300, 512, 1024, 896
     g = torch.Generator().manual_seed(8)
