@@ -118,7 +118,7 @@ quant_rows_scatter_kernel(const uint4* __restrict__ x, int64_t T, int K, const i
     if (t >= T) return;
     const int beg = naept[t], end = naept[t + 1];
     if (beg == end) return;
-    uint8_t* sq = s_rowbuf + (size_t)warp * (K + 4 * k_tiles);
+    uint8_t* sq = s_rowbuf + (size_t)warp * ((K + 4 * k_tiles + 15) & ~15);   // 16-byte aligned per warp
     uint32_t* ssc = reinterpret_cast<uint32_t*>(sq + K);
     for (int c0 = 0; c0 < K; c0 += 256) {
       const int col = c0 + lane * 8;
@@ -354,7 +354,7 @@ int smoe_quant_rows_scatter(const void* x_bf16, int64_t T, int64_t K, const int3
   if (!naept || !s_rev || !s_scatter_idx || !isa_scales) return SMOE_ERR_ARG;
   if (((uintptr_t)x_bf16 & 15) || ((uintptr_t)q & 15)) return SMOE_ERR_ALIGN;
   if (rows == 0) return SMOE_OK;
-  const int row_bytes = (int)(K + 4 * (K / 128));
+  const int row_bytes = (int)((K + 4 * (K / 128) + 15) & ~(int64_t)15);
   const int warps = row_bytes * 8 <= 48 * 1024 ? 8 : (row_bytes * 4 <= 48 * 1024 ? 4 : 2);
   const int token_blocks = (int)((T + warps - 1) / warps);
   int pad_blocks = (int)((rows + 63) / 64);
