@@ -136,9 +136,9 @@ static int run2(const void* a, int64_t a_rows, int64_t a_cols, const void* b, in
   if (rc) return rc;
   rc = make_tmap_u8(&tb, b, b_rows, b_cols, BK, bn / 2);
   if (rc) return rc;
-  rc = make_tmap(&tsa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, p.sfa, sfa_tiles, 128, 128, 1, CU_TENSOR_MAP_SWIZZLE_NONE);
+  rc = make_tmap(&tsa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, p.sfa, sfa_tiles, 128, 128, 4, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc) return rc;
-  rc = make_tmap(&tsb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, p.sfb, sfb_tiles, 128, 128, 1, CU_TENSOR_MAP_SWIZZLE_NONE);
+  rc = make_tmap(&tsb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, p.sfb, sfb_tiles, 128, 128, 4, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc) return rc;
   // upper bound of pair tiles: varlen-M: every expert may add one half-empty pair
   int64_t pair_tiles;
@@ -158,7 +158,7 @@ static int run(const void* a, int64_t a_rows, int64_t a_cols, const void* b, int
   if (p.E > kMaxExpertsSmem) return SMOE_ERR_SHAPE;
   {
     const int bn2 = pick_bn2<MODE>(p.N);
-    const bool ok2 = bn2 != 0 && (MODE != WGRAD || p.rows % 256 == 0);
+    const bool ok2 = bn2 != 0 && p.E <= kMaxExperts2 && (MODE != WGRAD || p.rows % 256 == 0);
     if (ok2) {
       OutMaps om{};
       int rc = SMOE_OK;
@@ -169,8 +169,8 @@ static int run(const void* a, int64_t a_rows, int64_t a_cols, const void* b, int
         rc = make_tmap(&om.c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.c, p.rows, p.N, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B);
         om.c2 = om.c;
       } else if (MODE == WGRAD) {
-        rc = make_tmap(&om.c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.c, (uint64_t)p.E * p.rows, p.N, 32, 32,
-                       CU_TENSOR_MAP_SWIZZLE_128B);
+        rc = make_tmap(&om.c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.c, (uint64_t)p.E * p.rows, p.N, 16, 32,
+                       CU_TENSOR_MAP_SWIZZLE_64B);
         om.c2 = om.c;
       } else if (MODE == DGATED) {
         rc = make_tmap(&om.c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.dz, p.rows, 2 * (uint64_t)p.N, 64, 32,

@@ -12,6 +12,7 @@ namespace smoe {
 
 constexpr int kEpiWarps2 = 8;
 constexpr int kThreads2 = 32 * (2 + kEpiWarps2);
+constexpr int kMaxExperts2 = 256;   // expert offsets cached in shared memory by the two-CTA kernel
 
 // ---- cluster helpers -------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -94,22 +95,29 @@ template <int BN, int MODE>
 struct Gemm2Smem {
   static constexpr int A_BYTES = BM * BK;                 // this CTA's 128 rows
   static constexpr int B_BYTES = (BN / 2) * BK;           // this CTA's half of the B tile
-  static constexpr int SF_BYTES = 2048;                   // SFA 512 + SFB 2 x 512, padded
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SF_BYTES;
-  // output staging per epilogue warp: PLAIN 2 x 2 KB (bf16 32x32), WGRAD 2 x 4 KB (f32 32x32),
-  // DGATED 4 KB (dz) + 2 KB (y1s) (+2 KB so that buffers stay 1 KB aligned), GATED none
-  static constexpr int EPI_BYTES_PER_WARP = MODE == PLAIN ? 4096 : (MODE == GATED ? 0 : 8192);
-  static constexpr int EPI_BYTES = kEpiWarps2 * EPI_BYTES_PER_WARP;
-  static constexpr int AUX_BYTES = 1024 + 2 * (kMaxExpertsSmem + 1) * 4;
-  static constexpr int STAGES_RAW = (227 * 1024 - 1024 - AUX_BYTES - EPI_BYTES) / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-  static constexpr int TOTAL = STAGES * STAGE_BYTES + EPI_BYTES + AUX_BYTES + 1024;
-  static constexpr int ACC_STAGES = (BN == 256) ? 1 : 2;  // TMEM: 512 columns
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int SFB_TILES = (BN == 128) ? 1 : 2;   // 128-row scale tiles covering the BN window
+  // Scales travel in their own ring: one slot holds the scales of kSfGroup consecutive K tiles
+  // (A: 4 x 512 B, B: 4 x 512 B per 128-row tile), fetched with one TMA copy per operand tile
+  // instead of one per K tile.
+  static constexpr int SF_GROUP = 4;
+  static constexpr int SF_SLOT_BYTES = SF_GROUP * 512 * (1 + SFB_TILES);
+  static constexpr int SF_SLOTS = 2;
+  static constexpr int SF_BYTES = ((SF_SLOTS * SF_SLOT_BYTES + 1023) / 1024) * 1024;
+  // output staging per epilogue warp: PLAIN 2 KB (bf16 32x32), WGRAD 2 KB (f32 32x16),
+  // DGATED 4 KB (dz) + 2 KB (y1s), GATED none
+  static constexpr int EPI_BYTES_PER_WARP = MODE == GATED ? 0 : (MODE == DGATED ? 6144 : 2048);
+  static constexpr int EPI_BYTES = kEpiWarps2 * EPI_BYTES_PER_WARP;
+  static constexpr int AUX_BYTES = 1024 + 2 * (kMaxExperts2 + 1) * 4;
+  static constexpr int STAGES_RAW = (227 * 1024 - 1024 - AUX_BYTES - EPI_BYTES - SF_BYTES) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + SF_BYTES + EPI_BYTES + AUX_BYTES + 1024;
+  static constexpr int ACC_STAGES = (BN == 256) ? 1 : 2;  // TMEM: 512 columns
   static constexpr int SF_COLS = 4 + 4 * SFB_TILES;
   static constexpr int SF_COL0 = ACC_STAGES * BN;
   static_assert(SF_COL0 + STAGES * SF_COLS <= 512, "TMEM budget");
-  static constexpr uint32_t TX_BYTES = 2u * (A_BYTES + B_BYTES + 512 + 512 * SFB_TILES);
+  static constexpr uint32_t TX_BYTES = 2u * (A_BYTES + B_BYTES);        // both CTAs' A and B per stage
+  static constexpr uint32_t SF_TX_BYTES = 2u * SF_SLOT_BYTES;            // both CTAs' scales per group
 };
 
 struct PairTile {
@@ -164,13 +172,14 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   const bool GATHER = p.a_idx != nullptr;   // rows of A fetched by index (TMA gather4) vs. a plain tile
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* epi = smem + S::STAGES * S::STAGE_BYTES;
+  uint8_t* sfring = smem + S::STAGES * S::STAGE_BYTES;
+  uint8_t* epi = sfring + S::SF_BYTES;
   uint8_t* aux = epi + S::EPI_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(aux);     // full[S], empty[S], tfull[2], tempty[2]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aux);     // full[S], empty[S], tfull[2], tempty[2], sffull[2], sfempty[2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux + 512);
   volatile int* s_abort = reinterpret_cast<volatile int*>(aux + 516);
   int* s_efo = reinterpret_cast<int*>(aux + 1024);
-  int* s_pairs = s_efo + (kMaxExpertsSmem + 1);
+  int* s_pairs = s_efo + (kMaxExperts2 + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -181,6 +190,8 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   const uint32_t bar_empty = bar_full + 8 * S::STAGES;
   const uint32_t bar_tfull = bar_empty + 8 * S::STAGES;
   const uint32_t bar_tempty = bar_tfull + 8 * 2;
+  const uint32_t bar_sffull = bar_tempty + 8 * 2;
+  const uint32_t bar_sfempty = bar_sffull + 8 * S::SF_SLOTS;
 
   for (int i = threadIdx.x; i <= p.E; i += blockDim.x) s_efo[i] = p.efo[i];
   __syncthreads();
@@ -199,6 +210,10 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       mbar_init(bar_tfull + 8 * s, 1);                   // commit arrival, in each CTA
       mbar_init(bar_tempty + 8 * s, 2 * kEpiWarps2);     // leader's: the epilogue warps of both CTAs
     }
+    for (int s = 0; s < S::SF_SLOTS; ++s) {
+      mbar_init(bar_sffull + 8 * s, 1);                  // leader's: armed by its producer, credited by both CTAs
+      mbar_init(bar_sfempty + 8 * s, 1);                 // commit arrival, in each CTA
+    }
     *s_abort = 0;
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -213,6 +228,7 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t smem_base = smem_u32(smem);
+  const uint32_t sf_base = smem_u32(sfring);
   const int n_total = (MODE == WGRAD) ? p.E * (p.rows / (2 * BM)) * (p.N / BN) : s_pairs[p.E] * (p.N / BN);
 
   if (warp == 0) {
@@ -221,8 +237,9 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       prefetch_tmap(&tmap_a); prefetch_tmap(&tmap_b); prefetch_tmap(&tmap_sfa); prefetch_tmap(&tmap_sfb);
     }
     const uint32_t full0 = map_to_cta(bar_full, 0);      // the leader's full barriers
-    int stage = 0;
-    uint32_t phase = 0;
+    const uint32_t sffull0 = map_to_cta(bar_sffull, 0);
+    int stage = 0, sfs = 0;
+    uint32_t phase = 0, sfphase = 0;
     bool ok = true;
     for (int tile = pair_id; tile < n_total && ok; tile += n_pairs_grid) {
       const PairTile t = pair_tile<BN, MODE>(tile, rank, p, s_efo, s_pairs);
@@ -236,26 +253,33 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       if (!t.valid) sfa_tile = 0;                        // phantom half: any in-range tile will do
       const int sfb_tile = b_base / 128;                 // first 128-row scale tile touching the BN window
       for (int kt = t.kt0; kt < t.kt0 + t.nkt; ++kt) {
+        if (((kt - t.kt0) & (S::SF_GROUP - 1)) == 0) {
+          // scales of the next SF_GROUP K tiles: rows [tile*ktiles + kt, +SF_GROUP) of the 512-byte-row scale
+          // tensors (rows past this operand tile's K range are fetched too and never used)
+          if (lane == 0) ok = mbar_wait(bar_sfempty + 8 * sfs, sfphase ^ 1);
+          ok = __shfl_sync(0xffffffff, ok, 0);
+          if (!ok) break;
+          if (lane == 0) {
+            const uint32_t sffull = sffull0 + 8 * sfs;
+            const uint32_t dst = sf_base + sfs * S::SF_SLOT_BYTES;
+            if (rank == 0) mbar_expect_tx(bar_sffull + 8 * sfs, S::SF_TX_BYTES);
+            tma_load_2d_pair(dst, &tmap_sfa, sffull, 0, sfa_tile * p.sfa_ktiles + kt);
+#pragma unroll
+            for (int j = 0; j < S::SFB_TILES; ++j)
+              tma_load_2d_pair(dst + 2048 * (1 + j), &tmap_sfb, sffull, 0, (sfb_tile + j) * p.sfb_ktiles + kt);
+          }
+          if (++sfs == S::SF_SLOTS) { sfs = 0; sfphase ^= 1; }
+        }
         if (lane == 0) ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1);
         ok = __shfl_sync(0xffffffff, ok, 0);
         if (!ok) break;
         const uint32_t full = full0 + 8 * stage;
         const uint32_t a_dst = smem_base + stage * S::STAGE_BYTES;
         const uint32_t b_dst = a_dst + S::A_BYTES;
-        const uint32_t sf_dst = b_dst + S::B_BYTES;
         if (lane == 0) {
-          const bool skip_sf = p.debug_skip_store != 0;   // timing experiment: no scale loads (stale scales)
-          if (rank == 0)
-            mbar_expect_tx(bar_full + 8 * stage,
-                           skip_sf ? 2u * (S::A_BYTES + S::B_BYTES) : S::TX_BYTES);
+          if (rank == 0) mbar_expect_tx(bar_full + 8 * stage, S::TX_BYTES);
           if (!GATHER) tma_load_2d_pair(a_dst, &tmap_a, full, kt * BK, t.valid ? t.m0 : 0);
           tma_load_2d_pair(b_dst, &tmap_b, full, kt * BK, b_row);
-          if (!skip_sf) {
-            tma_load_2d_pair(sf_dst, &tmap_sfa, full, 0, sfa_tile * p.sfa_ktiles + kt);
-#pragma unroll
-            for (int j = 0; j < S::SFB_TILES; ++j)
-              tma_load_2d_pair(sf_dst + 512 + 512 * j, &tmap_sfb, full, 0, (sfb_tile + j) * p.sfb_ktiles + kt);
-          }
         }
         if (GATHER) {
           __syncwarp();
@@ -269,8 +293,8 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (rank == 0 && elect_one()) {
       constexpr uint32_t idesc = make_idesc_mxf8(2 * BM, BN);
-      int stage = 0, as = 0;
-      uint32_t phase = 0, aphase = 0;
+      int stage = 0, as = 0, sfs = 0;
+      uint32_t phase = 0, aphase = 0, sfphase = 0;
       bool ok = true;
       for (int tile = pair_id; tile < n_total && ok; tile += n_pairs_grid) {
         const PairTile t = pair_tile<BN, MODE>(tile, 0, p, s_efo, s_pairs);
@@ -282,17 +306,22 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         // BN = 192: an odd column tile starts 64 rows into its first 128-row scale tile
         const uint32_t sfb_shift = (BN == 192) ? (((t.n0 / BN) & 1) ? 2u : 0u) : 0u;
         for (int k = 0; k < t.nkt; ++k) {
+          const int kg = k & (S::SF_GROUP - 1);
+          if (kg == 0) {
+            ok = mbar_wait(bar_sffull + 8 * sfs, sfphase);
+            if (!ok) break;
+          }
           ok = mbar_wait(bar_full + 8 * stage, phase);
           if (!ok) break;
           tc_fence_after();
           const uint32_t a_src = smem_base + stage * S::STAGE_BYTES;
           const uint32_t b_src = a_src + S::A_BYTES;
-          const uint32_t sf_src = b_src + S::B_BYTES;
+          const uint32_t sf_src = sf_base + sfs * S::SF_SLOT_BYTES + kg * 512;
           const uint32_t sfa_t = tmem_base + S::SF_COL0 + stage * S::SF_COLS;
           const uint32_t sfb_t = sfa_t + 4;
           tc_cp_sf_pair(sfa_t, make_desc_sf(sf_src));
 #pragma unroll
-          for (int j = 0; j < S::SFB_TILES; ++j) tc_cp_sf_pair(sfb_t + 4 * j, make_desc_sf(sf_src + 512 + 512 * j));
+          for (int j = 0; j < S::SFB_TILES; ++j) tc_cp_sf_pair(sfb_t + 4 * j, make_desc_sf(sf_src + 2048 * (1 + j)));
           const uint64_t a_desc = make_desc_kmajor_sw128(a_src);
           const uint64_t b_desc = make_desc_kmajor_sw128(b_src);
 #pragma unroll
@@ -302,6 +331,10 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           }
           tc_commit_pair(bar_empty + 8 * stage, 3);
           if (++stage == S::STAGES) { stage = 0; phase ^= 1; }
+          if (kg == S::SF_GROUP - 1 || k == t.nkt - 1) {      // last use of this scale slot
+            tc_commit_pair(bar_sfempty + 8 * sfs, 3);
+            if (++sfs == S::SF_SLOTS) { sfs = 0; sfphase ^= 1; }
+          }
         }
         if (!ok) break;
         tc_commit_pair(bar_tfull + 8 * as, 3);
@@ -321,7 +354,6 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     int as = 0;
     uint32_t aphase = 0;
     bool ok = true;
-    int buf = 0;
     for (int tile = pair_id; tile < n_total && ok; tile += n_pairs_grid) {
       const PairTile t = pair_tile<BN, MODE>(tile, rank, p, s_efo, s_pairs);
       const size_t grow = (size_t)t.m0 + row_in_tile;
@@ -361,8 +393,8 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         released = true;
 #pragma unroll
         for (int c = 0; c < NC; ++c) {
-          const uint32_t sb = stg + buf * 2048;
-          if (lane == 0) bulk_wait_group_read<1>();
+          const uint32_t sb = stg;                 // one 2 KB staging buffer per warp
+          if (lane == 0) bulk_wait_group_read<0>();
           __syncwarp();
           if (t.valid) {
 #pragma unroll
@@ -376,10 +408,9 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
               bulk_commit_group();
             }
           }
-          buf ^= 1;
         }
       } else if (MODE == WGRAD) {
-        // Same scheme with f32: 32 columns = 128-byte rows, SWIZZLE_128B, 2 x 4 KB; TMA reduce-add
+        // Same scheme with f32 in 16-column pieces: 64-byte rows, SWIZZLE_64B, one 2 KB buffer; TMA reduce-add
         // when accumulating into an existing gradient.
         constexpr int NC = COLS_PER_WARP / 32;
         uint32_t acc[NC][32];
@@ -391,23 +422,23 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * as);
         released = true;
 #pragma unroll
-        for (int c = 0; c < NC; ++c) {
-          const uint32_t sb = stg + buf * 4096;
-          if (lane == 0) bulk_wait_group_read<1>();
+        for (int c = 0; c < 2 * NC; ++c) {
+          const uint32_t sb = stg;
+          if (lane == 0) bulk_wait_group_read<0>();
           __syncwarp();
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            st_shared_v4(sb + lane * 128 + ((j ^ (lane & 7)) << 4), acc[c][4 * j], acc[c][4 * j + 1],
-                         acc[c][4 * j + 2], acc[c][4 * j + 3]);
+          for (int j = 0; j < 4; ++j)
+            st_shared_v4(sb + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4), acc[c >> 1][(c & 1) * 16 + 4 * j],
+                         acc[c >> 1][(c & 1) * 16 + 4 * j + 1], acc[c >> 1][(c & 1) * 16 + 4 * j + 2],
+                         acc[c >> 1][(c & 1) * 16 + 4 * j + 3]);
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
             const int crow = t.e * p.rows + t.m0 + q * 32;
-            if (p.accumulate) tma_reduce_add_2d(&tmap_c, sb, c_base + c * 32, crow);
-            else tma_store_2d(&tmap_c, sb, c_base + c * 32, crow);
+            if (p.accumulate) tma_reduce_add_2d(&tmap_c, sb, c_base + c * 16, crow);
+            else tma_store_2d(&tmap_c, sb, c_base + c * 16, crow);
             bulk_commit_group();
           }
-          buf ^= 1;
         }
       } else if (MODE == GATED) {
         // 64-column chunks of z (= 32 columns of y1 = one y1 scale group).  BN = 128: one chunk per warp;
