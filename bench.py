@@ -296,7 +296,7 @@ def run_ours(args):
         n = k.split("#")[0]
         if n == "gemm_gated":
             per_gemm_flops[k] = 4 * TKH_I
-        elif n == "gemm_dgated":
+        elif n in ("gemm_dgated", "gemm_dgated_fused"):
             per_gemm_flops[k] = 2 * TKH_I
         elif n == "gemm_varlen_m":      # first = down-proj (2), second = dgrad (4)
             per_gemm_flops[k] = (2 if seen[n] == 0 else 4) * TKH_I

@@ -94,7 +94,7 @@ static int pick_bn(int64_t N) {
 
 // ---- two-CTA kernel -----------------------------------------------------------
 struct OutMaps {
-  CUtensorMap c, c2;
+  CUtensorMap c, c2, c3;
 };
 
 template <int BN, int MODE>
@@ -111,7 +111,7 @@ static int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
   int64_t pairs = sm_count() / 2;
   if (max_pair_tiles < pairs) pairs = max_pair_tiles;
   if (pairs <= 0) return SMOE_OK;
-  kern<<<(unsigned)(2 * pairs), kThreads2, S::TOTAL, stream>>>(ta, tb, tsa, tsb, om.c, om.c2, p);
+  kern<<<(unsigned)(2 * pairs), kThreads2, S::TOTAL, stream>>>(ta, tb, tsa, tsb, om.c, om.c2, om.c3, p);
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }
 
@@ -120,6 +120,7 @@ template <int MODE>
 static int pick_bn2(int64_t N) {
   if (g_force_v1) return 0;
   const bool wide = (MODE == PLAIN || MODE == WGRAD);      // single-stage 256-column tiles
+  if (MODE == DGATEDQ) return (N % 192 == 0 && g_force_bn != 128) ? 192 : 128;
   if (g_force_bn == 128) return 128;
   if (g_force_bn == 192) return (N % 192 == 0) ? 192 : 128;
   if (g_force_bn == 256) return (wide && N % 256 == 0) ? 256 : 128;
@@ -172,6 +173,15 @@ static int run(const void* a, int64_t a_rows, int64_t a_cols, const void* b, int
         rc = make_tmap(&om.c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.c, (uint64_t)p.E * p.rows, p.N, 16, 32,
                        CU_TENSOR_MAP_SWIZZLE_64B);
         om.c2 = om.c;
+      } else if (MODE == DGATEDQ) {
+        rc = make_tmap(&om.c, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.dz, p.rows, 2 * (uint64_t)p.N, 64, 32,
+                       CU_TENSOR_MAP_SWIZZLE_64B);
+        if (!rc)
+          rc = make_tmap(&om.c2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.c, 2 * (uint64_t)p.N, p.rows, 128, 64,
+                         CU_TENSOR_MAP_SWIZZLE_128B);
+        if (!rc)
+          rc = make_tmap(&om.c3, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.y1s, p.N, p.rows, 128, 32,
+                         CU_TENSOR_MAP_SWIZZLE_128B);
       } else if (MODE == DGATED) {
         rc = make_tmap(&om.c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.dz, p.rows, 2 * (uint64_t)p.N, 64, 32,
                        CU_TENSOR_MAP_SWIZZLE_128B);
@@ -183,9 +193,12 @@ static int run(const void* a, int64_t a_rows, int64_t a_cols, const void* b, int
         om.c2 = om.c;
       }
       if (rc) return rc;
+      if (MODE != DGATEDQ) om.c3 = om.c;
       return run2<MODE>(a, a_rows, a_cols, b, b_rows, b_cols, p, om, bn2, sfa_tiles, sfb_tiles, stream);
     }
   }
+  if (MODE == DGATEDQ) return SMOE_ERR_SHAPE;     // fused-quantizer epilogue exists in the two-CTA kernel only
+  constexpr int M1 = (MODE == DGATEDQ) ? DGATED : MODE;
   const int bn = pick_bn(p.N);
   CUtensorMap ta, tb;
   const bool gather = p.a_idx != nullptr;
@@ -193,8 +206,8 @@ static int run(const void* a, int64_t a_rows, int64_t a_cols, const void* b, int
   if (rc) return rc;
   rc = make_tmap_u8(&tb, b, b_rows, b_cols, BK, bn);
   if (rc) return rc;
-  if (bn == 256) return launch<256, MODE>(ta, tb, p, max_tiles_128 / 2, stream);
-  return launch<128, MODE>(ta, tb, p, max_tiles_128, stream);
+  if (bn == 256) return launch<256, M1>(ta, tb, p, max_tiles_128 / 2, stream);
+  return launch<128, M1>(ta, tb, p, max_tiles_128, stream);
 }
 
 }  // namespace smoe
@@ -250,6 +263,24 @@ int smoe_gemm_dgated(const void* dout_fp8, int64_t T, const int* a_idx, const vo
   if (ds_partial_tiles) *ds_partial_tiles = smoe_gemm_dgated_partials(N);
   return run<DGATED>(dout_fp8, T, K, w2t_fp8, E * N, K, p, (int)((rows / 128) * (N / 128)), (cudaStream_t)stream);
 }
+
+int smoe_gemm_dgated_fused(const void* dout_fp8, const void* a_sf, const void* w2t_fp8, const void* w2t_sf,
+                           const int* efo, const void* z_fp8, const void* z_scales, const float* s, void* dz_q,
+                           void* dz_row_sf, void* dz_t, void* dz_col_sf, void* y1s_t, void* y1s_col_sf,
+                           float* ds_partial, int64_t rows, int64_t N, int64_t K, int64_t E, int* status,
+                           void* stream) {
+  if (rows % 128 || N % 128 || K % 128 || E <= 0) return SMOE_ERR_SHAPE;
+  GemmParams p{};
+  p.rows = (int)rows; p.N = (int)N; p.K = (int)K; p.E = (int)E;
+  p.efo = efo; p.a_idx = nullptr; p.sfa = (const uint8_t*)a_sf; p.sfb = (const uint8_t*)w2t_sf;
+  p.sfa_ktiles = (int)(K / 128); p.sfb_ktiles = (int)(K / 128);
+  p.z_fp8 = (uint8_t*)const_cast<void*>(z_fp8); p.z_sc = (uint8_t*)const_cast<void*>(z_scales);
+  p.s = s; p.dz = dz_q; p.c = dz_t; p.y1s = y1s_t; p.ds_partial = ds_partial; p.status = status;
+  p.dz_row_sf = (uint8_t*)dz_row_sf; p.dz_col_sf = (uint8_t*)dz_col_sf; p.y1s_col_sf = (uint8_t*)y1s_col_sf;
+  return run<DGATEDQ>(dout_fp8, rows, K, w2t_fp8, E * N, K, p, (int)((rows / 128) * (N / 128)), (cudaStream_t)stream);
+}
+
+int64_t smoe_gemm_dgated_fused_partials(int64_t N) { return 2 * (N / pick_bn2<DGATEDQ>(N)); }
 
 int64_t smoe_gemm_dgated_partials(int64_t N) {
   const int bn2 = pick_bn2<DGATED>(N);

@@ -16,7 +16,8 @@
 
 namespace smoe {
 
-enum GemmMode : int { PLAIN = 0, GATED = 1, DGATED = 2, WGRAD = 3 };
+// DGATEDQ = DGATED with the wgrad/dgrad operand quantizers fused into the epilogue (two-CTA kernel only)
+enum GemmMode : int { PLAIN = 0, GATED = 1, DGATED = 2, WGRAD = 3, DGATEDQ = 4 };
 
 constexpr int BM = 128;          // rows of the accumulator tile (TMEM lanes)
 constexpr int BK = 128;          // bytes (= e4m3 elements) along K per stage: one scale tile
@@ -46,6 +47,9 @@ struct GemmParams {
   void* dz;             // DGATED out: bf16 [TKp, 2N]
   void* y1s;            // DGATED out: bf16 [TKp, N]
   float* ds_partial;    // DGATED out: [N/BN, TKp]
+  uint8_t* dz_row_sf;   // DGATEDQ out: ISA scales of dz as a (TKp, 2N) operand (32x32 blocks share a scale)
+  uint8_t* dz_col_sf;   // DGATEDQ out: ISA scales of dz^T as a (2N, TKp) operand
+  uint8_t* y1s_col_sf;  // DGATEDQ out: ISA scales of y1s^T as a (N, TKp) operand (1x32 along TKp)
   int* status;          // device status word: 0 ok, else first failure code
   int debug_skip_store; // timing experiments only: drain TMEM but skip the global stores
 };

@@ -106,7 +106,8 @@ struct Gemm2Smem {
   static constexpr int SF_BYTES = ((SF_SLOTS * SF_SLOT_BYTES + 1023) / 1024) * 1024;
   // output staging per epilogue warp: PLAIN 2 KB (bf16 32x32), WGRAD 2 KB (f32 32x16),
   // DGATED 4 KB (dz) + 2 KB (y1s), GATED none
-  static constexpr int EPI_BYTES_PER_WARP = MODE == GATED ? 0 : (MODE == DGATED ? 6144 : 2048);
+  // DGATEDQ: per column half 4 x 2 KB row-major dz + 8 KB transposed dz + 4 KB transposed y1s = 20 KB
+  static constexpr int EPI_BYTES_PER_WARP = MODE == GATED ? 0 : (MODE == DGATED ? 6144 : (MODE == DGATEDQ ? 5120 : 2048));
   static constexpr int EPI_BYTES = kEpiWarps2 * EPI_BYTES_PER_WARP;
   static constexpr int AUX_BYTES = 1024 + 2 * (kMaxExperts2 + 1) * 4;
   static constexpr int STAGES_RAW = (227 * 1024 - 1024 - AUX_BYTES - EPI_BYTES - SF_BYTES) / STAGE_BYTES;
@@ -167,7 +168,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
 gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                   const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                   const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_c2,
-                  const GemmParams p) {
+                  const __grid_constant__ CUtensorMap tmap_c3, const GemmParams p) {
   using S = Gemm2Smem<BN, MODE>;
   const bool GATHER = p.a_idx != nullptr;   // rows of A fetched by index (TMA gather4) vs. a plain tile
   extern __shared__ uint8_t smem_raw[];
@@ -508,6 +509,145 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     (g % 4)] = (uint8_t)e;
           }
         }
+      } else if (MODE == DGATEDQ) {
+        // D columns [c_base, c_base + BN/2) in chunks of 32.  Per chunk dz (64 columns) and y1s (32 columns)
+        // are rounded to bf16 and quantised right here - dz with one scale per 32x32 block, y1s with one scale
+        // per column and 32 rows - and leave as e4m3: dz row-major (dgrad operand) and dz / y1s transposed
+        // (wgrad operands).  The four warps of a column half share the transposed staging tiles.
+        const int Nz = 2 * p.N;
+        const float s = t.valid ? p.s[grow] : 0.f;
+        const uint32_t half_base = smem_u32(epi) + half * 20480;
+        const uint32_t r_buf = half_base + q * 2048;   // this warp: 32 rows x 64 B of row-major dz (64B swizzle)
+        const uint32_t t_dz = half_base + 8192;        // [64 dz columns][128 rows] bytes (128B swizzle)
+        const uint32_t t_ys = half_base + 16384;       // [32 y1s columns][128 rows] bytes (128B swizzle)
+        const int rr = q * 32 + lane;                  // row within this CTA's 128
+        const uint32_t t_off = (uint32_t)(rr & 15);
+        const int rch = rr >> 4;
+        const int row_grp = (t.m0 + q * 32) >> 5;      // 32-row group index along TKp
+        const int kt_rows = p.rows >> 7;               // K tiles of the transposed operands
+        float ds_acc = 0.f;
+#pragma unroll 1
+        for (int c = 0; c < COLS_PER_WARP / 32; ++c) {
+          const int dcol = c_base + c * 32;            // first D / y1s column of the chunk
+          uint32_t r[32];
+          tmem_ld32(t_row + c * 32, r);
+          uint4 zb[4];
+          float sc0 = 0.f, sc1 = 0.f;
+          if (t.valid) {
+            const uint8_t* zrow = p.z_fp8 + grow * Nz + 2 * dcol;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) zb[i] = reinterpret_cast<const uint4*>(zrow)[i];
+            const uint32_t sc = *reinterpret_cast<const uint16_t*>(p.z_sc + grow * (Nz / 32) + (2 * dcol) / 32);
+            sc0 = __int_as_float((int)(sc & 0xFF) << 23);
+            sc1 = __int_as_float((int)(sc >> 8) << 23);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) zb[i] = make_uint4(0, 0, 0, 0);
+          }
+          tmem_ld_wait();
+          // the staged tiles of the previous chunk must have been read before anyone overwrites them
+          if (lane == 0) bulk_wait_group_read<0>();
+          asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
+          const uint32_t* zw = reinterpret_cast<const uint32_t*>(zb);
+          float ys[32];
+#pragma unroll
+          for (int b = 0; b < 2; ++b) {
+            float v[32];
+            float amax = 0.f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int pi = b * 16 + i;
+              const uint32_t pair = (zw[pi >> 1] >> (16 * (pi & 1))) & 0xFFFF;
+              const float scale = b ? sc1 : sc0;
+              const float2 gu = e4m3x2_to_f32(pair);
+              const float g = gu.x * scale, u = gu.y * scale;
+              const float D = __uint_as_float(r[pi]);
+              const float dout = s * D;
+              const float sig = fast_sigmoid(g);
+              const float silu = g * sig;
+              const float sd = silu * dout;
+              const float yv = silu * u;
+              ds_acc = fmaf(yv, D, ds_acc);
+              v[2 * i] = bf16_rne(((sig - silu * sig) * dout + sd) * u);
+              v[2 * i + 1] = bf16_rne(sd);
+              ys[pi] = bf16_rne(s * yv);
+              amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
+            }
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffff, amax, d));
+            const int e = e8m0_of(amax);
+            const float qs = qscale_of(e);
+            uint32_t w[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              w[i] = pack_e4m3x4(v[4 * i] * qs, v[4 * i + 1] * qs, v[4 * i + 2] * qs, v[4 * i + 3] * qs);
+            if (t.valid) {
+              st_shared_v4(r_buf + lane * 64 + (((2 * b) ^ ((lane >> 1) & 3)) << 4), w[0], w[1], w[2], w[3]);
+              st_shared_v4(r_buf + lane * 64 + (((2 * b + 1) ^ ((lane >> 1) & 3)) << 4), w[4], w[5], w[6], w[7]);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const int cc = b * 32 + i;
+                const uint32_t byte = (w[i >> 2] >> (8 * (i & 3))) & 0xFF;
+                asm volatile("st.shared.u8 [%0], %1;" ::"r"(t_dz + cc * 128 + ((rch ^ (cc & 7)) << 4) + t_off),
+                             "r"(byte) : "memory");
+              }
+              const int g_row = (2 * dcol) / 32 + b;
+              p.dz_row_sf[((grow >> 7) * (size_t)(Nz >> 7) + (g_row >> 2)) * 512 + (grow & 31) * 16 +
+                          ((grow & 127) >> 5) * 4 + (g_row & 3)] = (uint8_t)e;
+              const size_t zc = (size_t)(2 * dcol + 32 * b + lane);       // dz column owned by this lane
+              p.dz_col_sf[((zc >> 7) * (size_t)kt_rows + (row_grp >> 2)) * 512 + (zc & 31) * 16 +
+                          ((zc & 127) >> 5) * 4 + (row_grp & 3)] = (uint8_t)e;
+            }
+          }
+          // y1s: amax of each column over the warp's 32 rows (butterfly that halves the column set each step:
+          // lane L ends up with column L), then every lane quantises its row with the 32 column scales
+          float a[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) a[i] = fabsf(ys[i]);
+#pragma unroll
+          for (int sft = 16; sft >= 1; sft >>= 1) {
+            const bool up = (lane & sft) != 0;
+#pragma unroll
+            for (int i = 0; i < sft; ++i) {
+              const float send = up ? a[i] : a[i + sft];
+              const float recv = __shfl_xor_sync(0xffffffff, send, sft);
+              a[i] = fmaxf(up ? a[i + sft] : a[i], recv);
+            }
+          }
+          const int e_col = e8m0_of(a[0]);
+#pragma unroll
+          for (int i4 = 0; i4 < 8; ++i4) {
+            float qv[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              qv[j] = ys[4 * i4 + j] * qscale_of(__shfl_sync(0xffffffff, e_col, 4 * i4 + j));
+            const uint32_t w4 = pack_e4m3x4(qv[0], qv[1], qv[2], qv[3]);
+            if (t.valid) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int cc = 4 * i4 + j;
+                asm volatile("st.shared.u8 [%0], %1;" ::"r"(t_ys + cc * 128 + ((rch ^ (cc & 7)) << 4) + t_off),
+                             "r"((w4 >> (8 * j)) & 0xFF) : "memory");
+              }
+            }
+          }
+          if (t.valid) {
+            const size_t yc = (size_t)(dcol + lane);                      // y1s column owned by this lane
+            p.y1s_col_sf[((yc >> 7) * (size_t)kt_rows + (row_grp >> 2)) * 512 + (yc & 31) * 16 +
+                         ((yc & 127) >> 5) * 4 + (row_grp & 3)] = (uint8_t)e_col;
+          }
+          fence_proxy_async_smem();
+          asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
+          if (t.valid && lane == 0) {
+            tma_store_2d(&tmap_c, r_buf, 2 * dcol, t.m0 + q * 32);         // dz row-major [TKp, 2I]
+            if (q == 0) {
+              tma_store_2d(&tmap_c2, t_dz, t.m0, 2 * dcol);               // dz transposed [2I, TKp]
+              tma_store_2d(&tmap_c3, t_ys, t.m0, dcol);                   // y1s transposed [I, TKp]
+            }
+            bulk_commit_group();
+          }
+        }
+        if (t.valid) p.ds_partial[(size_t)((t.n0 / BN) * 2 + half) * p.rows + grow] = ds_acc;
       } else {  // DGATED
         // this warp: D columns [c_base, c_base + BN/2) of I in chunks of 32 -> dz 64 bf16 (128-byte rows,
         // SWIZZLE_128B, 4 KB) and y1s 32 bf16 (64-byte rows, SWIZZLE_64B, 2 KB)

@@ -33,6 +33,8 @@ SIGNATURES = {
     "smoe_gemm_gated": (_I, [_P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P, _P]),
     "smoe_gemm_dgated": (_I, [_P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P, _P]),
     "smoe_gemm_dgated_partials": (_L, [_L]),
+    "smoe_gemm_dgated_fused": (_I, [_P] * 15 + [_L, _L, _L, _L, _P, _P]),
+    "smoe_gemm_dgated_fused_partials": (_L, [_L]),
     "smoe_gemm_wgrad": (_I, [_P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _I, _P, _P]),
     "smoe_debug_force_bn": (_I, [_I]),
     "smoe_combine": (_I, [_P, _P, _P, _P, _P, _L, _L, _P]),

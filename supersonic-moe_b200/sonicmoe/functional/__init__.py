@@ -84,6 +84,9 @@ def _require_fp8():
 #          one tiled copy per 16 KB; measured far faster than per-row fetches on B200)
 #   True   rows are fetched inside the GEMM with TMA gather4 (4 rows of 128 bytes per copy, no gathered buffer)
 USE_TMA_GATHER = os.getenv("SONIC_MOE_TMA_GATHER", "0") == "1"
+# GemmDGated emits the e4m3 operands of the three GEMMs that follow it (dgrad, dw1, dw2) straight from its
+# epilogue instead of bf16 dz / y1s plus separate quantizer passes (same bytes either way).
+FUSE_DGATED_QUANT = os.getenv("SONIC_MOE_FUSE_DGATED_QUANT", "1") == "1"
 
 
 # ----------------------------------------------------------------------------
@@ -327,12 +330,20 @@ class _DownProjection(torch.autograd.Function):
                 dg_q, a_sf = ops.gather_rows_fp8(dout_q, dout_raw, x_gather_idx, TKp, efo[-1:])
             else:
                 dg_q, a_sf = ops.quant_rows_scatter(dout, naept, s_rev, s_scatter_idx, TKp, efo[-1:])
-            dz, y1s, dsp = ops.gemm_dgated(dg_q, None, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, TKp)
+            if FUSE_DGATED_QUANT and E <= 256:
+                # dz / y1s never exist in bf16: the epilogue emits the e4m3 operands of dgrad, dw1 and dw2
+                dz_q, dz_rsf, dz_t, dz_csf, y1s_t, y1s_sf, dsp = ops.gemm_dgated_fused(
+                    dg_q, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, TKp)
+                link["dz"] = (dz_q, dz_rsf, dz_t, dz_csf)
+                dz = y1s = None
+            else:
+                dz, y1s, dsp = ops.gemm_dgated(dg_q, None, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, TKp)
             del dg_q
         del z_q, z_sc
         dw2 = None
         if ctx.needs_input_grad[2]:
-            y1s_t, y1s_sf = ops.quant_cols_t(y1s, None, TKp)
+            if y1s is not None:
+                y1s_t, y1s_sf = ops.quant_cols_t(y1s, None, TKp)
             if dout is None:
                 dout_t, dout_sf = ops.requant_cols_t(dout_q, dout_raw, x_gather_idx, TKp)
             else:
@@ -342,10 +353,13 @@ class _DownProjection(torch.autograd.Function):
                 ops.gemm_wgrad(y1s_t, y1s_sf, dout_t, dout_sf, efo, mg, accumulate=True)
                 _after_accumulate(base)
             else:
-                out = torch.empty(E, I, H, dtype=torch.float32, device=y1s.device)
+                out = torch.empty(E, I, H, dtype=torch.float32, device=y1s_t.device)
                 ops.gemm_wgrad(y1s_t, y1s_sf, dout_t, dout_sf, efo, out, accumulate=False)
                 dw2 = out.transpose(1, 2).to(w2.dtype)
-        link["dz"] = ops.quant_iso32(dz)
+        if dz is not None:
+            link["dz"] = ops.quant_iso32(dz)
+        else:      # the gradient edge of z still needs a tensor of its shape; its contents are never read
+            dz = _placeholder(topk_scores, (TKp, 2 * I))
         # ds: token-major (length of the score buffer) and, when asked, scattered to the [T,K] source
         d_scores = d_source = None
         want_flat = ctx.needs_input_grad[4]

@@ -269,6 +269,28 @@ def gemm_dgated(dout_q, a_idx, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, rows):
 
 
 @_timed
+def gemm_dgated_fused(dg_q, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, rows):
+    """GemmDGated with fused operand quantizers.  dg_q u8 [rows,H] (expert-sorted), w2t_q u8 [E,I,H] ->
+    (dz_q [rows,2I], dz row ISA, dz_t [2I,rows], dz col ISA, y1s_t [I,rows], y1s col ISA, ds_partial)."""
+    _cuda(dg_q, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s)
+    K = dg_q.shape[1]
+    E, N, _ = w2t_q.shape
+    dev = dg_q.device
+    parts = lib.smoe_gemm_dgated_fused_partials(N)
+    dz_q = torch.empty(rows, 2 * N, dtype=_U8, device=dev)
+    dz_t = torch.empty(2 * N, rows, dtype=_U8, device=dev)
+    y1s_t = torch.empty(N, rows, dtype=_U8, device=dev)
+    dz_rsf = torch.empty(isa_bytes(rows, 2 * N), dtype=_U8, device=dev)
+    dz_csf = torch.empty(isa_bytes(2 * N, rows), dtype=_U8, device=dev)
+    y1s_sf = torch.empty(isa_bytes(N, rows), dtype=_U8, device=dev)
+    dsp = torch.zeros(parts, rows, dtype=torch.float32, device=dev)
+    check(lib.smoe_gemm_dgated_fused(_p(dg_q), _p(a_sf), _p(w2t_q), _p(w2t_sf), _p(efo), _p(z_q), _p(z_sc), _p(s),
+                                     _p(dz_q), _p(dz_rsf), _p(dz_t), _p(dz_csf), _p(y1s_t), _p(y1s_sf), _p(dsp),
+                                     rows, N, K, E, _p(status_word(dev)), _stream()), "gemm_dgated_fused")
+    return dz_q, dz_rsf, dz_t, dz_csf, y1s_t, y1s_sf, dsp
+
+
+@_timed
 def gemm_wgrad(a_t, a_sf, b_t, b_sf, efo, out, accumulate):
     """a_t u8 [M,TKp], b_t u8 [N,TKp]; out f32 [E,M,N] (+)= per-expert products."""
     _cuda(a_t, a_sf, b_t, b_sf, efo, out)

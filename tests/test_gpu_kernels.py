@@ -400,3 +400,39 @@ def test_gemm_wgrad(ops, bn, M, N, tiles):
         else:
             assert (fresh[e] == 0).all()
         torch.testing.assert_close(out[e], init[e].to(DEV) + ref, rtol=1e-4, atol=1e-2 * ref.abs().max().item() + 1e-6)
+
+
+@pytest.mark.parametrize("bn", [0, 128])
+@pytest.mark.parametrize("T,H,I,tiles", GATED_SHAPES)
+def test_gemm_dgated_fused_quantizers_match_separate_kernels(ops, T, H, I, tiles, bn):
+    """The fused epilogue must emit exactly the bytes of dgated -> quant_iso32(dz) / quant_cols_t(y1s)."""
+    from sonicmoe._lib import lib
+    g, E, efo, rows, dout, _, a_idx = gated_inputs(T, H, I, tiles, 17)
+    w2t = (torch.randn(E, I, H, generator=g) * 0.05).to(torch.bfloat16)
+    z = torch.randn(rows, 2 * I, generator=g)
+    zq, zs = Q.row_quant(z, amax_floor=1e-4)
+    s = torch.rand(rows, generator=g)
+    s[::5] = 0.0
+    dq, dsc = Q.row_quant(dout)
+    wq, ws = Q.row_quant(w2t.reshape(E * I, H))
+    a_sf = Q.gather_scales_to_isa(dsc, a_idx, H).to(DEV)
+    w_sf = Q.pack_isa(ws, E * I, H).to(DEV)
+    a_in = dq[a_idx.long()].contiguous().to(DEV)
+    args = (a_sf, wq.reshape(E, I, H).to(DEV), w_sf, efo.to(DEV), zq.to(DEV), zs.to(DEV), s.to(DEV), rows)
+    lib.smoe_debug_force_bn(bn)
+    try:
+        dz, y1s, dsp = ops.gemm_dgated(a_in, None, *args)
+        f_dzq, f_rsf, f_dzt, f_csf, f_yt, f_ysf, f_dsp = ops.gemm_dgated_fused(a_in, *args)
+        torch.cuda.synchronize()
+        ops.check_status(DEV)
+    finally:
+        lib.smoe_debug_force_bn(0)
+    r_q, r_rsf, r_qt, r_csf = ops.quant_iso32(dz)
+    r_yt, r_ysf = ops.quant_cols_t(y1s, None, rows)
+    n = int(efo[-1])          # rows of real segments (the tail of the allocation is never written)
+    assert torch.equal(f_dzq[:n], r_q[:n]) and torch.equal(f_dzt[:, :n], r_qt[:, :n])
+    assert torch.equal(f_yt[:, :n], r_yt[:, :n])
+    assert torch.equal(Q.unpack_isa(f_rsf.cpu(), rows, 2 * I)[:n], Q.unpack_isa(r_rsf.cpu(), rows, 2 * I)[:n])
+    assert torch.equal(Q.unpack_isa(f_csf.cpu(), 2 * I, rows)[:, :n // 32], Q.unpack_isa(r_csf.cpu(), 2 * I, rows)[:, :n // 32])
+    assert torch.equal(Q.unpack_isa(f_ysf.cpu(), I, rows)[:, :n // 32], Q.unpack_isa(r_ysf.cpu(), I, rows)[:, :n // 32])
+    assert torch.equal(f_dsp.sum(0)[:n], dsp.sum(0)[:n]) or torch.allclose(f_dsp.sum(0)[:n], dsp.sum(0)[:n], rtol=1e-5)
