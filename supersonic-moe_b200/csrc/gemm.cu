@@ -188,9 +188,11 @@ static int run(const void* a, int64_t a_rows, int64_t a_cols, const void* b, int
         if (!rc)
           rc = make_tmap(&om.c2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.y1s, p.rows, p.N, 32, 32,
                          CU_TENSOR_MAP_SWIZZLE_64B);
-      } else {  // GATED stores straight from registers; the output maps are unused
-        rc = make_tmap_u8(&om.c, p.z_fp8, p.rows, p.N, 32, 32);
-        om.c2 = om.c;
+      } else {  // GATED: z e4m3 [rows, N] in 32 x 64 boxes, y1 e4m3 [rows, N/2] in 32 x 32 boxes
+        rc = make_tmap(&om.c, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.z_fp8, p.rows, p.N, 64, 32, CU_TENSOR_MAP_SWIZZLE_64B);
+        if (!rc)
+          rc = make_tmap(&om.c2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.y1_fp8, p.rows, p.N / 2, 32, 32,
+                         CU_TENSOR_MAP_SWIZZLE_32B);
       }
       if (rc) return rc;
       if (MODE != DGATEDQ) om.c3 = om.c;
@@ -243,7 +245,7 @@ int smoe_gemm_gated(const void* x_fp8, int64_t T, const int* a_idx, const void* 
   p.efo = efo; p.a_idx = a_idx; p.sfa = (const uint8_t*)a_sf; p.sfb = (const uint8_t*)w1_sf;
   p.sfa_ktiles = (int)(K / 128); p.sfb_ktiles = (int)(K / 128);
   p.z_fp8 = (uint8_t*)z_fp8; p.z_sc = (uint8_t*)z_scales; p.y1_fp8 = (uint8_t*)y1_fp8; p.y1_sf = (uint8_t*)y1_sf;
-  p.status = status;
+  p.status = status; p.debug_skip_store = g_skip_store;
   return run<GATED>(x_fp8, T, K, w1_fp8, E * N, K, p, (int)((rows / 128) * (N / 128)), (cudaStream_t)stream);
 }
 

@@ -105,9 +105,9 @@ struct Gemm2Smem {
   static constexpr int SF_SLOTS = 2;
   static constexpr int SF_BYTES = ((SF_SLOTS * SF_SLOT_BYTES + 1023) / 1024) * 1024;
   // output staging per epilogue warp: PLAIN 2 KB (bf16 32x32), WGRAD 2 KB (f32 32x16),
-  // DGATED 4 KB (dz) + 2 KB (y1s), GATED none
+  // DGATED 4 KB (dz) + 2 KB (y1s), GATED 2 KB (z e4m3 32x64) + 1 KB (y1 e4m3 32x32)
   // DGATEDQ: per column half 4 x 2 KB row-major dz + 8 KB transposed dz + 4 KB transposed y1s = 20 KB
-  static constexpr int EPI_BYTES_PER_WARP = MODE == GATED ? 0 : (MODE == DGATED ? 6144 : (MODE == DGATEDQ ? 5120 : 2048));
+  static constexpr int EPI_BYTES_PER_WARP = MODE == GATED ? 3072 : (MODE == DGATED ? 6144 : (MODE == DGATEDQ ? 5120 : 2048));
   static constexpr int EPI_BYTES = kEpiWarps2 * EPI_BYTES_PER_WARP;
   static constexpr int AUX_BYTES = 1024 + 2 * (kMaxExperts2 + 1) * 4;
   static constexpr int STAGES_RAW = (227 * 1024 - 1024 - AUX_BYTES - EPI_BYTES - SF_BYTES) / STAGE_BYTES;
@@ -454,6 +454,9 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           const int zc = t.n0 + (ch0 + ci) * 64;           // first z column of the chunk
           float y[32];
           uint32_t zs = 0;
+          // staging: z 32 rows x 64 B (64B swizzle) at stg, y1 32 rows x 32 B (32B swizzle) at stg + 2048
+          if (lane == 0) bulk_wait_group_read<0>();
+          __syncwarp();
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             uint32_t r[32];
@@ -470,21 +473,17 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             const int e = e8m0_of(fmaxf(amax, 1e-4f));
             const float qs = qscale_of(e);
             zs |= (uint32_t)e << (8 * h);
-            if (t.valid) {
-              uint4* zd = reinterpret_cast<uint4*>(p.z_fp8 + grow * Nz + zc + h * 32);
 #pragma unroll
-              for (int i = 0; i < 2; ++i) {
-                uint4 v;
-                v.x = pack_e4m3x4(__uint_as_float(r[16 * i + 0]) * qs, __uint_as_float(r[16 * i + 1]) * qs,
-                                  __uint_as_float(r[16 * i + 2]) * qs, __uint_as_float(r[16 * i + 3]) * qs);
-                v.y = pack_e4m3x4(__uint_as_float(r[16 * i + 4]) * qs, __uint_as_float(r[16 * i + 5]) * qs,
-                                  __uint_as_float(r[16 * i + 6]) * qs, __uint_as_float(r[16 * i + 7]) * qs);
-                v.z = pack_e4m3x4(__uint_as_float(r[16 * i + 8]) * qs, __uint_as_float(r[16 * i + 9]) * qs,
-                                  __uint_as_float(r[16 * i + 10]) * qs, __uint_as_float(r[16 * i + 11]) * qs);
-                v.w = pack_e4m3x4(__uint_as_float(r[16 * i + 12]) * qs, __uint_as_float(r[16 * i + 13]) * qs,
-                                  __uint_as_float(r[16 * i + 14]) * qs, __uint_as_float(r[16 * i + 15]) * qs);
-                zd[i] = v;
-              }
+            for (int i = 0; i < 2; ++i) {
+              const uint32_t v0 = pack_e4m3x4(__uint_as_float(r[16 * i + 0]) * qs, __uint_as_float(r[16 * i + 1]) * qs,
+                                              __uint_as_float(r[16 * i + 2]) * qs, __uint_as_float(r[16 * i + 3]) * qs);
+              const uint32_t v1 = pack_e4m3x4(__uint_as_float(r[16 * i + 4]) * qs, __uint_as_float(r[16 * i + 5]) * qs,
+                                              __uint_as_float(r[16 * i + 6]) * qs, __uint_as_float(r[16 * i + 7]) * qs);
+              const uint32_t v2 = pack_e4m3x4(__uint_as_float(r[16 * i + 8]) * qs, __uint_as_float(r[16 * i + 9]) * qs,
+                                              __uint_as_float(r[16 * i + 10]) * qs, __uint_as_float(r[16 * i + 11]) * qs);
+              const uint32_t v3 = pack_e4m3x4(__uint_as_float(r[16 * i + 12]) * qs, __uint_as_float(r[16 * i + 13]) * qs,
+                                              __uint_as_float(r[16 * i + 14]) * qs, __uint_as_float(r[16 * i + 15]) * qs);
+              st_shared_v4(stg + lane * 64 + (((2 * h + i) ^ ((lane >> 1) & 3)) << 4), v0, v1, v2, v3);
             }
           }
           float amax = 0.f;
@@ -492,18 +491,23 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(y[i]));
           const int e = e8m0_of(amax);
           const float qs = qscale_of(e);
-          if (t.valid) {
-            *reinterpret_cast<uint16_t*>(p.z_sc + grow * (Nz / 32) + zc / 32) = (uint16_t)zs;
-            uint4* yd = reinterpret_cast<uint4*>(p.y1_fp8 + grow * Ny + zc / 2);
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-              uint4 v;
-              v.x = pack_e4m3x4(y[16 * i + 0] * qs, y[16 * i + 1] * qs, y[16 * i + 2] * qs, y[16 * i + 3] * qs);
-              v.y = pack_e4m3x4(y[16 * i + 4] * qs, y[16 * i + 5] * qs, y[16 * i + 6] * qs, y[16 * i + 7] * qs);
-              v.z = pack_e4m3x4(y[16 * i + 8] * qs, y[16 * i + 9] * qs, y[16 * i + 10] * qs, y[16 * i + 11] * qs);
-              v.w = pack_e4m3x4(y[16 * i + 12] * qs, y[16 * i + 13] * qs, y[16 * i + 14] * qs, y[16 * i + 15] * qs);
-              yd[i] = v;
+          for (int i = 0; i < 2; ++i) {
+            const uint32_t v0 = pack_e4m3x4(y[16 * i + 0] * qs, y[16 * i + 1] * qs, y[16 * i + 2] * qs, y[16 * i + 3] * qs);
+            const uint32_t v1 = pack_e4m3x4(y[16 * i + 4] * qs, y[16 * i + 5] * qs, y[16 * i + 6] * qs, y[16 * i + 7] * qs);
+            const uint32_t v2 = pack_e4m3x4(y[16 * i + 8] * qs, y[16 * i + 9] * qs, y[16 * i + 10] * qs, y[16 * i + 11] * qs);
+            const uint32_t v3 = pack_e4m3x4(y[16 * i + 12] * qs, y[16 * i + 13] * qs, y[16 * i + 14] * qs, y[16 * i + 15] * qs);
+            st_shared_v4(stg + 2048 + lane * 32 + ((i ^ ((lane >> 2) & 1)) << 4), v0, v1, v2, v3);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (t.valid && !p.debug_skip_store) {
+            if (lane == 0) {
+              tma_store_2d(&tmap_c, stg, zc, t.m0 + q * 32);                 // z e4m3 [rows, 2I]
+              tma_store_2d(&tmap_c2, stg + 2048, zc / 2, t.m0 + q * 32);     // y1 e4m3 [rows, I]
+              bulk_commit_group();
             }
+            *reinterpret_cast<uint16_t*>(p.z_sc + grow * (Nz / 32) + zc / 32) = (uint16_t)zs;
             const int g = zc / 64;
             p.y1_sf[((grow / 128) * (size_t)(Ny / 128) + g / 4) * 512 + (grow % 32) * 16 + ((grow % 128) / 32) * 4 +
                     (g % 4)] = (uint8_t)e;
