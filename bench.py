@@ -294,6 +294,8 @@ def run_ours(args):
     seen = {"gemm_varlen_m": 0, "gemm_wgrad": 0}
     for k in gemm_keys:
         n = k.split("#")[0]
+        if n.startswith("gemm_wgrad"):
+            n = "gemm_wgrad"
         if n == "gemm_gated":
             per_gemm_flops[k] = 4 * TKH_I
         elif n in ("gemm_dgated", "gemm_dgated_fused"):

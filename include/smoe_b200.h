@@ -162,16 +162,17 @@ int smoe_gemm_dgated(const void* dout_fp8, int64_t T, const int32_t* a_idx, cons
 int64_t smoe_gemm_dgated_partials(int64_t N);
 
 /* GemmDGated with the operand quantizers of the following GEMMs fused into its epilogue: instead of dz / y1s in
- * bf16 it emits, bit for bit what smoe_quant_iso32(dz) and smoe_quant_cols_t(y1s) would produce from the bf16
- * tensors: dz_q e4m3 [rows,2N] + row ISA scales (rows,2N), dz_t e4m3 [2N,rows] + column ISA scales (2N,rows)
- * (one scale per 32x32 block), y1s_t e4m3 [N,rows] + column ISA scales (N,rows).  A operand already gathered
- * ([rows,K]).  Replaces gemm_dgated + quantize_dz_dout + quantize_wgrad_operand(y1s)
- * (sonicmoe/quack_utils/sm100_funcs.py:824-944).  Two-CTA kernel only: E <= 256, else SMOE_ERR_SHAPE. */
+ * bf16 it emits the payload and scale bytes that smoe_quant_iso32(dz) and smoe_quant_cols_t(y1s) would produce
+ * from the bf16 tensors, both payloads row-major: dz_q e4m3 [rows,2N] with ISA scales for (rows,2N) and for
+ * (2N,rows) - one scale per 32x32 block, so the one payload is the activation-gradient operand and, fed MN-major
+ * through smoe_gemm_wgrad_mn, the weight-gradient operand - and y1s_q e4m3 [rows,N] with column ISA scales
+ * (N,rows).  A operand already gathered ([rows,K]).  Replaces gemm_dgated + quantize_dz_dout +
+ * quantize_wgrad_operand(y1s) (sonicmoe/quack_utils/sm100_funcs.py:824-944).  Two-CTA kernel only: E <= 256,
+ * else SMOE_ERR_SHAPE. */
 int smoe_gemm_dgated_fused(const void* dout_fp8, const void* a_sf, const void* w2t_fp8, const void* w2t_sf,
                            const int32_t* efo, const void* z_fp8, const void* z_scales, const float* s, void* dz_q,
-                           void* dz_row_sf, void* dz_t, void* dz_col_sf, void* y1s_t, void* y1s_col_sf,
-                           float* ds_partial, int64_t rows, int64_t N, int64_t K, int64_t E, int32_t* status,
-                           void* stream);
+                           void* dz_row_sf, void* dz_col_sf, void* y1s_q, void* y1s_col_sf, float* ds_partial,
+                           int64_t rows, int64_t N, int64_t K, int64_t E, int32_t* status, void* stream);
 int64_t smoe_gemm_dgated_fused_partials(int64_t N);
 
 /* Weight gradient: C[e] (M x N, f32) (+)= A_t[:, seg_e] . B_t[:, seg_e]^T with A_t e4m3 [M,TKp], B_t e4m3 [N,TKp]
@@ -180,6 +181,16 @@ int64_t smoe_gemm_dgated_fused_partials(int64_t N);
 int smoe_gemm_wgrad(const void* a_t_fp8, const void* a_sf, const void* b_t_fp8, const void* b_sf, const int32_t* efo,
                     float* c, int64_t M, int64_t N, int64_t TKp, int64_t E, int accumulate, int32_t* status,
                     void* stream);
+
+/* Weight gradient with operands in their natural orientation.  layout bit 0: A is e4m3 [TKp, M] (row = routed
+ * token position) instead of [M, TKp]; bit 1: B is e4m3 [TKp, N] instead of [N, TKp].  Such an operand is fed to
+ * the tensor core MN-major, so the activation-gradient GEMM's row-major outputs serve as weight-gradient operands
+ * without a transposed copy.  Scales are ISA-packed for (M,TKp) / (N,TKp) either way.  Same reference operation as
+ * smoe_gemm_wgrad (the reference's quantize_wgrad_operand writes transposed copies instead,
+ * sonicmoe/quack_utils/blockscaled_fp8_gemm.py:2210-2687).  Needs M % 256 == 0, N % 256 == 0, E <= 256. */
+int smoe_gemm_wgrad_mn(const void* a_fp8, const void* a_sf, const void* b_fp8, const void* b_sf, const int32_t* efo,
+                       float* c, int64_t M, int64_t N, int64_t TKp, int64_t E, int accumulate, int layout,
+                       int32_t* status, void* stream);
 
 /* Test hook: force the GEMM column tile (128 or 256; 0 = automatic). */
 int smoe_debug_force_bn(int bn);

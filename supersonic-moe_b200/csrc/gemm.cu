@@ -165,7 +165,8 @@ static int run(const void* a, int64_t a_rows, int64_t a_cols, const void* b, int
       int rc = SMOE_OK;
       const int64_t sfa_tiles = (MODE == WGRAD) ? (int64_t)(p.rows / 128) * p.sfa_ktiles
                                                 : (int64_t)(p.rows / 128) * p.sfa_ktiles;
-      const int64_t sfb_tiles = (b_rows / 128) * p.sfb_ktiles;
+      const int64_t sfb_tiles = (MODE == WGRAD) ? (int64_t)(p.N / 128) * p.sfb_ktiles : (b_rows / 128) * p.sfb_ktiles;
+      if (MODE == WGRAD && (p.a_mn || p.b_mn) && bn2 != 256) return SMOE_ERR_SHAPE;
       if (MODE == PLAIN) {
         rc = make_tmap(&om.c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.c, p.rows, p.N, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B);
         om.c2 = om.c;
@@ -177,11 +178,7 @@ static int run(const void* a, int64_t a_rows, int64_t a_cols, const void* b, int
         rc = make_tmap(&om.c, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.dz, p.rows, 2 * (uint64_t)p.N, 64, 32,
                        CU_TENSOR_MAP_SWIZZLE_64B);
         if (!rc)
-          rc = make_tmap(&om.c2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.c, 2 * (uint64_t)p.N, p.rows, 128, 64,
-                         CU_TENSOR_MAP_SWIZZLE_128B);
-        if (!rc)
-          rc = make_tmap(&om.c3, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.y1s, p.N, p.rows, 128, 32,
-                         CU_TENSOR_MAP_SWIZZLE_128B);
+          rc = make_tmap(&om.c2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.y1s, p.rows, p.N, 32, 32, CU_TENSOR_MAP_SWIZZLE_32B);
       } else if (MODE == DGATED) {
         rc = make_tmap(&om.c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.dz, p.rows, 2 * (uint64_t)p.N, 64, 32,
                        CU_TENSOR_MAP_SWIZZLE_128B);
@@ -195,11 +192,12 @@ static int run(const void* a, int64_t a_rows, int64_t a_cols, const void* b, int
                          CU_TENSOR_MAP_SWIZZLE_32B);
       }
       if (rc) return rc;
-      if (MODE != DGATEDQ) om.c3 = om.c;
+      om.c3 = om.c;
       return run2<MODE>(a, a_rows, a_cols, b, b_rows, b_cols, p, om, bn2, sfa_tiles, sfb_tiles, stream);
     }
   }
   if (MODE == DGATEDQ) return SMOE_ERR_SHAPE;     // fused-quantizer epilogue exists in the two-CTA kernel only
+  if (MODE == WGRAD && (p.a_mn || p.b_mn)) return SMOE_ERR_SHAPE;   // so do MN-major operands
   constexpr int M1 = (MODE == DGATEDQ) ? DGATED : MODE;
   const int bn = pick_bn(p.N);
   CUtensorMap ta, tb;
@@ -268,16 +266,15 @@ int smoe_gemm_dgated(const void* dout_fp8, int64_t T, const int* a_idx, const vo
 
 int smoe_gemm_dgated_fused(const void* dout_fp8, const void* a_sf, const void* w2t_fp8, const void* w2t_sf,
                            const int* efo, const void* z_fp8, const void* z_scales, const float* s, void* dz_q,
-                           void* dz_row_sf, void* dz_t, void* dz_col_sf, void* y1s_t, void* y1s_col_sf,
-                           float* ds_partial, int64_t rows, int64_t N, int64_t K, int64_t E, int* status,
-                           void* stream) {
+                           void* dz_row_sf, void* dz_col_sf, void* y1s_q, void* y1s_col_sf, float* ds_partial,
+                           int64_t rows, int64_t N, int64_t K, int64_t E, int* status, void* stream) {
   if (rows % 128 || N % 128 || K % 128 || E <= 0) return SMOE_ERR_SHAPE;
   GemmParams p{};
   p.rows = (int)rows; p.N = (int)N; p.K = (int)K; p.E = (int)E;
   p.efo = efo; p.a_idx = nullptr; p.sfa = (const uint8_t*)a_sf; p.sfb = (const uint8_t*)w2t_sf;
   p.sfa_ktiles = (int)(K / 128); p.sfb_ktiles = (int)(K / 128);
   p.z_fp8 = (uint8_t*)const_cast<void*>(z_fp8); p.z_sc = (uint8_t*)const_cast<void*>(z_scales);
-  p.s = s; p.dz = dz_q; p.c = dz_t; p.y1s = y1s_t; p.ds_partial = ds_partial; p.status = status;
+  p.s = s; p.dz = dz_q; p.y1s = y1s_q; p.ds_partial = ds_partial; p.status = status;
   p.dz_row_sf = (uint8_t*)dz_row_sf; p.dz_col_sf = (uint8_t*)dz_col_sf; p.y1s_col_sf = (uint8_t*)y1s_col_sf;
   return run<DGATEDQ>(dout_fp8, rows, K, w2t_fp8, E * N, K, p, (int)((rows / 128) * (N / 128)), (cudaStream_t)stream);
 }
@@ -299,6 +296,20 @@ int smoe_gemm_wgrad(const void* a_t_fp8, const void* a_sf, const void* b_t_fp8, 
   p.sfa_ktiles = (int)(TKp / 128); p.sfb_ktiles = (int)(TKp / 128);
   p.c = c; p.accumulate = accumulate; p.status = status;
   return run<WGRAD>(a_t_fp8, M, TKp, b_t_fp8, N, TKp, p, (int)(E * (M / 128) * (N / 128)), (cudaStream_t)stream);
+}
+
+int smoe_gemm_wgrad_mn(const void* a_fp8, const void* a_sf, const void* b_fp8, const void* b_sf, const int* efo,
+                       float* c, int64_t M, int64_t N, int64_t TKp, int64_t E, int accumulate, int layout,
+                       int* status, void* stream) {
+  if (M % 256 || N % 256 || TKp % 128 || E <= 0 || (layout & ~3)) return SMOE_ERR_SHAPE;
+  GemmParams p{};
+  p.rows = (int)M; p.N = (int)N; p.K = (int)TKp; p.E = (int)E;
+  p.efo = efo; p.sfa = (const uint8_t*)a_sf; p.sfb = (const uint8_t*)b_sf;
+  p.sfa_ktiles = (int)(TKp / 128); p.sfb_ktiles = (int)(TKp / 128);
+  p.c = c; p.accumulate = accumulate; p.status = status;
+  p.a_mn = layout & 1; p.b_mn = (layout >> 1) & 1;
+  return run<WGRAD>(a_fp8, p.a_mn ? TKp : M, p.a_mn ? M : TKp, b_fp8, p.b_mn ? TKp : N, p.b_mn ? N : TKp, p,
+                    (int)(E * (M / 128) * (N / 128)), (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -39,6 +39,7 @@ struct GemmParams {
   // outputs / epilogue operands
   void* c;              // PLAIN: bf16 [rows,N]; WGRAD: f32 [E,rows,N]
   int accumulate;       // WGRAD: add into c instead of overwriting
+  int a_mn, b_mn;       // WGRAD (two-CTA kernel): operand stored [TKp, M] / [TKp, N] (MN-major) instead of transposed
   uint8_t* z_fp8;       // GATED out / DGATED in: [TKp, N_z] e4m3
   uint8_t* z_sc;        // raw ue8m0 [TKp, N_z/32]
   uint8_t* y1_fp8;      // GATED out: [TKp, N/2] e4m3

@@ -91,6 +91,13 @@ __device__ __forceinline__ float fast_sigmoid(float x) {
   return r;
 }
 
+// max |x| over the warp, delivered to every lane
+__device__ __forceinline__ float warp_max_abs(float x) {
+  float r;
+  asm volatile("redux.sync.max.abs.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(x));
+  return r;
+}
+
 template <int BN, int MODE>
 struct Gemm2Smem {
   static constexpr int A_BYTES = BM * BK;                 // this CTA's 128 rows
@@ -106,8 +113,8 @@ struct Gemm2Smem {
   static constexpr int SF_BYTES = ((SF_SLOTS * SF_SLOT_BYTES + 1023) / 1024) * 1024;
   // output staging per epilogue warp: PLAIN 2 KB (bf16 32x32), WGRAD 2 KB (f32 32x16),
   // DGATED 4 KB (dz) + 2 KB (y1s), GATED 2 KB (z e4m3 32x64) + 1 KB (y1 e4m3 32x32)
-  // DGATEDQ: per column half 4 x 2 KB row-major dz + 8 KB transposed dz + 4 KB transposed y1s = 20 KB
-  static constexpr int EPI_BYTES_PER_WARP = MODE == GATED ? 3072 : (MODE == DGATED ? 6144 : (MODE == DGATEDQ ? 5120 : 2048));
+  // DGATEDQ 2 KB (dz e4m3 32x64) + 1 KB (y1s e4m3 32x32)
+  static constexpr int EPI_BYTES_PER_WARP = MODE == GATED ? 3072 : (MODE == DGATED ? 6144 : (MODE == DGATEDQ ? 3072 : 2048));
   static constexpr int EPI_BYTES = kEpiWarps2 * EPI_BYTES_PER_WARP;
   static constexpr int AUX_BYTES = 1024 + 2 * (kMaxExperts2 + 1) * 4;
   static constexpr int STAGES_RAW = (227 * 1024 - 1024 - AUX_BYTES - EPI_BYTES - SF_BYTES) / STAGE_BYTES;
@@ -279,8 +286,10 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const uint32_t b_dst = a_dst + S::A_BYTES;
         if (lane == 0) {
           if (rank == 0) mbar_expect_tx(bar_full + 8 * stage, S::TX_BYTES);
-          if (!GATHER) tma_load_2d_pair(a_dst, &tmap_a, full, kt * BK, t.valid ? t.m0 : 0);
-          tma_load_2d_pair(b_dst, &tmap_b, full, kt * BK, b_row);
+          if (MODE == WGRAD && p.a_mn) tma_load_2d_pair(a_dst, &tmap_a, full, t.m0, kt * BK);
+          else if (!GATHER) tma_load_2d_pair(a_dst, &tmap_a, full, kt * BK, t.valid ? t.m0 : 0);
+          if (MODE == WGRAD && p.b_mn) tma_load_2d_pair(b_dst, &tmap_b, full, b_row, kt * BK);
+          else tma_load_2d_pair(b_dst, &tmap_b, full, kt * BK, b_row);
         }
         if (GATHER) {
           __syncwarp();
@@ -293,7 +302,10 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (rank == 0 && elect_one()) {
-      constexpr uint32_t idesc = make_idesc_mxf8(2 * BM, BN);
+      // WGRAD may take either operand MN-major: [K rows, M or N bytes] tiles instead of [M or N rows, K bytes]
+      const bool a_mn = MODE == WGRAD && p.a_mn, b_mn = MODE == WGRAD && p.b_mn;
+      const uint32_t idesc = make_idesc_mxf8(2 * BM, BN) | (a_mn ? 1u << 15 : 0u) | (b_mn ? 1u << 16 : 0u);
+      const uint32_t a_step = a_mn ? 256u : 2u, b_step = b_mn ? 256u : 2u;   // descriptor units of 16 bytes per 32 K
       int stage = 0, as = 0, sfs = 0;
       uint32_t phase = 0, aphase = 0, sfphase = 0;
       bool ok = true;
@@ -323,11 +335,11 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           tc_cp_sf_pair(sfa_t, make_desc_sf(sf_src));
 #pragma unroll
           for (int j = 0; j < S::SFB_TILES; ++j) tc_cp_sf_pair(sfb_t + 4 * j, make_desc_sf(sf_src + 2048 * (1 + j)));
-          const uint64_t a_desc = make_desc_kmajor_sw128(a_src);
-          const uint64_t b_desc = make_desc_kmajor_sw128(b_src);
+          const uint64_t a_desc = a_mn ? make_desc_mnmajor_sw128(a_src, S::A_BYTES) : make_desc_kmajor_sw128(a_src);
+          const uint64_t b_desc = b_mn ? make_desc_mnmajor_sw128(b_src, S::B_BYTES) : make_desc_kmajor_sw128(b_src);
 #pragma unroll
           for (int kb = 0; kb < BK / 32; ++kb) {
-            mma_mxf8_pair(d_tmem, a_desc + 2 * kb, b_desc + 2 * kb, idesc_with_sf_ids(idesc, kb, kb), sfa_t,
+            mma_mxf8_pair(d_tmem, a_desc + a_step * kb, b_desc + b_step * kb, idesc_with_sf_ids(idesc, kb, kb), sfa_t,
                           sfb_t + sfb_shift, (k | kb) != 0);
           }
           tc_commit_pair(bar_empty + 8 * stage, 3);
@@ -516,142 +528,128 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       } else if (MODE == DGATEDQ) {
         // D columns [c_base, c_base + BN/2) in chunks of 32.  Per chunk dz (64 columns) and y1s (32 columns)
         // are rounded to bf16 and quantised right here - dz with one scale per 32x32 block, y1s with one scale
-        // per column and 32 rows - and leave as e4m3: dz row-major (dgrad operand) and dz / y1s transposed
-        // (wgrad operands).  The four warps of a column half share the transposed staging tiles.
-        const int Nz = 2 * p.N;
-        const float s = t.valid ? p.s[grow] : 0.f;
-        const uint32_t half_base = smem_u32(epi) + half * 20480;
-        const uint32_t r_buf = half_base + q * 2048;   // this warp: 32 rows x 64 B of row-major dz (64B swizzle)
-        const uint32_t t_dz = half_base + 8192;        // [64 dz columns][128 rows] bytes (128B swizzle)
-        const uint32_t t_ys = half_base + 16384;       // [32 y1s columns][128 rows] bytes (128B swizzle)
-        const int rr = q * 32 + lane;                  // row within this CTA's 128
-        const uint32_t t_off = (uint32_t)(rr & 15);
-        const int rch = rr >> 4;
-        const int row_grp = (t.m0 + q * 32) >> 5;      // 32-row group index along TKp
-        const int kt_rows = p.rows >> 7;               // K tiles of the transposed operands
-        float ds_acc = 0.f;
-#pragma unroll 1
-        for (int c = 0; c < COLS_PER_WARP / 32; ++c) {
-          const int dcol = c_base + c * 32;            // first D / y1s column of the chunk
-          uint32_t r[32];
-          tmem_ld32(t_row + c * 32, r);
+        // per column and 32 rows - and leave as e4m3 in row-major order.  A 32x32-block scale serves dz both as
+        // the activation-gradient operand (scales along 2I) and as the weight-gradient operand (scales along
+        // TKp, fed MN-major), so one copy of the payload is enough.  Each warp works on its own.
+        if (t.valid) {
+          const int Nz = 2 * p.N;
+          const float s = p.s[grow];
+          const int row_grp = (t.m0 + q * 32) >> 5;      // 32-row group index along TKp
+          const int kt_rows = p.rows >> 7;               // K tiles of the weight-gradient operands
+          constexpr int NCH = COLS_PER_WARP / 32;
+          float ds_acc = 0.f;
           uint4 zb[4];
-          float sc0 = 0.f, sc1 = 0.f;
-          if (t.valid) {
-            const uint8_t* zrow = p.z_fp8 + grow * Nz + 2 * dcol;
+          uint32_t sc;
+          {
+            const uint8_t* zrow = p.z_fp8 + grow * Nz + 2 * c_base;
 #pragma unroll
             for (int i = 0; i < 4; ++i) zb[i] = reinterpret_cast<const uint4*>(zrow)[i];
-            const uint32_t sc = *reinterpret_cast<const uint16_t*>(p.z_sc + grow * (Nz / 32) + (2 * dcol) / 32);
-            sc0 = __int_as_float((int)(sc & 0xFF) << 23);
-            sc1 = __int_as_float((int)(sc >> 8) << 23);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) zb[i] = make_uint4(0, 0, 0, 0);
+            sc = *reinterpret_cast<const uint16_t*>(p.z_sc + grow * (Nz / 32) + (2 * c_base) / 32);
           }
-          tmem_ld_wait();
-          // the staged tiles of the previous chunk must have been read before anyone overwrites them
-          if (lane == 0) bulk_wait_group_read<0>();
-          asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
-          const uint32_t* zw = reinterpret_cast<const uint32_t*>(zb);
-          float ys[32];
+#pragma unroll 1
+          for (int c = 0; c < NCH; ++c) {
+            const int dcol = c_base + c * 32;            // first D / y1s column of the chunk
+            uint32_t r[32];
+            tmem_ld32(t_row + c * 32, r);
+            uint4 zn[4];
+            uint32_t scn = 0;
+            if (c + 1 < NCH) {                           // next chunk's z travels while this one is computed
+              const uint8_t* zrow = p.z_fp8 + grow * Nz + 2 * (dcol + 32);
 #pragma unroll
-          for (int b = 0; b < 2; ++b) {
-            float v[32];
-            float amax = 0.f;
+              for (int i = 0; i < 4; ++i) zn[i] = reinterpret_cast<const uint4*>(zrow)[i];
+              scn = *reinterpret_cast<const uint16_t*>(p.z_sc + grow * (Nz / 32) + (2 * (dcol + 32)) / 32);
+            } else {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int pi = b * 16 + i;
-              const uint32_t pair = (zw[pi >> 1] >> (16 * (pi & 1))) & 0xFFFF;
-              const float scale = b ? sc1 : sc0;
-              const float2 gu = e4m3x2_to_f32(pair);
-              const float g = gu.x * scale, u = gu.y * scale;
-              const float D = __uint_as_float(r[pi]);
-              const float dout = s * D;
-              const float sig = fast_sigmoid(g);
-              const float silu = g * sig;
-              const float sd = silu * dout;
-              const float yv = silu * u;
-              ds_acc = fmaf(yv, D, ds_acc);
-              v[2 * i] = bf16_rne(((sig - silu * sig) * dout + sd) * u);
-              v[2 * i + 1] = bf16_rne(sd);
-              ys[pi] = bf16_rne(s * yv);
-              amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
+              for (int i = 0; i < 4; ++i) zn[i] = make_uint4(0, 0, 0, 0);
             }
+            const float sc0 = __int_as_float((int)(sc & 0xFF) << 23);
+            const float sc1 = __int_as_float((int)(sc >> 8) << 23);
+            tmem_ld_wait();
+            const uint32_t* zw = reinterpret_cast<const uint32_t*>(zb);
+            float ys[32];
+            uint32_t w[16];
+            uint32_t e_blk = 0;
 #pragma unroll
-            for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffff, amax, d));
-            const int e = e8m0_of(amax);
-            const float qs = qscale_of(e);
-            uint32_t w[8];
+            for (int b = 0; b < 2; ++b) {
+              float v[32];
+              float amax = 0.f;
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-              w[i] = pack_e4m3x4(v[4 * i] * qs, v[4 * i + 1] * qs, v[4 * i + 2] * qs, v[4 * i + 3] * qs);
-            if (t.valid) {
-              st_shared_v4(r_buf + lane * 64 + (((2 * b) ^ ((lane >> 1) & 3)) << 4), w[0], w[1], w[2], w[3]);
-              st_shared_v4(r_buf + lane * 64 + (((2 * b + 1) ^ ((lane >> 1) & 3)) << 4), w[4], w[5], w[6], w[7]);
-#pragma unroll
-              for (int i = 0; i < 32; ++i) {
-                const int cc = b * 32 + i;
-                const uint32_t byte = (w[i >> 2] >> (8 * (i & 3))) & 0xFF;
-                asm volatile("st.shared.u8 [%0], %1;" ::"r"(t_dz + cc * 128 + ((rch ^ (cc & 7)) << 4) + t_off),
-                             "r"(byte) : "memory");
+              for (int i = 0; i < 16; ++i) {
+                const int pi = b * 16 + i;
+                const uint32_t pair = (zw[pi >> 1] >> (16 * (pi & 1))) & 0xFFFF;
+                const float scale = b ? sc1 : sc0;
+                const float2 gu = e4m3x2_to_f32(pair);
+                const float g = gu.x * scale, u = gu.y * scale;
+                const float D = __uint_as_float(r[pi]);
+                const float dout = s * D;
+                const float sig = fast_sigmoid(g);
+                const float silu = g * sig;
+                const float sd = silu * dout;
+                const float yv = silu * u;
+                ds_acc = fmaf(yv, D, ds_acc);
+                v[2 * i] = bf16_rne(((sig - silu * sig) * dout + sd) * u);
+                v[2 * i + 1] = bf16_rne(sd);
+                ys[pi] = bf16_rne(s * yv);
+                amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
               }
-              const int g_row = (2 * dcol) / 32 + b;
-              p.dz_row_sf[((grow >> 7) * (size_t)(Nz >> 7) + (g_row >> 2)) * 512 + (grow & 31) * 16 +
-                          ((grow & 127) >> 5) * 4 + (g_row & 3)] = (uint8_t)e;
-              const size_t zc = (size_t)(2 * dcol + 32 * b + lane);       // dz column owned by this lane
-              p.dz_col_sf[((zc >> 7) * (size_t)kt_rows + (row_grp >> 2)) * 512 + (zc & 31) * 16 +
-                          ((zc & 127) >> 5) * 4 + (row_grp & 3)] = (uint8_t)e;
+              const int e = e8m0_of(warp_max_abs(amax));
+              const float qs = qscale_of(e);
+              e_blk |= (uint32_t)e << (8 * b);
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                w[8 * b + i] = pack_e4m3x4(v[4 * i] * qs, v[4 * i + 1] * qs, v[4 * i + 2] * qs, v[4 * i + 3] * qs);
             }
-          }
-          // y1s: amax of each column over the warp's 32 rows (butterfly that halves the column set each step:
-          // lane L ends up with column L), then every lane quantises its row with the 32 column scales
-          float a[32];
+            // y1s: one scale per column over the warp's 32 rows
+            uint32_t wy[8];
+            int e_mine = 0;                              // lane L keeps the scale of column L
 #pragma unroll
-          for (int i = 0; i < 32; ++i) a[i] = fabsf(ys[i]);
-#pragma unroll
-          for (int sft = 16; sft >= 1; sft >>= 1) {
-            const bool up = (lane & sft) != 0;
-#pragma unroll
-            for (int i = 0; i < sft; ++i) {
-              const float send = up ? a[i] : a[i + sft];
-              const float recv = __shfl_xor_sync(0xffffffff, send, sft);
-              a[i] = fmaxf(up ? a[i + sft] : a[i], recv);
-            }
-          }
-          const int e_col = e8m0_of(a[0]);
-#pragma unroll
-          for (int i4 = 0; i4 < 8; ++i4) {
-            float qv[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-              qv[j] = ys[4 * i4 + j] * qscale_of(__shfl_sync(0xffffffff, e_col, 4 * i4 + j));
-            const uint32_t w4 = pack_e4m3x4(qv[0], qv[1], qv[2], qv[3]);
-            if (t.valid) {
+            for (int i4 = 0; i4 < 8; ++i4) {
+              float qv[4];
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
-                const int cc = 4 * i4 + j;
-                asm volatile("st.shared.u8 [%0], %1;" ::"r"(t_ys + cc * 128 + ((rch ^ (cc & 7)) << 4) + t_off),
-                             "r"((w4 >> (8 * j)) & 0xFF) : "memory");
+                const int e = e8m0_of(warp_max_abs(ys[4 * i4 + j]));
+                if (lane == 4 * i4 + j) e_mine = e;
+                qv[j] = ys[4 * i4 + j] * qscale_of(e);
               }
+              wy[i4] = pack_e4m3x4(qv[0], qv[1], qv[2], qv[3]);
             }
-          }
-          if (t.valid) {
-            const size_t yc = (size_t)(dcol + lane);                      // y1s column owned by this lane
+            if (lane == 0) bulk_wait_group_read<0>();    // the previous chunk's stores have read the staging
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              st_shared_v4(stg + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4), w[4 * j], w[4 * j + 1], w[4 * j + 2],
+                           w[4 * j + 3]);
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+              st_shared_v4(stg + 2048 + lane * 32 + ((j ^ ((lane >> 2) & 1)) << 4), wy[4 * j], wy[4 * j + 1],
+                           wy[4 * j + 2], wy[4 * j + 3]);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmap_c, stg, 2 * dcol, t.m0 + q * 32);          // dz e4m3 [TKp, 2I]
+              tma_store_2d(&tmap_c2, stg + 2048, dcol, t.m0 + q * 32);      // y1s e4m3 [TKp, I]
+              bulk_commit_group();
+            }
+            // scales: dz as a (TKp, 2I) operand - this row, two adjacent 32-column groups
+            const int g_row = (2 * dcol) >> 5;
+            *reinterpret_cast<uint16_t*>(p.dz_row_sf + ((grow >> 7) * (size_t)(Nz >> 7) + (g_row >> 2)) * 512 +
+                                         (grow & 31) * 16 + ((grow & 127) >> 5) * 4 + (g_row & 3)) = (uint16_t)e_blk;
+            // dz as a (2I, TKp) operand - lane = column, this warp's 32-row group
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+              const size_t zc = (size_t)(2 * dcol + 32 * b + lane);
+              p.dz_col_sf[((zc >> 7) * (size_t)kt_rows + (row_grp >> 2)) * 512 + (zc & 31) * 16 +
+                          ((zc & 127) >> 5) * 4 + (row_grp & 3)] = (uint8_t)(e_blk >> (8 * b));
+            }
+            const size_t yc = (size_t)(dcol + lane);
             p.y1s_col_sf[((yc >> 7) * (size_t)kt_rows + (row_grp >> 2)) * 512 + (yc & 31) * 16 +
-                         ((yc & 127) >> 5) * 4 + (row_grp & 3)] = (uint8_t)e_col;
+                         ((yc & 127) >> 5) * 4 + (row_grp & 3)] = (uint8_t)e_mine;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) zb[i] = zn[i];
+            sc = scn;
           }
-          fence_proxy_async_smem();
-          asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
-          if (t.valid && lane == 0) {
-            tma_store_2d(&tmap_c, r_buf, 2 * dcol, t.m0 + q * 32);         // dz row-major [TKp, 2I]
-            if (q == 0) {
-              tma_store_2d(&tmap_c2, t_dz, t.m0, 2 * dcol);               // dz transposed [2I, TKp]
-              tma_store_2d(&tmap_c3, t_ys, t.m0, dcol);                   // y1s transposed [I, TKp]
-            }
-            bulk_commit_group();
-          }
+          p.ds_partial[(size_t)((t.n0 / BN) * 2 + half) * p.rows + grow] = ds_acc;
         }
-        if (t.valid) p.ds_partial[(size_t)((t.n0 / BN) * 2 + half) * p.rows + grow] = ds_acc;
       } else {  // DGATED
         // this warp: D columns [c_base, c_base + BN/2) of I in chunks of 32 -> dz 64 bf16 (128-byte rows,
         // SWIZZLE_128B, 4 KB) and y1s 32 bf16 (64-byte rows, SWIZZLE_64B, 2 KB)

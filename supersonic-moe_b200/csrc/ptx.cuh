@@ -182,6 +182,18 @@ __device__ __forceinline__ uint64_t make_desc_kmajor_sw128(uint32_t saddr) {
   d |= (uint64_t)2 << 61;                         // SWIZZLE_128B
   return d;
 }
+// MN-major operand tile, 128-byte swizzle: K rows of 128 bytes (128 consecutive M or N indices of
+// one K index), 8-row groups 1024 bytes apart.  One MMA K step (32 rows) is 4096 bytes further on.
+// The leading byte offset is the distance to the next 128-wide M/N block; tiles here have one block.
+__device__ __forceinline__ uint64_t make_desc_mnmajor_sw128(uint32_t saddr, uint32_t block_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+  d |= (uint64_t)((block_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
 // Scale-factor source for tc_cp_sf: 32 rows x 16 bytes, no swizzle, 8-row
 // groups 128 bytes apart.
 __device__ __forceinline__ uint64_t make_desc_sf(uint32_t saddr) {

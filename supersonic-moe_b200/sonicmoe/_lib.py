@@ -33,9 +33,10 @@ SIGNATURES = {
     "smoe_gemm_gated": (_I, [_P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P, _P]),
     "smoe_gemm_dgated": (_I, [_P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P, _P]),
     "smoe_gemm_dgated_partials": (_L, [_L]),
-    "smoe_gemm_dgated_fused": (_I, [_P] * 15 + [_L, _L, _L, _L, _P, _P]),
+    "smoe_gemm_dgated_fused": (_I, [_P] * 14 + [_L, _L, _L, _L, _P, _P]),
     "smoe_gemm_dgated_fused_partials": (_L, [_L]),
     "smoe_gemm_wgrad": (_I, [_P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _I, _P, _P]),
+    "smoe_gemm_wgrad_mn": (_I, [_P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _I, _I, _P, _P]),
     "smoe_debug_force_bn": (_I, [_I]),
     "smoe_combine": (_I, [_P, _P, _P, _P, _P, _L, _L, _P]),
     "smoe_gather_scores": (_I, [_P, _P, _L, _P, _P]),

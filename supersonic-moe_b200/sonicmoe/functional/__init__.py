@@ -250,12 +250,14 @@ class _UpProjection(torch.autograd.Function):
             else:
                 x_t, x_sf = ops.quant_cols_t(x, x_gather_idx, TKp)
             mg, base = _grad_target(w1, (E, N2, H))
+            out = mg if mg is not None else torch.empty(E, N2, H, dtype=torch.float32, device=dz_q.device)
+            if dz_t is None:     # the row-major dz payload doubles as the MN-major weight-gradient operand
+                ops.gemm_wgrad_mn(dz_q, dz_csf, x_t, x_sf, efo, out, mg is not None, True, False)
+            else:
+                ops.gemm_wgrad(dz_t, dz_csf, x_t, x_sf, efo, out, accumulate=mg is not None)
             if mg is not None:
-                ops.gemm_wgrad(dz_t, dz_csf, x_t, x_sf, efo, mg, accumulate=True)
                 _after_accumulate(base)
             else:
-                out = torch.empty(E, N2, H, dtype=torch.float32, device=dz_q.device)
-                ops.gemm_wgrad(dz_t, dz_csf, x_t, x_sf, efo, out, accumulate=False)
                 dw1 = out.to(w1.dtype)
         dx = None
         if ctx.needs_input_grad[0]:
@@ -330,11 +332,13 @@ class _DownProjection(torch.autograd.Function):
                 dg_q, a_sf = ops.gather_rows_fp8(dout_q, dout_raw, x_gather_idx, TKp, efo[-1:])
             else:
                 dg_q, a_sf = ops.quant_rows_scatter(dout, naept, s_rev, s_scatter_idx, TKp, efo[-1:])
-            if FUSE_DGATED_QUANT and E <= 256:
-                # dz / y1s never exist in bf16: the epilogue emits the e4m3 operands of dgrad, dw1 and dw2
-                dz_q, dz_rsf, dz_t, dz_csf, y1s_t, y1s_sf, dsp = ops.gemm_dgated_fused(
+            y1s_q = None
+            if FUSE_DGATED_QUANT and E <= 256 and I % 256 == 0 and H % 256 == 0:
+                # dz / y1s never exist in bf16: the epilogue emits the e4m3 operands of dgrad, dw1 and dw2,
+                # row-major; the weight-gradient GEMMs read them MN-major (needs 256-multiples of I and H)
+                dz_q, dz_rsf, dz_csf, y1s_q, y1s_sf, dsp = ops.gemm_dgated_fused(
                     dg_q, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, TKp)
-                link["dz"] = (dz_q, dz_rsf, dz_t, dz_csf)
+                link["dz"] = (dz_q, dz_rsf, None, dz_csf)
                 dz = y1s = None
             else:
                 dz, y1s, dsp = ops.gemm_dgated(dg_q, None, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, TKp)
@@ -349,12 +353,14 @@ class _DownProjection(torch.autograd.Function):
             else:
                 dout_t, dout_sf = ops.quant_cols_t(dout, x_gather_idx, TKp)
             mg, base = _grad_target(w2, (E, I, H))
+            out = mg if mg is not None else torch.empty(E, I, H, dtype=torch.float32, device=dout_t.device)
+            if y1s_q is not None:
+                ops.gemm_wgrad_mn(y1s_q, y1s_sf, dout_t, dout_sf, efo, out, mg is not None, True, False)
+            else:
+                ops.gemm_wgrad(y1s_t, y1s_sf, dout_t, dout_sf, efo, out, accumulate=mg is not None)
             if mg is not None:
-                ops.gemm_wgrad(y1s_t, y1s_sf, dout_t, dout_sf, efo, mg, accumulate=True)
                 _after_accumulate(base)
             else:
-                out = torch.empty(E, I, H, dtype=torch.float32, device=y1s_t.device)
-                ops.gemm_wgrad(y1s_t, y1s_sf, dout_t, dout_sf, efo, out, accumulate=False)
                 dw2 = out.transpose(1, 2).to(w2.dtype)
         if dz is not None:
             link["dz"] = ops.quant_iso32(dz)

@@ -271,23 +271,23 @@ def gemm_dgated(dout_q, a_idx, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, rows):
 @_timed
 def gemm_dgated_fused(dg_q, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, rows):
     """GemmDGated with fused operand quantizers.  dg_q u8 [rows,H] (expert-sorted), w2t_q u8 [E,I,H] ->
-    (dz_q [rows,2I], dz row ISA, dz_t [2I,rows], dz col ISA, y1s_t [I,rows], y1s col ISA, ds_partial)."""
+    (dz_q [rows,2I], dz ISA scales for (rows,2I), dz ISA scales for (2I,rows), y1s_q [rows,I], y1s ISA scales for
+    (I,rows), ds_partial).  dz_q / y1s_q stay row-major; gemm_wgrad_mn takes them as they are."""
     _cuda(dg_q, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s)
     K = dg_q.shape[1]
     E, N, _ = w2t_q.shape
     dev = dg_q.device
     parts = lib.smoe_gemm_dgated_fused_partials(N)
     dz_q = torch.empty(rows, 2 * N, dtype=_U8, device=dev)
-    dz_t = torch.empty(2 * N, rows, dtype=_U8, device=dev)
-    y1s_t = torch.empty(N, rows, dtype=_U8, device=dev)
+    y1s_q = torch.empty(rows, N, dtype=_U8, device=dev)
     dz_rsf = torch.empty(isa_bytes(rows, 2 * N), dtype=_U8, device=dev)
     dz_csf = torch.empty(isa_bytes(2 * N, rows), dtype=_U8, device=dev)
     y1s_sf = torch.empty(isa_bytes(N, rows), dtype=_U8, device=dev)
     dsp = torch.zeros(parts, rows, dtype=torch.float32, device=dev)
     check(lib.smoe_gemm_dgated_fused(_p(dg_q), _p(a_sf), _p(w2t_q), _p(w2t_sf), _p(efo), _p(z_q), _p(z_sc), _p(s),
-                                     _p(dz_q), _p(dz_rsf), _p(dz_t), _p(dz_csf), _p(y1s_t), _p(y1s_sf), _p(dsp),
+                                     _p(dz_q), _p(dz_rsf), _p(dz_csf), _p(y1s_q), _p(y1s_sf), _p(dsp),
                                      rows, N, K, E, _p(status_word(dev)), _stream()), "gemm_dgated_fused")
-    return dz_q, dz_rsf, dz_t, dz_csf, y1s_t, y1s_sf, dsp
+    return dz_q, dz_rsf, dz_csf, y1s_q, y1s_sf, dsp
 
 
 @_timed
@@ -300,6 +300,22 @@ def gemm_wgrad(a_t, a_sf, b_t, b_sf, efo, out, accumulate):
     assert out.dtype == torch.float32 and out.shape == (E, M, N)
     check(lib.smoe_gemm_wgrad(_p(a_t), _p(a_sf), _p(b_t), _p(b_sf), _p(efo), _p(out), M, N, TKp, E, int(accumulate),
                               _p(status_word(a_t.device)), _stream()), "gemm_wgrad")
+    return out
+
+
+@_timed
+def gemm_wgrad_mn(a, a_sf, b, b_sf, efo, out, accumulate, a_rowmajor_tk, b_rowmajor_tk):
+    """Weight gradient with either operand kept as u8 [TKp, dim] (row = routed position) instead of [dim, TKp];
+    out f32 [E,M,N] (+)= per-expert products.  Needs M, N multiples of 256."""
+    _cuda(a, a_sf, b, b_sf, efo, out)
+    E, M, N = out.shape
+    TKp = a.shape[0] if a_rowmajor_tk else a.shape[1]
+    assert tuple(a.shape) == ((TKp, M) if a_rowmajor_tk else (M, TKp))
+    assert tuple(b.shape) == ((TKp, N) if b_rowmajor_tk else (N, TKp))
+    assert out.dtype == torch.float32
+    layout = (1 if a_rowmajor_tk else 0) | (2 if b_rowmajor_tk else 0)
+    check(lib.smoe_gemm_wgrad_mn(_p(a), _p(a_sf), _p(b), _p(b_sf), _p(efo), _p(out), M, N, TKp, E, int(accumulate),
+                                 layout, _p(status_word(a.device)), _stream()), "gemm_wgrad_mn")
     return out
 
 

@@ -402,6 +402,37 @@ def test_gemm_wgrad(ops, bn, M, N, tiles):
         torch.testing.assert_close(out[e], init[e].to(DEV) + ref, rtol=1e-4, atol=1e-2 * ref.abs().max().item() + 1e-6)
 
 
+@pytest.mark.parametrize("layout", [1, 2, 3])
+@pytest.mark.parametrize("M,N,tiles", [(256, 256, [1, 0, 2, 1]), (512, 768, [3, 2, 0, 0, 4, 1, 1, 2]), (768, 256, [2, 1, 3])])
+def test_gemm_wgrad_mn_major_operands(ops, layout, M, N, tiles):
+    """Operands kept [TKp, dim] (MN-major for the tensor core) give the bits of the transposed-copy path."""
+    g = torch.Generator().manual_seed(M + N + layout)
+    E = len(tiles)
+    efo = make_efo(tiles)
+    TKp = int(efo[-1]) + 128
+    a_q, a_sc = rand_fp8((M, TKp), g)
+    b_q, b_sc = rand_fp8((N, TKp), g)
+    a_sf, b_sf = Q.pack_isa(a_sc, M, TKp).to(DEV), Q.pack_isa(b_sc, N, TKp).to(DEV)
+    a_d, b_d, efo_d = a_q.to(DEV), b_q.to(DEV), efo.to(DEV)
+    a_in = a_d.t().contiguous() if layout & 1 else a_d
+    b_in = b_d.t().contiguous() if layout & 2 else b_d
+    init = torch.randn(E, M, N, generator=g).to(DEV)
+    for accumulate in (False, True):
+        want = init.clone()
+        ops.gemm_wgrad(a_d, a_sf, b_d, b_sf, efo_d, want, accumulate=accumulate)
+        got = init.clone()
+        ops.gemm_wgrad_mn(a_in, a_sf, b_in, b_sf, efo_d, got, accumulate, bool(layout & 1), bool(layout & 2))
+        torch.cuda.synchronize()
+        ops.check_status(DEV)
+        assert torch.equal(got, want), (accumulate, (got - want).abs().max().item())
+    A, B = deq(a_q, a_sc).to(DEV), deq(b_q, b_sc).to(DEV)
+    for e in range(E):
+        a, b = int(efo[e]), int(efo[e + 1])
+        if b > a:
+            cos, rr = stats(got[e] - init[e], A[:, a:b] @ B[:, a:b].T)
+            assert cos > 0.9999 and rr < 1e-3, (e, cos, rr)
+
+
 @pytest.mark.parametrize("bn", [0, 128])
 @pytest.mark.parametrize("T,H,I,tiles", GATED_SHAPES)
 def test_gemm_dgated_fused_quantizers_match_separate_kernels(ops, T, H, I, tiles, bn):
@@ -422,7 +453,7 @@ def test_gemm_dgated_fused_quantizers_match_separate_kernels(ops, T, H, I, tiles
     lib.smoe_debug_force_bn(bn)
     try:
         dz, y1s, dsp = ops.gemm_dgated(a_in, None, *args)
-        f_dzq, f_rsf, f_dzt, f_csf, f_yt, f_ysf, f_dsp = ops.gemm_dgated_fused(a_in, *args)
+        f_dzq, f_rsf, f_csf, f_yq, f_ysf, f_dsp = ops.gemm_dgated_fused(a_in, *args)
         torch.cuda.synchronize()
         ops.check_status(DEV)
     finally:
@@ -430,8 +461,8 @@ def test_gemm_dgated_fused_quantizers_match_separate_kernels(ops, T, H, I, tiles
     r_q, r_rsf, r_qt, r_csf = ops.quant_iso32(dz)
     r_yt, r_ysf = ops.quant_cols_t(y1s, None, rows)
     n = int(efo[-1])          # rows of real segments (the tail of the allocation is never written)
-    assert torch.equal(f_dzq[:n], r_q[:n]) and torch.equal(f_dzt[:, :n], r_qt[:, :n])
-    assert torch.equal(f_yt[:, :n], r_yt[:, :n])
+    assert torch.equal(f_dzq[:n], r_q[:n]) and torch.equal(f_dzq[:n].t(), r_qt[:, :n])
+    assert torch.equal(f_yq[:n].t(), r_yt[:, :n])
     assert torch.equal(Q.unpack_isa(f_rsf.cpu(), rows, 2 * I)[:n], Q.unpack_isa(r_rsf.cpu(), rows, 2 * I)[:n])
     assert torch.equal(Q.unpack_isa(f_csf.cpu(), 2 * I, rows)[:, :n // 32], Q.unpack_isa(r_csf.cpu(), 2 * I, rows)[:, :n // 32])
     assert torch.equal(Q.unpack_isa(f_ysf.cpu(), I, rows)[:, :n // 32], Q.unpack_isa(r_ysf.cpu(), I, rows)[:, :n // 32])
