@@ -92,6 +92,17 @@ int smoe_quant_rows(const void* x_bf16, int64_t M, int64_t K, void* q, void* raw
 int smoe_quant_rows_gather(const void* x_bf16, const int32_t* idx, const int32_t* valid_rows, int64_t rows, int64_t K,
                            void* q, void* isa_scales, void* stream);
 
+/* Gathered quantizer for both GEMM directions in one pass over 32-row groups of the expert-sorted order:
+ * q_row[r,:] = row-wise 1x32 quantisation of x[idx[r],:] with ISA scales for (rows,K) (what smoe_quant_rows_gather
+ * writes; both pointers may be null to skip it) and q_col[r,:] = the same rows quantised with one scale per column
+ * and 32 consecutive rows, ISA scales for (K,rows) - the bytes of smoe_quant_cols_t, not transposed: the payload
+ * stays [rows,K] and smoe_gemm_wgrad_mn reads it MN-major.  Rows at or beyond *valid_rows are left untouched.
+ * Replaces dual_quantize_and_pack with gather_idx and dual_quantize_varlen
+ * (sonicmoe/quack_utils/blockscaled_fp8_gemm.py:1428-1500, :1964-2148), whose column-quantised payload is likewise
+ * kept (TK, dim).  K % 256 == 0, rows % 128 == 0. */
+int smoe_quant_dual_gather(const void* x_bf16, const int32_t* idx, const int32_t* valid_rows, int64_t rows, int64_t K,
+                           void* q_row, void* row_isa, void* q_col, void* col_isa, void* stream);
+
 /* Same result in scatter form: every token row of x [T,K] is read and quantised once and written to each
  * expert-sorted position it occupies, s_rev[naept[t] .. naept[t+1]); pad rows (s_scatter_idx[row] >= naept[T]) are
  * zero-filled (the gather form copies token 0 there; either way they are multiplied by a zero score downstream).

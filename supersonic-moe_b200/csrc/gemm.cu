@@ -111,7 +111,7 @@ static int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
   int64_t pairs = sm_count() / 2;
   if (max_pair_tiles < pairs) pairs = max_pair_tiles;
   if (pairs <= 0) return SMOE_OK;
-  kern<<<(unsigned)(2 * pairs), kThreads2, S::TOTAL, stream>>>(ta, tb, tsa, tsb, om.c, om.c2, om.c3, p);
+  kern<<<(unsigned)(2 * pairs), S::THREADS, S::TOTAL, stream>>>(ta, tb, tsa, tsb, om.c, om.c2, om.c3, p);
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }
 
@@ -119,7 +119,7 @@ static int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
 template <int MODE>
 static int pick_bn2(int64_t N) {
   if (g_force_v1) return 0;
-  const bool wide = (MODE == PLAIN || MODE == WGRAD);      // single-stage 256-column tiles
+  const bool wide = (MODE == PLAIN || MODE == WGRAD || MODE == GATED);      // single-stage 256-column tiles
   if (MODE == DGATEDQ) return (N % 192 == 0 && g_force_bn != 128) ? 192 : 128;
   if (g_force_bn == 128) return 128;
   if (g_force_bn == 192) return (N % 192 == 0) ? 192 : 128;
@@ -146,7 +146,7 @@ static int run2(const void* a, int64_t a_rows, int64_t a_cols, const void* b, in
   if (MODE == WGRAD) pair_tiles = (int64_t)p.E * (p.rows / 256) * (p.N / bn);
   else pair_tiles = ((int64_t)p.rows / 256 + p.E) * (p.N / bn);
   if (bn == 256) {
-    constexpr int M256 = (MODE == PLAIN || MODE == WGRAD) ? MODE : PLAIN;   // only the wide modes reach here
+    constexpr int M256 = (MODE == PLAIN || MODE == WGRAD || MODE == GATED) ? MODE : PLAIN;   // only the wide modes reach here
     return launch2<256, M256>(ta, tb, tsa, tsb, om, p, pair_tiles, stream);
   }
   if (bn == 192) return launch2<192, MODE>(ta, tb, tsa, tsb, om, p, pair_tiles, stream);
@@ -218,7 +218,7 @@ extern "C" {
 
 int smoe_debug_force_bn(int bn) {
   g_force_bn = bn & 0xFFFF;
-  g_skip_store = (bn >> 16) & 1;
+  g_skip_store = ((bn >> 16) & 1) | (((bn >> 18) & 7) << 1);   // bit 16: no stores; bits 18-20: timing experiments
   g_force_v1 = (bn >> 17) & 1;
   return SMOE_OK;
 }
@@ -276,10 +276,14 @@ int smoe_gemm_dgated_fused(const void* dout_fp8, const void* a_sf, const void* w
   p.z_fp8 = (uint8_t*)const_cast<void*>(z_fp8); p.z_sc = (uint8_t*)const_cast<void*>(z_scales);
   p.s = s; p.dz = dz_q; p.y1s = y1s_q; p.ds_partial = ds_partial; p.status = status;
   p.dz_row_sf = (uint8_t*)dz_row_sf; p.dz_col_sf = (uint8_t*)dz_col_sf; p.y1s_col_sf = (uint8_t*)y1s_col_sf;
+  p.debug_skip_store = g_skip_store;
   return run<DGATEDQ>(dout_fp8, rows, K, w2t_fp8, E * N, K, p, (int)((rows / 128) * (N / 128)), (cudaStream_t)stream);
 }
 
-int64_t smoe_gemm_dgated_fused_partials(int64_t N) { return 2 * (N / pick_bn2<DGATEDQ>(N)); }
+int64_t smoe_gemm_dgated_fused_partials(int64_t N) {
+  const int bn = pick_bn2<DGATEDQ>(N);
+  return (bn == 192 ? Gemm2Smem<192, DGATEDQ>::COL_GROUPS : Gemm2Smem<128, DGATEDQ>::COL_GROUPS) * (N / bn);
+}
 
 int64_t smoe_gemm_dgated_partials(int64_t N) {
   const int bn2 = pick_bn2<DGATED>(N);

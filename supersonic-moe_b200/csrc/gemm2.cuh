@@ -91,6 +91,12 @@ __device__ __forceinline__ float fast_sigmoid(float x) {
   return r;
 }
 
+// element-wise max of two bf16 pairs
+__device__ __forceinline__ uint32_t max_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
 // max |x| over the warp, delivered to every lane
 __device__ __forceinline__ float warp_max_abs(float x) {
   float r;
@@ -115,7 +121,12 @@ struct Gemm2Smem {
   // DGATED 4 KB (dz) + 2 KB (y1s), GATED 2 KB (z e4m3 32x64) + 1 KB (y1 e4m3 32x32)
   // DGATEDQ 2 KB (dz e4m3 32x64) + 1 KB (y1s e4m3 32x32)
   static constexpr int EPI_BYTES_PER_WARP = MODE == GATED ? 3072 : (MODE == DGATED ? 6144 : (MODE == DGATEDQ ? 3072 : 2048));
-  static constexpr int EPI_BYTES = kEpiWarps2 * EPI_BYTES_PER_WARP;
+  // epilogue warps: four TMEM lane quadrants x COL_GROUPS column groups.  (Three groups of 64 columns on the
+  // 192-column gated tiles measured slower than two: 646 vs 619 us up-projection, 412 vs 385 us fused dgated.)
+  static constexpr int COL_GROUPS = 2;
+  static constexpr int EPI_WARPS = 4 * COL_GROUPS;
+  static constexpr int THREADS = 32 * (2 + EPI_WARPS);
+  static constexpr int EPI_BYTES = EPI_WARPS * EPI_BYTES_PER_WARP;
   static constexpr int AUX_BYTES = 1024 + 2 * (kMaxExperts2 + 1) * 4;
   static constexpr int STAGES_RAW = (227 * 1024 - 1024 - AUX_BYTES - EPI_BYTES - SF_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
@@ -171,7 +182,7 @@ __device__ __forceinline__ PairTile pair_tile(int tile, int rank, const GemmPara
 }
 
 template <int BN, int MODE>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((Gemm2Smem<BN, MODE>::THREADS), 1)
 gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                   const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                   const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_c2,
@@ -216,7 +227,7 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_tfull + 8 * s, 1);                   // commit arrival, in each CTA
-      mbar_init(bar_tempty + 8 * s, 2 * kEpiWarps2);     // leader's: the epilogue warps of both CTAs
+      mbar_init(bar_tempty + 8 * s, 2 * S::EPI_WARPS);     // leader's: the epilogue warps of both CTAs
     }
     for (int s = 0; s < S::SF_SLOTS; ++s) {
       mbar_init(bar_sffull + 8 * s, 1);                  // leader's: armed by its producer, credited by both CTAs
@@ -357,11 +368,11 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------ epilogue (8 warps per CTA)
+    // ------------------------------------------------------------ epilogue (8 or 12 warps per CTA)
     const int q = warp & 3;                       // TMEM lane quadrant of this warp
-    const int half = (warp - 2) >> 2;             // which half of the tile's columns
+    const int half = (warp - 2) >> 2;             // which group of the tile's columns
     const int row_in_tile = q * 32 + lane;
-    constexpr int COLS_PER_WARP = BN / 2;
+    constexpr int COLS_PER_WARP = BN / S::COL_GROUPS;
     const uint32_t stg = smem_u32(epi + (warp - 2) * S::EPI_BYTES_PER_WARP);
     const uint32_t tempty0 = map_to_cta(bar_tempty, 0);
     int as = 0;
@@ -378,6 +389,19 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           for (int i = 0; i < COLS_PER_WARP / 4; ++i) dst[i] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
         continue;
+      }
+      // DGATEDQ: the first chunk of z and the row's score are fetched before the wait for the accumulator,
+      // so their latency hides behind this tile's main loop
+      uint4 zb[4];
+      uint32_t sc = 0;
+      float s_row = 0.f;
+      if (MODE == DGATEDQ && t.valid) {
+        const int Nz = 2 * p.N;
+        const uint8_t* zrow = p.z_fp8 + grow * Nz + 2 * c_base;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) zb[i] = reinterpret_cast<const uint4*>(zrow)[i];
+        sc = *reinterpret_cast<const uint16_t*>(p.z_sc + grow * (Nz / 32) + (2 * c_base) / 32);
+        s_row = p.s[grow];
       }
       if (lane == 0) ok = mbar_wait(bar_tfull + 8 * as, aphase);
       ok = __shfl_sync(0xffffffff, ok, 0);
@@ -454,15 +478,29 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           }
         }
       } else if (MODE == GATED) {
-        // 64-column chunks of z (= 32 columns of y1 = one y1 scale group).  BN = 128: one chunk per warp;
-        // BN = 192: the first warp of a quadrant takes chunks 0 and 1, the second takes chunk 2.
-        static_assert(MODE != GATED || BN == 128 || BN == 192, "GATED column tiles");
+        // 64-column chunks of z (= 32 columns of y1 = one y1 scale group), dealt to the column groups in order;
+        // BN = 192 with two groups: the first takes chunks 0 and 1, the second chunk 2.
+        // BN = 256 has a single accumulator stage: the warp first drains its 128 columns into registers and
+        // hands the accumulator back, so the next tile's MMAs run under the arithmetic below.
+        constexpr int CHUNKS = BN / 64, PER = (CHUNKS + S::COL_GROUPS - 1) / S::COL_GROUPS;
+        constexpr bool DRAIN = (S::ACC_STAGES == 1);
         const int Nz = p.N, Ny = p.N / 2;
-        const int ch0 = (BN == 128) ? half : (half == 0 ? 0 : 2);
-        const int nch = (BN == 128) ? 1 : (half == 0 ? 2 : 1);
+        const int ch0 = half * PER;
+        const int nch = min(PER, CHUNKS - ch0);
         const uint32_t t_tile = tmem_base + ((uint32_t)(q * 32) << 16) + as * BN;
-#pragma unroll 1
-        for (int ci = 0; ci < nch; ++ci) {
+        uint32_t acc[DRAIN ? PER * 2 : 1][32];
+        if (DRAIN) {
+#pragma unroll
+          for (int c = 0; c < PER * 2; ++c) tmem_ld32(t_tile + ch0 * 64 + c * 32, acc[DRAIN ? c : 0]);
+          tmem_ld_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * as);
+          released = true;
+        }
+#pragma unroll
+        for (int ci = 0; ci < PER; ++ci) {
+          if (ci >= nch) break;
           const int zc = t.n0 + (ch0 + ci) * 64;           // first z column of the chunk
           float y[32];
           uint32_t zs = 0;
@@ -471,9 +509,12 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           __syncwarp();
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            uint32_t r[32];
-            tmem_ld32(t_tile + (ch0 + ci) * 64 + h * 32, r);
-            tmem_ld_wait();
+            uint32_t rl[32];
+            if (!DRAIN) {
+              tmem_ld32(t_tile + (ch0 + ci) * 64 + h * 32, rl);
+              tmem_ld_wait();
+            }
+            const uint32_t* r = DRAIN ? acc[DRAIN ? ci * 2 + h : 0] : rl;
             float amax = 0.f;
 #pragma unroll
             for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(__uint_as_float(r[i])));
@@ -531,21 +572,13 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         // per column and 32 rows - and leave as e4m3 in row-major order.  A 32x32-block scale serves dz both as
         // the activation-gradient operand (scales along 2I) and as the weight-gradient operand (scales along
         // TKp, fed MN-major), so one copy of the payload is enough.  Each warp works on its own.
-        if (t.valid) {
+        if (t.valid && !(p.debug_skip_store & 2)) {
           const int Nz = 2 * p.N;
-          const float s = p.s[grow];
+          const float s = s_row;
           const int row_grp = (t.m0 + q * 32) >> 5;      // 32-row group index along TKp
           const int kt_rows = p.rows >> 7;               // K tiles of the weight-gradient operands
           constexpr int NCH = COLS_PER_WARP / 32;
           float ds_acc = 0.f;
-          uint4 zb[4];
-          uint32_t sc;
-          {
-            const uint8_t* zrow = p.z_fp8 + grow * Nz + 2 * c_base;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) zb[i] = reinterpret_cast<const uint4*>(zrow)[i];
-            sc = *reinterpret_cast<const uint16_t*>(p.z_sc + grow * (Nz / 32) + (2 * c_base) / 32);
-          }
 #pragma unroll 1
           for (int c = 0; c < NCH; ++c) {
             const int dcol = c_base + c * 32;            // first D / y1s column of the chunk
@@ -566,31 +599,37 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             const float sc1 = __int_as_float((int)(sc >> 8) << 23);
             tmem_ld_wait();
             const uint32_t* zw = reinterpret_cast<const uint32_t*>(zb);
-            float ys[32];
+            uint32_t Y[16];                              // y1s of this lane's row, bf16 pairs of adjacent columns
             uint32_t w[16];
             uint32_t e_blk = 0;
 #pragma unroll
             for (int b = 0; b < 2; ++b) {
               float v[32];
               float amax = 0.f;
+              const float scale = b ? sc1 : sc0;
 #pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                const int pi = b * 16 + i;
-                const uint32_t pair = (zw[pi >> 1] >> (16 * (pi & 1))) & 0xFFFF;
-                const float scale = b ? sc1 : sc0;
-                const float2 gu = e4m3x2_to_f32(pair);
-                const float g = gu.x * scale, u = gu.y * scale;
-                const float D = __uint_as_float(r[pi]);
-                const float dout = s * D;
-                const float sig = fast_sigmoid(g);
-                const float silu = g * sig;
-                const float sd = silu * dout;
-                const float yv = silu * u;
-                ds_acc = fmaf(yv, D, ds_acc);
-                v[2 * i] = bf16_rne(((sig - silu * sig) * dout + sd) * u);
-                v[2 * i + 1] = bf16_rne(sd);
-                ys[pi] = bf16_rne(s * yv);
-                amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
+              for (int i2 = 0; i2 < 8; ++i2) {
+                float yq[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                  const int pi = b * 16 + 2 * i2 + h;
+                  const uint32_t pair = (zw[pi >> 1] >> (16 * (pi & 1))) & 0xFFFF;
+                  const float2 gu = e4m3x2_to_f32(pair);
+                  const float g = gu.x * scale, u = gu.y * scale;
+                  const float D = __uint_as_float(r[pi]);
+                  const float dout = s * D;
+                  const float sig = fast_sigmoid(g);
+                  const float silu = g * sig;
+                  const float sd = silu * dout;
+                  const float yv = silu * u;
+                  ds_acc = fmaf(yv, D, ds_acc);
+                  const uint32_t dzp = pack_bf16x2(((sig - silu * sig) * dout + sd) * u, sd);   // rounds to bf16
+                  v[4 * i2 + 2 * h] = __uint_as_float(dzp << 16);
+                  v[4 * i2 + 2 * h + 1] = __uint_as_float(dzp & 0xFFFF0000u);
+                  yq[h] = s * yv;
+                  amax = fmaxf(amax, fmaxf(fabsf(v[4 * i2 + 2 * h]), fabsf(v[4 * i2 + 2 * h + 1])));
+                }
+                Y[b * 8 + i2] = pack_bf16x2(yq[0], yq[1]);
               }
               const int e = e8m0_of(warp_max_abs(amax));
               const float qs = qscale_of(e);
@@ -599,17 +638,33 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
               for (int i = 0; i < 8; ++i)
                 w[8 * b + i] = pack_e4m3x4(v[4 * i] * qs, v[4 * i + 1] * qs, v[4 * i + 2] * qs, v[4 * i + 3] * qs);
             }
-            // y1s: one scale per column over the warp's 32 rows
+            // y1s: one scale per column over the warp's 32 rows.  Column maxima by a butterfly on bf16 pairs that
+            // halves the column set at each step: lane L ends with the pair holding column L.
+            uint32_t A[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) A[i] = Y[i] & 0x7FFF7FFFu;
+#pragma unroll
+            for (int sft = 16; sft >= 2; sft >>= 1) {
+              const bool up = (lane & sft) != 0;
+#pragma unroll
+              for (int i = 0; i < sft / 2; ++i) {
+                const uint32_t send = up ? A[i] : A[i + sft / 2];
+                const uint32_t keep = up ? A[i + sft / 2] : A[i];
+                A[i] = max_bf16x2(keep, __shfl_xor_sync(0xffffffff, send, sft));
+              }
+            }
+            A[0] = max_bf16x2(A[0], __shfl_xor_sync(0xffffffff, A[0], 1));
+            const int e_mine = e8m0_of(__uint_as_float((lane & 1) ? (A[0] & 0xFFFF0000u) : (A[0] << 16)));
+            const float qs_mine = qscale_of(e_mine);
             uint32_t wy[8];
-            int e_mine = 0;                              // lane L keeps the scale of column L
 #pragma unroll
             for (int i4 = 0; i4 < 8; ++i4) {
               float qv[4];
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
-                const int e = e8m0_of(warp_max_abs(ys[4 * i4 + j]));
-                if (lane == 4 * i4 + j) e_mine = e;
-                qv[j] = ys[4 * i4 + j] * qscale_of(e);
+                const int cc = 4 * i4 + j;
+                const float yv = __uint_as_float((cc & 1) ? (Y[cc >> 1] & 0xFFFF0000u) : (Y[cc >> 1] << 16));
+                qv[j] = yv * __shfl_sync(0xffffffff, qs_mine, cc);
               }
               wy[i4] = pack_e4m3x4(qv[0], qv[1], qv[2], qv[3]);
             }
@@ -625,6 +680,7 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                            wy[4 * j + 2], wy[4 * j + 3]);
             fence_proxy_async_smem();
             __syncwarp();
+            if (p.debug_skip_store & 1) continue;
             if (lane == 0) {
               tma_store_2d(&tmap_c, stg, 2 * dcol, t.m0 + q * 32);          // dz e4m3 [TKp, 2I]
               tma_store_2d(&tmap_c2, stg + 2048, dcol, t.m0 + q * 32);      // y1s e4m3 [TKp, I]
@@ -648,7 +704,7 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             for (int i = 0; i < 4; ++i) zb[i] = zn[i];
             sc = scn;
           }
-          p.ds_partial[(size_t)((t.n0 / BN) * 2 + half) * p.rows + grow] = ds_acc;
+          p.ds_partial[(size_t)((t.n0 / BN) * S::COL_GROUPS + half) * p.rows + grow] = ds_acc;
         }
       } else {  // DGATED
         // this warp: D columns [c_base, c_base + BN/2) of I in chunks of 32 -> dz 64 bf16 (128-byte rows,

@@ -331,6 +331,78 @@ quant_cols_kernel(const void* __restrict__ src_, const uint8_t* __restrict__ src
 
 using namespace smoe;
 
+// ------------------------------------------------- gathered rows, both directions
+// One warp owns 32 consecutive expert-sorted rows x 256 columns (a lane: 8 columns of every row, 32 x 16-byte
+// loads in flight).  Column scales (one per column and 32 rows) need no communication at all, row scales
+// (one per row and 32 columns) two shuffles per row.  Both payloads leave row-major: the column-scaled one is a
+// weight-gradient operand read MN-major by the tensor core, so no transposed copy is written.
+template <bool WITH_ROWS>
+__global__ void __launch_bounds__(128)
+quant_dual_kernel(const uint4* __restrict__ x, const int* __restrict__ idx, const int* __restrict__ valid_rows,
+                  int64_t rows, int K, uint2* __restrict__ q_row, uint8_t* __restrict__ row_isa,
+                  uint2* __restrict__ q_col, uint8_t* __restrict__ col_isa) {
+  const int lane = threadIdx.x & 31;
+  const int64_t task = blockIdx.x * (int64_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int cbs = K >> 8;
+  const int64_t rg = task / cbs;
+  const int cb = (int)(task - rg * cbs);
+  const int64_t r0 = rg * 32;
+  int64_t limit = rows;
+  if (valid_rows) limit = min(limit, (int64_t)*valid_rows);
+  if (r0 >= limit) return;
+  const int col0 = cb * 256 + lane * 8;
+  const int64_t my_row = idx ? (int64_t)idx[r0 + lane] : r0 + lane;
+  uint4 v[32];
+#pragma unroll
+  for (int r = 0; r < 32; ++r) {
+    const int64_t srow = __shfl_sync(0xffffffff, my_row, r);
+    v[r] = x[(srow * K + col0) >> 3];
+  }
+  float cam[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) cam[j] = 0.f;
+  const size_t row_kt = (size_t)((K + 127) >> 7);
+#pragma unroll
+  for (int r = 0; r < 32; ++r) {
+    float f[8];
+    bf16x8_to_f32(v[r], f);
+    float ram = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      cam[j] = fmaxf(cam[j], fabsf(f[j]));
+      ram = fmaxf(ram, fabsf(f[j]));
+    }
+    if (WITH_ROWS) {
+      ram = fmaxf(ram, __shfl_xor_sync(0xffffffff, ram, 1));
+      ram = fmaxf(ram, __shfl_xor_sync(0xffffffff, ram, 2));
+      const int e = q_e8m0_of(ram);
+      const float qs = q_scale_of(e);
+      uint2 o;
+      o.x = q_pack4(f[0] * qs, f[1] * qs, f[2] * qs, f[3] * qs);
+      o.y = q_pack4(f[4] * qs, f[5] * qs, f[6] * qs, f[7] * qs);
+      q_row[((r0 + r) * K + col0) >> 3] = o;
+      if ((lane & 3) == 0) row_isa[isa_offset((size_t)(r0 + r), (size_t)(col0 >> 5), row_kt)] = (uint8_t)e;
+    }
+  }
+  float qs[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int e = q_e8m0_of(cam[j]);
+    qs[j] = q_scale_of(e);
+    col_isa[isa_offset((size_t)(col0 + j), (size_t)rg, (size_t)(rows >> 7))] = (uint8_t)e;
+  }
+#pragma unroll
+  for (int r = 0; r < 32; ++r) {
+    float f[8];
+    bf16x8_to_f32(v[r], f);
+    uint2 o;
+    o.x = q_pack4(f[0] * qs[0], f[1] * qs[1], f[2] * qs[2], f[3] * qs[3]);
+    o.y = q_pack4(f[4] * qs[4], f[5] * qs[5], f[6] * qs[6], f[7] * qs[7]);
+    q_col[((r0 + r) * K + col0) >> 3] = o;
+  }
+}
+
+
 extern "C" {
 
 int smoe_quant_rows(const void* x_bf16, int64_t M, int64_t K, void* q, void* raw_scales, void* isa_scales,
@@ -429,6 +501,23 @@ int smoe_quant_iso32(const void* x_bf16, int64_t rows, int64_t cols, void* q, vo
   quant_cols_kernel<true, false><<<grid, 256, 0, (cudaStream_t)stream>>>(x_bf16, nullptr, nullptr, rows, (int)cols,
                                                                          (uint8_t*)q_t, (uint8_t*)col_isa, (uint8_t*)q,
                                                                          (uint8_t*)row_isa);
+  return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
+}
+
+int smoe_quant_dual_gather(const void* x_bf16, const int32_t* idx, const int32_t* valid_rows, int64_t rows, int64_t K,
+                           void* q_row, void* row_isa, void* q_col, void* col_isa, void* stream) {
+  if (rows < 0 || rows % 128 || K <= 0 || K % 256) return SMOE_ERR_SHAPE;
+  if (!q_col || !col_isa || ((q_row == nullptr) != (row_isa == nullptr))) return SMOE_ERR_ARG;
+  if (rows == 0) return SMOE_OK;
+  const int64_t tasks = (rows / 32) * (K / 256);
+  const unsigned blocks = (unsigned)((tasks + 3) / 4);
+  if (q_row)
+    quant_dual_kernel<true><<<blocks, 128, 0, (cudaStream_t)stream>>>(
+        (const uint4*)x_bf16, idx, valid_rows, rows, (int)K, (uint2*)q_row, (uint8_t*)row_isa, (uint2*)q_col,
+        (uint8_t*)col_isa);
+  else
+    quant_dual_kernel<false><<<blocks, 128, 0, (cudaStream_t)stream>>>(
+        (const uint4*)x_bf16, idx, valid_rows, rows, (int)K, nullptr, nullptr, (uint2*)q_col, (uint8_t*)col_isa);
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }
 

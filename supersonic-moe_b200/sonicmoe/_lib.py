@@ -23,6 +23,7 @@ SIGNATURES = {
     "smoe_topk_metadata_static_capacity": (_L, []),
     "smoe_quant_rows": (_I, [_P, _L, _L, _P, _P, _P, _P]),
     "smoe_quant_rows_gather": (_I, [_P, _P, _P, _L, _L, _P, _P, _P]),
+    "smoe_quant_dual_gather": (_I, [_P, _P, _P, _L, _L, _P, _P, _P, _P, _P]),
     "smoe_quant_rows_scatter": (_I, [_P, _L, _L, _P, _P, _P, _P, _L, _P, _P, _P]),
     "smoe_gather_scales_isa": (_I, [_P, _P, _L, _L, _P, _P]),
     "smoe_gather_rows_fp8": (_I, [_P, _P, _P, _P, _L, _L, _P, _P, _P]),

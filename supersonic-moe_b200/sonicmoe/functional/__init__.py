@@ -89,6 +89,19 @@ USE_TMA_GATHER = os.getenv("SONIC_MOE_TMA_GATHER", "0") == "1"
 FUSE_DGATED_QUANT = os.getenv("SONIC_MOE_FUSE_DGATED_QUANT", "1") == "1"
 
 
+def _mn_wgrad_ok(E: int, M: int, N: int) -> bool:
+    """Shapes the weight-gradient GEMM accepts with operands left [TKp, dim] (MN-major)."""
+    return E <= 256 and M % 256 == 0 and N % 256 == 0
+
+
+def _wgrad(a, a_sf, a_rows_tk, b, b_sf, b_rows_tk, efo, out, accumulate):
+    """out[e] (+)= A_e^T B_e over expert e's rows; either operand is [dim, TKp] or, *_rows_tk, [TKp, dim]."""
+    if a_rows_tk or b_rows_tk:
+        ops.gemm_wgrad_mn(a, a_sf, b, b_sf, efo, out, accumulate, a_rows_tk, b_rows_tk)
+    else:
+        ops.gemm_wgrad(a, a_sf, b, b_sf, efo, out, accumulate=accumulate)
+
+
 # ----------------------------------------------------------------------------
 # FP8 weight cache (four row-wise 1x32 layouts, refreshed when a weight's
 # version counter moves, i.e. once per optimizer step)
@@ -245,16 +258,18 @@ class _UpProjection(torch.autograd.Function):
         TKp = dz_q.shape[0]
         dw1 = None
         if ctx.needs_input_grad[1]:
+            mn = _mn_wgrad_ok(E, N2, H)
             if ctx.x_is_fp8:     # x is e4m3 + raw scales: dequantise, then column-wise re-quantise
-                x_t, x_sf = ops.requant_cols_t(x, x_raw, x_gather_idx, TKp)
+                xc, x_sf, xc_rows = *ops.requant_cols_t(x, x_raw, x_gather_idx, TKp), False
+            elif mn:             # column scales, payload left [TKp, H]
+                _, _, xc, x_sf = ops.quant_dual_gather(x, x_gather_idx, TKp, efo[-1:], with_rows=False)
+                xc_rows = True
             else:
-                x_t, x_sf = ops.quant_cols_t(x, x_gather_idx, TKp)
+                xc, x_sf, xc_rows = *ops.quant_cols_t(x, x_gather_idx, TKp), False
             mg, base = _grad_target(w1, (E, N2, H))
             out = mg if mg is not None else torch.empty(E, N2, H, dtype=torch.float32, device=dz_q.device)
-            if dz_t is None:     # the row-major dz payload doubles as the MN-major weight-gradient operand
-                ops.gemm_wgrad_mn(dz_q, dz_csf, x_t, x_sf, efo, out, mg is not None, True, False)
-            else:
-                ops.gemm_wgrad(dz_t, dz_csf, x_t, x_sf, efo, out, accumulate=mg is not None)
+            # a row-major dz payload (32x32-block scales) doubles as the MN-major weight-gradient operand
+            _wgrad(dz_q if dz_t is None else dz_t, dz_csf, dz_t is None, xc, x_sf, xc_rows, efo, out, mg is not None)
             if mg is not None:
                 _after_accumulate(base)
             else:
@@ -323,6 +338,7 @@ class _DownProjection(torch.autograd.Function):
             dout_q = dout_raw = None
             if USE_TMA_GATHER:
                 dout_q, dout_raw, _ = ops.quant_rows(dout, raw=True)
+        y1s_q = dout_c = None
         w2t_q, w2t_sf = weight_fp8(w2, True)
         if USE_TMA_GATHER:
             a_sf = ops.gather_scales_isa(dout_raw, x_gather_idx, TKp, H)
@@ -331,9 +347,12 @@ class _DownProjection(torch.autograd.Function):
             if dout_q is not None:
                 dg_q, a_sf = ops.gather_rows_fp8(dout_q, dout_raw, x_gather_idx, TKp, efo[-1:])
             else:
+                # row scales in scatter form (each token read once: 68 us on T=8192, H=3072, K=8), column scales
+                # in a second, gathered pass (93 us); the one-pass dual kernel measured 209 us there
                 dg_q, a_sf = ops.quant_rows_scatter(dout, naept, s_rev, s_scatter_idx, TKp, efo[-1:])
-            y1s_q = None
-            if FUSE_DGATED_QUANT and E <= 256 and I % 256 == 0 and H % 256 == 0:
+                if ctx.needs_input_grad[2] and _mn_wgrad_ok(E, I, H):
+                    _, _, dout_c, dout_sf = ops.quant_dual_gather(dout, x_gather_idx, TKp, efo[-1:], with_rows=False)
+            if FUSE_DGATED_QUANT and _mn_wgrad_ok(E, I, H):
                 # dz / y1s never exist in bf16: the epilogue emits the e4m3 operands of dgrad, dw1 and dw2,
                 # row-major; the weight-gradient GEMMs read them MN-major (needs 256-multiples of I and H)
                 dz_q, dz_rsf, dz_csf, y1s_q, y1s_sf, dsp = ops.gemm_dgated_fused(
@@ -348,16 +367,15 @@ class _DownProjection(torch.autograd.Function):
         if ctx.needs_input_grad[2]:
             if y1s is not None:
                 y1s_t, y1s_sf = ops.quant_cols_t(y1s, None, TKp)
-            if dout is None:
-                dout_t, dout_sf = ops.requant_cols_t(dout_q, dout_raw, x_gather_idx, TKp)
-            else:
-                dout_t, dout_sf = ops.quant_cols_t(dout, x_gather_idx, TKp)
+            if dout_c is None:
+                if dout is None:
+                    dout_t, dout_sf = ops.requant_cols_t(dout_q, dout_raw, x_gather_idx, TKp)
+                else:
+                    dout_t, dout_sf = ops.quant_cols_t(dout, x_gather_idx, TKp)
             mg, base = _grad_target(w2, (E, I, H))
-            out = mg if mg is not None else torch.empty(E, I, H, dtype=torch.float32, device=dout_t.device)
-            if y1s_q is not None:
-                ops.gemm_wgrad_mn(y1s_q, y1s_sf, dout_t, dout_sf, efo, out, mg is not None, True, False)
-            else:
-                ops.gemm_wgrad(y1s_t, y1s_sf, dout_t, dout_sf, efo, out, accumulate=mg is not None)
+            out = mg if mg is not None else torch.empty(E, I, H, dtype=torch.float32, device=s.device)
+            _wgrad(y1s_q if y1s_q is not None else y1s_t, y1s_sf, y1s_q is not None,
+                   dout_c if dout_c is not None else dout_t, dout_sf, dout_c is not None, efo, out, mg is not None)
             if mg is not None:
                 _after_accumulate(base)
             else:

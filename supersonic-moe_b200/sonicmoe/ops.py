@@ -146,6 +146,23 @@ def quant_rows_gather(x, idx, rows, valid_rows=None):
 
 
 @_timed
+def quant_dual_gather(x, idx, rows, valid_rows=None, with_rows=True):
+    """bf16 [T,K] -> gathered rows x[idx] quantised row-wise (e4m3 [rows,K] + ISA scales of (rows,K); skipped when
+    with_rows is false) and column-wise (e4m3 [rows,K], not transposed, + ISA scales of (K,rows))."""
+    _cuda(x, idx, valid_rows)
+    assert x.dtype == torch.bfloat16 and x.ndim == 2
+    K = x.shape[1]
+    dev = x.device
+    q_row = torch.empty(rows, K, dtype=_U8, device=dev) if with_rows else None
+    row_isa = torch.empty(isa_bytes(rows, K), dtype=_U8, device=dev) if with_rows else None
+    q_col = torch.empty(rows, K, dtype=_U8, device=dev)
+    col_isa = torch.empty(isa_bytes(K, rows), dtype=_U8, device=dev)
+    check(lib.smoe_quant_dual_gather(_p(x), _p(idx), _p(valid_rows), rows, K, _p(q_row), _p(row_isa), _p(q_col),
+                                     _p(col_isa), _stream()), "quant_dual_gather")
+    return q_row, row_isa, q_col, col_isa
+
+
+@_timed
 def quant_rows_scatter(x, naept, s_rev, s_scatter_idx, rows, valid_rows=None):
     """bf16 [T,K] -> (e4m3 rows in expert-sorted order [rows,K], ISA scales of (rows,K)); each token is
     quantised once and written to all its positions; pad rows are zero."""

@@ -293,6 +293,32 @@ def _force(mode):
     lib.smoe_debug_force_bn((1 << 17) if mode.endswith("_1cta") else 0)
 
 
+@pytest.mark.parametrize("T,H,I,tiles", GATED_SHAPES)
+def test_gemm_gated_same_bytes_for_every_column_tile(ops, T, H, I, tiles):
+    """128-, 192- and 256-column tiles (two accumulator stages vs. one drained into registers) agree bit for bit."""
+    from sonicmoe._lib import lib
+    g, E, efo, rows, x, w1, a_idx = gated_inputs(T, H, I, tiles, 11)
+    xq, xs = Q.row_quant(x)
+    wq, ws = Q.row_quant(w1.reshape(E * 2 * I, H))
+    args = (xq[a_idx.long()].contiguous().to(DEV), None, Q.gather_scales_to_isa(xs, a_idx, H).to(DEV),
+            wq.reshape(E, 2 * I, H).to(DEV), Q.pack_isa(ws, E * 2 * I, H).to(DEV), efo.to(DEV), rows)
+    outs = {}
+    for bn in (128, 192, 256):
+        lib.smoe_debug_force_bn(bn)
+        try:
+            outs[bn] = ops.gemm_gated(*args)
+            torch.cuda.synchronize()
+            ops.check_status(DEV)
+        finally:
+            lib.smoe_debug_force_bn(0)
+    n = int(efo[-1])
+    for bn in (192, 256):
+        for got, want in zip(outs[bn], outs[128]):
+            if got.ndim == 2:
+                assert torch.equal(got[:n], want[:n]), bn
+        assert torch.equal(Q.unpack_isa(outs[bn][3].cpu(), rows, I)[:n], Q.unpack_isa(outs[128][3].cpu(), rows, I)[:n])
+
+
 @pytest.mark.parametrize("mode", GATHER_MODES)
 @pytest.mark.parametrize("T,H,I,tiles", GATED_SHAPES)
 def test_gemm_gated(ops, T, H, I, tiles, mode):
@@ -400,6 +426,32 @@ def test_gemm_wgrad(ops, bn, M, N, tiles):
         else:
             assert (fresh[e] == 0).all()
         torch.testing.assert_close(out[e], init[e].to(DEV) + ref, rtol=1e-4, atol=1e-2 * ref.abs().max().item() + 1e-6)
+
+
+@pytest.mark.parametrize("T,K,rows,valid", [(64, 256, 256, 256), (300, 768, 1024, 896), (128, 512, 384, 128)])
+def test_quant_dual_gather_matches_single_direction_kernels(ops, T, K, rows, valid):
+    """One pass over gathered rows = the bytes of quant_rows_gather (row-wise) and quant_cols_t (column-wise)."""
+    g = torch.Generator().manual_seed(T + K)
+    x = (torch.randn(T, K, generator=g) * torch.exp(2 * torch.randn(T, 1, generator=g))).to(torch.bfloat16)
+    x[3] = 0
+    idx = torch.randint(0, T, (rows,), generator=g, dtype=torch.int32)
+    xd, idxd = x.to(DEV), idx.to(DEV)
+    vr = torch.tensor([valid], dtype=torch.int32, device=DEV)
+    q_row, row_isa, q_col, col_isa = ops.quant_dual_gather(xd, idxd, rows, vr)
+    c_only = ops.quant_dual_gather(xd, idxd, rows, vr, with_rows=False)
+    r_q, r_isa = ops.quant_rows_gather(xd, idxd, rows, vr)
+    r_qt, r_cisa = ops.quant_cols_t(xd, idxd, rows)
+    torch.cuda.synchronize()
+    assert c_only[0] is None and torch.equal(c_only[2][:valid], q_col[:valid])
+    assert torch.equal(q_row[:valid], r_q[:valid])
+    assert torch.equal(Q.unpack_isa(row_isa.cpu(), rows, K)[:valid], Q.unpack_isa(r_isa.cpu(), rows, K)[:valid])
+    assert torch.equal(q_col[:valid].t(), r_qt[:, :valid])
+    got, want = Q.unpack_isa(col_isa.cpu(), K, rows), Q.unpack_isa(r_cisa.cpu(), K, rows)
+    assert torch.equal(got[:, :valid // 32], want[:, :valid // 32])
+    assert torch.equal(Q.unpack_isa(c_only[3].cpu(), K, rows)[:, :valid // 32], want[:, :valid // 32])
+    # against the CPU restatement
+    o_q, o_sc = Q.col_quant(x[idx[:valid].long()].float())
+    assert torch.equal(q_col[:valid].cpu(), o_q) and torch.equal(got[:, :valid // 32], o_sc)
 
 
 @pytest.mark.parametrize("layout", [1, 2, 3])
