@@ -78,8 +78,30 @@ class ClockSampler:
 
     def __init__(self, gpu_index):
         self.idx, self.proc, self.lines = gpu_index, None, []
+        self.nvml, self.samples, self.stop_flag = None, [], False
+
+    def _physical_index(self):
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [v.strip() for v in vis.split(",") if v.strip()]
+            if self.idx < len(ids) and ids[self.idx].isdigit():
+                return int(ids[self.idx])
+        return self.idx
 
     def start(self):
+        """Read-only NVML polling every ~2 ms in a thread (a timed region lasts tens of ms); nvidia-smi at 100 ms
+        is the fallback when the NVML binding is missing."""
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index())
+            self.max_sm = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
                                           "-lms", "100", "-i", str(self.idx)], stdout=subprocess.PIPE, text=True)
@@ -88,11 +110,44 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
+    def _poll(self):
+        n = self.nvml
+        while not self.stop_flag:
+            try:
+                clk = n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)
+                rs = n.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                pw = n.nvmlDeviceGetPowerUsage(self.handle) / 1000.0
+                self.samples.append((clk, rs, pw))
+            except Exception:
+                pass
+            time.sleep(0.002)
+
     def _read(self):
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
     def stop(self):
+        if self.nvml is not None:
+            self.stop_flag = True
+            self.thread.join(timeout=1.0)
+            n = self.nvml
+            names = (("hw_slowdown", "nvmlClocksEventReasonHwSlowdown"),
+                     ("hw_thermal_slowdown", "nvmlClocksEventReasonHwThermalSlowdown"),
+                     ("sw_thermal_slowdown", "nvmlClocksEventReasonSwThermalSlowdown"),
+                     ("sw_power_cap", "nvmlClocksEventReasonSwPowerCap"))
+            reasons = set()
+            for _, rs, _ in self.samples:
+                for name, attr in names:
+                    bit = getattr(n, attr, None)
+                    if bit is None:
+                        bit = getattr(n, attr.replace("ClocksEventReason", "ClocksThrottleReason"), 0)
+                    if rs & bit:
+                        reasons.add(name)
+            sm = [c for c, _, _ in self.samples]
+            pw = [p for _, _, p in self.samples]
+            return dict(sm_mhz=statistics.median(sm) if sm else None, sm_min_mhz=min(sm) if sm else None,
+                        sm_max_mhz=self.max_sm, reasons=sorted(reasons), samples=len(sm),
+                        power_w=round(statistics.median(pw), 0) if pw else None, source="nvml, 2 ms polling")
         if self.proc is None:
             return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
         time.sleep(0.15)
@@ -110,7 +165,7 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None,
-                    reasons=sorted(reasons), samples=len(sm))
+                    reasons=sorted(reasons), samples=len(sm), source="nvidia-smi -lms 100")
 
 
 def flops_of(cfg, T=None):
@@ -162,7 +217,25 @@ def run_ours(args):
     import sonicmoe
     from sonicmoe import ops
 
-    cname = args.config or ("C2" if world == 1 else "C4")
+    # One GPU: the reference-shape layer C2.  N GPUs: the same layer per rank (T tokens per rank, its E experts
+    # sharded over the ranks), so the per-rank work equals the 1-GPU run and the values form one weak-scaling series;
+    # the skewed fine-grained config C4, which the expert-parallel case is specified on, is measured too and
+    # reported under "ep_c4".
+    cname = args.config or "C2"
+    line = _measure(args, cname, world, rank, dev, dist, sonicmoe, ops)
+    if world > 1 and args.config is None and not args.lean:
+        extra = _measure(args, "C4", world, rank, dev, dist, sonicmoe, ops)
+        if line is not None and extra is not None:
+            line["ep_c4"] = {k: extra[k] for k in ("value", "unit", "config", "tokens_per_s", "tflops", "per_step_ms",
+                                                   "e2e", "kernel_us")}
+    if line is not None:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def _measure(args, cname, world, rank, dev, dist, sonicmoe, ops):
+    local = dev.index
     cfg = CONFIGS[cname]
     E, K, H, I, T = cfg["E"], cfg["K"], cfg["H"], cfg["I"], cfg["T"]
     inp = make_inputs(cfg, dev)
@@ -212,20 +285,18 @@ def run_ours(args):
         step(d["x"], d["dy"], d["idx"], d["scores"])
         ev[i + 1].record()
     barrier()
-    clocks = sampler.stop()
     ops.check_status(dev)
     total_ms = ev[0].elapsed_time(ev[-1])
     per_step = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
     ms = total_ms / args.steps
 
     if args.lean:      # profiling runs: warm-up + timed steps only, nothing else launches
+        sampler.stop()
         if rank == 0:
             print(json.dumps({"metric": "MoE fwd+bwd us/iter", "value": round(ms * 1e3, 1), "unit": "us/iter",
                               "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "lean": True,
                               "config": {"workload": cname}}), flush=True)
-        if world > 1:
-            dist.destroy_process_group()
-        return
+        return None
 
     # ---- end to end through the public API with host buffers
     e2e_ev0, e2e_ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -249,6 +320,7 @@ def run_ours(args):
         e2e_step()
     e2e_ev1.record()
     barrier()
+    clocks = sampler.stop()      # sampled over the timed steps and the end-to-end steps that follow them
     e2e_ms = e2e_ev0.elapsed_time(e2e_ev1) / e2e_steps
     h2d = sum(pin[k].numel() * pin[k].element_size() for k in pin)
     d2h = 2 * T * H * 2
@@ -278,9 +350,7 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_ms = t.tolist()
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
+        return None
 
     pk = peaks()
     us = ms * 1e3
@@ -335,9 +405,7 @@ def run_ours(args):
     }
     if world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_reference(cfg)
-    print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    return line
 
 
 def run_reference(args):
@@ -345,7 +413,7 @@ def run_reference(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return
-    cname = args.config or ("C2" if world == 1 else "C4")
+    cname = args.config or "C2"           # same workload as the GPU arm at every N
     cfg = CONFIGS[cname]
     cb = cpu_reference(cfg, budget_s=10.0 * max(1, min(args.steps, 6)))
     T = cfg["T"] * world
@@ -357,7 +425,9 @@ def run_reference(args):
         "value": round(us, 1), "unit": "us/iter", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(us / 1e3, 3), "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16 params, fp32 accumulate (reference CPU path)", "data": "synthetic",
-        "config": {"workload": f"{cname}: T={T} H={cfg['H']} I={cfg['I']} E={cfg['E']} K={cfg['K']}, seed {cfg['seed']}"},
+        "config": {"workload": f"{cname}: T={cfg['T']}{' per rank' if world > 1 else ''} H={cfg['H']} I={cfg['I']} "
+                               f"E={cfg['E']} K={cfg['K']}, seed {cfg['seed']}"
+                               + (f", the {world} ranks' tokens ({T}) on one host" if world > 1 else "")},
         "cpu_baseline": cb,
         "e2e": {"value": round(us, 1), "unit": "us/iter", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,

@@ -37,33 +37,74 @@ class DispatchPlan:
                          copy_pos[copy_off[t]:copy_off[t+1]], ascending destination rank
     """
 
-    def __init__(self, idx: torch.Tensor, E: int, group):
-        world = dist.get_world_size(group)
+    def __init__(self, idx: torch.Tensor, E: int, group, world: int | None = None):
+        world = dist.get_world_size(group) if world is None else world
         assert E % world == 0
         El = E // world
         T, K = idx.shape
-        dest = torch.div(idx, El, rounding_mode="floor")                     # [T,K] owning rank
+        self.T, self.K, self.El, self.group = T, K, El, group
+        valid = idx >= 0
+        dest = torch.where(valid, torch.div(idx, El, rounding_mode="floor"), torch.full_like(idx, -1))   # owning rank
+        # routed pairs per destination expert: the receiver sums them over sources to size its buffers exactly
+        pairs = torch.bincount(idx.flatten().clamp(min=-1).long() + 1, minlength=E + 1)[1:].view(world, El)
+        if idx.is_cuda:
+            self._build_cuda(idx, dest, pairs, world)
+        else:
+            self._build_torch(idx, dest, valid, pairs, world)
+
+    def _exchange_counts(self, rows_to, pairs, world):
+        """One small exchange + ONE read-back: rows per peer both ways and the pairs per local expert."""
+        counts = torch.cat([rows_to.view(world, 1).to(torch.int64), pairs.to(torch.int64)], dim=1).contiguous()
+        recv = torch.empty_like(counts)
+        dist.all_to_all_single(recv, counts, group=self.group)
+        host = torch.cat([counts[:, 0], recv[:, 0], recv[:, 1:].sum(dim=0)]).tolist()
+        self.send_counts, self.recv_counts = host[:world], host[world:2 * world]
+        self.tokens_per_local_expert = host[2 * world:]
+        self.n_send, self.n_recv = sum(self.send_counts), sum(self.recv_counts)
+
+    def _build_cuda(self, idx, dest, pairs, world):
+        """The plan is the routing-metadata problem with destination ranks in the role of experts: one call of the
+        metadata kernels on the de-duplicated destination list gives the send order (rank-major, token ascending),
+        the per-rank offsets and each token's copies in ascending rank order."""
+        from . import ops
+        T, K, El = self.T, self.K, self.El
+        # a token goes once to a rank: keep the first slot of every distinct destination
+        same = dest.unsqueeze(2) == dest.unsqueeze(1)                                    # [T,K,K]
+        earlier = torch.ones(K, K, dtype=torch.bool, device=idx.device).tril(-1)
+        dest_u = torch.where((same & earlier).any(dim=2), torch.full_like(dest, -1), dest).to(torch.int32)
+        cap = T * min(K, world)
+        md = ops.topk_metadata(dest_u.contiguous(), torch.zeros(T, K, dtype=torch.float32, device=idx.device), world,
+                               alignment=1, TK_alloc=cap, TKp_alloc=cap + world)
+        self._exchange_counts(md["counts"], pairs, world)
+        n = self.n_send
+        self.send_tok = md["x_gather_idx"][:n].long()
+        self.send_rank = torch.searchsorted(md["efo"][1:].contiguous(), torch.arange(n, device=idx.device,
+                                                                                   dtype=torch.int32), right=True)
+        own = idx[self.send_tok]                                                         # [n,K] global expert ids
+        r = self.send_rank.view(n, 1)
+        mine = (own >= 0) & (torch.div(own, El, rounding_mode="floor") == r)
+        self.send_idx = torch.where(mine, own - r * El, torch.full_like(own, -1)).to(torch.int32).contiguous()
+        self.copy_pos = md["s_reverse_scatter_idx"][:n].contiguous()
+        self.copy_off = md["naept"]
+
+    def _build_torch(self, idx, dest, valid, pairs, world):
+        """Device-agnostic construction (CPU tensors, gloo)."""
+        T, K, El = self.T, self.K, self.El
         ranks = torch.arange(world, device=idx.device).view(world, 1, 1)
-        hit = (dest.unsqueeze(0) == ranks) & (idx.unsqueeze(0) >= 0)          # [P,T,K]
+        hit = (dest.unsqueeze(0) == ranks) & valid.unsqueeze(0)                # [P,T,K]
         goes = hit.any(dim=2)                                                 # [P,T]
         pt = goes.nonzero()                                                   # rank-major, token ascending
         self.send_rank, self.send_tok = pt[:, 0], pt[:, 1]
         local = idx.unsqueeze(0) - ranks * El
         local = torch.where(hit, local, torch.full_like(local, -1))          # [P,T,K]
         self.send_idx = local[self.send_rank, self.send_tok].to(torch.int32).contiguous()
-        counts = goes.sum(dim=1).to(torch.int64)
-        recv = torch.empty_like(counts)
-        dist.all_to_all_single(recv, counts, group=group)
-        self.send_counts = counts.tolist()
-        self.recv_counts = recv.tolist()
-        self.n_send, self.n_recv = sum(self.send_counts), sum(self.recv_counts)
+        self._exchange_counts(goes.sum(dim=1), pairs, world)
         # copies of a token, ascending rank: stable sort of the outgoing rows by token
         order = torch.sort(self.send_tok, stable=True).indices
         self.copy_pos = order.to(torch.int32).contiguous()
         off = torch.zeros(T + 1, dtype=torch.int64, device=idx.device)
         off[1:] = goes.sum(dim=0).cumsum(0)
         self.copy_off = off.to(torch.int32).contiguous()
-        self.T, self.K, self.El, self.group = T, K, El, group
 
     def a2a(self, send: torch.Tensor, reverse: bool = False) -> torch.Tensor:
         """Rows travel to their destination (or, reversed, back to their source)."""
@@ -85,6 +126,21 @@ class DispatchPlan:
         return out.to(rows.dtype)
 
 
+def _pack(parts):
+    """[n, *] tensors of any dtype -> one uint8 [n, total bytes] (one all-to-all instead of one per tensor)."""
+    return torch.cat([p.contiguous().view(torch.uint8).reshape(p.shape[0], -1) for p in parts], dim=1)
+
+
+def _unpack(buf, specs):
+    """Inverse of _pack; specs = [(dtype, columns)]."""
+    out, at = [], 0
+    for dtype, cols in specs:
+        w = cols * torch.empty((), dtype=dtype).element_size()
+        out.append(buf[:, at:at + w].contiguous().view(dtype).reshape(buf.shape[0], cols))
+        at += w
+    return out
+
+
 class _Dispatch(torch.autograd.Function):
     """x [T,H], probs [T,K] -> rows received by this rank.  FP8 payload: outputs (placeholder [N,H] carrying
     the graph, probs [N,K], e4m3 bytes [N,H], raw scales [N,H/32]); bf16 payload: (x rows, probs, None, None)."""
@@ -92,22 +148,29 @@ class _Dispatch(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, probs, plan: DispatchPlan, fp8: bool):
         ctx.plan, ctx.x_dtype = plan, x.dtype
-        tok = plan.send_tok
-        p_recv = plan.a2a(probs.float()[tok])
+        tok, K, H = plan.send_tok, plan.K, x.shape[1]
+        # the wide payload travels as it is (no repacking copies); scales, expert ids and probabilities share
+        # one narrow exchange
+        meta = [plan.send_idx, probs.float()[tok]]
         if fp8:
             from . import ops
             q, raw, _ = ops.quant_rows(x.contiguous(), raw=True)
-            q_recv, raw_recv = plan.a2a(q[tok]), plan.a2a(raw[tok])
-            holder = torch.empty((), dtype=x.dtype, device=x.device).expand(plan.n_recv, x.shape[1])
-            ctx.mark_non_differentiable(q_recv, raw_recv)
-            return holder, p_recv, q_recv, raw_recv
-        return plan.a2a(x[tok]), p_recv, None, None
+            q_recv = plan.a2a(q[tok])
+            raw_recv, idx_recv, p_recv = _unpack(plan.a2a(_pack([raw[tok]] + meta)),
+                                                 [(torch.uint8, H // 32), (torch.int32, K), (torch.float32, K)])
+            holder = torch.empty((), dtype=x.dtype, device=x.device).expand(plan.n_recv, H)
+            ctx.mark_non_differentiable(q_recv, raw_recv, idx_recv)
+            return holder, p_recv, q_recv, raw_recv, idx_recv
+        x_recv = plan.a2a(x[tok])
+        idx_recv, p_recv = _unpack(plan.a2a(_pack(meta)), [(torch.int32, K), (torch.float32, K)])
+        ctx.mark_non_differentiable(idx_recv)
+        return x_recv, p_recv, None, None, idx_recv
 
     @staticmethod
-    def backward(ctx, dx_recv, dp_recv, _dq, _draw):
+    def backward(ctx, dx_recv, dp_recv, _dq, _draw, _didx):
         plan = ctx.plan
         dx = dp = None
-        if ctx.needs_input_grad[0]:
+        if ctx.needs_input_grad[0] and dx_recv is not None:
             dx = plan.sum_copies(plan.a2a(dx_recv.contiguous(), reverse=True)).to(ctx.x_dtype)
         if ctx.needs_input_grad[1] and dp_recv is not None:
             back = plan.a2a(dp_recv.contiguous().float(), reverse=True)
@@ -149,9 +212,9 @@ class ExpertParallelMoE:
 
     def _sonic_experts(self, rows, local_idx, probs, w1, w2, fp8_scale, handle):
         from .interface import run_sonic_moe
-        # the exchange already synchronised with the host for its split sizes; one more small read-back
-        # sizes the expert-sorted buffers exactly instead of at the N*K upper bound
-        counts = torch.bincount(local_idx.flatten().clamp(min=-1) + 1, minlength=self.El + 1)[1:].tolist()
+        # the plan's count exchange already brought the routed pairs per local expert: the expert-sorted buffers
+        # are sized exactly instead of at the N*K upper bound, with no further read-back
+        counts = self.tokens_per_local_expert
         if fp8_scale is not None:
             holder, qbytes = rows
             return run_sonic_moe(qbytes, local_idx, probs, self.K, self.El, w1, w2, fp8=True, fp8_scale=fp8_scale,
@@ -162,12 +225,12 @@ class ExpertParallelMoE:
         plan = DispatchPlan(topk_idx, self.E, self.group)
         self.El = plan.El
         fp8 = self.payload == "fp8"
-        rows, probs, q, raw = _Dispatch.apply(x, topk_scores, plan, fp8)
+        self.tokens_per_local_expert = plan.tokens_per_local_expert
+        rows, probs, q, raw, local_idx = _Dispatch.apply(x, topk_scores, plan, fp8)
         handle = None
         if fp8:
             from .functional import Fp8CombineGradHandle
             handle = Fp8CombineGradHandle()
             rows = (rows, q)
-        local_idx = plan.a2a(plan.send_idx)
         o_recv = self.expert_fn(rows, local_idx, probs, w1, w2, raw, handle)
         return _Combine.apply(o_recv, plan, handle)

@@ -66,7 +66,8 @@ def _worker(rank, world, port, out_q):
     plan = DispatchPlan(idx, E, dist.group.WORLD)
     res = dict(out=out.detach(), dx=x.grad, ds=scores.grad, dw1=w1l.grad, dw2=w2l.grad,
                n_send=plan.n_send, n_recv=plan.n_recv, send_counts=plan.send_counts,
-               copies=(plan.copy_off[1:] - plan.copy_off[:-1]).clone())
+               copies=(plan.copy_off[1:] - plan.copy_off[:-1]).clone(),
+               per_expert=list(plan.tokens_per_local_expert))
     # host-side failure: an exchange whose split sizes disagree with the buffer is refused before any data moves
     try:
         plan.send_counts = [c + 1 for c in plan.send_counts]
@@ -127,6 +128,10 @@ def test_ep_two_ranks_matches_single_process_oracle():
         dest = torch.div(idx, El, rounding_mode="floor")
         n_dest = torch.tensor([len(set(row.tolist())) for row in dest])
         assert torch.equal(r["copies"].long(), n_dest)
+        # routed pairs per local expert, summed over all source ranks (sizes the expert-sorted buffers)
+        all_idx = torch.cat([_inputs(rk, world)[3] for rk in range(world)])
+        want = torch.bincount(all_idx.flatten(), minlength=E)[rank * El:(rank + 1) * El]
+        assert r["per_expert"] == want.tolist()
         assert r["n_send"] == int(n_dest.sum()) and sum(r["send_counts"]) == r["n_send"]
         assert r["bad_split_raises"]
         # this rank's tokens contribute to every rank's expert gradients

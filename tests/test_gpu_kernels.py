@@ -519,3 +519,29 @@ def test_gemm_dgated_fused_quantizers_match_separate_kernels(ops, T, H, I, tiles
     assert torch.equal(Q.unpack_isa(f_csf.cpu(), 2 * I, rows)[:, :n // 32], Q.unpack_isa(r_csf.cpu(), 2 * I, rows)[:, :n // 32])
     assert torch.equal(Q.unpack_isa(f_ysf.cpu(), I, rows)[:, :n // 32], Q.unpack_isa(r_ysf.cpu(), I, rows)[:, :n // 32])
     assert torch.equal(f_dsp.sum(0)[:n], dsp.sum(0)[:n]) or torch.allclose(f_dsp.sum(0)[:n], dsp.sum(0)[:n], rtol=1e-5)
+
+
+@pytest.mark.parametrize("T,K,E,world", [(333, 4, 16, 4), (1000, 8, 8, 8), (64, 2, 6, 2)])
+def test_ep_dispatch_plan_from_metadata_kernels_matches_torch_construction(ops, T, K, E, world):
+    """The plan built with the routing-metadata kernels (destination ranks as experts) equals the device-agnostic
+    torch construction; the count exchange is replaced by a loop-back so one GPU suffices."""
+    from sonicmoe.ep import DispatchPlan
+
+    class LoopbackPlan(DispatchPlan):
+        def _exchange_counts(self, rows_to, pairs, world):
+            self.send_counts = rows_to.tolist()
+            self.recv_counts = list(self.send_counts)
+            self.tokens_per_local_expert = pairs.sum(0).tolist()
+            self.n_send = self.n_recv = sum(self.send_counts)
+
+    g = torch.Generator().manual_seed(T)
+    idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32)
+    idx[::7, -1] = -1                                 # dropped slots
+    got = LoopbackPlan(idx.to(DEV), E, None, world=world)
+    want = LoopbackPlan(idx, E, None, world=world)
+    assert got.send_counts == want.send_counts and got.n_send == want.n_send
+    assert torch.equal(got.send_tok.cpu(), want.send_tok)
+    assert torch.equal(got.send_rank.cpu().long(), want.send_rank.long())
+    assert torch.equal(got.send_idx.cpu(), want.send_idx)
+    assert torch.equal(got.copy_off.cpu(), want.copy_off)
+    assert torch.equal(got.copy_pos.cpu(), want.copy_pos)
