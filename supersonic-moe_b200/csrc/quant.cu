@@ -120,32 +120,37 @@ quant_rows_scatter_kernel(const uint4* __restrict__ x, int64_t T, int K, const i
     if (beg == end) return;
     uint8_t* sq = s_rowbuf + (size_t)warp * ((K + 4 * k_tiles + 15) & ~15);   // 16-byte aligned per warp
     uint32_t* ssc = reinterpret_cast<uint32_t*>(sq + K);
-    for (int c0 = 0; c0 < K; c0 += 256) {
-      const int col = c0 + lane * 8;
-      const bool in = col < K;
-      float f[8];
-      if (in) {
-        bf16x8_to_f32(x[(t * K + col) >> 3], f);
-      } else {
+    constexpr int NB = 4;                       // 16-byte loads in flight per lane
+    for (int cb = 0; cb < K; cb += 256 * NB) {
+      uint4 v[NB];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] = 0.f;
+      for (int b = 0; b < NB; ++b) {
+        const int col = cb + b * 256 + lane * 8;
+        v[b] = col < K ? x[(t * K + col) >> 3] : make_uint4(0, 0, 0, 0);
       }
-      float amax = 0.f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffff, amax, 1));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffff, amax, 2));
-      const int e = q_e8m0_of(amax);
-      const float qs = q_scale_of(e);
-      const uint32_t b1 = __shfl_down_sync(0xffffffff, (uint32_t)e, 4);
-      const uint32_t b2 = __shfl_down_sync(0xffffffff, (uint32_t)e, 8);
-      const uint32_t b3 = __shfl_down_sync(0xffffffff, (uint32_t)e, 12);
-      if (in) {
-        uint2 o;
-        o.x = q_pack4(f[0] * qs, f[1] * qs, f[2] * qs, f[3] * qs);
-        o.y = q_pack4(f[4] * qs, f[5] * qs, f[6] * qs, f[7] * qs);
-        *reinterpret_cast<uint2*>(sq + col) = o;
-        if ((lane & 15) == 0) ssc[col >> 7] = (uint32_t)e | (b1 << 8) | (b2 << 16) | (b3 << 24);
+      for (int b = 0; b < NB; ++b) {
+        const int col = cb + b * 256 + lane * 8;
+        const bool in = col < K;
+        float f[8];
+        bf16x8_to_f32(v[b], f);
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffff, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffff, amax, 2));
+        const int e = q_e8m0_of(amax);
+        const float qs = q_scale_of(e);
+        const uint32_t b1 = __shfl_down_sync(0xffffffff, (uint32_t)e, 4);
+        const uint32_t b2 = __shfl_down_sync(0xffffffff, (uint32_t)e, 8);
+        const uint32_t b3 = __shfl_down_sync(0xffffffff, (uint32_t)e, 12);
+        if (in) {
+          uint2 o;
+          o.x = q_pack4(f[0] * qs, f[1] * qs, f[2] * qs, f[3] * qs);
+          o.y = q_pack4(f[4] * qs, f[5] * qs, f[6] * qs, f[7] * qs);
+          *reinterpret_cast<uint2*>(sq + col) = o;
+          if ((lane & 15) == 0) ssc[col >> 7] = (uint32_t)e | (b1 << 8) | (b2 << 16) | (b3 << 24);
+        }
       }
     }
     __syncwarp();
