@@ -416,13 +416,19 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         constexpr int NC = COLS_PER_WARP / 32;
         uint32_t pk[NC][16];
 #pragma unroll
-        for (int c = 0; c < NC; ++c) {
-          uint32_t r[32];
-          tmem_ld32(t_row + c * 32, r);
+        for (int c = 0; c < NC; c += 2) {      // two TMEM loads in flight per wait: the drain is what the MMA waits for
+          uint32_t r0[32], r1[32];
+          tmem_ld32(t_row + c * 32, r0);
+          if (c + 1 < NC) tmem_ld32(t_row + (c + 1) * 32, r1);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 16; ++i)
-            pk[c][i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+            pk[c][i] = pack_bf16x2(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]));
+          if (c + 1 < NC) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              pk[c + 1][i] = pack_bf16x2(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]));
+          }
         }
         tc_fence_before();
         __syncwarp();
