@@ -36,6 +36,11 @@ CONFIGS = {
     # C2's layer at T=2048: small enough for multi-pass ncu captures, weights (453 MB bf16 + 226 MB fp8) >> L2
     "P1": dict(T=2048, H=3072, I=1536, E=8, K=8, seed=0, skew=False),
 }
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the six GEMMs on C2, one 1-pass ncu capture of
+# `python bench.py --steps 1 --warmup 1 --no-cpu --lean` (profiles/gemm_dram_traffic_c2.md); key = op name and its
+# occurrence within a step
+NCU_DRAM_BYTES_C2 = {("gemm_gated", 0): 560.8e6, ("gemm_varlen_m", 0): 490.1e6, ("gemm_dgated_fused", 0): 743.4e6,
+                     ("gemm_wgrad", 0): 628.5e6, ("gemm_wgrad", 1): 1064.9e6, ("gemm_varlen_m", 1): 644.6e6}
 PUBLISHED_US = {"C2": 2659.8, "C3": 8521.7}       # reference README.md:28-38,348 (its own FP8 path, 1x SM100)
 FP8_PEAK_NOMINAL = 4.5e15
 # kernels launched per wrapper call (sonicmoe/ops.py)
@@ -378,6 +383,13 @@ def _measure(args, cname, world, rank, dev, dist, sonicmoe, ops):
             seen[n] += 1
     fp8_peak = 2.0 * pk["bf16_sustained"]
     ach = per_gemm_flops[dom] / (breakdown[dom] * 1e-6) / 1e12
+    traffic = None
+    if world == 1 and cname == "C2":
+        dn = dom.split("#")[0]
+        dn = "gemm_wgrad" if dn.startswith("gemm_wgrad") else dn
+        occ = sum(1 for k in gemm_keys[:gemm_keys.index(dom)]
+                  if (k.split("#")[0] == dn or (dn == "gemm_wgrad" and k.startswith("gemm_wgrad"))))
+        traffic = NCU_DRAM_BYTES_C2.get((dn, occ))
     line = {
         "metric": "MoE fwd+bwd us/iter (FP8 MXFP8 1x32, pre-routed expert compute incl. routing metadata, quant, "
                   "6 GEMMs, combines, wgrad into fp32 main_grad)",
@@ -398,7 +410,8 @@ def _measure(args, cname, world, rank, dev, dist, sonicmoe, ops):
                 "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,
         "roofline": {"bound": "tensor", "kernel": dom, "achieved": round(ach, 1), "peak": round(fp8_peak, 1),
-                     "unit": "TFLOP/s", "frac": round(ach / fp8_peak, 4), "traffic": None,
+                     "unit": "TFLOP/s", "frac": round(ach / fp8_peak, 4), "traffic": traffic,
+                     "traffic_unit": "bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum)",
                      "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({pk['source']}); fp8 "
                                     "tensor rate is twice the bf16 rate"},
         "kernel_us": breakdown,
