@@ -141,7 +141,9 @@ class ClockSampler:
                      ("sw_thermal_slowdown", "nvmlClocksEventReasonSwThermalSlowdown"),
                      ("sw_power_cap", "nvmlClocksEventReasonSwPowerCap"))
             reasons = set()
+            raw = 0
             for _, rs, _ in self.samples:
+                raw |= rs
                 for name, attr in names:
                     bit = getattr(n, attr, None)
                     if bit is None:
@@ -152,7 +154,8 @@ class ClockSampler:
             pw = [p for _, _, p in self.samples]
             return dict(sm_mhz=statistics.median(sm) if sm else None, sm_min_mhz=min(sm) if sm else None,
                         sm_max_mhz=self.max_sm, reasons=sorted(reasons), samples=len(sm),
-                        power_w=round(statistics.median(pw), 0) if pw else None, source="nvml, 2 ms polling")
+                        power_w=round(statistics.median(pw), 0) if pw else None, reasons_mask=hex(raw),
+                        source="nvml, 2 ms polling")
         if self.proc is None:
             return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
         time.sleep(0.15)
@@ -416,9 +419,44 @@ def _measure(args, cname, world, rank, dev, dist, sonicmoe, ops):
                                     "tensor rate is twice the bf16 rate"},
         "kernel_us": breakdown,
     }
+    if world == 1:
+        line["full_layer"] = _full_layer(args, cfg, inp, dev, sonicmoe, ops)
     if world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_reference(cfg)
     return line
+
+
+def _full_layer(args, cfg, inp, dev, sonicmoe, ops):
+    """The same layer through the `MoE` module: router linear, top-k + softmax, the expert compute above, and the
+    backward through the scores into the router weight (the region the headline number leaves out, as the
+    reference's own benchmark does)."""
+    E, K, H, I = cfg["E"], cfg["K"], cfg["H"], cfg["I"]
+    moe = sonicmoe.MoE(E, K, H, I, sonicmoe.ActivationType.SWIGLU, add_bias=False, std=0.02).to(dev).to(torch.bfloat16)
+    with torch.no_grad():
+        moe.c_fc.weight.copy_(inp["w1"])
+        moe.c_proj.weight.copy_(inp["w2"])
+    moe.c_fc.weight.main_grad = torch.zeros(E, 2 * I, H, dtype=torch.float32, device=dev)
+    moe.c_proj.weight.main_grad = torch.zeros(E, I, H, dtype=torch.float32, device=dev)
+    x, dy = inp["x"].to(dev), inp["dy"].to(dev)
+
+    def step():
+        xg = x.detach().requires_grad_(True)
+        out, _ = moe(xg, use_fp8=True)
+        out.backward(dy)
+
+    for _ in range(max(3, args.warmup // 2)):
+        step()
+    torch.cuda.synchronize()
+    n = max(3, min(args.steps, 8))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ops.check_status(dev)
+    return {"value": round(e0.elapsed_time(e1) / n * 1e3, 1), "unit": "us/iter", "steps": n,
+            "includes": "router linear + top-k softmax + drouter around the timed region of `value`"}
 
 
 def run_reference(args):
