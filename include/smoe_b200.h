@@ -77,6 +77,22 @@ int smoe_topk_metadata_static(const int32_t* idx, const float* probs, int64_t N,
                               int32_t* score_src_idx, int32_t* counts, void* stream);
 int64_t smoe_topk_metadata_static_capacity(void);
 
+/* ---- expert-parallel dispatch planning --------------------------------------
+ * No counterpart in the reference, which ships no communication code (its host framework calls DeepEP around
+ * run_sonic_moe); these two kernels bracket smoe_topk_metadata, run with destination ranks in the role of experts,
+ * to build the send order of the all-to-all dispatch on the device. */
+
+/* idx [T,K] global expert ids (valid iff 0 <= e < E; E % world == 0, rank r owns [r*E/world, (r+1)*E/world)) ->
+ * dest_u [T,K]: owning rank of each slot, -1 for invalid slots and for every slot after the first that goes to the
+ * same rank (a token travels once per rank); pairs [E]: routed (token, slot) pairs per global expert (zeroed here). */
+int smoe_ep_plan_dest(const int32_t* idx, int64_t T, int64_t K, int64_t E, int64_t world, int32_t* dest_u,
+                      int32_t* pairs, void* stream);
+
+/* Per outgoing row i < n_send (send_tok[i] = its token, efo = per-rank offsets of the send order):
+ * send_rank[i] and send_idx[i,K] = the token's expert ids local to that rank, -1 for slots owned elsewhere. */
+int smoe_ep_plan_send_idx(const int32_t* idx, const int32_t* send_tok, const int32_t* efo, int64_t n_send, int64_t K,
+                          int64_t E, int64_t world, int32_t* send_idx, int32_t* send_rank, void* stream);
+
 /* ---- MXFP8 1x32 ue8m0 quantizers ------------------------------------------ */
 
 /* Row-wise: x bf16 [M,K] -> e4m3 [M,K] + raw scales [M,K/32] and/or ISA-packed scales

@@ -40,56 +40,51 @@ class DispatchPlan:
     def __init__(self, idx: torch.Tensor, E: int, group, world: int | None = None):
         world = dist.get_world_size(group) if world is None else world
         assert E % world == 0
-        El = E // world
         T, K = idx.shape
-        self.T, self.K, self.El, self.group = T, K, El, group
-        valid = idx >= 0
-        dest = torch.where(valid, torch.div(idx, El, rounding_mode="floor"), torch.full_like(idx, -1))   # owning rank
-        # routed pairs per destination expert: the receiver sums them over sources to size its buffers exactly
-        pairs = torch.bincount(idx.flatten().clamp(min=-1).long() + 1, minlength=E + 1)[1:].view(world, El)
+        self.T, self.K, self.El, self.E, self.group = T, K, E // world, E, group
         if idx.is_cuda:
-            self._build_cuda(idx, dest, pairs, world)
+            self._build_cuda(idx, world)
         else:
-            self._build_torch(idx, dest, valid, pairs, world)
+            self._build_torch(idx, world)
 
     def _exchange_counts(self, rows_to, pairs, world):
-        """One small exchange + ONE read-back: rows per peer both ways and the pairs per local expert."""
-        counts = torch.cat([rows_to.view(world, 1).to(torch.int64), pairs.to(torch.int64)], dim=1).contiguous()
+        """One small exchange + ONE read-back: rows per peer both ways and the routed pairs per local expert (the
+        receiver sums them over sources to size its expert-sorted buffers exactly)."""
+        counts = torch.cat([rows_to.view(world, 1), pairs.view(world, self.El)], dim=1).contiguous()
         recv = torch.empty_like(counts)
         dist.all_to_all_single(recv, counts, group=self.group)
-        host = torch.cat([counts[:, 0], recv[:, 0], recv[:, 1:].sum(dim=0)]).tolist()
+        host = torch.cat([counts[:, 0], recv[:, 0], recv[:, 1:].sum(dim=0).to(counts.dtype)]).tolist()
         self.send_counts, self.recv_counts = host[:world], host[world:2 * world]
         self.tokens_per_local_expert = host[2 * world:]
         self.n_send, self.n_recv = sum(self.send_counts), sum(self.recv_counts)
 
-    def _build_cuda(self, idx, dest, pairs, world):
+    def _build_cuda(self, idx, world):
         """The plan is the routing-metadata problem with destination ranks in the role of experts: one call of the
         metadata kernels on the de-duplicated destination list gives the send order (rank-major, token ascending),
-        the per-rank offsets and each token's copies in ascending rank order."""
+        the per-rank offsets and each token's copies in ascending rank order.  Two small kernels bracket it; the
+        host issues about a dozen launches and reads back once."""
         from . import ops
-        T, K, El = self.T, self.K, self.El
-        # a token goes once to a rank: keep the first slot of every distinct destination
-        same = dest.unsqueeze(2) == dest.unsqueeze(1)                                    # [T,K,K]
-        earlier = torch.ones(K, K, dtype=torch.bool, device=idx.device).tril(-1)
-        dest_u = torch.where((same & earlier).any(dim=2), torch.full_like(dest, -1), dest).to(torch.int32)
+        T, K = self.T, self.K
+        idx = idx.to(torch.int32).contiguous()
+        dest_u, pairs = ops.ep_plan_dest(idx, self.E, world)
         cap = T * min(K, world)
-        md = ops.topk_metadata(dest_u.contiguous(), torch.zeros(T, K, dtype=torch.float32, device=idx.device), world,
-                               alignment=1, TK_alloc=cap, TKp_alloc=cap + world)
+        # the probability operand of the metadata kernels is not needed here: any f32 buffer of the right size
+        md = ops.topk_metadata(dest_u, dest_u.view(torch.float32), world, alignment=1, TK_alloc=cap,
+                               TKp_alloc=cap + world)
         self._exchange_counts(md["counts"], pairs, world)
         n = self.n_send
-        self.send_tok = md["x_gather_idx"][:n].long()
-        self.send_rank = torch.searchsorted(md["efo"][1:].contiguous(), torch.arange(n, device=idx.device,
-                                                                                   dtype=torch.int32), right=True)
-        own = idx[self.send_tok]                                                         # [n,K] global expert ids
-        r = self.send_rank.view(n, 1)
-        mine = (own >= 0) & (torch.div(own, El, rounding_mode="floor") == r)
-        self.send_idx = torch.where(mine, own - r * El, torch.full_like(own, -1)).to(torch.int32).contiguous()
-        self.copy_pos = md["s_reverse_scatter_idx"][:n].contiguous()
+        self.send_tok_i32 = md["x_gather_idx"][:n]
+        self.send_idx, self.send_rank = ops.ep_plan_send_idx(idx, self.send_tok_i32, md["efo"], n, self.E, world)
+        self.send_tok = self.send_tok_i32.long()
+        self.copy_pos = md["s_reverse_scatter_idx"][:n]
         self.copy_off = md["naept"]
 
-    def _build_torch(self, idx, dest, valid, pairs, world):
+    def _build_torch(self, idx, world):
         """Device-agnostic construction (CPU tensors, gloo)."""
         T, K, El = self.T, self.K, self.El
+        valid = idx >= 0
+        dest = torch.where(valid, torch.div(idx, El, rounding_mode="floor"), torch.full_like(idx, -1))   # owning rank
+        pairs = torch.bincount(idx.flatten().clamp(min=-1).long() + 1, minlength=self.E + 1)[1:]
         ranks = torch.arange(world, device=idx.device).view(world, 1, 1)
         hit = (dest.unsqueeze(0) == ranks) & valid.unsqueeze(0)                # [P,T,K]
         goes = hit.any(dim=2)                                                 # [P,T]
@@ -98,7 +93,7 @@ class DispatchPlan:
         local = idx.unsqueeze(0) - ranks * El
         local = torch.where(hit, local, torch.full_like(local, -1))          # [P,T,K]
         self.send_idx = local[self.send_rank, self.send_tok].to(torch.int32).contiguous()
-        self._exchange_counts(goes.sum(dim=1), pairs, world)
+        self._exchange_counts(goes.sum(dim=1).to(torch.int64), pairs.to(torch.int64), world)
         # copies of a token, ascending rank: stable sort of the outgoing rows by token
         order = torch.sort(self.send_tok, stable=True).indices
         self.copy_pos = order.to(torch.int32).contiguous()

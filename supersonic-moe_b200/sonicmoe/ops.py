@@ -118,6 +118,28 @@ def topk_metadata(idx, probs, E, alignment=128, TK_alloc=None, TKp_alloc=None, l
     return out
 
 
+# ---------------------------------------------------------------- expert-parallel planning
+def ep_plan_dest(idx, E, world):
+    """idx i32 [T,K] -> (dest_u i32 [T,K]: owning rank per slot, first slot per rank only; pairs i32 [E])."""
+    _cuda(idx)
+    T, K = idx.shape
+    dest_u = torch.empty(T, K, dtype=_I32, device=idx.device)
+    pairs = torch.empty(E, dtype=_I32, device=idx.device)
+    check(lib.smoe_ep_plan_dest(_p(idx), T, K, E, world, _p(dest_u), _p(pairs), _stream()), "ep_plan_dest")
+    return dest_u, pairs
+
+
+def ep_plan_send_idx(idx, send_tok, efo, n_send, E, world):
+    """-> (send_idx i32 [n_send,K] local expert ids per outgoing row, send_rank i32 [n_send])."""
+    _cuda(idx, send_tok, efo)
+    K = idx.shape[1]
+    send_idx = torch.empty(n_send, K, dtype=_I32, device=idx.device)
+    send_rank = torch.empty(n_send, dtype=_I32, device=idx.device)
+    check(lib.smoe_ep_plan_send_idx(_p(idx), _p(send_tok), _p(efo), n_send, K, E, world, _p(send_idx),
+                                    _p(send_rank), _stream()), "ep_plan_send_idx")
+    return send_idx, send_rank
+
+
 # ---------------------------------------------------------------- quantizers
 @_timed
 def quant_rows(x, raw=True, isa=False):

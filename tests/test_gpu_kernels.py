@@ -531,7 +531,7 @@ def test_ep_dispatch_plan_from_metadata_kernels_matches_torch_construction(ops, 
         def _exchange_counts(self, rows_to, pairs, world):
             self.send_counts = rows_to.tolist()
             self.recv_counts = list(self.send_counts)
-            self.tokens_per_local_expert = pairs.sum(0).tolist()
+            self.tokens_per_local_expert = pairs.view(world, -1).sum(0).tolist()
             self.n_send = self.n_recv = sum(self.send_counts)
 
     g = torch.Generator().manual_seed(T)
@@ -545,3 +545,4 @@ def test_ep_dispatch_plan_from_metadata_kernels_matches_torch_construction(ops, 
     assert torch.equal(got.send_idx.cpu(), want.send_idx)
     assert torch.equal(got.copy_off.cpu(), want.copy_off)
     assert torch.equal(got.copy_pos.cpu(), want.copy_pos)
+    assert got.tokens_per_local_expert == want.tokens_per_local_expert
