@@ -306,26 +306,46 @@ def _measure(args, cname, world, rank, dev, dist, sonicmoe, ops):
                               "config": {"workload": cname}}), flush=True)
         return None
 
-    # ---- end to end through the public API with host buffers
-    e2e_ev0, e2e_ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # ---- end to end through the public API with host buffers.  Every step copies its inputs from pinned host memory
+    # and returns out / dx to pinned host memory; the copies run on their own streams (inputs of step i+1 and results
+    # of step i-1 move while step i computes, as a data loader would), with two device input buffer sets.
     out_h = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
     dx_h = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
-    e2e_steps = max(3, min(args.steps, 6))
+    e2e_steps = max(4, min(args.steps, 8))
+    main_s = torch.cuda.current_stream()
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    bufs = [{k: torch.empty_like(d[k]) for k in pin} for _ in range(2)]
 
-    def e2e_step():
-        xd = pin["x"].to(dev, non_blocking=True)
-        dyd = pin["dy"].to(dev, non_blocking=True)
-        idxd = pin["idx"].to(dev, non_blocking=True)
-        scd = pin["scores"].to(dev, non_blocking=True)
-        out, dx = step(xd, dyd, idxd, scd)
-        out_h.copy_(out, non_blocking=True)
-        dx_h.copy_(dx, non_blocking=True)
+    def e2e_run(n):
+        in_ready = [torch.cuda.Event() for _ in range(n)]
+        used = [torch.cuda.Event() for _ in range(n)]
+        for i in range(n + 1):
+            if i < n:                                   # inputs of step i -> buffer set i % 2
+                with torch.cuda.stream(s_in):
+                    if i >= 2:
+                        s_in.wait_event(used[i - 2])    # that buffer set has been consumed
+                    for k in pin:
+                        bufs[i % 2][k].copy_(pin[k], non_blocking=True)
+                    in_ready[i].record(s_in)
+            if i >= 1:                                  # step i-1
+                j = i - 1
+                main_s.wait_event(in_ready[j])
+                b = bufs[j % 2]
+                out, dx = step(b["x"], b["dy"], b["idx"], b["scores"])
+                used[j].record(main_s)
+                s_out.wait_event(used[j])
+                with torch.cuda.stream(s_out):
+                    out_h.copy_(out, non_blocking=True)
+                    dx_h.copy_(dx, non_blocking=True)
+                out.record_stream(s_out)
+                dx.record_stream(s_out)
+        main_s.wait_stream(s_out)
 
-    e2e_step()
+    e2e_run(2)
     barrier()
+    e2e_ev0, e2e_ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e2e_ev0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
+    e2e_run(e2e_steps)
     e2e_ev1.record()
     barrier()
     clocks = sampler.stop()      # sampled over the timed steps and the end-to-end steps that follow them
