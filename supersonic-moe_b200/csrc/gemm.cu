@@ -218,7 +218,7 @@ extern "C" {
 
 int smoe_debug_force_bn(int bn) {
   g_force_bn = bn & 0xFFFF;
-  g_skip_store = ((bn >> 16) & 1) | (((bn >> 18) & 7) << 1);   // bit 16: no stores; bits 18-20: timing experiments
+  g_skip_store = ((bn >> 16) & 1) | (((bn >> 18) & 1) << 1);   // bit 16: no stores; bit 18: no epilogue (fused dgated)
   g_force_v1 = (bn >> 17) & 1;
   return SMOE_OK;
 }

@@ -560,7 +560,7 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           }
           fence_proxy_async_smem();
           __syncwarp();
-          if (t.valid && !p.debug_skip_store) {
+          if (t.valid && !(p.debug_skip_store & 1)) {
             if (lane == 0) {
               tma_store_2d(&tmap_c, stg, zc, t.m0 + q * 32);                 // z e4m3 [rows, 2I]
               tma_store_2d(&tmap_c2, stg + 2048, zc / 2, t.m0 + q * 32);     // y1 e4m3 [rows, I]
@@ -588,8 +588,9 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 #pragma unroll 1
           for (int c = 0; c < NCH; ++c) {
             const int dcol = c_base + c * 32;            // first D / y1s column of the chunk
-            uint32_t r[32];
-            tmem_ld32(t_row + c * 32, r);
+            uint32_t r0[16], r1[16];                     // the accumulator arrives in two 16-column halves
+            tmem_ld16(t_row + c * 32, r0);
+            tmem_ld16(t_row + c * 32 + 16, r1);
             uint4 zn[4];
             uint32_t scn = 0;
             if (c + 1 < NCH) {                           // next chunk's z travels while this one is computed
@@ -604,13 +605,16 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             const float sc0 = __int_as_float((int)(sc & 0xFF) << 23);
             const float sc1 = __int_as_float((int)(sc >> 8) << 23);
             tmem_ld_wait();
+            if (lane == 0) bulk_wait_group_read<0>();    // the previous chunk's stores have read the staging
+            __syncwarp();
             const uint32_t* zw = reinterpret_cast<const uint32_t*>(zb);
             uint32_t Y[16];                              // y1s of this lane's row, bf16 pairs of adjacent columns
-            uint32_t w[16];
             uint32_t e_blk = 0;
 #pragma unroll
             for (int b = 0; b < 2; ++b) {
-              float v[32];
+              // 16 D columns -> 32 dz columns = one 32x32 scale block; dz stays packed in bf16 pairs until its
+              // block maximum is known
+              uint32_t P[16];
               float amax = 0.f;
               const float scale = b ? sc1 : sc0;
 #pragma unroll
@@ -622,7 +626,7 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                   const uint32_t pair = (zw[pi >> 1] >> (16 * (pi & 1))) & 0xFFFF;
                   const float2 gu = e4m3x2_to_f32(pair);
                   const float g = gu.x * scale, u = gu.y * scale;
-                  const float D = __uint_as_float(r[pi]);
+                  const float D = __uint_as_float(b ? r1[2 * i2 + h] : r0[2 * i2 + h]);
                   const float dout = s * D;
                   const float sig = fast_sigmoid(g);
                   const float silu = g * sig;
@@ -630,22 +634,30 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                   const float yv = silu * u;
                   ds_acc = fmaf(yv, D, ds_acc);
                   const uint32_t dzp = pack_bf16x2(((sig - silu * sig) * dout + sd) * u, sd);   // rounds to bf16
-                  v[4 * i2 + 2 * h] = __uint_as_float(dzp << 16);
-                  v[4 * i2 + 2 * h + 1] = __uint_as_float(dzp & 0xFFFF0000u);
+                  P[2 * i2 + h] = dzp;
                   yq[h] = s * yv;
-                  amax = fmaxf(amax, fmaxf(fabsf(v[4 * i2 + 2 * h]), fabsf(v[4 * i2 + 2 * h + 1])));
+                  amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(dzp << 16)), fabsf(__uint_as_float(dzp & 0xFFFF0000u))));
                 }
                 Y[b * 8 + i2] = pack_bf16x2(yq[0], yq[1]);
               }
+              uint32_t w[8];
               const int e = e8m0_of(warp_max_abs(amax));
               const float qs = qscale_of(e);
               e_blk |= (uint32_t)e << (8 * b);
 #pragma unroll
               for (int i = 0; i < 8; ++i)
-                w[8 * b + i] = pack_e4m3x4(v[4 * i] * qs, v[4 * i + 1] * qs, v[4 * i + 2] * qs, v[4 * i + 3] * qs);
+                w[i] = pack_e4m3x4(__uint_as_float(P[2 * i] << 16) * qs, __uint_as_float(P[2 * i] & 0xFFFF0000u) * qs,
+                                   __uint_as_float(P[2 * i + 1] << 16) * qs,
+                                   __uint_as_float(P[2 * i + 1] & 0xFFFF0000u) * qs);
+              // this half's 32 dz bytes of the row go to the staging tile right away
+#pragma unroll
+              for (int j = 0; j < 2; ++j)
+                st_shared_v4(stg + lane * 64 + (((2 * b + j) ^ ((lane >> 1) & 3)) << 4), w[4 * j], w[4 * j + 1],
+                             w[4 * j + 2], w[4 * j + 3]);
             }
             // y1s: one scale per column over the warp's 32 rows.  Column maxima by a butterfly on bf16 pairs that
             // halves the column set at each step: lane L ends with the pair holding column L.
+            uint32_t wy[8];
             uint32_t A[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) A[i] = Y[i] & 0x7FFF7FFFu;
@@ -662,7 +674,6 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             A[0] = max_bf16x2(A[0], __shfl_xor_sync(0xffffffff, A[0], 1));
             const int e_mine = e8m0_of(__uint_as_float((lane & 1) ? (A[0] & 0xFFFF0000u) : (A[0] << 16)));
             const float qs_mine = qscale_of(e_mine);
-            uint32_t wy[8];
 #pragma unroll
             for (int i4 = 0; i4 < 8; ++i4) {
               float qv[4];
@@ -674,12 +685,6 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
               }
               wy[i4] = pack_e4m3x4(qv[0], qv[1], qv[2], qv[3]);
             }
-            if (lane == 0) bulk_wait_group_read<0>();    // the previous chunk's stores have read the staging
-            __syncwarp();
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-              st_shared_v4(stg + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4), w[4 * j], w[4 * j + 1], w[4 * j + 2],
-                           w[4 * j + 3]);
 #pragma unroll
             for (int j = 0; j < 2; ++j)
               st_shared_v4(stg + 2048 + lane * 32 + ((j ^ ((lane >> 2) & 1)) << 4), wy[4 * j], wy[4 * j + 1],
