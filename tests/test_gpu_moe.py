@@ -230,3 +230,52 @@ def test_all_masked_and_single_token(sm):
     sm.ops.check_status(DEV)
     check("out", out, gold["o"], cos_min=0.99, rr_max=0.12)     # 256 values: loose statistics
     check("dx", xd.grad, gold["dx"], cos_min=0.99, rr_max=0.12)
+
+
+def test_mlp_node_split_half_experts_and_main_grad_flush(sm):
+    """SonicMoEMlpNode on dispatched rows: per-expert split-half weights in, per-expert main_grad in the
+    framework's layouts out (after step()), two micro-batches accumulated."""
+    from sonicmoe.ernie_compat import SonicMoEMlpNode
+    T, H, I, E, K = 768, 512, 256, 8, 4
+    x, dy, w1, w2, _, _ = make_layer(T, H, I, E, K, 21)
+    idx, scores = masked_routing(T, E, K, E, 22)
+
+    class Lin:
+        def __init__(self, w):
+            self.weight = w
+
+    class Expert:
+        def __init__(self, e):
+            # split-half [H, 2I]: gates are the even rows of the interleaved w1, ups the odd rows
+            self.up_gate_proj = Lin(torch.cat([w1[e, 0::2].T, w1[e, 1::2].T], dim=1).contiguous().to(DEV))
+            self.down_proj = Lin(w2[e].T.contiguous().to(DEV))
+
+    experts = [Expert(e) for e in range(E)]
+    node = SonicMoEMlpNode(experts, E, H, I)
+    counts = torch.bincount(idx[idx >= 0].long(), minlength=E)
+    outs = []
+    for _ in range(2):
+        xd = x.to(DEV).requires_grad_(True)
+        pd = scores.to(DEV).requires_grad_(True)
+        out = node(xd, counts.tolist(), idx.to(DEV), pd)
+        out.backward(dy.to(DEV))
+        outs.append((out.detach(), xd.grad, pd.grad))
+    node.step()
+    torch.cuda.synchronize()
+    sm.ops.check_status(DEV)
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    md = R.topk_metadata(idx, scores, E, 128)
+    gold = OM.moe_fp32(x, w1, w2, md, dy)
+    emu = OM.moe_fp8_emulated(x, w1, w2, md, dy)
+    check("node out", outs[0][0], gold["o"], emu=emu["o"])
+    check("node dx", outs[0][1], gold["dx"], emu=emu["dx"])
+    # per-expert main_grad, framework layouts, two micro-batches
+    g1 = torch.stack([e.up_gate_proj.weight.main_grad for e in experts]).cpu() / 2       # [E, H, 2I] split-half
+    g2 = torch.stack([e.down_proj.weight.main_grad for e in experts]).cpu() / 2          # [E, I, H]
+    to_split = lambda d: torch.cat([d[:, 0::2].transpose(1, 2), d[:, 1::2].transpose(1, 2)], dim=2)
+    check("node dw1 (split-half)", g1, to_split(gold["dw1"]), emu=to_split(emu["dw1"]))
+    check("node dw2 [E,I,H]", g2, gold["dw2_IH"], emu=emu["dw2_IH"])
+    # a second step() without a backward in between must not flush again
+    before = experts[0].up_gate_proj.weight.main_grad.clone()
+    node.step()
+    assert torch.equal(before, experts[0].up_gate_proj.weight.main_grad)
