@@ -40,13 +40,17 @@ class SonicMoEConfig:
     def __post_init__(self) -> None:
         if self.use_fp8 is True and self.use_quack_gemm is None:
             self.use_quack_gemm = True
-        if self.recompute_z:
-            raise NotImplementedError("recompute_z is not built (z is saved as e4m3 + ue8m0 scales)")
         if self.swiglu_clamp_value:
             raise NotImplementedError("swiglu_clamp_value is not built")
 
     def resolve_use_fp8(self) -> bool:
         return bool(self.use_fp8)
+
+    def resolve_recompute_z(self) -> bool:
+        """Drop z after the forward and regenerate it in the backward by re-running the up-projection GEMM
+        (sonicmoe/config.py:154-170, functional/__init__.py:884-903,2047-2053 of the reference): trades one extra
+        up-projection per step for TKp x 2I bytes (+ scales) of saved activations per layer."""
+        return bool(self.recompute_z)
 
     @contextmanager
     def activate(self):

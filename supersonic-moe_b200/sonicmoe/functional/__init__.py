@@ -18,6 +18,7 @@ Dataflow (one code path, MXFP8 1x32 ue8m0 everywhere a GEMM runs):
 from __future__ import annotations
 
 import os
+import weakref
 from contextlib import contextmanager
 
 import torch
@@ -122,7 +123,9 @@ def weight_fp8(w: torch.Tensor, transposed: bool):
     key = (w.data_ptr(), tuple(w.shape), tuple(w.stride()), transposed, w.device.index)
     ver = base._version
     hit = _WEIGHT_CACHE.get(key)
-    if hit is not None and hit[0] == ver:
+    # address + version are not enough: a freed weight's address is handed out again by the caching allocator,
+    # with a fresh version counter that can coincide - the entry also remembers WHICH tensor it was made from
+    if hit is not None and hit[0] == ver and hit[3]() is base:
         return hit[1], hit[2]
     with torch.no_grad():
         src = w.detach().transpose(1, 2) if transposed else w.detach()
@@ -134,7 +137,7 @@ def weight_fp8(w: torch.Tensor, transposed: bool):
         q = q.view(E, N, K)
     if len(_WEIGHT_CACHE) >= _WEIGHT_CACHE_MAX:
         _WEIGHT_CACHE.pop(next(iter(_WEIGHT_CACHE)))
-    _WEIGHT_CACHE[key] = (ver, q, sf)
+    _WEIGHT_CACHE[key] = (ver, q, sf, weakref.ref(base))
     return q, sf
 
 
@@ -237,6 +240,13 @@ class _UpProjection(torch.autograd.Function):
             z_q, z_sc, y1_q, y1_sf = ops.gemm_gated(xg_q, None, a_sf, w1_q, w1_sf, efo, TKp)
             del xg_q
         link = {"y1": (y1_q, y1_sf), "z": (z_q, z_sc)}
+        cfg = fp8_config if fp8_config is not None else get_active_config()
+        if cfg is not None and cfg.resolve_recompute_z() and not is_inference:
+            # keep what regenerates z instead of z itself; the backward re-runs this GEMM and gets the same bytes
+            link["z"] = None
+            link["z_recompute"] = (x if prequant_payload is None else None, x_q, x_raw, w1, efo, x_gather_idx,
+                                   s_scatter_idx, s_rev, naept, TKp)
+            del z_q, z_sc
         _HANDOFF.append(link)
         ctx.link = link
         ctx.T = x.shape[0]
@@ -284,6 +294,26 @@ class _UpProjection(torch.autograd.Function):
         return (dx, dw1) + (None,) * 15
 
 
+def _recompute_z(args):
+    """z as e4m3 + raw scales, regenerated from the up-projection's inputs (same kernels, same bytes as the
+    forward produced; the re-computed y1 is discarded)."""
+    x, x_q, x_raw, w1, efo, x_gather_idx, s_scatter_idx, s_rev, naept, TKp = args
+    H = w1.shape[2]
+    w1_q, w1_sf = weight_fp8(w1, False)
+    if USE_TMA_GATHER:
+        if x_q is None:
+            x_q, x_raw, _ = ops.quant_rows(x.contiguous(), raw=True)
+        a_sf = ops.gather_scales_isa(x_raw, x_gather_idx, TKp, H)
+        z_q, z_sc, _, _ = ops.gemm_gated(x_q, x_gather_idx, a_sf, w1_q, w1_sf, efo, TKp)
+    else:
+        if x_q is not None:
+            xg_q, a_sf = ops.gather_rows_fp8(x_q, x_raw, x_gather_idx, TKp, efo[-1:])
+        else:
+            xg_q, a_sf = ops.quant_rows_scatter(x.contiguous(), naept, s_rev, s_scatter_idx, TKp, efo[-1:])
+        z_q, z_sc, _, _ = ops.gemm_gated(xg_q, None, a_sf, w1_q, w1_sf, efo, TKp)
+    return z_q, z_sc
+
+
 class _DownProjection(torch.autograd.Function):
     @classmethod
     def apply(cls, y1, z, w2, b2, topk_scores, selected_experts, expert_frequency_offset, T, K, stream_id,
@@ -321,7 +351,8 @@ class _DownProjection(torch.autograd.Function):
     def backward(ctx, dout):
         w2, topk_scores, efo, x_gather_idx, s_scatter_idx, s_rev, naept, src_idx = ctx.saved_tensors
         link = ctx.link
-        z_q, z_sc = link.pop("z")
+        z_saved = link.pop("z")
+        z_q, z_sc = z_saved if z_saved is not None else _recompute_z(link.pop("z_recompute"))
         E, H, I = w2.shape
         TKp = z_q.shape[0]
         s = ops.gather_scores(topk_scores, s_scatter_idx)

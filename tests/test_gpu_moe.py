@@ -279,3 +279,49 @@ def test_mlp_node_split_half_experts_and_main_grad_flush(sm):
     before = experts[0].up_gate_proj.weight.main_grad.clone()
     node.step()
     assert torch.equal(before, experts[0].up_gate_proj.weight.main_grad)
+
+
+def test_recompute_z_gives_the_same_bits_and_does_not_keep_z(sm):
+    """`SonicMoEConfig(recompute_z=True)`: z is dropped after the forward and regenerated in the backward by the
+    same kernels, so every output and gradient is bit-identical to the default (z saved)."""
+    T, H, I, E, K = 1024, 512, 256, 8, 4
+    x, dy, w1, w2, _, _ = make_layer(T, H, I, E, K, 31)
+    idx, scores = masked_routing(T, E, K, E, 32)
+
+    def run(cfg):
+        xd = x.to(DEV).requires_grad_(True)
+        sd = scores.to(DEV).requires_grad_(True)
+        w1d, w2d = w1.to(DEV).requires_grad_(True), w2.to(DEV).requires_grad_(True)
+        out = sm.run_sonic_moe(xd, idx.to(DEV), sd, K, E, w1d, w2d, fp8=True, fp8_config=cfg)
+        links = [f for f in (out.grad_fn, ) if f is not None]
+        out.backward(dy.to(DEV))
+        torch.cuda.synchronize()
+        sm.ops.check_status(DEV)
+        return out.detach(), xd.grad, sd.grad, w1d.grad, w2d.grad
+
+    base = run(None)
+    rec = run(sm.SonicMoEConfig(use_fp8=True, recompute_z=True))
+    for name, a, b in zip(("out", "dx", "ds", "dw1", "dw2"), base, rec):
+        assert torch.equal(a, b), name
+    # and through the thread-local activation, as the reference's callers set it
+    with sm.SonicMoEConfig(use_fp8=True, recompute_z=True).activate():
+        act = run(None)
+    for a, b in zip(base, act):
+        assert torch.equal(a, b)
+
+
+def test_weight_cache_is_not_fooled_by_a_recycled_address(sm):
+    """A weight that is freed and another of the same shape allocated at the same address (the caching allocator
+    does that) must not be served the first one's FP8 copy."""
+    from sonicmoe.functional import weight_fp8
+    g = torch.Generator().manual_seed(5)
+    a = (torch.randn(4, 256, 128, generator=g) * 0.02).to(torch.bfloat16).to(DEV)
+    qa = weight_fp8(a, False)[0].clone()
+    ptr = a.data_ptr()
+    del a
+    b = (torch.randn(4, 256, 128, generator=g) * 0.02).to(torch.bfloat16).to(DEV)
+    if b.data_ptr() != ptr:
+        pytest.skip("allocator did not recycle the address")
+    qb = weight_fp8(b, False)[0]
+    want = sm.ops.quant_rows(b.view(4 * 256, 128), raw=False, isa=True)[0].view(4, 256, 128)
+    assert torch.equal(qb, want) and not torch.equal(qb, qa)
