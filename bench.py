@@ -62,15 +62,25 @@ def make_inputs(cfg, device, T=None):
     expert permutation when skewed); top-K of the logits, softmax over the K selected."""
     T = T or cfg["T"]
     H, I, E, K = cfg["H"], cfg["I"], cfg["E"], cfg["K"]
-    g = torch.Generator().manual_seed(cfg["seed"])
-    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
-    dy = torch.randn(T, H, generator=g).to(torch.bfloat16)
-    w1 = (torch.randn(E, 2 * I, H, generator=g) * 0.02).to(torch.bfloat16)
-    w2 = (torch.randn(E, H, I, generator=g) * 0.02).to(torch.bfloat16)
-    logits = torch.randn(T, E, generator=g)
+    # the largest config (C5: 2.4 G weight elements) is drawn on the device, expert by expert, from a seeded
+    # device generator: the host-side draw would need tens of GB of fp32 scratch; everything else is drawn on the
+    # host so that the numbers match the CPU oracle's inputs
+    big = E * 2 * I * H > (1 << 30)
+    gdev = torch.device(device) if big else torch.device("cpu")
+    g = torch.Generator(device=gdev).manual_seed(cfg["seed"])
+    rn = lambda *shape: torch.randn(*shape, generator=g, device=gdev)
+    x = rn(T, H).to(torch.bfloat16)
+    dy = rn(T, H).to(torch.bfloat16)
+    if big:
+        w1 = torch.stack([(rn(2 * I, H) * 0.02).to(torch.bfloat16) for _ in range(E)])
+        w2 = torch.stack([(rn(H, I) * 0.02).to(torch.bfloat16) for _ in range(E)])
+    else:
+        w1 = (rn(E, 2 * I, H) * 0.02).to(torch.bfloat16)
+        w2 = (rn(E, H, I) * 0.02).to(torch.bfloat16)
+    logits = rn(T, E)
     if cfg["skew"]:
-        p = torch.arange(1, E + 1, dtype=torch.float32) ** -1.2
-        logits = logits + torch.log(p / p.sum())[torch.randperm(E, generator=g)]
+        p = torch.arange(1, E + 1, dtype=torch.float32, device=gdev) ** -1.2
+        logits = logits + torch.log(p / p.sum())[torch.randperm(E, generator=g, device=gdev)]
     vals, idx = logits.topk(K, dim=-1)
     scores = torch.softmax(vals, dim=-1)
     return dict(x=x, dy=dy, w1=w1, w2=w2, idx=idx.to(torch.int32), scores=scores.float())
@@ -247,7 +257,7 @@ def _measure(args, cname, world, rank, dev, dist, sonicmoe, ops):
     cfg = CONFIGS[cname]
     E, K, H, I, T = cfg["E"], cfg["K"], cfg["H"], cfg["I"], cfg["T"]
     inp = make_inputs(cfg, dev)
-    pin = {k: inp[k].pin_memory() for k in ("x", "dy", "idx", "scores")}
+    pin = {k: inp[k].cpu().pin_memory() for k in ("x", "dy", "idx", "scores")}
     if world > 1:
         from sonicmoe.ep import ExpertParallelMoE
         assert E % world == 0
@@ -439,7 +449,7 @@ def _measure(args, cname, world, rank, dev, dist, sonicmoe, ops):
                                     "tensor rate is twice the bf16 rate"},
         "kernel_us": breakdown,
     }
-    if world == 1:
+    if world == 1 and cname in ("C2", "P1"):
         line["full_layer"] = _full_layer(args, cfg, inp, dev, sonicmoe, ops)
     if world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_reference(cfg)

@@ -120,7 +120,12 @@ template <int MODE>
 static int pick_bn2(int64_t N) {
   if (g_force_v1) return 0;
   const bool wide = (MODE == PLAIN || MODE == WGRAD || MODE == GATED);      // single-stage 256-column tiles
-  if (MODE == DGATEDQ) return (N % 192 == 0 && g_force_bn != 128) ? 192 : 128;
+  if (MODE == DGATEDQ) {
+    // 192-column tiles also when N is not a multiple of 192, with a ragged last tile, as long as that wastes
+    // at most a tenth of the columns (N = 4096: 22 tiles for 21.3)
+    const int64_t padded = (N + 191) / 192 * 192;
+    return ((N % 192 == 0 || padded * 10 <= N * 11) && g_force_bn != 128) ? 192 : 128;
+  }
   if (g_force_bn == 128) return 128;
   if (g_force_bn == 192) return (N % 192 == 0) ? 192 : 128;
   if (g_force_bn == 256) return (wide && N % 256 == 0) ? 256 : 128;
@@ -144,7 +149,7 @@ static int run2(const void* a, int64_t a_rows, int64_t a_cols, const void* b, in
   // upper bound of pair tiles: varlen-M: every expert may add one half-empty pair
   int64_t pair_tiles;
   if (MODE == WGRAD) pair_tiles = (int64_t)p.E * (p.rows / 256) * (p.N / bn);
-  else pair_tiles = ((int64_t)p.rows / 256 + p.E) * (p.N / bn);
+  else pair_tiles = ((int64_t)p.rows / 256 + p.E) * ((p.N + bn - 1) / bn);
   if (bn == 256) {
     constexpr int M256 = (MODE == PLAIN || MODE == WGRAD || MODE == GATED) ? MODE : PLAIN;   // only the wide modes reach here
     return launch2<256, M256>(ta, tb, tsa, tsb, om, p, pair_tiles, stream);
@@ -282,7 +287,7 @@ int smoe_gemm_dgated_fused(const void* dout_fp8, const void* a_sf, const void* w
 
 int64_t smoe_gemm_dgated_fused_partials(int64_t N) {
   const int bn = pick_bn2<DGATEDQ>(N);
-  return (bn == 192 ? Gemm2Smem<192, DGATEDQ>::COL_GROUPS : Gemm2Smem<128, DGATEDQ>::COL_GROUPS) * (N / bn);
+  return (bn == 192 ? Gemm2Smem<192, DGATEDQ>::COL_GROUPS : Gemm2Smem<128, DGATEDQ>::COL_GROUPS) * ((N + bn - 1) / bn);
 }
 
 int64_t smoe_gemm_dgated_partials(int64_t N) {

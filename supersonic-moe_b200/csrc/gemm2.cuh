@@ -152,7 +152,7 @@ template <int BN, int MODE>
 __device__ __forceinline__ PairTile pair_tile(int tile, int rank, const GemmParams& p, const int* s_efo,
                                               const int* s_pairs) {
   PairTile t;
-  const int n_tiles = p.N / BN;
+  const int n_tiles = (p.N + BN - 1) / BN;     // DGATEDQ may run a ragged last column tile
   if (MODE == WGRAD) {
     const int m_pairs = p.rows / (2 * BM);
     const int per_e = m_pairs * n_tiles;
@@ -248,7 +248,8 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t sf_base = smem_u32(sfring);
-  const int n_total = (MODE == WGRAD) ? p.E * (p.rows / (2 * BM)) * (p.N / BN) : s_pairs[p.E] * (p.N / BN);
+  const int n_col_tiles = (p.N + BN - 1) / BN;
+  const int n_total = (MODE == WGRAD) ? p.E * (p.rows / (2 * BM)) * n_col_tiles : s_pairs[p.E] * n_col_tiles;
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer (both CTAs)
@@ -395,7 +396,7 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       uint4 zb[4];
       uint32_t sc = 0;
       float s_row = 0.f;
-      if (MODE == DGATEDQ && t.valid) {
+      if (MODE == DGATEDQ && t.valid && c_base < p.N) {
         const int Nz = 2 * p.N;
         const uint8_t* zrow = p.z_fp8 + grow * Nz + 2 * c_base;
 #pragma unroll
@@ -578,7 +579,9 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         // per column and 32 rows - and leave as e4m3 in row-major order.  A 32x32-block scale serves dz both as
         // the activation-gradient operand (scales along 2I) and as the weight-gradient operand (scales along
         // TKp, fed MN-major), so one copy of the payload is enough.  Each warp works on its own.
-        if (t.valid && !(p.debug_skip_store & 2)) {
+        // a ragged last column tile (N not a multiple of BN): chunks at or beyond column N hold products with
+        // rows of the next expert's weights (or TMA zero fill) and are skipped whole (N is a multiple of 32)
+        if (t.valid && c_base < p.N && !(p.debug_skip_store & 2)) {
           const int Nz = 2 * p.N;
           const float s = s_row;
           const int row_grp = (t.m0 + q * 32) >> 5;      // 32-row group index along TKp
@@ -588,12 +591,13 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 #pragma unroll 1
           for (int c = 0; c < NCH; ++c) {
             const int dcol = c_base + c * 32;            // first D / y1s column of the chunk
+            if (dcol >= p.N) break;
             uint32_t r0[16], r1[16];                     // the accumulator arrives in two 16-column halves
             tmem_ld16(t_row + c * 32, r0);
             tmem_ld16(t_row + c * 32 + 16, r1);
             uint4 zn[4];
             uint32_t scn = 0;
-            if (c + 1 < NCH) {                           // next chunk's z travels while this one is computed
+            if (c + 1 < NCH && dcol + 32 < p.N) {        // next chunk's z travels while this one is computed
               const uint8_t* zrow = p.z_fp8 + grow * Nz + 2 * (dcol + 32);
 #pragma unroll
               for (int i = 0; i < 4; ++i) zn[i] = reinterpret_cast<const uint4*>(zrow)[i];

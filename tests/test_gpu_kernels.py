@@ -485,8 +485,9 @@ def test_gemm_wgrad_mn_major_operands(ops, layout, M, N, tiles):
             assert cos > 0.9999 and rr < 1e-3, (e, cos, rr)
 
 
+# I = 2048 is not a multiple of 192: the fused kernel runs 11 column tiles, the last one ragged (128 of 192 columns)
 @pytest.mark.parametrize("bn", [0, 128])
-@pytest.mark.parametrize("T,H,I,tiles", GATED_SHAPES)
+@pytest.mark.parametrize("T,H,I,tiles", GATED_SHAPES + [(600, 256, 2048, [2, 1, 3])])
 def test_gemm_dgated_fused_quantizers_match_separate_kernels(ops, T, H, I, tiles, bn):
     """The fused epilogue must emit exactly the bytes of dgated -> quant_iso32(dz) / quant_cols_t(y1s)."""
     from sonicmoe._lib import lib
@@ -518,7 +519,9 @@ def test_gemm_dgated_fused_quantizers_match_separate_kernels(ops, T, H, I, tiles
     assert torch.equal(Q.unpack_isa(f_rsf.cpu(), rows, 2 * I)[:n], Q.unpack_isa(r_rsf.cpu(), rows, 2 * I)[:n])
     assert torch.equal(Q.unpack_isa(f_csf.cpu(), 2 * I, rows)[:, :n // 32], Q.unpack_isa(r_csf.cpu(), 2 * I, rows)[:, :n // 32])
     assert torch.equal(Q.unpack_isa(f_ysf.cpu(), I, rows)[:, :n // 32], Q.unpack_isa(r_ysf.cpu(), I, rows)[:, :n // 32])
-    assert torch.equal(f_dsp.sum(0)[:n], dsp.sum(0)[:n]) or torch.allclose(f_dsp.sum(0)[:n], dsp.sum(0)[:n], rtol=1e-5)
+    # ds partials are summed over column tiles of different widths in the two kernels: fp32 re-association only
+    a, b = f_dsp.sum(0)[:n], dsp.sum(0)[:n]
+    assert torch.equal(a, b) or torch.allclose(a, b, rtol=1e-5, atol=1e-5 * float(b.abs().max()))
 
 
 @pytest.mark.parametrize("T,K,E,world", [(333, 4, 16, 4), (1000, 8, 8, 8), (64, 2, 6, 2)])
