@@ -140,6 +140,13 @@ int smoe_gather_scales_isa(const void* raw_scales, const int32_t* idx, int64_t r
 int smoe_gather_rows_fp8(const void* q, const void* raw_scales, const int32_t* idx, const int32_t* valid_rows,
                          int64_t rows, int64_t K, void* q_out, void* isa_out, void* stream);
 
+/* Same result in scatter form (pad rows zero instead of a copy of row idx[r]): every source row is read once and
+ * written to its positions s_rev[naept[t] .. naept[t+1]); used for the e4m3 payload an expert-parallel dispatch
+ * delivers, where a received row feeds several local experts. */
+int smoe_scatter_rows_fp8(const void* q, const void* raw_scales, int64_t T, int64_t K, const int32_t* naept,
+                          const int32_t* s_rev, const int32_t* s_scatter_idx, const int32_t* valid_rows, int64_t rows,
+                          void* q_out, void* isa_out, void* stream);
+
 /* Column-wise (groups of 32 consecutive rows) of src[idx] (idx may be null): src bf16 [T,dim] ->
  *   q_t  e4m3 [dim, rows]  (TRANSPOSED: the reduction dimension of the weight-gradient GEMM is contiguous)
  *   isa  ISA-packed scales for the logical (dim, rows) operand.

@@ -210,6 +210,57 @@ gather_rows_kernel(const uint4* __restrict__ q, const uint8_t* __restrict__ raw,
         *reinterpret_cast<const uint32_t*>(raw + src * groups + kt * 4);
 }
 
+// ------------------------------------------------------------- row scatter (already quantised rows)
+// The scatter form of gather_rows_kernel: every source row (e4m3 bytes + raw 1x32 scales) is read once and written
+// to each expert-sorted position it occupies, s_rev[naept[t] .. naept[t+1]); pad rows are zero-filled by the
+// trailing blocks, as in quant_rows_scatter_kernel.  One warp per source row.
+__global__ void __launch_bounds__(256)
+scatter_rows_fp8_kernel(const uint4* __restrict__ q, const uint8_t* __restrict__ raw, int64_t T, int K,
+                        const int* __restrict__ naept, const int* __restrict__ s_rev,
+                        const int* __restrict__ s_scatter, const int* __restrict__ valid_rows, int64_t rows,
+                        uint4* __restrict__ out, uint8_t* __restrict__ isa, int token_blocks) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int k_tiles = K >> 7, k16 = K >> 4, groups = K >> 5;
+  if ((int)blockIdx.x < token_blocks) {
+    const int64_t t = (int64_t)blockIdx.x * nw + warp;
+    if (t >= T) return;
+    const int beg = naept[t], end = naept[t + 1];
+    if (beg == end) return;
+    for (int c0 = 0; c0 < k16; c0 += 32 * 4) {          // four 16-byte loads in flight per lane
+      uint4 v[4];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const int c = c0 + b * 32 + lane;
+        v[b] = c < k16 ? q[t * k16 + c] : make_uint4(0, 0, 0, 0);
+      }
+      for (int j = beg; j < end; ++j) {
+        const int64_t pos = s_rev[j];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const int c = c0 + b * 32 + lane;
+          if (c < k16) out[pos * k16 + c] = v[b];
+        }
+      }
+    }
+    for (int kt = lane; kt < k_tiles; kt += 32) {
+      const uint32_t word = *reinterpret_cast<const uint32_t*>(raw + t * groups + kt * 4);
+      for (int j = beg; j < end; ++j)
+        *reinterpret_cast<uint32_t*>(isa + isa_offset((size_t)s_rev[j], (size_t)kt * 4, k_tiles)) = word;
+    }
+  } else {
+    const int real_tk = naept[T];
+    const int64_t m_end = valid_rows ? min((int64_t)*valid_rows, rows) : rows;
+    const int64_t w0 = (int64_t)(blockIdx.x - token_blocks) * nw + warp;
+    const int64_t nwarps = (int64_t)(gridDim.x - token_blocks) * nw;
+    for (int64_t row = w0; row < m_end; row += nwarps) {
+      if (s_scatter[row] < real_tk) continue;
+      for (int c = lane; c < k16; c += 32) out[row * k16 + c] = make_uint4(0, 0, 0, 0);
+      for (int kt = lane; kt < k_tiles; kt += 32)
+        *reinterpret_cast<uint32_t*>(isa + isa_offset(row, (size_t)kt * 4, k_tiles)) = 0u;
+    }
+  }
+}
+
 // ------------------------------------------------------------------ columns
 // Tile = 128 rows x 64 columns of src[idx].  Groups run down the rows; the
 // e4m3 bytes are written transposed ([dim, rows]) so that the reduction
@@ -523,6 +574,20 @@ int smoe_quant_dual_gather(const void* x_bf16, const int32_t* idx, const int32_t
   else
     quant_dual_kernel<false><<<blocks, 128, 0, (cudaStream_t)stream>>>(
         (const uint4*)x_bf16, idx, valid_rows, rows, (int)K, nullptr, nullptr, (uint2*)q_col, (uint8_t*)col_isa);
+  return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
+}
+
+int smoe_scatter_rows_fp8(const void* q, const void* raw_scales, int64_t T, int64_t K, const int32_t* naept,
+                          const int32_t* s_rev, const int32_t* s_scatter_idx, const int32_t* valid_rows, int64_t rows,
+                          void* q_out, void* isa_out, void* stream) {
+  if (T < 0 || rows < 0 || K <= 0 || K % 128) return SMOE_ERR_SHAPE;
+  if (((uintptr_t)q & 15) || ((uintptr_t)q_out & 15) || ((uintptr_t)raw_scales & 3)) return SMOE_ERR_ALIGN;
+  if (rows == 0) return SMOE_OK;
+  const int token_blocks = (int)((T + 7) / 8);
+  const int pad_blocks = 148;
+  scatter_rows_fp8_kernel<<<(unsigned)(token_blocks + pad_blocks), 256, 0, (cudaStream_t)stream>>>(
+      (const uint4*)q, (const uint8_t*)raw_scales, T, (int)K, naept, s_rev, s_scatter_idx, valid_rows, rows,
+      (uint4*)q_out, (uint8_t*)isa_out, token_blocks);
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }
 

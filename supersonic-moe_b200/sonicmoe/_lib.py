@@ -29,6 +29,7 @@ SIGNATURES = {
     "smoe_quant_rows_scatter": (_I, [_P, _L, _L, _P, _P, _P, _P, _L, _P, _P, _P]),
     "smoe_gather_scales_isa": (_I, [_P, _P, _L, _L, _P, _P]),
     "smoe_gather_rows_fp8": (_I, [_P, _P, _P, _P, _L, _L, _P, _P, _P]),
+    "smoe_scatter_rows_fp8": (_I, [_P, _P, _L, _L, _P, _P, _P, _P, _L, _P, _P, _P]),
     "smoe_quant_cols_t": (_I, [_P, _P, _L, _L, _P, _P, _P]),
     "smoe_requant_cols_t": (_I, [_P, _P, _P, _L, _L, _P, _P, _P]),
     "smoe_quant_iso32": (_I, [_P, _L, _L, _P, _P, _P, _P, _P]),

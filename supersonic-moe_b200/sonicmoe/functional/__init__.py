@@ -234,7 +234,7 @@ class _UpProjection(torch.autograd.Function):
             z_q, z_sc, y1_q, y1_sf = ops.gemm_gated(x_q, x_gather_idx, a_sf, w1_q, w1_sf, efo, TKp)
         else:
             if x_q is not None:
-                xg_q, a_sf = ops.gather_rows_fp8(x_q, x_raw, x_gather_idx, TKp, efo[-1:])
+                xg_q, a_sf = ops.scatter_rows_fp8(x_q, x_raw, naept, s_rev, s_scatter_idx, TKp, efo[-1:])
             else:      # quantise straight into expert-sorted order
                 xg_q, a_sf = ops.quant_rows_scatter(x.contiguous(), naept, s_rev, s_scatter_idx, TKp, efo[-1:])
             z_q, z_sc, y1_q, y1_sf = ops.gemm_gated(xg_q, None, a_sf, w1_q, w1_sf, efo, TKp)
@@ -307,7 +307,7 @@ def _recompute_z(args):
         z_q, z_sc, _, _ = ops.gemm_gated(x_q, x_gather_idx, a_sf, w1_q, w1_sf, efo, TKp)
     else:
         if x_q is not None:
-            xg_q, a_sf = ops.gather_rows_fp8(x_q, x_raw, x_gather_idx, TKp, efo[-1:])
+            xg_q, a_sf = ops.scatter_rows_fp8(x_q, x_raw, naept, s_rev, s_scatter_idx, TKp, efo[-1:])
         else:
             xg_q, a_sf = ops.quant_rows_scatter(x.contiguous(), naept, s_rev, s_scatter_idx, TKp, efo[-1:])
         z_q, z_sc, _, _ = ops.gemm_gated(xg_q, None, a_sf, w1_q, w1_sf, efo, TKp)
@@ -376,7 +376,7 @@ class _DownProjection(torch.autograd.Function):
             dz, y1s, dsp = ops.gemm_dgated(dout_q, x_gather_idx, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, TKp)
         else:
             if dout_q is not None:
-                dg_q, a_sf = ops.gather_rows_fp8(dout_q, dout_raw, x_gather_idx, TKp, efo[-1:])
+                dg_q, a_sf = ops.scatter_rows_fp8(dout_q, dout_raw, naept, s_rev, s_scatter_idx, TKp, efo[-1:])
             else:
                 # row scales in scatter form (each token read once: 68 us on T=8192, H=3072, K=8), column scales
                 # in a second, gathered pass (93 us); the one-pass dual kernel measured 209 us there

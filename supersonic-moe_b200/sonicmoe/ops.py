@@ -219,6 +219,19 @@ def gather_rows_fp8(q, raw, idx, rows, valid_rows=None):
 
 
 @_timed
+def scatter_rows_fp8(q, raw, naept, s_rev, s_scatter_idx, rows, valid_rows=None):
+    """q u8 [T,K], raw scales u8 [T,K/32] -> (rows in expert-sorted order [rows,K], ISA scales of (rows,K)); each
+    source row is read once and written to all its positions; pad rows are zero."""
+    _cuda(q, raw, naept, s_rev, s_scatter_idx, valid_rows)
+    T, K = q.shape
+    out = torch.empty(rows, K, dtype=_U8, device=q.device)
+    isa = torch.empty(isa_bytes(rows, K), dtype=_U8, device=q.device)
+    check(lib.smoe_scatter_rows_fp8(_p(q), _p(raw), T, K, _p(naept), _p(s_rev), _p(s_scatter_idx), _p(valid_rows),
+                                    rows, _p(out), _p(isa), _stream()), "scatter_rows_fp8")
+    return out, isa
+
+
+@_timed
 def quant_cols_t(src, idx, rows):
     """bf16 [T,dim] (rows gathered by idx, or None) -> (e4m3 bytes [dim, rows], ISA scales for (dim, rows))."""
     _cuda(src, idx)

@@ -155,6 +155,29 @@ def test_gather_rows_fp8(ops):
     assert torch.equal(Q.unpack_isa(isa.cpu(), rows, K)[:valid], raw[idx.long()][:valid])
 
 
+@pytest.mark.parametrize("N,K,E,topk,p_mask", [(300, 512, 8, 4, 0.3), (1000, 3072, 16, 8, 0.0), (64, 128, 4, 2, 0.9)])
+def test_scatter_rows_fp8_matches_gather_form(ops, N, K, E, topk, p_mask):
+    """Scatter form of the row copy = gather form on real rows; pad rows are zero (bytes and scales)."""
+    idx, probs = make_routing(N, topk, E, p_mask, seed=N + K)
+    md = ops.topk_metadata(idx.to(DEV), probs.to(DEV), E, 128)
+    g = torch.Generator().manual_seed(K)
+    q = torch.randint(0, 256, (N, K), generator=g, dtype=torch.uint8).to(DEV)
+    raw = torch.randint(0, 256, (N, K // 32), generator=g, dtype=torch.uint8).to(DEV)
+    rows = md["TKp_alloc"]
+    valid = md["efo"][-1:]
+    got_q, got_isa = ops.scatter_rows_fp8(q, raw, md["naept"], md["s_reverse_scatter_idx"], md["s_scatter_idx"],
+                                          rows, valid)
+    ref_q, ref_isa = ops.gather_rows_fp8(q, raw, md["x_gather_idx"], rows, valid)
+    torch.cuda.synchronize()
+    n = int(valid)
+    real_tk = int(md["naept"][-1])
+    real = (md["s_scatter_idx"][:n] < real_tk).cpu()
+    assert torch.equal(got_q[:n].cpu()[real], ref_q[:n].cpu()[real])
+    gs, rs = Q.unpack_isa(got_isa.cpu(), rows, K)[:n], Q.unpack_isa(ref_isa.cpu(), rows, K)[:n]
+    assert torch.equal(gs[real], rs[real])
+    assert (got_q[:n].cpu()[~real] == 0).all() and (gs[~real] == 0).all()
+
+
 @pytest.mark.parametrize("T,dim,rows", [(256, 256, 512), (1000, 3072, 2048), (64, 64, 128)])
 def test_quant_cols_transposed_bit_exact(ops, T, dim, rows):
     x = adversarial_rows(T, dim, T + dim)
