@@ -35,13 +35,21 @@ CONFIGS = {
     "C5": dict(T=65536, H=6144, I=3072, E=64, K=8, seed=3, skew=False),
     # C2's layer at T=2048: small enough for multi-pass ncu captures, weights (453 MB bf16 + 226 MB fp8) >> L2
     "P1": dict(T=2048, H=3072, I=1536, E=8, K=8, seed=0, skew=False),
+    # the reference's published sweeps around C2 (README.md:343-347, HANDOFF.md:27-33)
+    "T1024": dict(T=1024, H=3072, I=1536, E=8, K=8, seed=0, skew=False),
+    "T4096": dict(T=4096, H=3072, I=1536, E=8, K=8, seed=0, skew=False),
+    "T16384": dict(T=16384, H=3072, I=1536, E=8, K=8, seed=0, skew=False),
+    "E16": dict(T=8192, H=3072, I=1536, E=16, K=8, seed=0, skew=False),
+    "E32": dict(T=8192, H=3072, I=1536, E=32, K=8, seed=0, skew=False),
 }
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the six GEMMs on C2, one 1-pass ncu capture of
 # `python bench.py --steps 1 --warmup 1 --no-cpu --lean` (profiles/gemm_dram_traffic_c2.md); key = op name and its
 # occurrence within a step
 NCU_DRAM_BYTES_C2 = {("gemm_gated", 0): 560.8e6, ("gemm_varlen_m", 0): 490.1e6, ("gemm_dgated_fused", 0): 743.4e6,
                      ("gemm_wgrad", 0): 628.5e6, ("gemm_wgrad", 1): 1064.9e6, ("gemm_varlen_m", 1): 644.6e6}
-PUBLISHED_US = {"C2": 2659.8, "C3": 8521.7}       # reference README.md:28-38,348 (its own FP8 path, 1x SM100)
+# reference README.md:28-38,343-348, HANDOFF.md:27-34 (its own FP8 path, 1x SM100)
+PUBLISHED_US = {"C2": 2659.8, "C3": 8521.7, "T1024": 566.0, "P1": 870.1, "T4096": 1459.1, "T16384": 5224.9,
+                "E16": 2800.7, "E32": 3187.5}
 FP8_PEAK_NOMINAL = 4.5e15
 # kernels launched per wrapper call (sonicmoe/ops.py)
 LAUNCHES = dict(topk_metadata=3, count_cumsum=3)
