@@ -93,6 +93,16 @@ int smoe_ep_plan_dest(const int32_t* idx, int64_t T, int64_t K, int64_t E, int64
 int smoe_ep_plan_send_idx(const int32_t* idx, const int32_t* send_tok, const int32_t* efo, int64_t n_send, int64_t K,
                           int64_t E, int64_t world, int32_t* send_idx, int32_t* send_rank, void* stream);
 
+/* Combine over NVLink peer memory: out[t,:] (bf16) = sum, in ascending destination rank and fp32, of the partial
+ * output rows the owning ranks hold for token t, read straight from their buffers (peer_bases[r]: rank r's bf16
+ * [rows,H] buffer as mapped into this process; host arrays of `world` entries).  Outgoing row i (send order) went to
+ * send_rank[i] and is row first_row[rank] + (i - send_off[rank]) there; copy_pos / copy_off list every token's
+ * outgoing rows.  The caller must order "every rank has written its buffer" before this call on the stream (any
+ * collective on that stream does).  No counterpart in the reference (DeepEP's combine plays this role outside it). */
+int smoe_ep_combine_pull(const void* const* peer_bases, const int32_t* first_row, const int32_t* send_off,
+                         int64_t world, const int32_t* copy_pos, const int32_t* copy_off, const int32_t* send_rank,
+                         void* out_bf16, int64_t T, int64_t H, void* stream);
+
 /* ---- MXFP8 1x32 ue8m0 quantizers ------------------------------------------ */
 
 /* Row-wise: x bf16 [M,K] -> e4m3 [M,K] + raw scales [M,K/32] and/or ISA-packed scales

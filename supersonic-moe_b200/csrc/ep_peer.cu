@@ -1,0 +1,92 @@
+// Expert-parallel combine over NVLink peer memory: the return exchange and the reduction of a token's copies in ONE
+// kernel.  Every rank leaves its partial outputs (one bf16 row per received token) in a buffer that all ranks of the
+// node have mapped (symmetric memory); the source rank then reads the copies of each of its tokens straight from
+// the owners' buffers with plain 16-byte loads and adds them in ascending rank order.  No receive buffer, no second
+// pass.  The kernel waits on nothing: the host orders "all ranks have written" before it with a stream-ordered
+// collective, so a rank that never arrives can at worst stall that collective, not this kernel.
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "smoe_b200.h"
+
+namespace smoe {
+
+constexpr int kMaxPeers = 16;
+
+struct PeerTable {
+  const uint4* base[kMaxPeers];   // rank r's partial-output buffer, mapped into this process
+  int first_row[kMaxPeers];       // row, in rank r's buffer, of this rank's first row sent to r
+  int send_off[kMaxPeers];        // offset of rank r's segment in this rank's send order
+};
+
+__device__ __forceinline__ void acc8(const uint4& v, float (&a)[8]) {
+  const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    a[2 * i] += __uint_as_float(u[i] << 16);
+    a[2 * i + 1] += __uint_as_float(u[i] & 0xFFFF0000u);
+  }
+}
+__device__ __forceinline__ uint32_t bf16x2_of(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// One block per token; a thread owns 8 consecutive columns.  copy_pos[copy_off[t] .. copy_off[t+1]) are the token's
+// outgoing rows in ascending destination rank; row i of the send order went to send_rank[i] and sits there at
+// first_row[rank] + (i - send_off[rank]).
+__global__ void __launch_bounds__(512)
+ep_combine_pull_kernel(PeerTable tab, const int* __restrict__ copy_pos, const int* __restrict__ copy_off,
+                       const int* __restrict__ send_rank, uint4* __restrict__ out, int H8) {
+  const int64_t t = blockIdx.x;
+  const int beg = copy_off[t], end = copy_off[t + 1];
+  for (int c = threadIdx.x; c < H8; c += blockDim.x) {
+    float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    int j = beg;
+    for (; j + 4 <= end; j += 4) {       // four remote loads in flight
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = copy_pos[j + u];
+        const int r = send_rank[i];
+        v[u] = tab.base[r][(int64_t)(tab.first_row[r] + i - tab.send_off[r]) * H8 + c];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) acc8(v[u], a);
+    }
+    for (; j < end; ++j) {
+      const int i = copy_pos[j];
+      const int r = send_rank[i];
+      acc8(tab.base[r][(int64_t)(tab.first_row[r] + i - tab.send_off[r]) * H8 + c], a);
+    }
+    out[t * H8 + c] = make_uint4(bf16x2_of(a[0], a[1]), bf16x2_of(a[2], a[3]), bf16x2_of(a[4], a[5]),
+                                 bf16x2_of(a[6], a[7]));
+  }
+}
+
+}  // namespace smoe
+
+extern "C" {
+
+int smoe_ep_combine_pull(const void* const* peer_bases, const int32_t* first_row, const int32_t* send_off,
+                         int64_t world, const int32_t* copy_pos, const int32_t* copy_off, const int32_t* send_rank,
+                         void* out_bf16, int64_t T, int64_t H, void* stream) {
+  if (world <= 0 || world > smoe::kMaxPeers || T < 0 || H <= 0 || H % 8) return SMOE_ERR_SHAPE;
+  if ((uintptr_t)out_bf16 & 15) return SMOE_ERR_ALIGN;
+  if (T == 0) return SMOE_OK;
+  smoe::PeerTable tab{};
+  for (int r = 0; r < world; ++r) {
+    if ((uintptr_t)peer_bases[r] & 15) return SMOE_ERR_ALIGN;
+    tab.base[r] = (const uint4*)peer_bases[r];
+    tab.first_row[r] = first_row[r];
+    tab.send_off[r] = send_off[r];
+  }
+  const int H8 = (int)(H / 8);
+  int threads = H8 >= 512 ? 512 : ((H8 + 31) / 32) * 32;
+  smoe::ep_combine_pull_kernel<<<(unsigned)T, threads, 0, (cudaStream_t)stream>>>(
+      tab, copy_pos, copy_off, send_rank, (uint4*)out_bf16, H8);
+  return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
+}
+
+}  // extern "C"

@@ -23,8 +23,39 @@ only the FP8 payload and the expert compute need the CUDA kernels.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
+
+# The two bf16 return exchanges (forward combine, backward dx) read the partial rows straight from the owners'
+# memory over NVLink, fused with the per-token reduction (csrc/ep_peer.cu), when the ranks can map each other's
+# memory (torch symmetric memory); SONIC_MOE_EP_PEER=0 keeps them on NCCL all-to-all + a local reduction.
+USE_PEER_COMBINE = os.getenv("SONIC_MOE_EP_PEER", "1") == "1"
+
+
+class PeerArena:
+    """A bf16 [rows, H] buffer per rank that every rank of the group has mapped.  Allocation and mapping are
+    collective calls; the size is derived from quantities all ranks share."""
+
+    def __init__(self, group, rows: int, H: int, device):
+        import torch.distributed._symmetric_memory as symm
+        self.rows, self.H = rows, H
+        self.buf = symm.empty(rows * H, dtype=torch.bfloat16, device=device)
+        self.hdl = symm.rendezvous(self.buf, group.group_name)
+        self.ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+        self.token = torch.zeros(1, dtype=torch.float32, device=device)
+        self.group = group
+
+    def view(self, n: int) -> torch.Tensor:
+        return self.buf[: n * self.H].view(n, self.H)
+
+    def holds(self, t: torch.Tensor) -> bool:
+        return t is not None and t.is_cuda and t.data_ptr() == self.buf.data_ptr() and t.is_contiguous()
+
+    def everyone_has_written(self):
+        """Stream-ordered: returns (on the stream) once every rank's earlier work on its stream is done."""
+        dist.all_reduce(self.token, group=self.group)
 
 
 class DispatchPlan:
@@ -48,15 +79,25 @@ class DispatchPlan:
             self._build_torch(idx, world)
 
     def _exchange_counts(self, rows_to, pairs, world):
-        """One small exchange + ONE read-back: rows per peer both ways and the routed pairs per local expert (the
-        receiver sums them over sources to size its expert-sorted buffers exactly)."""
-        counts = torch.cat([rows_to.view(world, 1), pairs.view(world, self.El)], dim=1).contiguous()
-        recv = torch.empty_like(counts)
-        dist.all_to_all_single(recv, counts, group=self.group)
-        host = torch.cat([counts[:, 0], recv[:, 0], recv[:, 1:].sum(dim=0).to(counts.dtype)]).tolist()
-        self.send_counts, self.recv_counts = host[:world], host[world:2 * world]
-        self.tokens_per_local_expert = host[2 * world:]
+        """One small all-gather + ONE read-back gives every rank the whole picture: rows each rank sends to each
+        other rank, routed pairs per expert (summed over sources they size the expert-sorted buffers exactly) and
+        every rank's token count."""
+        me = dist.get_rank(self.group)
+        El = self.El
+        row = torch.cat([rows_to.reshape(-1).to(torch.int64), pairs.reshape(-1).to(torch.int64),
+                         torch.tensor([self.T], dtype=torch.int64, device=rows_to.device)])
+        parts = [torch.empty_like(row) for _ in range(world)]
+        dist.all_gather(parts, row.contiguous(), group=self.group)
+        M = torch.stack(parts).tolist()
+        self.send_counts = [int(v) for v in M[me][:world]]
+        self.recv_counts = [int(M[s][me]) for s in range(world)]
+        self.tokens_per_local_expert = [sum(int(M[s][world + me * El + j]) for s in range(world)) for j in range(El)]
         self.n_send, self.n_recv = sum(self.send_counts), sum(self.recv_counts)
+        # where this rank's rows start inside rank r's receive order (sources ascending), and the send offsets
+        self.first_row_at = [sum(int(M[s][r]) for s in range(me)) for r in range(world)]
+        self.send_off = [sum(self.send_counts[:r]) for r in range(world)]
+        self.max_recv_rows = max(sum(int(M[s][r]) for s in range(world)) for r in range(world))
+        self.tokens_all = [int(M[s][-1]) for s in range(world)]
 
     def _build_cuda(self, idx, world):
         """The plan is the routing-metadata problem with destination ranks in the role of experts: one call of the
@@ -107,6 +148,13 @@ class DispatchPlan:
         out = send.new_empty((sum(r),) + tuple(send.shape[1:]))
         dist.all_to_all_single(out, send.contiguous(), output_split_sizes=r, input_split_sizes=s, group=self.group)
         return out
+
+    def pull_and_sum(self, arena: "PeerArena") -> torch.Tensor:
+        """[T, H]: every token's partial rows read from the owning ranks' arenas and added in ascending rank order."""
+        from . import ops
+        arena.everyone_has_written()
+        return ops.ep_combine_pull(arena.ptrs, self.first_row_at, self.send_off, self.copy_pos, self.copy_off,
+                                   self.send_rank, self.T, arena.H, arena.buf.device)
 
     def sum_copies(self, rows: torch.Tensor) -> torch.Tensor:
         """[n_send, C] -> [T, C]: add a token's copies in ascending rank order (fp32 accumulate)."""
@@ -166,7 +214,13 @@ class _Dispatch(torch.autograd.Function):
         plan = ctx.plan
         dx = dp = None
         if ctx.needs_input_grad[0] and dx_recv is not None:
-            dx = plan.sum_copies(plan.a2a(dx_recv.contiguous(), reverse=True)).to(ctx.x_dtype)
+            arena = getattr(plan, "arena", None)
+            if arena is not None:       # the choice of path must not depend on this rank's data: all ranks pull
+                if dx_recv.numel() and not arena.holds(dx_recv):    # normally already where the peers read it
+                    arena.view(dx_recv.shape[0]).copy_(dx_recv)
+                dx = plan.pull_and_sum(arena).to(ctx.x_dtype)
+            else:
+                dx = plan.sum_copies(plan.a2a(dx_recv.contiguous(), reverse=True)).to(ctx.x_dtype)
         if ctx.needs_input_grad[1] and dp_recv is not None:
             back = plan.a2a(dp_recv.contiguous().float(), reverse=True)
             # a slot lives on exactly one rank: every other copy contributes an exact zero
@@ -181,6 +235,11 @@ class _Combine(torch.autograd.Function):
     @staticmethod
     def forward(ctx, o_recv, plan: DispatchPlan, handle):
         ctx.plan, ctx.handle = plan, handle
+        arena = getattr(plan, "arena", None)
+        if arena is not None:           # the choice of path must not depend on this rank's data: all ranks pull
+            if o_recv.numel() and not arena.holds(o_recv):
+                arena.view(o_recv.shape[0]).copy_(o_recv)
+            return plan.pull_and_sum(arena)
         return plan.sum_copies(plan.a2a(o_recv.contiguous(), reverse=True))
 
     @staticmethod
@@ -204,6 +263,25 @@ class ExpertParallelMoE:
     def __init__(self, num_experts: int, top_k: int, group=None, payload: str = "fp8", expert_fn=None):
         self.E, self.K, self.group, self.payload = num_experts, top_k, group, payload
         self.expert_fn = expert_fn or self._sonic_experts
+        self._arena = None
+        self._peer_ok = USE_PEER_COMBINE and expert_fn is None
+        self._place = None
+
+    def _arena_for(self, plan: DispatchPlan, H: int, device):
+        """The mapped buffer for this call's partial rows, (re)allocated collectively when the largest receive
+        count of any rank (known to all ranks from the plan) outgrows it."""
+        if not self._peer_ok or device.type != "cuda" or dist.get_world_size(self.group) < 2:
+            return None
+        need = plan.max_recv_rows
+        if self._arena is None or self._arena.H != H or self._arena.rows < need:
+            rows = max(need, sum(plan.tokens_all))      # every rank sending everything to one rank always fits
+            try:
+                self._arena = PeerArena(self.group if self.group is not None else dist.group.WORLD, rows, H, device)
+            except Exception as exc:      # no peer mapping on this system: every rank fails alike
+                import warnings
+                warnings.warn(f"expert-parallel peer-memory combine unavailable ({exc!r}); using NCCL all-to-all")
+                self._peer_ok, self._arena = False, None
+        return self._arena
 
     def _sonic_experts(self, rows, local_idx, probs, w1, w2, fp8_scale, handle):
         from .interface import run_sonic_moe
@@ -213,7 +291,8 @@ class ExpertParallelMoE:
         if fp8_scale is not None:
             holder, qbytes = rows
             return run_sonic_moe(qbytes, local_idx, probs, self.K, self.El, w1, w2, fp8=True, fp8_scale=fp8_scale,
-                                 fp8_combine_grad_handle=handle, tokens_per_expert=counts, grad_holder=holder)
+                                 fp8_combine_grad_handle=handle, tokens_per_expert=counts, grad_holder=holder,
+                                 out=self._place, dx_out=self._place)
         return run_sonic_moe(rows, local_idx, probs, self.K, self.El, w1, w2, fp8=True, tokens_per_expert=counts)
 
     def __call__(self, x, topk_idx, topk_scores, w1, w2):
@@ -227,5 +306,10 @@ class ExpertParallelMoE:
             from .functional import Fp8CombineGradHandle
             handle = Fp8CombineGradHandle()
             rows = (rows, q)
+        arena = self._arena_for(plan, x.shape[1], x.device) if fp8 else None
+        plan.arena = arena
+        # forward output and, later, dx of the local experts land in the mapped buffer (one region, used in turn)
+        self._place = arena.view(plan.n_recv) if (arena is not None and plan.n_recv > 0) else None
         o_recv = self.expert_fn(rows, local_idx, probs, w1, w2, raw, handle)
+        self._place = None
         return _Combine.apply(o_recv, plan, handle)

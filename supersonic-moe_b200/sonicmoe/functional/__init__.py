@@ -173,6 +173,22 @@ def _after_accumulate(base):
         hook()
 
 
+# Where the next layer call should put its two token-side results (forward output, dx).  The expert-parallel layer
+# points them at memory that the peer GPUs have mapped, so that the return exchange reads them in place.
+_PLACEMENT: dict = {}
+
+
+@contextmanager
+def place_results(out: torch.Tensor | None = None, dx: torch.Tensor | None = None):
+    """Within the block, the next `_UpProjection` / `_DownProjection` pair writes its forward output into `out` and,
+    in its backward, dx into `dx` (contiguous bf16 [N,H] CUDA tensors) instead of fresh allocations."""
+    _PLACEMENT.update(out_buf=out, dx_buf=dx)
+    try:
+        yield
+    finally:
+        _PLACEMENT.clear()
+
+
 # hand-off of FP8 payloads from _UpProjection.forward to _DownProjection.forward
 # (the returned y1 / z tensors are zero-stride placeholders that only carry the
 # autograd edges)
@@ -239,7 +255,8 @@ class _UpProjection(torch.autograd.Function):
                 xg_q, a_sf = ops.quant_rows_scatter(x.contiguous(), naept, s_rev, s_scatter_idx, TKp, efo[-1:])
             z_q, z_sc, y1_q, y1_sf = ops.gemm_gated(xg_q, None, a_sf, w1_q, w1_sf, efo, TKp)
             del xg_q
-        link = {"y1": (y1_q, y1_sf), "z": (z_q, z_sc)}
+        link = {"y1": (y1_q, y1_sf), "z": (z_q, z_sc), "out_buf": _PLACEMENT.get("out_buf")}
+        ctx.dx_buf = _PLACEMENT.get("dx_buf")
         cfg = fp8_config if fp8_config is not None else get_active_config()
         if cfg is not None and cfg.resolve_recompute_z() and not is_inference:
             # keep what regenerates z instead of z itself; the backward re-runs this GEMM and gets the same bytes
@@ -288,7 +305,8 @@ class _UpProjection(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             w1t_q, w1t_sf = weight_fp8(w1, True)
             dx_exp = ops.gemm_varlen_m(dz_q, dz_rsf, w1t_q, w1t_sf, efo)
-            dx = ops.combine(dx_exp, s_rev, naept, None, ctx.T)
+            buf = ctx.dx_buf if (ctx.dx_buf is not None and ctx.x_dtype == torch.bfloat16) else None
+            dx = ops.combine(dx_exp, s_rev, naept, None, ctx.T, out=buf)
             if dx.dtype != ctx.x_dtype:
                 dx = dx.to(ctx.x_dtype)
         return (dx, dw1) + (None,) * 15
@@ -339,7 +357,7 @@ class _DownProjection(torch.autograd.Function):
         y1_q, y1_sf = link.pop("y1")
         w2_q, w2_sf = weight_fp8(w2, False)
         y2 = ops.gemm_varlen_m(y1_q, y1_sf, w2_q, w2_sf, efo)
-        o = ops.combine(y2, s_rev, naept, topk_scores, int(T))
+        o = ops.combine(y2, s_rev, naept, topk_scores, int(T), out=link.pop("out_buf", None))
         ctx.link = link
         ctx.T = int(T)
         ctx.grad_handle = fp8_combine_grad_handle

@@ -7,12 +7,13 @@ import torch
 
 from . import ops
 from .enums import ActivationType
-from .functional import _DownProjection, _UpProjection, enable_fp8
+from .functional import _DownProjection, _UpProjection, enable_fp8, place_results
 
 
 def run_sonic_moe(hidden_states, topk_indices, topk_scores, K, E, w1, w2, fp8=False, tokens_per_expert=None,
                   fp8_scale=None, fp8_combine_grad_handle=None, fp8_config=None, release_fp8_weights=False,
-                  activation_type=ActivationType.SWIGLU, sync_free_sizing=False, grad_holder=None):
+                  activation_type=ActivationType.SWIGLU, sync_free_sizing=False, grad_holder=None, out=None,
+                  dx_out=None):
     """hidden_states [N,H] bf16 (or e4m3 with `fp8_scale` = raw 1x32 ue8m0 bytes [N,H/32]);
     topk_indices [N,K] with -1 for slots whose expert is not local (a row's valid experts distinct);
     topk_scores [N,K] f32; w1 [E,2I,H]; w2 [E,H,I].  Returns [N,H] bf16.
@@ -20,6 +21,10 @@ def run_sonic_moe(hidden_states, topk_indices, topk_scores, K, E, w1, w2, fp8=Fa
     With an e4m3 `hidden_states` no gradient can flow to it (torch has no differentiable 8-bit tensors);
     `grad_holder` - a bf16 [N,H] tensor that requires grad, contents ignored - then receives dx in its place
     (the expert-parallel dispatch passes its placeholder here; not part of the reference signature).
+
+    `out` / `dx_out` - contiguous bf16 [N,H] CUDA buffers that receive the forward output and, in the backward,
+    dx (the returned tensor / the gradient ARE those buffers); used by the expert-parallel layer to leave both in
+    memory its peers can read (not part of the reference signature).
 
     `tokens_per_expert` (host list / tensor) sizes the expert-sorted buffers exactly; with
     `sync_free_sizing` (or without counts) they are sized at the shape-only upper bound and no
@@ -44,7 +49,7 @@ def run_sonic_moe(hidden_states, topk_indices, topk_scores, K, E, w1, w2, fp8=Fa
         hidden_states = grad_holder if grad_holder is not None else torch.empty(
             (), dtype=torch.bfloat16, device=hidden_states.device).expand(N, hidden_states.shape[1])
     need_router_grad = topk_scores.requires_grad
-    with enable_fp8(True):
+    with enable_fp8(True), place_results(out, dx_out):
         y1, z = _UpProjection.apply(hidden_states, w1, None, md["efo"], md["TKp_alloc"], K, stream_id,
                                     md["x_gather_idx"], md["s_scatter_idx"], md["s_reverse_scatter_idx"],
                                     md["naept"], True, activation_type, False, False, payload, fp8_config)

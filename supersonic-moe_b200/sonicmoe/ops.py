@@ -140,6 +140,22 @@ def ep_plan_send_idx(idx, send_tok, efo, n_send, E, world):
     return send_idx, send_rank
 
 
+@_timed
+def ep_combine_pull(peer_ptrs, first_row, send_off, copy_pos, copy_off, send_rank, T, H, device):
+    """Sum every token's partial-output rows straight from the owning ranks' buffers (peer_ptrs: device addresses of
+    their bf16 [rows,H] buffers in this process; first_row / send_off: host ints per rank) -> bf16 [T,H]."""
+    import ctypes
+    _cuda(copy_pos, copy_off, send_rank)
+    world = len(peer_ptrs)
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=device)
+    bases = (ctypes.c_void_p * world)(*[int(p) for p in peer_ptrs])
+    fr = (ctypes.c_int32 * world)(*[int(v) for v in first_row])
+    so = (ctypes.c_int32 * world)(*[int(v) for v in send_off])
+    check(lib.smoe_ep_combine_pull(bases, fr, so, world, _p(copy_pos), _p(copy_off), _p(send_rank), _p(out), T, H,
+                                   _stream()), "ep_combine_pull")
+    return out
+
+
 # ---------------------------------------------------------------- quantizers
 @_timed
 def quant_rows(x, raw=True, isa=False):
@@ -373,10 +389,15 @@ def gemm_wgrad_mn(a, a_sf, b, b_sf, efo, out, accumulate, a_rowmajor_tk, b_rowma
 
 # ---------------------------------------------------------------- token side
 @_timed
-def combine(y, s_rev, naept, scores, T):
+def combine(y, s_rev, naept, scores, T, out=None):
+    """out[t] = sum over the token's lanes of scores * y[row] (bf16, fp32 accumulate); `out` places the result in a
+    caller-owned bf16 [T,H] buffer (e.g. memory that peer GPUs read)."""
     _cuda(y, s_rev, naept, scores)
     H = y.shape[1]
-    out = torch.empty(T, H, dtype=torch.bfloat16, device=y.device)
+    if out is None:
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=y.device)
+    elif out.dtype != torch.bfloat16 or tuple(out.shape) != (T, H) or not out.is_contiguous() or not out.is_cuda:
+        raise ValueError(f"combine: out must be contiguous CUDA bf16 [{T},{H}]")
     check(lib.smoe_combine(_p(y), _p(s_rev), _p(naept), _p(scores), _p(out), T, H, _stream()), "combine")
     return out
 

@@ -559,6 +559,7 @@ def test_ep_dispatch_plan_from_metadata_kernels_matches_torch_construction(ops, 
             self.recv_counts = list(self.send_counts)
             self.tokens_per_local_expert = pairs.view(world, -1).sum(0).tolist()
             self.n_send = self.n_recv = sum(self.send_counts)
+            self.send_off = [sum(self.send_counts[:r]) for r in range(world)]
 
     g = torch.Generator().manual_seed(T)
     idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32)
@@ -572,3 +573,36 @@ def test_ep_dispatch_plan_from_metadata_kernels_matches_torch_construction(ops, 
     assert torch.equal(got.copy_off.cpu(), want.copy_off)
     assert torch.equal(got.copy_pos.cpu(), want.copy_pos)
     assert got.tokens_per_local_expert == want.tokens_per_local_expert
+
+
+@pytest.mark.parametrize("T,K,E,world,H", [(333, 4, 16, 4, 256), (500, 8, 8, 8, 512), (64, 2, 6, 2, 128)])
+def test_ep_combine_pull_on_one_gpu_with_local_stand_ins_for_the_peers(ops, T, K, E, world, H):
+    """The peer-memory combine kernel with every 'peer' buffer on this GPU: result = sum of a token's copies in
+    ascending rank order, rows addressed as first_row[rank] + (i - send_off[rank])."""
+    from sonicmoe.ep import DispatchPlan
+
+    class LoopbackPlan(DispatchPlan):
+        def _exchange_counts(self, rows_to, pairs, world):
+            self.send_counts = rows_to.tolist()
+            self.recv_counts = list(self.send_counts)
+            self.tokens_per_local_expert = pairs.view(world, -1).sum(0).tolist()
+            self.n_send = self.n_recv = sum(self.send_counts)
+            self.send_off = [sum(self.send_counts[:r]) for r in range(world)]
+
+    g = torch.Generator().manual_seed(T + H)
+    idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32)
+    idx[::5, 0] = -1
+    plan = LoopbackPlan(idx.to(DEV), E, None, world=world)
+    first_row = [int(v) for v in torch.randint(0, 50, (world,), generator=g)]      # this rank's rows start anywhere
+    bufs = [torch.randn(first_row[r] + plan.send_counts[r] + 7, H, generator=g).to(torch.bfloat16).to(DEV)
+            for r in range(world)]
+    out = ops.ep_combine_pull([b.data_ptr() for b in bufs], first_row, plan.send_off, plan.copy_pos, plan.copy_off,
+                              plan.send_rank, T, H, torch.device(DEV))
+    torch.cuda.synchronize()
+    want = torch.zeros(T, H)
+    send_rank, copy_pos, copy_off = plan.send_rank.cpu(), plan.copy_pos.cpu(), plan.copy_off.cpu()
+    for t in range(T):
+        for c in range(int(copy_off[t]), int(copy_off[t + 1])):
+            i = int(copy_pos[c]); r = int(send_rank[i])
+            want[t] += bufs[r][first_row[r] + i - plan.send_off[r]].float().cpu()
+    assert torch.equal(out.cpu(), want.to(torch.bfloat16))
