@@ -28,10 +28,11 @@ import os
 import torch
 import torch.distributed as dist
 
-# The two bf16 return exchanges (forward combine, backward dx) read the partial rows straight from the owners'
-# memory over NVLink, fused with the per-token reduction (csrc/ep_peer.cu), when the ranks can map each other's
-# memory (torch symmetric memory); SONIC_MOE_EP_PEER=0 keeps them on NCCL all-to-all + a local reduction.
-USE_PEER_COMBINE = os.getenv("SONIC_MOE_EP_PEER", "1") == "1"
+# SONIC_MOE_EP_PEER=1: the two bf16 return exchanges (forward combine, backward dx) read the partial rows straight
+# from the owners' memory over NVLink, fused with the per-token reduction (csrc/ep_peer.cu); needs ranks that can map
+# each other's memory (torch symmetric memory).  Default: NCCL all-to-all + a local reduction - the peer path is
+# verified on 2 GPUs only so far.
+USE_PEER_COMBINE = os.getenv("SONIC_MOE_EP_PEER", "0") == "1"
 
 
 class PeerArena:
@@ -264,7 +265,7 @@ class ExpertParallelMoE:
         self.E, self.K, self.group, self.payload = num_experts, top_k, group, payload
         self.expert_fn = expert_fn or self._sonic_experts
         self._arena = None
-        self._peer_ok = USE_PEER_COMBINE and expert_fn is None
+        self._peer_ok = USE_PEER_COMBINE and expert_fn is None      # read at construction
         self._place = None
 
     def _arena_for(self, plan: DispatchPlan, H: int, device):

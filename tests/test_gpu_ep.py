@@ -31,14 +31,16 @@ def _inputs(rank):
     return x, dy, scores, idx.to(torch.int32), w1, w2
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, peer):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     import sonicmoe
+    import sonicmoe.ep as ep_mod
     from sonicmoe.ep import ExpertParallelMoE
+    ep_mod.USE_PEER_COMBINE = peer          # return exchanges over mapped peer memory vs NCCL all-to-all
     x, dy, scores, idx, w1, w2 = _inputs(rank)
     El = E // world
     xd = x.to(dev).requires_grad_(True)
@@ -50,6 +52,7 @@ def _worker(rank, world, port, q):
     out.backward(dy.to(dev))
     torch.cuda.synchronize()
     sonicmoe.ops.check_status(dev)
+    used_peer = ep._arena is not None
     # every rank's tokens through the single-GPU layer with all experts local; weight gradients of the local
     # expert slice summed over both ranks' tokens
     dw1_ref = torch.zeros(El, 2 * I, H, device=dev)
@@ -73,19 +76,21 @@ def _worker(rank, world, port, q):
         return float((a * b).sum() / (a.norm() * b.norm())), float((a - b).norm() / b.norm())
     res = dict(out=st(out, mine[0]), dx=st(xd.grad, mine[1]), ds=st(sd.grad, mine[2]), dw1=st(w1l.grad, dw1_ref),
                dw2=st(w2l.grad, dw2_ref))
+    res["used_peer"] = used_peer
     q.put((rank, res))
     dist.barrier()
     dist.destroy_process_group()
 
 
-def test_ep_two_gpus_matches_single_gpu_layer():
+@pytest.mark.parametrize("peer", [False, True])
+def test_ep_two_gpus_matches_single_gpu_layer(peer):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, peer)) for r in range(2)]
     for p in procs:
         p.start()
     results = dict(q.get(timeout=300) for _ in range(2))
@@ -93,6 +98,7 @@ def test_ep_two_gpus_matches_single_gpu_layer():
         p.join(timeout=60)
         assert p.exitcode == 0
     for rank, res in results.items():
+        assert res.pop("used_peer") == peer, "the requested return-exchange path was not the one that ran"
         for name, (cos, rr) in res.items():
             # same quantisation points; differences: bf16 rounding of the per-rank partial sums (out, dx) and
             # the column-wise re-quantisation of the FP8 payload for the weight gradients

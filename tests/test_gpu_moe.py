@@ -325,3 +325,35 @@ def test_weight_cache_is_not_fooled_by_a_recycled_address(sm):
     qb = weight_fp8(b, False)[0]
     want = sm.ops.quant_rows(b.view(4 * 256, 128), raw=False, isa=True)[0].view(4, 256, 128)
     assert torch.equal(qb, want) and not torch.equal(qb, qa)
+
+
+def test_caller_owned_buffers_for_output_and_dx(sm):
+    """`run_sonic_moe(out=..., dx_out=...)`: the forward output and dx are written straight into the caller's bf16
+    buffers (the expert-parallel layer points them at memory its peers read), with the same bits as without."""
+    T, H, I, E, K = 512, 512, 256, 8, 4
+    x, dy, w1, w2, _, _ = make_layer(T, H, I, E, K, 41)
+    idx, scores = masked_routing(T, E, K, E, 42)
+    w1d, w2d = w1.to(DEV), w2.to(DEV)
+
+    def run(**kw):
+        xd = x.to(DEV).requires_grad_(True)
+        out = sm.run_sonic_moe(xd, idx.to(DEV), scores.to(DEV), K, E, w1d, w2d, fp8=True, **kw)
+        out.backward(dy.to(DEV))
+        torch.cuda.synchronize()
+        return out, xd.grad
+
+    ref_out, ref_dx = run()
+    buf_o = torch.full((T, H), 7.0, dtype=torch.bfloat16, device=DEV)
+    buf_dx = torch.full((T, H), 7.0, dtype=torch.bfloat16, device=DEV)
+    out, dx = run(out=buf_o, dx_out=buf_dx)
+    # (a leaf's .grad is autograd's own copy; a non-leaf consumer, like the EP dispatch, gets the buffer itself)
+    assert out.data_ptr() == buf_o.data_ptr() and torch.equal(buf_dx, ref_dx)
+    assert torch.equal(out, ref_out) and torch.equal(dx, ref_dx)
+    one = torch.empty(T, H, dtype=torch.bfloat16, device=DEV)          # one region used in turn, as the EP layer does
+    out, dx = run(out=one, dx_out=one)
+    assert torch.equal(dx, ref_dx) and torch.equal(one, ref_dx)
+    with pytest.raises(ValueError):
+        run(out=torch.empty(T, H + 8, dtype=torch.bfloat16, device=DEV))
+    # nothing leaks into the next call
+    out, dx = run()
+    assert out.data_ptr() not in (buf_o.data_ptr(), one.data_ptr()) and torch.equal(out, ref_out)
