@@ -67,7 +67,8 @@ def _worker(rank, world, port, out_q):
     res = dict(out=out.detach(), dx=x.grad, ds=scores.grad, dw1=w1l.grad, dw2=w2l.grad,
                n_send=plan.n_send, n_recv=plan.n_recv, send_counts=plan.send_counts,
                copies=(plan.copy_off[1:] - plan.copy_off[:-1]).clone(),
-               per_expert=list(plan.tokens_per_local_expert))
+               per_expert=list(plan.tokens_per_local_expert), first_row_at=list(plan.first_row_at),
+               recv_counts=list(plan.recv_counts), send_off=list(plan.send_off), max_recv=plan.max_recv_rows)
     # host-side failure: an exchange whose split sizes disagree with the buffer is refused before any data moves
     try:
         plan.send_counts = [c + 1 for c in plan.send_counts]
@@ -132,6 +133,12 @@ def test_ep_two_ranks_matches_single_process_oracle():
         all_idx = torch.cat([_inputs(rk, world)[3] for rk in range(world)])
         want = torch.bincount(all_idx.flatten(), minlength=E)[rank * El:(rank + 1) * El]
         assert r["per_expert"] == want.tolist()
+        # the count matrix every rank holds: where this rank's rows start in each peer's receive order
+        sent = [results[s]["send_counts"] for s in range(world)]
+        assert r["recv_counts"] == [sent[s][rank] for s in range(world)]
+        assert r["first_row_at"] == [sum(sent[s][d] for s in range(rank)) for d in range(world)]
+        assert r["send_off"] == [sum(sent[rank][:d]) for d in range(world)]
+        assert r["max_recv"] == max(sum(sent[s][d] for s in range(world)) for d in range(world))
         assert r["n_send"] == int(n_dest.sum()) and sum(r["send_counts"]) == r["n_send"]
         assert r["bad_split_raises"]
         # this rank's tokens contribute to every rank's expert gradients
