@@ -440,6 +440,8 @@ def _measure(args, cname, world, rank, dev, dist, sonicmoe, ops):
         "dtype": "fp8_e4m3 (ue8m0 1x32 scales), f32 accumulate", "data": "synthetic",
         "config": {"workload": f"{cname}: T={T}{' per rank' if world > 1 else ''} H={H} I={I} E={E} K={K}, seed "
                                f"{cfg['seed']}" + (", expert-parallel over %d ranks" % world if world > 1 else ""),
+                   **({"ep_return_exchange": "peer memory (SONIC_MOE_EP_PEER=1)" if os.getenv("SONIC_MOE_EP_PEER", "0")
+                       == "1" else "nccl all_to_all"} if world > 1 else {}),
                    "l2": "no flush: one step touches ~2.5 GB (> 126 MB L2)",
                    "timed_region": "same as the reference's bench (router linear/top-k outside)"},
         "mfu_fp8_of_4.5PF": round(F / (ms * 1e-3) / FP8_PEAK_NOMINAL / world, 4),
