@@ -5,7 +5,8 @@
  *     cudaStream_t passed as void*; nothing is allocated, nothing synchronises:
  *     work is enqueued on `stream` and the call returns.
  *   - return value 0 (SMOE_OK) or a SMOE_ERR_* code for argument / launch errors
- *     detected on the host.  Failures detected on the device (a bounded wait
+ *     detected on the host.  A problem with zero rows (nothing routed to this
+ *     rank) is not an error: the call returns SMOE_OK without a launch.  Failures detected on the device (a bounded wait
  *     that ran out) are written to the caller's `status` word (0 = ok).
  *   - "ISA-packed" scales: for a logical (rows, cols) operand with one ue8m0
  *     byte per 1x32 group, byte(row, g) lives at
@@ -52,7 +53,9 @@ int64_t smoe_topk_metadata_workspace(int64_t N, int64_t E);
  *   lane_order: 0 = a token's lanes by ascending expert id (kernel.cu:567-578),
  *               1 = by top-k slot (dense path, functional/triton_kernels/__init__.py:66-155)
  *   pad_mode:   0 = pad rows scatter to real_TK (kernel.cu:611-650),
- *               1 = i-th pad row scatters to real_TK + i (functional/__init__.py:226-234) */
+ *               1 = i-th pad row scatters to real_TK + i (functional/__init__.py:226-234)
+ *   TK_alloc / TKp_alloc smaller than what idx really holds (buffers sized from stale per-expert counts): the rows
+ *   that do not fit are dropped and efo is clamped to TKp_alloc - nothing is written outside the buffers. */
 int smoe_topk_metadata(const int32_t* idx, const float* probs, int64_t N, int64_t K, int64_t E, int64_t alignment,
                        int64_t TK_alloc, int64_t TKp_alloc, int lane_order, int pad_mode, int32_t* efo,
                        int32_t* x_gather_idx, int32_t* s_scatter_idx, int32_t* s_reverse_scatter_idx, int32_t* naept,
@@ -235,9 +238,6 @@ int smoe_gemm_wgrad(const void* a_t_fp8, const void* a_sf, const void* b_t_fp8, 
 int smoe_gemm_wgrad_mn(const void* a_fp8, const void* a_sf, const void* b_fp8, const void* b_sf, const int32_t* efo,
                        float* c, int64_t M, int64_t N, int64_t TKp, int64_t E, int accumulate, int layout,
                        int32_t* status, void* stream);
-
-/* Test hook: force the GEMM column tile (128 or 256; 0 = automatic). */
-int smoe_debug_force_bn(int bn);
 
 /* ---- combine / router ------------------------------------------------------ */
 

@@ -75,7 +75,10 @@ __global__ void ds_finalize_kernel(const float* __restrict__ part, int partials,
 }
 
 // One warp per row: K rounds of arg-max (lowest index wins ties), then softmax
-// over the K selected logits in fp32.
+// over the K selected logits in fp32.  A NaN logit counts as -inf.  A row with
+// fewer than K finite logits still gets K distinct, in-range indices: once the
+// finite ones are used up, the lowest not-yet-selected index is taken with a
+// score of exactly zero (all K scores are zero when nothing in the row is finite).
 __global__ void __launch_bounds__(256)
 topk_softmax_kernel(const float* __restrict__ logits, int64_t T, int E, int K, float* __restrict__ scores,
                     int* __restrict__ idx) {
@@ -85,10 +88,14 @@ topk_softmax_kernel(const float* __restrict__ logits, int64_t T, int E, int K, f
   constexpr int PER = 32;  // up to 1024 experts
   float v[PER];
   const int per = (E + 31) / 32;
+  uint32_t open = 0;       // bit i: this lane's i-th expert exists and has not been selected yet
 #pragma unroll
   for (int i = 0; i < PER; ++i) {
     const int e = i * 32 + lane;
-    v[i] = (i < per && e < E) ? logits[row * E + e] : -INFINITY;
+    const bool in = (i < per && e < E);
+    const float x = in ? logits[row * E + e] : -INFINITY;
+    v[i] = (x != x) ? -INFINITY : x;
+    if (in) open |= 1u << i;
   }
   float sel_v = 0.f;
   int sel_i = 0;
@@ -98,9 +105,9 @@ topk_softmax_kernel(const float* __restrict__ logits, int64_t T, int E, int K, f
     int bi = 0x7fffffff;
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
-      if (i < per) {
+      if (i < per && ((open >> i) & 1u)) {
         const int e = i * 32 + lane;
-        if (v[i] > bv) { bv = v[i]; bi = e; }
+        if (bi == 0x7fffffff || v[i] > bv) { bv = v[i]; bi = e; }
       }
     }
 #pragma unroll
@@ -111,18 +118,14 @@ topk_softmax_kernel(const float* __restrict__ logits, int64_t T, int E, int K, f
     }
     if (k == 0) vmax = bv;
     if (lane == k) { sel_v = bv; sel_i = bi; }
-    if ((bi & 31) == lane) {
-#pragma unroll
-      for (int i = 0; i < PER; ++i)
-        if (i == (bi >> 5)) v[i] = -INFINITY;
-    }
+    if ((bi & 31) == lane) open &= ~(1u << (bi >> 5));     // K <= E: an open slot always exists
   }
-  float ex = lane < K ? expf(sel_v - vmax) : 0.f;
+  float ex = (lane < K && sel_v != -INFINITY) ? expf(sel_v - vmax) : 0.f;
   float sum = ex;
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffff, sum, d);
   if (lane < K) {
-    scores[row * K + lane] = ex / sum;
+    scores[row * K + lane] = sum > 0.f ? ex / sum : 0.f;
     idx[row * K + lane] = sel_i;
   }
 }
@@ -140,7 +143,10 @@ topk_softmax_bwd_kernel(const float* __restrict__ scores, const int* __restrict_
   float dot = s * g;
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) dot += __shfl_xor_sync(0xffffffff, dot, d);
-  if (lane < K) dlogits[row * E + idx[row * K + lane]] = s * (g - dot);
+  if (lane < K) {
+    const int e = idx[row * K + lane];
+    if (e >= 0 && e < E) dlogits[row * E + e] = s * (g - dot);     // an out-of-range index is ignored, never written
+  }
 }
 
 }  // namespace smoe

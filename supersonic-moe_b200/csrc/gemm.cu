@@ -8,6 +8,7 @@
 #include "gemm.cuh"
 #include "gemm2.cuh"
 #include "smoe_b200.h"
+#include "smoe_internal.h"
 
 namespace smoe {
 
@@ -58,28 +59,41 @@ static int make_tmap(CUtensorMap* m, CUtensorMapDataType dt, int esize, const vo
 static int g_force_bn = 0;
 static int g_skip_store = 0;
 static int g_force_v1 = 0;
-static int g_sm_count = 0;
+
+// Per-device state: the SM count and the "large dynamic shared memory" function attribute belong to a device,
+// not to the process, so both are kept per device ordinal.
+constexpr int kMaxDevices = 64;
+static int g_sm_count[kMaxDevices] = {};
+
+static int current_device() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return (dev >= 0 && dev < kMaxDevices) ? dev : 0;
+}
 
 static int sm_count() {
-  if (g_sm_count == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
-  }
-  return g_sm_count;
+  const int dev = current_device();
+  if (g_sm_count[dev] == 0) cudaDeviceGetAttribute(&g_sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+  return g_sm_count[dev];
+}
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (kernel instantiation, device)
+template <typename Kern>
+static bool ensure_smem_attr(Kern kern, int bytes, bool (&done)[kMaxDevices]) {
+  const int dev = current_device();
+  if (done[dev]) return true;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
+  done[dev] = true;
+  return true;
 }
 
 template <int BN, int MODE>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int max_tiles,
                   cudaStream_t stream) {
   using S = GemmSmem<BN>;
-  static bool attr_set = false;
+  static bool attr_set[kMaxDevices] = {};
   auto kern = gemm_mxf8_kernel<BN, MODE>;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL) != cudaSuccess)
-      return SMOE_ERR_LAUNCH;
-    attr_set = true;
-  }
+  if (!ensure_smem_attr(kern, S::TOTAL, attr_set)) return SMOE_ERR_LAUNCH;
   int grid = sm_count();
   if (max_tiles < grid) grid = max_tiles;
   if (grid <= 0) return SMOE_OK;
@@ -101,13 +115,9 @@ template <int BN, int MODE>
 static int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa, const CUtensorMap& tsb,
                    const OutMaps& om, const GemmParams& p, int64_t max_pair_tiles, cudaStream_t stream) {
   using S = Gemm2Smem<BN, MODE>;
-  static bool attr_set = false;
+  static bool attr_set[kMaxDevices] = {};
   auto kern = gemm2_mxf8_kernel<BN, MODE>;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL) != cudaSuccess)
-      return SMOE_ERR_LAUNCH;
-    attr_set = true;
-  }
+  if (!ensure_smem_attr(kern, S::TOTAL, attr_set)) return SMOE_ERR_LAUNCH;
   int64_t pairs = sm_count() / 2;
   if (max_pair_tiles < pairs) pairs = max_pair_tiles;
   if (pairs <= 0) return SMOE_OK;
@@ -215,22 +225,32 @@ static int run(const void* a, int64_t a_rows, int64_t a_cols, const void* b, int
   return launch<128, M1>(ta, tb, p, max_tiles_128, stream);
 }
 
+// A weight-gradient call over zero routed rows: the product is empty, so an accumulating call leaves c as it is and
+// an overwriting call stores zeros.
+static int wgrad_nothing_routed(float* c, int64_t M, int64_t N, int64_t E, int accumulate, cudaStream_t stream) {
+  if (accumulate) return SMOE_OK;
+  if (c == nullptr) return SMOE_ERR_ARG;
+  return cudaMemsetAsync(c, 0, (size_t)E * M * N * sizeof(float), stream) == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
+}
+
 }  // namespace smoe
 
 using namespace smoe;
 
 extern "C" {
 
-int smoe_debug_force_bn(int bn) {
+int smoe_internal_gemm_knobs(int bn) {
   g_force_bn = bn & 0xFFFF;
   g_skip_store = ((bn >> 16) & 1) | (((bn >> 18) & 1) << 1);   // bit 16: no stores; bit 18: no epilogue (fused dgated)
   g_force_v1 = (bn >> 17) & 1;
+  g_skip_store |= ((bn >> 19) & 0x1F) << 2;    // bits 19..23 -> timing-experiment bits 2..6 of GemmParams::debug_skip_store
   return SMOE_OK;
 }
 
 int smoe_gemm_varlen_m(const void* a_fp8, const void* a_sf, const void* b_fp8, const void* b_sf, const int* efo,
                        void* c_bf16, int64_t rows, int64_t N, int64_t K, int64_t E, int* status, void* stream) {
-  if (rows % 128 || N % 128 || K % 128 || E <= 0) return SMOE_ERR_SHAPE;
+  if (rows < 0 || rows % 128 || N % 128 || K % 128 || E <= 0) return SMOE_ERR_SHAPE;
+  if (rows == 0) return SMOE_OK;                  // no routed rows (an expert-parallel rank may receive none)
   GemmParams p{};
   p.rows = (int)rows; p.N = (int)N; p.K = (int)K; p.E = (int)E;
   p.efo = efo; p.sfa = (const uint8_t*)a_sf; p.sfb = (const uint8_t*)b_sf;
@@ -242,7 +262,9 @@ int smoe_gemm_varlen_m(const void* a_fp8, const void* a_sf, const void* b_fp8, c
 int smoe_gemm_gated(const void* x_fp8, int64_t T, const int* a_idx, const void* a_sf, const void* w1_fp8,
                     const void* w1_sf, const int* efo, void* z_fp8, void* z_scales, void* y1_fp8, void* y1_sf,
                     int64_t rows, int64_t N, int64_t K, int64_t E, int* status, void* stream) {
-  if (rows % 128 || N % 256 || K % 128 || E <= 0 || T <= 0) return SMOE_ERR_SHAPE;
+  if (rows < 0 || rows % 128 || N % 256 || K % 128 || E <= 0 || T < 0) return SMOE_ERR_SHAPE;
+  if (rows == 0) return SMOE_OK;
+  if (T == 0) return SMOE_ERR_SHAPE;              // rows to compute but nothing to read them from
   GemmParams p{};
   p.rows = (int)rows; p.N = (int)N; p.K = (int)K; p.E = (int)E;
   p.efo = efo; p.a_idx = a_idx; p.sfa = (const uint8_t*)a_sf; p.sfb = (const uint8_t*)w1_sf;
@@ -258,14 +280,16 @@ int smoe_gemm_dgated(const void* dout_fp8, int64_t T, const int* a_idx, const vo
                      const void* w2t_sf, const int* efo, const void* z_fp8, const void* z_scales, const float* s,
                      void* dz_bf16, void* y1s_bf16, float* ds_partial, int64_t* ds_partial_tiles, int64_t rows,
                      int64_t N, int64_t K, int64_t E, int* status, void* stream) {
-  if (rows % 128 || N % 128 || K % 128 || E <= 0 || T <= 0) return SMOE_ERR_SHAPE;
+  if (rows < 0 || rows % 128 || N % 128 || K % 128 || E <= 0 || T < 0) return SMOE_ERR_SHAPE;
+  if (ds_partial_tiles) *ds_partial_tiles = smoe_gemm_dgated_partials(N);
+  if (rows == 0) return SMOE_OK;
+  if (T == 0) return SMOE_ERR_SHAPE;
   GemmParams p{};
   p.rows = (int)rows; p.N = (int)N; p.K = (int)K; p.E = (int)E;
   p.efo = efo; p.a_idx = a_idx; p.sfa = (const uint8_t*)a_sf; p.sfb = (const uint8_t*)w2t_sf;
   p.sfa_ktiles = (int)(K / 128); p.sfb_ktiles = (int)(K / 128);
   p.z_fp8 = (uint8_t*)const_cast<void*>(z_fp8); p.z_sc = (uint8_t*)const_cast<void*>(z_scales);
   p.s = s; p.dz = dz_bf16; p.y1s = y1s_bf16; p.ds_partial = ds_partial; p.status = status;
-  if (ds_partial_tiles) *ds_partial_tiles = smoe_gemm_dgated_partials(N);
   return run<DGATED>(dout_fp8, T, K, w2t_fp8, E * N, K, p, (int)((rows / 128) * (N / 128)), (cudaStream_t)stream);
 }
 
@@ -273,7 +297,8 @@ int smoe_gemm_dgated_fused(const void* dout_fp8, const void* a_sf, const void* w
                            const int* efo, const void* z_fp8, const void* z_scales, const float* s, void* dz_q,
                            void* dz_row_sf, void* dz_col_sf, void* y1s_q, void* y1s_col_sf, float* ds_partial,
                            int64_t rows, int64_t N, int64_t K, int64_t E, int* status, void* stream) {
-  if (rows % 128 || N % 128 || K % 128 || E <= 0) return SMOE_ERR_SHAPE;
+  if (rows < 0 || rows % 128 || N % 128 || K % 128 || E <= 0) return SMOE_ERR_SHAPE;
+  if (rows == 0) return SMOE_OK;
   GemmParams p{};
   p.rows = (int)rows; p.N = (int)N; p.K = (int)K; p.E = (int)E;
   p.efo = efo; p.a_idx = nullptr; p.sfa = (const uint8_t*)a_sf; p.sfb = (const uint8_t*)w2t_sf;
@@ -298,7 +323,8 @@ int64_t smoe_gemm_dgated_partials(int64_t N) {
 int smoe_gemm_wgrad(const void* a_t_fp8, const void* a_sf, const void* b_t_fp8, const void* b_sf, const int* efo,
                     float* c, int64_t M, int64_t N, int64_t TKp, int64_t E, int accumulate, int* status,
                     void* stream) {
-  if (M % 128 || N % 128 || TKp % 128 || E <= 0) return SMOE_ERR_SHAPE;
+  if (M <= 0 || N <= 0 || M % 128 || N % 128 || TKp < 0 || TKp % 128 || E <= 0) return SMOE_ERR_SHAPE;
+  if (TKp == 0) return wgrad_nothing_routed(c, M, N, E, accumulate, (cudaStream_t)stream);
   GemmParams p{};
   p.rows = (int)M; p.N = (int)N; p.K = (int)TKp; p.E = (int)E;
   p.efo = efo; p.sfa = (const uint8_t*)a_sf; p.sfb = (const uint8_t*)b_sf;
@@ -310,7 +336,8 @@ int smoe_gemm_wgrad(const void* a_t_fp8, const void* a_sf, const void* b_t_fp8, 
 int smoe_gemm_wgrad_mn(const void* a_fp8, const void* a_sf, const void* b_fp8, const void* b_sf, const int* efo,
                        float* c, int64_t M, int64_t N, int64_t TKp, int64_t E, int accumulate, int layout,
                        int* status, void* stream) {
-  if (M % 256 || N % 256 || TKp % 128 || E <= 0 || (layout & ~3)) return SMOE_ERR_SHAPE;
+  if (M <= 0 || N <= 0 || M % 256 || N % 256 || TKp < 0 || TKp % 128 || E <= 0 || (layout & ~3)) return SMOE_ERR_SHAPE;
+  if (TKp == 0) return wgrad_nothing_routed(c, M, N, E, accumulate, (cudaStream_t)stream);
   GemmParams p{};
   p.rows = (int)M; p.N = (int)N; p.K = (int)TKp; p.E = (int)E;
   p.efo = efo; p.sfa = (const uint8_t*)a_sf; p.sfb = (const uint8_t*)b_sf;

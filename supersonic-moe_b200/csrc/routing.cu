@@ -136,8 +136,10 @@ scatter_fill_kernel(const int* __restrict__ idx, const float* __restrict__ probs
     s_base[E] = tot_u;
   }
   __syncthreads();
+  // published offsets never point past the allocation (they can only exceed it when the caller sized the buffers
+  // from counts that do not match idx): the GEMMs that walk efo then stay inside the buffers too
   if (blockIdx.x == 0)
-    for (int e = threadIdx.x; e <= E; e += blockDim.x) efo_out[e] = s_efo[e];
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) efo_out[e] = min(s_efo[e], TKp_alloc / alignment * alignment);
   const int real_TK = tot_u;        // == naept[N]
   const int real_TKp = tot_p;
 
@@ -176,11 +178,17 @@ scatter_fill_kernel(const int* __restrict__ idx, const float* __restrict__ probs
             }
             ++slot_rank;
             const int tm = tm_base + rank;
-            x_gather[pos] = row;
-            s_scatter[pos] = tm;
-            s_rev[tm] = pos;
-            scores[tm] = probs[(size_t)row * K + k];
-            src_idx[tm] = row * K + k;
+            // buffers sized from a caller's (possibly stale) per-expert counts may be too small for what the
+            // indices really hold: the excess is dropped, never written past the allocation
+            if (pos < TKp_alloc) {
+              x_gather[pos] = row;
+              s_scatter[pos] = tm;
+            }
+            if (tm < TK_alloc) {
+              s_rev[tm] = pos < TKp_alloc ? pos : 0;
+              src_idx[tm] = row * K + k;
+            }
+            if (tm < TKp_alloc) scores[tm] = probs[(size_t)row * K + k];
           }
         }
       }

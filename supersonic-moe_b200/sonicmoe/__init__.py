@@ -13,6 +13,8 @@ from .ernie_compat.deepep_metadata import deepep_topk_to_sonic_metadata  # noqa:
 from .functional import (  # noqa: F401
     _DownProjection,
     _UpProjection,
+    clear_weight_cache,
+    drop_weight_fp8,
     enable_fp8,
     enable_quack_gemm,
     moe_TC_softmax_topk_layer,

@@ -42,12 +42,16 @@ SIGNATURES = {
     "smoe_gemm_dgated_fused_partials": (_L, [_L]),
     "smoe_gemm_wgrad": (_I, [_P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _I, _P, _P]),
     "smoe_gemm_wgrad_mn": (_I, [_P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _I, _I, _P, _P]),
-    "smoe_debug_force_bn": (_I, [_I]),
     "smoe_combine": (_I, [_P, _P, _P, _P, _P, _L, _L, _P]),
     "smoe_gather_scores": (_I, [_P, _P, _L, _P, _P]),
     "smoe_ds_finalize": (_I, [_P, _L, _L, _P, _L, _P, _P, _P, _P, _P]),
     "smoe_topk_softmax": (_I, [_P, _L, _L, _L, _P, _P, _P]),
     "smoe_topk_softmax_bwd": (_I, [_P, _P, _P, _L, _L, _L, _P, _P]),
+}
+
+# exported for the library's own tests and timing experiments only (csrc/smoe_internal.h); not product ABI
+INTERNAL_SIGNATURES = {
+    "smoe_internal_gemm_knobs": (_I, [_I]),
 }
 
 ERRORS = {1: "SMOE_ERR_SHAPE", 2: "SMOE_ERR_ALIGN", 3: "SMOE_ERR_DRIVER", 4: "SMOE_ERR_TMAP", 5: "SMOE_ERR_LAUNCH",
@@ -64,7 +68,7 @@ def _load():
             f"{LIB_PATH} is missing: build it with `python supersonic-moe_b200/build.py` "
             "(there is no CPU or PyTorch fallback for the MoE kernels)")
     lib = ctypes.CDLL(LIB_PATH)
-    for name, (res, args) in SIGNATURES.items():
+    for name, (res, args) in {**SIGNATURES, **INTERNAL_SIGNATURES}.items():
         fn = getattr(lib, name)  # AttributeError if the symbol is not exported
         fn.restype = res
         fn.argtypes = args

@@ -196,6 +196,12 @@ class SonicMoEMlpNode:
         layout.  Call before `optimizer.step()`."""
         self._flush_native_grads()
         self._warmed_for_step = False
+        # The optimizer is about to change the expert weights, often through `param.data.copy_(master)`, which does
+        # not move the tensor version counter the caches look at: drop the stacked copies and their FP8 forms now
+        # (they would be rebuilt after the update anyway; the fp32 gradient buffers stay).
+        from ..functional import drop_weight_fp8
+        for k in [k for k in self._w_cache if isinstance(k, tuple) and k[0] == "w"]:
+            drop_weight_fp8(*self._w_cache.pop(k))
 
     def invalidate_caches(self) -> None:
         """Drop the stacked weights, the gradient buffers and the FP8 weight cache."""

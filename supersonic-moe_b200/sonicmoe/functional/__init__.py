@@ -149,7 +149,18 @@ def precompute_weight_fp8(w1: torch.Tensor, w2: torch.Tensor):
 
 
 def clear_weight_cache():
+    """Forget every cached FP8 weight copy.  Freshness is judged by (address, tensor version counter, identity);
+    an in-place update that bypasses the version counter - `param.data.copy_(master)`, the usual pattern of
+    master-weight optimizers - is invisible to it, so such a training loop calls this (or `drop_weight_fp8`)
+    once per optimizer step."""
     _WEIGHT_CACHE.clear()
+
+
+def drop_weight_fp8(*weights: torch.Tensor):
+    """Forget the cached FP8 copies (both orientations) of the given weights only."""
+    for w in weights:
+        for transposed in (False, True):
+            _WEIGHT_CACHE.pop((w.data_ptr(), tuple(w.shape), tuple(w.stride()), transposed, w.device.index), None)
 
 
 # ----------------------------------------------------------------------------
@@ -175,28 +186,57 @@ def _after_accumulate(base):
 
 # Where the next layer call should put its two token-side results (forward output, dx).  The expert-parallel layer
 # points them at memory that the peer GPUs have mapped, so that the return exchange reads them in place.
-_PLACEMENT: dict = {}
+_PLACEMENT: list = []       # innermost `place_results` block last
 
 
 @contextmanager
 def place_results(out: torch.Tensor | None = None, dx: torch.Tensor | None = None):
     """Within the block, the next `_UpProjection` / `_DownProjection` pair writes its forward output into `out` and,
-    in its backward, dx into `dx` (contiguous bf16 [N,H] CUDA tensors) instead of fresh allocations."""
-    _PLACEMENT.update(out_buf=out, dx_buf=dx)
+    in its backward, dx into `dx` (contiguous bf16 [N,H] CUDA tensors) instead of fresh allocations.  The request
+    is consumed by the first `_UpProjection.forward` that runs inside the block."""
+    frame = {"out_buf": out, "dx_buf": dx}
+    _PLACEMENT.append(frame)
     try:
         yield
     finally:
-        _PLACEMENT.clear()
+        _PLACEMENT.remove(frame)
 
 
-# hand-off of FP8 payloads from _UpProjection.forward to _DownProjection.forward
-# (the returned y1 / z tensors are zero-stride placeholders that only carry the
-# autograd edges)
-_HANDOFF: list = []
+def _take_placement():
+    if not _PLACEMENT:
+        return None, None
+    frame = _PLACEMENT[-1]
+    out, dx = frame["out_buf"], frame["dx_buf"]
+    frame["out_buf"] = frame["dx_buf"] = None
+    return out, dx
+
+
+# Hand-off of the FP8 payloads from _UpProjection.forward to _DownProjection.forward.  The y1 / z tensors the first
+# Function returns are zero-stride placeholders that only carry the autograd edges; each invocation allocates a fresh
+# one-element storage for its z placeholder, and the address of that storage is the invocation's token: it is unique
+# while the placeholder is alive, and it survives autograd handing the second Function a new Tensor object over the
+# same storage (the reference stamps a token attribute on the returned tensors instead,
+# sonicmoe/functional/__init__.py:438-488).  Two layers whose forwards interleave therefore pair up correctly.
+_HANDOFF: dict = {}
+_HANDOFF_MAX = 64           # entries of invocations whose second half never ran are dropped oldest-first
 
 
 def _placeholder(like: torch.Tensor, shape):
     return torch.empty((), dtype=torch.bfloat16, device=like.device).expand(*shape)
+
+
+def _handoff_put(z_placeholder: torch.Tensor, link: dict):
+    if len(_HANDOFF) >= _HANDOFF_MAX:
+        _HANDOFF.pop(next(iter(_HANDOFF)))
+    _HANDOFF[z_placeholder.data_ptr()] = link
+
+
+def _handoff_take(z_placeholder: torch.Tensor) -> dict:
+    link = _HANDOFF.pop(z_placeholder.data_ptr(), None)
+    if link is None:
+        raise RuntimeError("_DownProjection got a z that no _UpProjection.forward produced: the FP8 hand-off is "
+                           "addressed by the z placeholder _UpProjection returned, pass that tensor on unchanged")
+    return link
 
 
 class Fp8CombineGradHandle:
@@ -255,8 +295,8 @@ class _UpProjection(torch.autograd.Function):
                 xg_q, a_sf = ops.quant_rows_scatter(x.contiguous(), naept, s_rev, s_scatter_idx, TKp, efo[-1:])
             z_q, z_sc, y1_q, y1_sf = ops.gemm_gated(xg_q, None, a_sf, w1_q, w1_sf, efo, TKp)
             del xg_q
-        link = {"y1": (y1_q, y1_sf), "z": (z_q, z_sc), "out_buf": _PLACEMENT.get("out_buf")}
-        ctx.dx_buf = _PLACEMENT.get("dx_buf")
+        out_buf, ctx.dx_buf = _take_placement()
+        link = {"y1": (y1_q, y1_sf), "z": (z_q, z_sc), "out_buf": out_buf}
         cfg = fp8_config if fp8_config is not None else get_active_config()
         if cfg is not None and cfg.resolve_recompute_z() and not is_inference:
             # keep what regenerates z instead of z itself; the backward re-runs this GEMM and gets the same bytes
@@ -264,7 +304,6 @@ class _UpProjection(torch.autograd.Function):
             link["z_recompute"] = (x if prequant_payload is None else None, x_q, x_raw, w1, efo, x_gather_idx,
                                    s_scatter_idx, s_rev, naept, TKp)
             del z_q, z_sc
-        _HANDOFF.append(link)
         ctx.link = link
         ctx.T = x.shape[0]
         ctx.x_is_fp8 = prequant_payload is not None
@@ -273,6 +312,7 @@ class _UpProjection(torch.autograd.Function):
                               w1, efo, x_gather_idx, s_rev, naept)
         y1 = _placeholder(x, (TKp, N2 // 2))
         z = _placeholder(x, (TKp, N2))
+        _handoff_put(z, link)
         ctx.mark_non_differentiable(y1)
         return y1, z
 
@@ -309,6 +349,7 @@ class _UpProjection(torch.autograd.Function):
             dx = ops.combine(dx_exp, s_rev, naept, None, ctx.T, out=buf)
             if dx.dtype != ctx.x_dtype:
                 dx = dx.to(ctx.x_dtype)
+        ops.post_status(dz_q.device)      # last kernels of the layer's backward: let the next call see their status
         return (dx, dw1) + (None,) * 15
 
 
@@ -351,13 +392,12 @@ class _DownProjection(torch.autograd.Function):
         _require_fp8()
         if b2 is not None:
             raise NotImplementedError("expert biases are not supported on the MXFP8 path")
-        if not _HANDOFF:
-            raise RuntimeError("_DownProjection must directly follow _UpProjection (FP8 hand-off is empty)")
-        link = _HANDOFF.pop()
+        link = _handoff_take(z)
         y1_q, y1_sf = link.pop("y1")
         w2_q, w2_sf = weight_fp8(w2, False)
         y2 = ops.gemm_varlen_m(y1_q, y1_sf, w2_q, w2_sf, efo)
         o = ops.combine(y2, s_rev, naept, topk_scores, int(T), out=link.pop("out_buf", None))
+        ops.post_status(o.device)
         ctx.link = link
         ctx.T = int(T)
         ctx.grad_handle = fp8_combine_grad_handle
@@ -489,6 +529,7 @@ def moe_TC_softmax_topk_layer(x, router_w, w1, b1, w2, b2, K, stream_id, activat
     expert_frequency [E] int32); differentiable w.r.t. x, router_w, w1, w2."""
     _require_fp8()
     require_swiglu(activation_type)
+    ops.poll_status(x.device)         # a device-side failure of an earlier pass surfaces here, without a sync
     T, H = x.shape
     E = router_w.shape[0]
     w1_e, w2_e = _expert_major(w1), _expert_major(w2)

@@ -31,6 +31,7 @@ def run_sonic_moe(hidden_states, topk_indices, topk_scores, K, E, w1, w2, fp8=Fa
     device-to-host copy happens."""
     if not fp8:
         raise NotImplementedError("run_sonic_moe: only fp8=True (MXFP8) is built")
+    ops.poll_status(hidden_states.device)     # a device-side failure of an earlier pass surfaces here, without a sync
     N = hidden_states.shape[0]
     idx = topk_indices if topk_indices.dtype == torch.int32 else topk_indices.to(torch.int32)
     probs = topk_scores.detach()

@@ -68,11 +68,51 @@ def status_word(device) -> torch.Tensor:
     return _status[key]
 
 
+def _raise_status(device, code):
+    status_word(device).zero_()
+    raise RuntimeError(f"sonicmoe GEMM kernel reported device failure code {code} on {torch.device(device)} "
+                       "(a bounded wait inside a kernel ran out; results of that step are invalid)")
+
+
 def check_status(device):
+    """Synchronous read of the device status word; raises when a kernel recorded a failure."""
     s = int(status_word(device).item())
     if s != 0:
-        status_word(device).zero_()
-        raise RuntimeError(f"sonicmoe GEMM kernel reported device failure code {s} (a bounded wait ran out)")
+        _raise_status(device, s)
+
+
+# The layer reads the status word without ever waiting for the GPU: the end of a forward / backward enqueues a
+# 4-byte copy of the word into pinned host memory plus an event; the next entry into the layer looks at the copies
+# whose event has completed and raises if one is non-zero.  A failure therefore surfaces one call late at the
+# latest, and a healthy run pays one tiny copy per pass and no synchronisation.
+_posted = {}     # device index -> [(pinned int32 tensor, event), ...] not yet looked at
+
+
+def post_status(device):
+    """Enqueue, on the current stream, a copy of the status word to the host (no-op while a graph is captured)."""
+    device = torch.device(device)
+    if device.type != "cuda" or torch.cuda.is_current_stream_capturing():
+        return
+    q = _posted.setdefault(device.index, [])
+    if len(q) >= 8:           # nobody polls (e.g. a forward-only loop through the raw Functions): keep the newest
+        del q[:-4]
+    host = torch.empty(1, dtype=_I32, pin_memory=True)
+    host.copy_(status_word(device), non_blocking=True)
+    ev = torch.cuda.Event()
+    ev.record()
+    q.append((host, ev))
+
+
+def poll_status(device):
+    """Look at the posted copies that have arrived; raise on a recorded failure.  Never waits."""
+    device = torch.device(device)
+    q = _posted.get(device.index)
+    while q and q[0][1].query():
+        host, _ = q.pop(0)
+        code = int(host[0])
+        if code != 0:
+            q.clear()
+            _raise_status(device, code)
 
 
 # ---------------------------------------------------------------- routing

@@ -277,13 +277,13 @@ def test_gemm_varlen_m(ops, bn, tiles, N, K):
     b_q, b_sc = rand_fp8((E, N, K), g)
     a_sf = Q.pack_isa(a_sc, rows, K)
     b_sf = Q.pack_isa(b_sc.reshape(E * N, K // 32), E * N, K)
-    lib.smoe_debug_force_bn(bn)
+    lib.smoe_internal_gemm_knobs(bn)
     try:
         c = ops.gemm_varlen_m(a_q.to(DEV), a_sf.to(DEV), b_q.to(DEV), b_sf.to(DEV), efo.to(DEV))
         torch.cuda.synchronize()
         ops.check_status(DEV)
     finally:
-        lib.smoe_debug_force_bn(0)
+        lib.smoe_internal_gemm_knobs(0)
     A, B = deq(a_q, a_sc).to(DEV), deq(b_q, b_sc).to(DEV)
     for e in range(E):
         a, b = int(efo[e]), int(efo[e + 1])
@@ -313,7 +313,7 @@ GATHER_MODES = ["tma_gather", "gathered", "tma_gather_1cta", "gathered_1cta"]
 
 def _force(mode):
     from sonicmoe._lib import lib
-    lib.smoe_debug_force_bn((1 << 17) if mode.endswith("_1cta") else 0)
+    lib.smoe_internal_gemm_knobs((1 << 17) if mode.endswith("_1cta") else 0)
 
 
 @pytest.mark.parametrize("T,H,I,tiles", GATED_SHAPES)
@@ -327,13 +327,13 @@ def test_gemm_gated_same_bytes_for_every_column_tile(ops, T, H, I, tiles):
             wq.reshape(E, 2 * I, H).to(DEV), Q.pack_isa(ws, E * 2 * I, H).to(DEV), efo.to(DEV), rows)
     outs = {}
     for bn in (128, 192, 256):
-        lib.smoe_debug_force_bn(bn)
+        lib.smoe_internal_gemm_knobs(bn)
         try:
             outs[bn] = ops.gemm_gated(*args)
             torch.cuda.synchronize()
             ops.check_status(DEV)
         finally:
-            lib.smoe_debug_force_bn(0)
+            lib.smoe_internal_gemm_knobs(0)
     n = int(efo[-1])
     for bn in (192, 256):
         for got, want in zip(outs[bn], outs[128]):
@@ -430,7 +430,7 @@ def test_gemm_wgrad(ops, bn, M, N, tiles):
     a_sf, b_sf = Q.pack_isa(a_sc, M, TKp), Q.pack_isa(b_sc, N, TKp)
     A, B = deq(a_q, a_sc).to(DEV), deq(b_q, b_sc).to(DEV)
     init = torch.randn(E, M, N, generator=g)
-    lib.smoe_debug_force_bn(bn)
+    lib.smoe_internal_gemm_knobs(bn)
     try:
         out = init.clone().to(DEV)
         ops.gemm_wgrad(a_q.to(DEV), a_sf.to(DEV), b_q.to(DEV), b_sf.to(DEV), efo.to(DEV), out, accumulate=True)
@@ -439,7 +439,7 @@ def test_gemm_wgrad(ops, bn, M, N, tiles):
         torch.cuda.synchronize()
         ops.check_status(DEV)
     finally:
-        lib.smoe_debug_force_bn(0)
+        lib.smoe_internal_gemm_knobs(0)
     for e in range(E):
         a, b = int(efo[e]), int(efo[e + 1])
         ref = A[:, a:b] @ B[:, a:b].T if b > a else torch.zeros(M, N, device=DEV)
@@ -526,14 +526,14 @@ def test_gemm_dgated_fused_quantizers_match_separate_kernels(ops, T, H, I, tiles
     w_sf = Q.pack_isa(ws, E * I, H).to(DEV)
     a_in = dq[a_idx.long()].contiguous().to(DEV)
     args = (a_sf, wq.reshape(E, I, H).to(DEV), w_sf, efo.to(DEV), zq.to(DEV), zs.to(DEV), s.to(DEV), rows)
-    lib.smoe_debug_force_bn(bn)
+    lib.smoe_internal_gemm_knobs(bn)
     try:
         dz, y1s, dsp = ops.gemm_dgated(a_in, None, *args)
         f_dzq, f_rsf, f_csf, f_yq, f_ysf, f_dsp = ops.gemm_dgated_fused(a_in, *args)
         torch.cuda.synchronize()
         ops.check_status(DEV)
     finally:
-        lib.smoe_debug_force_bn(0)
+        lib.smoe_internal_gemm_knobs(0)
     r_q, r_rsf, r_qt, r_csf = ops.quant_iso32(dz)
     r_yt, r_ysf = ops.quant_cols_t(y1s, None, rows)
     n = int(efo[-1])          # rows of real segments (the tail of the allocation is never written)
