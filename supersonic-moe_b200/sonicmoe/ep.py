@@ -299,6 +299,7 @@ class ExpertParallelMoE:
     def __call__(self, x, topk_idx, topk_scores, w1, w2):
         plan = DispatchPlan(topk_idx, self.E, self.group)
         self.El = plan.El
+        self.last_rows_received = plan.n_recv
         fp8 = self.payload == "fp8"
         self.tokens_per_local_expert = plan.tokens_per_local_expert
         rows, probs, q, raw, local_idx = _Dispatch.apply(x, topk_scores, plan, fp8)
@@ -314,3 +315,83 @@ class ExpertParallelMoE:
         o_recv = self.expert_fn(rows, local_idx, probs, w1, w2, raw, handle)
         self._place = None
         return _Combine.apply(o_recv, plan, handle)
+
+
+def parity_against_single_gpu(group=None, device=None, T=1024, H=512, I=256, K=4, experts_per_rank=8, seed=200,
+                              starve_last_rank=False):
+    """Self-check of the expert-parallel step on the ranks of `group` (every rank calls it): each rank draws its own
+    seeded tokens, the step runs expert-parallel, and every rank then pushes ALL ranks' tokens through the
+    single-GPU layer with all experts local.  Returns {tensor: (cosine, relative RMS error)} of the expert-parallel
+    out / dx / dscores (this rank's tokens) and dw1 / dw2 (this rank's experts, summed over all ranks' tokens)
+    against that single-GPU result.  Both sides use the same quantisation points; they differ by the bf16 rounding
+    of per-rank partial sums and by the column-wise re-quantisation of the FP8 payload for the weight gradients.
+    `starve_last_rank` routes every token to the experts of the other ranks, so that the last rank runs the step
+    with zero received rows."""
+    from . import ops
+    from .interface import run_sonic_moe
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    dev = torch.device(device if device is not None else torch.device("cuda", torch.cuda.current_device()))
+    E = experts_per_rank * world
+    if starve_last_rank and (world < 2 or (world - 1) * experts_per_rank < K):
+        raise ValueError("starve_last_rank needs at least K experts outside the last rank")
+
+    def inputs(r):
+        g = torch.Generator().manual_seed(seed + r)
+        x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+        dy = torch.randn(T, H, generator=g).to(torch.bfloat16)
+        logits = torch.randn(T, E, generator=g)
+        if starve_last_rank:
+            logits[:, (world - 1) * experts_per_rank:] = float("-inf")
+        vals, idx = logits.topk(K, dim=-1)
+        return x, dy, torch.softmax(vals, -1), idx.to(torch.int32)
+
+    gw = torch.Generator().manual_seed(seed - 1)
+    w1 = (torch.randn(E, 2 * I, H, generator=gw) * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, generator=gw) * 0.02).to(torch.bfloat16)
+    El, lo = experts_per_rank, rank * experts_per_rank
+    x, dy, scores, idx = inputs(rank)
+    xd = x.to(dev).requires_grad_(True)
+    sd = scores.to(dev).requires_grad_(True)
+    w1l = w1[lo:lo + El].contiguous().to(dev).requires_grad_(True)
+    w2l = w2[lo:lo + El].contiguous().to(dev).requires_grad_(True)
+    ep = ExpertParallelMoE(E, K, group if group is not None else dist.group.WORLD)
+    out = ep(xd, idx.to(dev), sd, w1l, w2l)
+    out.backward(dy.to(dev))
+    torch.cuda.synchronize(dev)
+    ops.check_status(dev)
+    dw1_ref = torch.zeros(El, 2 * I, H, device=dev)
+    dw2_ref = torch.zeros(El, H, I, device=dev)
+    mine = None
+    w1a, w2a = w1.to(dev), w2.to(dev)
+    for r in range(world):
+        xr, dyr, sr, ir = inputs(r)
+        xa = xr.to(dev).requires_grad_(True)
+        sa = sr.to(dev).requires_grad_(True)
+        w1g, w2g = w1a.detach().requires_grad_(True), w2a.detach().requires_grad_(True)
+        o = run_sonic_moe(xa, ir.to(dev), sa, K, E, w1g, w2g, fp8=True)
+        o.backward(dyr.to(dev))
+        dw1_ref += w1g.grad[lo:lo + El].float()
+        dw2_ref += w2g.grad[lo:lo + El].float()
+        if r == rank:
+            mine = (o.detach(), xa.grad, sa.grad)
+    torch.cuda.synchronize(dev)
+    ops.check_status(dev)
+
+    def st(a, b):
+        a, b = a.float().flatten(), b.float().flatten()
+        if float(b.norm()) == 0.0:         # nothing routed to this rank's experts: both sides must be exactly zero
+            return (1.0, 0.0) if float(a.norm()) == 0.0 else (0.0, float("inf"))
+        return float((a * b).sum() / (a.norm() * b.norm())), float((a - b).norm() / b.norm())
+
+    w1_grad = w1l.grad if w1l.grad is not None else torch.zeros_like(dw1_ref)
+    w2_grad = w2l.grad if w2l.grad is not None else torch.zeros_like(dw2_ref)
+    res = dict(out=st(out, mine[0]), dx=st(xd.grad, mine[1]), ds=st(sd.grad, mine[2]), dw1=st(w1_grad, dw1_ref),
+               dw2=st(w2_grad, dw2_ref))
+    res["used_peer"] = ep._arena is not None
+    res["rows_received"] = int(ep.last_rows_received)
+    return res
+
+
+# per-tensor limits for `parity_against_single_gpu` (cosine above, relative RMS error below)
+PARITY_LIMITS = {"out": (0.999, 0.01), "dx": (0.999, 0.01), "ds": (0.999, 0.01), "dw1": (0.999, 0.04),
+                 "dw2": (0.999, 0.04)}

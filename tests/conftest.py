@@ -35,3 +35,20 @@ def built_library():
 @pytest.fixture(scope="session", autouse=True)
 def _library_present(built_library):
     return built_library
+
+
+def pytest_sessionfinish(session, exitstatus):
+    """With SMOE_PARITY_REPORT=<path>: the measured cosine / relative RMS error of every tensor that went through
+    tests/parity_util.gate in this session (GPU vs fp32 gold, emulation vs gold, GPU vs emulation), as a table."""
+    path = os.environ.get("SMOE_PARITY_REPORT")
+    try:
+        from parity_util import REPORT
+    except Exception:
+        return
+    if not path or not REPORT:
+        return
+    with open(path, "w") as f:
+        f.write("| tensor | gate | GPU vs fp32: cos | rrmse | emulation vs fp32: cos | rrmse | GPU vs emulation: cos | rrmse |\n")
+        f.write("|---|---|---|---|---|---|---|---|\n")
+        for name, kind, a, b, c, d, e, g in REPORT:
+            f.write(f"| {name} | {kind} | {a:.5f} | {b:.5f} | {c:.5f} | {d:.5f} | {e:.5f} | {g:.5f} |\n")

@@ -1,51 +1,67 @@
-"""The reference-shape layer (T=8192, H=3072, I=1536, E=8, K=8, seed 0) at FULL size on the GPU.
+"""The benchmark layers at FULL size on the GPU, forward AND backward:
 
-The CPU oracle cannot run the whole layer at this size in seconds, so parity is checked through properties that do
-not depend on the size:
+  C2  T=8192  H=3072 I=1536 E=8   K=8, seed 0  (the reference shape; every token goes to every expert)
+  C4  T=16384 H=2048 I=768  E=128 K=8, seed 2  (Zipf-skewed routing: empty experts, up to 127 pad rows per expert)
+
+The CPU oracle cannot run a whole layer of this size in seconds, so parity is checked through pieces that can be
+carved out exactly (tests/parity_util.py, proven bit-exact on the oracles in tests/test_parity_util.py) and through
+size-independent properties:
 
 * routing metadata: bit-exact against the (vectorised) CPU restatement at full size;
-* forward output of a token depends on that token alone (row-wise quantizers, per-row GEMMs): a seeded sample of
-  tokens is pushed through the FP8-emulating oracle and the fp32 gold as a tiny layer of its own and must meet the
-  same two gates as the small configs;
+* out, dx, dscores of a seeded sample of tokens: the 32-row blocks holding their routed rows form a small layer with
+  identical quantisation groups -> FP8-emulating oracle and fp32 gold;
+* dw1[e], dw2[e] (whole matrices) of chosen experts: the expert alone with all its tokens -> both oracles;
+* empty experts: exactly-zero weight gradients; pad rows never leak: everything finite, masked / padded slots zero;
 * determinism: a repeated step is bit-identical, including the fp32 main_grad increments;
 * power-of-two homogeneity of the backward: every quantizer uses power-of-two scales, so doubling dy must double dx,
-  dscores and the main_grad increments exactly (a checksum over the whole backward dataflow);
-* pad rows and the over-allocated tail never leak: gradients of the scores of real slots are finite everywhere.
+  dscores and the main_grad increments exactly (a checksum over the whole backward dataflow).
+
+The inputs are N(0,1) (the distributions the benchmark configs name); on those the emulation of the reference
+dataflow itself sits a little above the published 7.6 % for some tensors, so the gold gate is the
+emulation-relative one (tests/test_gpu_moe.py holds the strict gate on the reference's own distribution).
 """
 import pytest
 import torch
 
 from oracle import moe as OM
 from oracle import routing as R
+from parity_util import block_closure, ds_by_slot, gate, oracles_on, single_expert
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
-T, H, I, E, K, SEED = 8192, 3072, 1536, 8, 8, 0
+CONFIGS = {
+    "C2": dict(T=8192, H=3072, I=1536, E=8, K=8, seed=0, skew=False),
+    "C4": dict(T=16384, H=2048, I=768, E=128, K=8, seed=2, skew=True),
+}
 
 
-def stats(got, ref):
-    got, ref = got.detach().float().cpu().flatten(), ref.detach().float().cpu().flatten()
-    cos = float((got * ref).sum() / (got.norm() * ref.norm()).clamp(min=1e-30))
-    rr = float((got - ref).norm() / ref.norm().clamp(min=1e-30))
-    return cos, rr
-
-
-@pytest.fixture(scope="module")
-def layer():
-    if not torch.cuda.is_available():
-        pytest.skip("no CUDA device")
-    import sonicmoe
-    g = torch.Generator().manual_seed(SEED)
+def make_inputs(cfg):
+    T, H, I, E, K = cfg["T"], cfg["H"], cfg["I"], cfg["E"], cfg["K"]
+    g = torch.Generator().manual_seed(cfg["seed"])
     x = torch.randn(T, H, generator=g).to(torch.bfloat16)
     dy = torch.randn(T, H, generator=g).to(torch.bfloat16)
     w1 = (torch.randn(E, 2 * I, H, generator=g) * 0.02).to(torch.bfloat16)
     w2 = (torch.randn(E, H, I, generator=g) * 0.02).to(torch.bfloat16)
     logits = torch.randn(T, E, generator=g)
+    if cfg["skew"]:
+        p = torch.arange(1, E + 1, dtype=torch.float32) ** -1.2
+        logits = logits + torch.log(p / p.sum())[torch.randperm(E, generator=g)]
     scores, idx = OM.router_topk_softmax(logits, K)
+    return x, dy, w1, w2, idx.to(torch.int32), scores.float()
+
+
+@pytest.fixture(scope="module", params=list(CONFIGS))
+def layer(request):
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import sonicmoe
+    cfg = CONFIGS[request.param]
+    T, H, I, E, K = cfg["T"], cfg["H"], cfg["I"], cfg["E"], cfg["K"]
+    x, dy, w1, w2, idx, scores = make_inputs(cfg)
     w1d, w2d = torch.nn.Parameter(w1.to(DEV)), torch.nn.Parameter(w2.to(DEV))
     w1d.main_grad = torch.zeros(E, 2 * I, H, dtype=torch.float32, device=DEV)
     w2d.main_grad = torch.zeros(E, I, H, dtype=torch.float32, device=DEV)
-    xd, dyd, idxd = x.to(DEV), dy.to(DEV), idx.to(torch.int32).to(DEV)
+    xd, dyd, idxd = x.to(DEV), dy.to(DEV), idx.to(DEV)
 
     def step(dy_scale=1.0):
         xg = xd.detach().requires_grad_(True)
@@ -58,46 +74,85 @@ def layer():
         sonicmoe.ops.check_status(DEV)
         return dict(out=out.detach(), dx=xg.grad, ds=sg.grad, dw1=w1d.main_grad.clone(), dw2=w2d.main_grad.clone())
 
-    return dict(sm=sonicmoe, x=x, dy=dy, w1=w1, w2=w2, idx=idx, scores=scores, step=step, first=step())
+    yield dict(name=request.param, cfg=cfg, sm=sonicmoe, x=x, dy=dy, w1=w1, w2=w2, idx=idx, scores=scores, step=step,
+               first=step(), md=R.topk_metadata(idx, scores, E, 128))
+    del w1d.main_grad, w2d.main_grad
+    torch.cuda.empty_cache()
 
 
 def test_routing_metadata_full_size_bit_exact(layer):
-    ops = layer["sm"].ops
-    idx, scores = layer["idx"].to(torch.int32), layer["scores"].float()
+    ops, cfg = layer["sm"].ops, layer["cfg"]
+    T, E, K = cfg["T"], cfg["E"], cfg["K"]
+    idx, scores = layer["idx"], layer["scores"]
     md = ops.topk_metadata(idx.to(DEV), scores.to(DEV), E, 128)
     ref = R.topk_metadata(idx, scores, E, 128, TK_alloc=md["TK_alloc"], TKp_alloc=md["TKp_alloc"])
     for key in ("efo", "x_gather_idx", "s_scatter_idx", "s_reverse_scatter_idx", "naept", "topk_scores",
-                "score_src_idx"):
+                "score_src_idx", "counts"):
         assert torch.equal(md[key].cpu(), ref[key]), key
     assert int(md["efo"][-1]) % 128 == 0 and bool((md["efo"][1:] >= md["efo"][:-1]).all())
     tk = T * K
-    # inverse-permutation property: position -> slot -> position
     rev = md["s_reverse_scatter_idx"][:tk].long()
-    assert torch.equal(torch.sort(rev).values, torch.sort(torch.unique(rev)).values)      # no position used twice
+    assert torch.unique(rev).numel() == tk                                                # no position used twice
+    if cfg["skew"]:
+        counts = ref["counts"]
+        assert int((counts == 0).sum()) > 0, "the skewed config is expected to leave experts empty"
+        assert int((ref["efo"][-1] - counts.sum())) > 0, "and to need pad rows"
 
 
-def test_sampled_tokens_forward_matches_oracles(layer):
-    """out[t] depends on token t only: a sample of tokens, run through the oracles as a 48-token layer, must agree."""
-    g = torch.Generator().manual_seed(123)
-    sample = torch.randperm(T, generator=g)[:48]
-    x, idx, scores = layer["x"][sample], layer["idx"][sample].to(torch.int32), layer["scores"][sample].float()
-    md = R.topk_metadata(idx, scores, E, 128)
-    gold = OM.moe_fp32(x, layer["w1"], layer["w2"], md)["o"]
-    emu = OM.moe_fp8_emulated(x, layer["w1"], layer["w2"], md)["o"]
-    got = layer["first"]["out"].cpu()[sample]
-    c_e, r_e = stats(got, emu)
-    assert c_e >= 0.9995 and r_e <= 0.03, ("vs FP8-emulating oracle", c_e, r_e)
-    c_g, r_g = stats(got, gold)
-    e_c, e_r = stats(emu, gold)
-    assert c_g >= min(0.997, e_c - 5e-4) and r_g <= max(0.076, 1.03 * e_r), ("vs fp32 gold", c_g, r_g, e_c, e_r)
+def test_sampled_tokens_forward_and_backward_match_oracles(layer):
+    """out[t], dx[t], dscores[t,:] of sampled tokens against both oracles on the block closure of the sample."""
+    cfg = layer["cfg"]
+    T, E, K = cfg["T"], cfg["E"], cfg["K"]
+    sample = torch.randperm(T, generator=torch.Generator().manual_seed(123))[:12].sort().values
+    U, idx_m, sc_m, used, where = block_closure(layer["idx"], layer["scores"], layer["md"], sample, E)
+    md_m, gold, emu = oracles_on(layer["x"][U], layer["dy"][U], layer["w1"][used], layer["w2"][used], idx_m, sc_m,
+                                 len(used))
+    got = layer["first"]
+    n = U.numel()
+    gate(f"{layer['name']} out", got["out"].cpu()[sample], gold["o"][where], emu["o"][where], strict=False)
+    gate(f"{layer['name']} dx", got["dx"].cpu()[sample], gold["dx"][where], emu["dx"][where], strict=False)
+    gate(f"{layer['name']} ds", got["ds"].cpu()[sample], ds_by_slot(gold["ds"], md_m, n, K)[where],
+         ds_by_slot(emu["ds"], md_m, n, K)[where], strict=False)
+
+
+def test_weight_gradients_of_chosen_experts_match_oracles(layer):
+    """dw1[e] and dw2[e] in full for the busiest expert (C2: one of eight equal ones) and, under skew, for a small
+    one whose last 128-row tile is mostly padding."""
+    cfg, idx, scores = layer["cfg"], layer["idx"], layer["scores"]
+    E = cfg["E"]
+    counts = torch.bincount(idx.flatten().long(), minlength=E)
+    chosen = [int(counts.argmax())]
+    if cfg["skew"]:
+        small = ((counts >= 16) & (counts < 128)).nonzero().flatten()
+        if small.numel():
+            chosen.append(int(small[0]))
+        if int(counts[chosen[0]]) > 6000:           # keep the CPU oracle's share to seconds
+            mid = (counts - 3000).abs().argmin()
+            chosen[0] = int(mid)
+    got = layer["first"]
+    for e in chosen:
+        tok, idx1, sc1 = single_expert(idx, scores, e)
+        _, gold, emu = oracles_on(layer["x"][tok], layer["dy"][tok], layer["w1"][e:e + 1], layer["w2"][e:e + 1],
+                                  idx1, sc1, 1)
+        gate(f"{layer['name']} dw1[{e}]", got["dw1"][e].cpu(), gold["dw1"][0], emu["dw1"][0], strict=False)
+        gate(f"{layer['name']} dw2[{e}]", got["dw2"][e].cpu(), gold["dw2_IH"][0], emu["dw2_IH"][0], strict=False)
+
+
+def test_empty_experts_masked_slots_and_finiteness(layer):
+    cfg, got = layer["cfg"], layer["first"]
+    counts = torch.bincount(layer["idx"].flatten().long(), minlength=cfg["E"])
+    empty = (counts == 0).nonzero().flatten().to(DEV)
+    if empty.numel():
+        assert (got["dw1"][empty] == 0).all() and (got["dw2"][empty] == 0).all()
+    for k in ("out", "dx", "ds", "dw1", "dw2"):
+        assert torch.isfinite(got[k].float()).all(), k
+    assert got["dw1"].abs().sum() > 0 and got["dw2"].abs().sum() > 0
 
 
 def test_repeat_is_bit_exact(layer):
     a, b = layer["first"], layer["step"]()
     for k in ("out", "dx", "ds", "dw1", "dw2"):
         assert torch.equal(a[k], b[k]), k
-    assert torch.isfinite(a["ds"]).all() and torch.isfinite(a["dx"].float()).all()
-    assert a["dw1"].abs().sum() > 0 and a["dw2"].abs().sum() > 0
 
 
 def test_backward_is_exactly_homogeneous_in_powers_of_two(layer):

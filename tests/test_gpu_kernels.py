@@ -237,6 +237,73 @@ def test_topk_softmax_fwd_bwd(ops, T, E, K):
     torch.testing.assert_close(dl.cpu(), OM.router_backward(s.cpu(), ri, dsc, E), rtol=1e-5, atol=1e-6)
 
 
+def test_topk_softmax_rows_with_fewer_than_k_finite_logits(ops):
+    """-inf-masked and NaN logits: the K indices stay distinct and in range (the finite ones first, then the lowest
+    unused index with a score of exactly zero), the scores of the finite picks are their softmax, and the backward
+    writes nothing outside [0, E)."""
+    T, E, K = 64, 16, 4
+    g = torch.Generator().manual_seed(7)
+    logits = torch.randn(T, E, generator=g)
+    logits[0, :] = float("-inf")                           # nothing selectable
+    logits[1, 2:] = float("-inf")                          # two finite logits
+    logits[2, :] = float("nan")                            # NaN counts as -inf
+    logits[3, 5] = float("nan")                            # one NaN among finite ones: never picked first
+    logits[4, 3:] = float("-inf"); logits[4, 1] = float("nan")
+    s, i = ops.topk_softmax(logits.to(DEV), K)
+    s, i = s.cpu(), i.cpu()
+    assert ((i >= 0) & (i < E)).all()
+    assert all(len(set(row.tolist())) == K for row in i)
+    assert torch.isfinite(s).all()
+    assert (s[0] == 0).all() and i[0].tolist() == [0, 1, 2, 3]
+    assert set(i[1, :2].tolist()) == {0, 1} and (s[1, 2:] == 0).all() and abs(float(s[1, :2].sum()) - 1) < 1e-6
+    assert (s[2] == 0).all()
+    assert 5 not in i[3].tolist()
+    assert set(i[4, :2].tolist()) == {0, 2} and (s[4, 2:] == 0).all()
+    clean = torch.nan_to_num(logits[5:], nan=float("-inf"))
+    rs, ri = OM.router_topk_softmax(clean, K)
+    assert torch.equal(i[5:], ri)
+    torch.testing.assert_close(s[5:], rs, rtol=1e-5, atol=1e-7)
+    # backward with a deliberately out-of-range index: ignored, neighbours untouched
+    bad = i.clone()
+    bad[0, 0] = 0x7fffffff
+    bad[1, 1] = -3
+    guard = torch.full((T + 2, E), 7.0, device=DEV)
+    dl = guard[1:-1]
+    from sonicmoe._lib import lib, check
+    dsc = torch.randn(T, K, generator=g).to(DEV)
+    sd, bd = s.to(DEV), bad.to(DEV)
+    check(lib.smoe_topk_softmax_bwd(sd.data_ptr(), bd.data_ptr(), dsc.data_ptr(), T, E, K, dl.data_ptr(),
+                                    torch.cuda.current_stream().cuda_stream), "topk_softmax_bwd")
+    torch.cuda.synchronize()
+    assert (guard[0] == 7).all() and (guard[-1] == 7).all() and torch.isfinite(dl).all()
+
+
+def test_topk_metadata_with_undersized_buffers_stays_in_bounds(ops):
+    """Buffers sized from per-expert counts that are too small for what idx holds: the rows that do not fit are
+    dropped and the published offsets are clamped - nothing is written past the allocations."""
+    N, K, E = 512, 4, 8
+    g = torch.Generator().manual_seed(3)
+    idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(N)]).to(torch.int32)
+    probs = torch.rand(N, K, generator=g)
+    TK, TKp = 1024, 1024                                    # the truth is 2048 routed pairs
+    from sonicmoe._lib import lib, check
+    dev = DEV
+    e = lambda n, dt=torch.int32: torch.full((n + 64,), -77, dtype=dt, device=dev)
+    efo, xg, ss, sr, na = e(E + 1), e(TKp), e(TKp), e(TK), e(N + 1)
+    sc, si, cnt = torch.full((TKp + 64,), -77.0, device=dev), e(TK), e(E)
+    ws = torch.empty(lib.smoe_topk_metadata_workspace(N, E), dtype=torch.uint8, device=dev)
+    check(lib.smoe_topk_metadata(idx.to(dev).data_ptr(), probs.to(dev).data_ptr(), N, K, E, 128, TK, TKp, 0, 0,
+                                 efo.data_ptr(), xg.data_ptr(), ss.data_ptr(), sr.data_ptr(), na.data_ptr(),
+                                 sc.data_ptr(), si.data_ptr(), cnt.data_ptr(), ws.data_ptr(),
+                                 torch.cuda.current_stream().cuda_stream), "topk_metadata")
+    torch.cuda.synchronize()
+    for buf, n in ((efo, E + 1), (xg, TKp), (ss, TKp), (sr, TK), (na, N + 1), (si, TK), (cnt, E)):
+        assert (buf[n:] == -77).all()
+    assert (sc[TKp:] == -77.0).all()
+    assert int(efo[:E + 1].max()) <= TKp and int(cnt[:E].sum()) == N * K
+    assert ((xg[:TKp] >= 0) & (xg[:TKp] < N)).all() and ((sr[:TK] >= 0) & (sr[:TK] < TKp)).all()
+
+
 # ------------------------------------------------------------------ GEMMs
 def rand_fp8(shape, g, lo_exp=118, hi_exp=126):
     """Random e4m3 bytes (no NaN) and random ue8m0 scale bytes per 1x32 group."""

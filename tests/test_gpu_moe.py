@@ -357,3 +357,209 @@ def test_caller_owned_buffers_for_output_and_dx(sm):
     # nothing leaks into the next call
     out, dx = run()
     assert out.data_ptr() not in (buf_o.data_ptr(), one.data_ptr()) and torch.equal(out, ref_out)
+
+
+def test_exact_sizing_with_nothing_routed(sm):
+    """`tokens_per_expert` all zero (what an expert-parallel rank passes when it received no routed pairs): every
+    expert-sorted buffer has zero rows, the GEMM entry points return without a launch, out / dx are zero and the
+    weight gradients are exactly zero - returned, and accumulated into main_grad."""
+    H, I, E, K = 256, 128, 8, 2
+    x, dy, w1, w2, _, _ = make_layer(64, H, I, E, K, 3)
+    idx = torch.full((64, K), -1, dtype=torch.int32)
+    scores = torch.rand(64, K)
+    xd = x.to(DEV).requires_grad_(True)
+    sd = scores.to(DEV).requires_grad_(True)
+    w1d, w2d = w1.to(DEV).requires_grad_(True), w2.to(DEV).requires_grad_(True)
+    out = sm.run_sonic_moe(xd, idx.to(DEV), sd, K, E, w1d, w2d, fp8=True, tokens_per_expert=[0] * E)
+    out.backward(dy.to(DEV))
+    torch.cuda.synchronize()
+    sm.ops.check_status(DEV)
+    assert (out == 0).all() and (xd.grad == 0).all() and (sd.grad == 0).all()
+    assert (w1d.grad == 0).all() and (w2d.grad == 0).all()
+    # with main_grad: the accumulators are left as they were
+    w1p, w2p = torch.nn.Parameter(w1.to(DEV)), torch.nn.Parameter(w2.to(DEV))
+    w1p.main_grad = torch.full((E, 2 * I, H), 3.0, dtype=torch.float32, device=DEV)
+    w2p.main_grad = torch.full((E, I, H), 5.0, dtype=torch.float32, device=DEV)
+    out = sm.run_sonic_moe(x.to(DEV).requires_grad_(True), idx.to(DEV), scores.to(DEV), K, E, w1p, w2p, fp8=True,
+                           tokens_per_expert=torch.zeros(E, dtype=torch.int64))
+    out.backward(dy.to(DEV))
+    torch.cuda.synchronize()
+    assert (w1p.main_grad == 3.0).all() and (w2p.main_grad == 5.0).all()
+    # the C ABI itself: zero rows are not an error, an overwriting weight gradient stores zeros
+    from sonicmoe._lib import lib
+    st = sm.ops.status_word(DEV)
+    assert lib.smoe_gemm_varlen_m(None, None, None, None, None, None, 0, 256, 128, E, st.data_ptr(), None) == 0
+    assert lib.smoe_gemm_gated(None, 0, None, None, None, None, None, None, None, None, None, 0, 256, 128, E,
+                               st.data_ptr(), None) == 0
+    c = torch.full((E, 256, 256), 9.0, dtype=torch.float32, device=DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.smoe_gemm_wgrad_mn(None, None, None, None, None, c.data_ptr(), 256, 256, 0, E, 0, 3, st.data_ptr(),
+                                  stream) == 0
+    assert lib.smoe_gemm_wgrad(None, None, None, None, None, c.data_ptr(), 256, 256, 0, E, 1, st.data_ptr(),
+                               stream) == 0
+    torch.cuda.synchronize()
+    assert (c == 0).all()
+
+
+def test_two_layers_forward_interleaved_before_their_backwards(sm):
+    """Two layers (different weights, different tokens) whose `_UpProjection`s both run before either
+    `_DownProjection`, and whose backwards run in the opposite order: each pair must find its own FP8 payloads
+    (reference: tests/ops/test_mlpnode_multilayer.py; hand-off keyed per invocation)."""
+    from sonicmoe import ops
+    from sonicmoe.functional import _DownProjection, _UpProjection, enable_fp8
+    T, H, I, E, K = 512, 512, 256, 8, 4
+    layers = []
+    for seed in (51, 52):
+        x, dy, w1, w2, _, _ = make_layer(T, H, I, E, K, seed)
+        idx, scores = masked_routing(T, E, K, E, seed + 10)
+        layers.append(dict(x=x, dy=dy, w1=w1, w2=w2, idx=idx, scores=scores))
+
+    def alone(L):
+        xd = L["x"].to(DEV).requires_grad_(True)
+        w1d, w2d = L["w1"].to(DEV).requires_grad_(True), L["w2"].to(DEV).requires_grad_(True)
+        out = sm.run_sonic_moe(xd, L["idx"].to(DEV), L["scores"].to(DEV), K, E, w1d, w2d, fp8=True)
+        out.backward(L["dy"].to(DEV))
+        return out.detach(), xd.grad, w1d.grad, w2d.grad
+
+    want = [alone(L) for L in layers]
+    st = []
+    with enable_fp8(True):
+        for L in layers:                                    # both up-projections first
+            xd = L["x"].to(DEV).requires_grad_(True)
+            w1d, w2d = L["w1"].to(DEV).requires_grad_(True), L["w2"].to(DEV).requires_grad_(True)
+            md = ops.topk_metadata(L["idx"].to(DEV), L["scores"].to(DEV), E, 128)
+            y1, z = _UpProjection.apply(xd, w1d, None, md["efo"], md["TKp_alloc"], K, 0, md["x_gather_idx"],
+                                        md["s_scatter_idx"], md["s_reverse_scatter_idx"], md["naept"], True,
+                                        sm.ActivationType.SWIGLU, False)
+            st.append(dict(xd=xd, w1d=w1d, w2d=w2d, md=md, y1=y1, z=z))
+        for L, s in zip(layers, st):                        # then both down-projections
+            md = s["md"]
+            s["out"] = _DownProjection.apply(s["y1"], s["z"], s["w2d"], None, md["topk_scores"], md["s_scatter_idx"],
+                                             md["efo"], T, K, 0, md["x_gather_idx"], md["s_scatter_idx"],
+                                             md["s_reverse_scatter_idx"], md["naept"], True,
+                                             sm.ActivationType.SWIGLU, None)
+        for L, s in reversed(list(zip(layers, st))):        # backwards in the opposite order
+            s["out"].backward(L["dy"].to(DEV))
+    torch.cuda.synchronize()
+    sm.ops.check_status(DEV)
+    for w, s in zip(want, st):
+        for name, a, b in zip(("out", "dx", "dw1", "dw2"), w, (s["out"].detach(), s["xd"].grad, s["w1d"].grad,
+                                                                 s["w2d"].grad)):
+            assert torch.equal(a, b), name
+    # a z that did not come from _UpProjection is refused instead of silently pairing with someone else's payload
+    with enable_fp8(True), pytest.raises(RuntimeError):
+        md = st[0]["md"]
+        _DownProjection.apply(torch.zeros(1, device=DEV), torch.zeros(1, device=DEV), st[0]["w2d"], None,
+                              md["topk_scores"], md["s_scatter_idx"], md["efo"], T, K, 0, md["x_gather_idx"],
+                              md["s_scatter_idx"], md["s_reverse_scatter_idx"], md["naept"], True,
+                              sm.ActivationType.SWIGLU, None)
+
+
+def test_weight_update_through_data_copy_is_seen_after_invalidation(sm):
+    """`param.data.copy_(master)` does not move the tensor version counter the FP8 weight cache looks at: the
+    cached copy stays in use until `drop_weight_fp8` / `clear_weight_cache` is called, and `SonicMoEMlpNode.step()`
+    drops its stacked weights and their FP8 copies itself."""
+    from sonicmoe.ernie_compat import SonicMoEMlpNode
+    T, H, I, E, K = 256, 256, 128, 8, 2
+    x, dy, w1, w2, _, _ = make_layer(T, H, I, E, K, 61)
+    idx, scores = masked_routing(T, E, K, E, 62)
+    w1d, w2d = w1.to(DEV), w2.to(DEV)
+    run = lambda: sm.run_sonic_moe(x.to(DEV), idx.to(DEV), scores.to(DEV), K, E, w1d, w2d, fp8=True)
+    a = run().clone()
+    w1d.data.copy_(w1d * 2)                       # invisible to the version counter
+    stale = run().clone()
+    sm.drop_weight_fp8(w1d)
+    fresh = run().clone()
+    assert torch.equal(a, stale) and not torch.equal(a, fresh)
+
+    class Lin:
+        def __init__(self, w):
+            self.weight = w
+
+    class Expert:
+        def __init__(self, e):
+            self.up_gate_proj = Lin(torch.cat([w1[e, 0::2].T, w1[e, 1::2].T], dim=1).contiguous().to(DEV))
+            self.down_proj = Lin(w2[e].T.contiguous().to(DEV))
+
+    experts = [Expert(e) for e in range(E)]
+    node = SonicMoEMlpNode(experts, E, H, I)
+    counts = torch.bincount(idx[idx >= 0].long(), minlength=E).tolist()
+    o1 = node(x.to(DEV), counts, idx.to(DEV), scores.to(DEV)).detach().clone()
+    node.step()
+    for e in experts:                             # "optimizer step" through .data
+        e.down_proj.weight.data.copy_(e.down_proj.weight * 2)
+    o2 = node(x.to(DEV), counts, idx.to(DEV), scores.to(DEV)).detach()
+    torch.cuda.synchronize()
+    c, r = stats(o2, o1 * 2)
+    assert not torch.equal(o1, o2) and c > 0.9999 and r < 0.01
+
+
+def test_device_failure_code_surfaces_at_the_next_call_without_a_sync(sm):
+    """The layer posts the GEMM status word to pinned host memory at the end of each pass and looks at it on the
+    next entry: a non-zero code (here written by hand; a kernel writes it when a bounded wait runs out) raises."""
+    T, H, I, E, K = 256, 256, 128, 8, 2
+    x, dy, w1, w2, _, _ = make_layer(T, H, I, E, K, 71)
+    idx, scores = masked_routing(T, E, K, E, 72)
+    w1d, w2d = w1.to(DEV), w2.to(DEV)
+    run = lambda: sm.run_sonic_moe(x.to(DEV), idx.to(DEV), scores.to(DEV), K, E, w1d, w2d, fp8=True)
+    run()
+    torch.cuda.synchronize()
+    run()                                          # healthy: the posted copy is zero, nothing raises
+    sm.ops.status_word(DEV).fill_(202)
+    run()                                          # this pass posts the non-zero word ...
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="202"):
+        run()                                      # ... and the next entry reports it
+    torch.cuda.synchronize()
+    assert int(sm.ops.status_word(DEV).item()) == 0
+    run()
+    torch.cuda.synchronize()
+    sm.ops.check_status(DEV)
+
+
+def make_layer_reference_bench(T, H, I, E, K, seed):
+    """Inputs as the reference's own benchmark draws them (tests/ops/bench_mlpnode_topk_nsys.py:113-200), the
+    distribution its published precision (cos >= 0.997, RRMSE < 7.6 %) was measured on: x = randn * 0.02,
+    dy = randn * 0.01, weights = randn / sqrt(fan_in), experts = top-k of randn(T,E), probabilities = U(0.5,1)
+    normalised over the K slots."""
+    g = torch.Generator().manual_seed(seed)
+    w1 = (torch.randn(E, 2 * I, H, generator=g) / H ** 0.5).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, generator=g) / I ** 0.5).to(torch.bfloat16)
+    _, idx = torch.randn(T, E, generator=g).topk(K, dim=-1)
+    p = torch.rand(T, K, generator=g) * 0.5 + 0.5
+    p = (p / p.sum(dim=1, keepdim=True)).float()
+    x = (torch.randn(T, H, generator=g) * 0.02).to(torch.bfloat16)
+    dy = (torch.randn(T, H, generator=g) * 0.01).to(torch.bfloat16)
+    return x, dy, w1, w2, idx.to(torch.int32), p
+
+
+@pytest.mark.parametrize("T,H,I,E,K,seed", [(1024, 512, 256, 16, 4, 42), (512, 1024, 384, 8, 8, 123),
+                                             (2048, 512, 256, 8, 8, 777)])
+def test_reference_bench_distribution_meets_the_published_tolerance_as_it_stands(sm, T, H, I, E, K, seed):
+    """On the reference's own input distribution every tensor - out, dx, dscores, dw1, dw2 - must meet the published
+    bound itself: cosine >= 0.997 and RRMSE <= 7.6 % against the fp32 gold, no emulation-relative widening.  (The
+    CPU emulation of the reference dataflow lands on the reference's published per-tensor figures here: out 0.9978,
+    dx 0.9975, ds 0.9972, dw1 0.9977, dw2 0.9972.)"""
+    from parity_util import gate
+    x, dy, w1, w2, idx, p = make_layer_reference_bench(T, H, I, E, K, seed)
+    md = R.topk_metadata(idx, p, E, 128)
+    gold = OM.moe_fp32(x, w1, w2, md, dy)
+    emu = OM.moe_fp8_emulated(x, w1, w2, md, dy)
+    xd = x.to(DEV).requires_grad_(True)
+    pd = p.to(DEV).requires_grad_(True)
+    w1d, w2d = w1.to(DEV).requires_grad_(True), w2.to(DEV).requires_grad_(True)
+    counts = torch.bincount(idx.flatten().long(), minlength=E).tolist()
+    out = sm.run_sonic_moe(xd, idx.to(DEV), pd, K, E, w1d, w2d, fp8=True, tokens_per_expert=counts)
+    out.backward(dy.to(DEV))
+    torch.cuda.synchronize()
+    sm.ops.check_status(DEV)
+    tk = md["real_TK"]
+    ds_of = lambda r: torch.zeros(T * K).index_put_((md["score_src_idx"][:tk].long(),), r["ds"][:tk].float())
+    report = []
+    for name, got, ref, em in [("out", out, gold["o"], emu["o"]), ("dx", xd.grad, gold["dx"], emu["dx"]),
+                               ("ds", pd.grad.flatten(), ds_of(gold), ds_of(emu)),
+                               ("dw1", w1d.grad, gold["dw1"], emu["dw1"]),
+                               ("dw2", w2d.grad, gold["dw2"], emu["dw2_IH"].transpose(1, 2))]:
+        gate(name, got, ref, em, strict=True, report=report)
+    print("\n" + "\n".join(f"refdist {T}x{H}x{I} E{E} K{K} {n}: gpu cos {a:.5f} rrmse {b:.5f} | emulation "
+                           f"{c:.5f} {d:.5f} | gpu vs emulation {e:.5f} {f:.5f}" for n, a, b, c, d, e, f in report))
