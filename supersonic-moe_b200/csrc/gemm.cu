@@ -7,6 +7,7 @@
 
 #include "gemm.cuh"
 #include "gemm2.cuh"
+#include "gemm3.cuh"
 #include "smoe_b200.h"
 #include "smoe_internal.h"
 
@@ -59,6 +60,8 @@ static int make_tmap(CUtensorMap* m, CUtensorMapDataType dt, int esize, const vo
 static int g_force_bn = 0;
 static int g_skip_store = 0;
 static int g_force_v1 = 0;
+static int g_stage_cut = 0;
+static int g_l2_prefetch = -1;     // -1: the kernel's default
 
 // Per-device state: the SM count and the "large dynamic shared memory" function attribute belong to a device,
 // not to the process, so both are kept per device ordinal.
@@ -121,8 +124,66 @@ static int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
   int64_t pairs = sm_count() / 2;
   if (max_pair_tiles < pairs) pairs = max_pair_tiles;
   if (pairs <= 0) return SMOE_OK;
-  kern<<<(unsigned)(2 * pairs), S::THREADS, S::TOTAL, stream>>>(ta, tb, tsa, tsb, om.c, om.c2, om.c3, p);
+  GemmParams q = p;
+  q.dbg_stage_cut = g_stage_cut;
+  q.l2_prefetch = g_l2_prefetch >= 0 ? g_l2_prefetch : kDefaultL2Prefetch;
+  kern<<<(unsigned)(2 * pairs), S::THREADS, S::TOTAL, stream>>>(ta, tb, tsa, tsb, om.c, om.c2, om.c3, q);
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
+}
+
+// ---- two-CTA kernel with the 256 x 384 double-accumulator tile (PLAIN and WGRAD) ------------------------------
+template <int MODE>
+static int launch3(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa, const CUtensorMap& tsb,
+                   const CUtensorMap& tc, const GemmParams& p, int64_t max_pair_tiles, cudaStream_t stream) {
+  using S = Gemm3Smem<MODE>;
+  static bool attr_set[kMaxDevices] = {};
+  auto kern = gemm3_mxf8_kernel<MODE>;
+  if (!ensure_smem_attr(kern, S::TOTAL, attr_set)) return SMOE_ERR_LAUNCH;
+  int64_t pairs = sm_count() / 2;
+  if (max_pair_tiles < pairs) pairs = max_pair_tiles;
+  if (pairs <= 0) return SMOE_OK;
+  kern<<<(unsigned)(2 * pairs), S::THREADS, S::TOTAL, stream>>>(ta, tb, tsa, tsb, tc, p);
+  return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
+}
+
+// Whether the 384-wide kernel takes this problem.  WGRAD: B must be K-major ([N, TKp]); A either way.
+template <int MODE>
+static bool use_gemm3(const GemmParams& p) {
+  if (MODE != PLAIN && MODE != WGRAD) return false;
+  if (g_force_v1 || (g_force_bn != 0 && g_force_bn != kBN3)) return false;
+  if (p.N % kBN3 != 0 || p.E > kMaxExperts2) return false;
+  if (MODE == WGRAD && (p.rows % 256 != 0 || p.b_mn)) return false;
+  return true;
+}
+
+template <int MODE>
+static int run3(const void* a, int64_t a_rows, int64_t a_cols, const void* b, int64_t b_rows, int64_t b_cols,
+                GemmParams& p, cudaStream_t stream) {
+  CUtensorMap ta, tb, tsa, tsb, tc;
+  int rc = make_tmap_u8(&ta, a, a_rows, a_cols, BK, BM);
+  if (rc) return rc;
+  rc = make_tmap_u8(&tb, b, b_rows, b_cols, BK, kHN3 / 2);
+  if (rc) return rc;
+  const int64_t sfa_tiles = (int64_t)(p.rows / 128) * p.sfa_ktiles;
+  const int64_t sfb_tiles = (MODE == WGRAD) ? (int64_t)(p.N / 128) * p.sfb_ktiles : (b_rows / 128) * p.sfb_ktiles;
+  rc = make_tmap(&tsa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, p.sfa, sfa_tiles, 128, 128, kSfGroup2,
+                 CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc) return rc;
+  rc = make_tmap(&tsb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, p.sfb, sfb_tiles, 128, 128, kSfGroup2,
+                 CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc) return rc;
+  int64_t pair_tiles;
+  if (MODE == WGRAD) {
+    rc = make_tmap(&tc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.c, (uint64_t)p.E * p.rows, p.N, 16, 32,
+                   CU_TENSOR_MAP_SWIZZLE_64B);
+    pair_tiles = (int64_t)p.E * (p.rows / 256) * (p.N / kBN3);
+  } else {
+    rc = make_tmap(&tc, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.c, p.rows, p.N, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B);
+    pair_tiles = ((int64_t)p.rows / 256 + p.E) * (p.N / kBN3);
+  }
+  if (rc) return rc;
+  constexpr int M3 = (MODE == WGRAD) ? WGRAD : PLAIN;
+  return launch3<M3>(ta, tb, tsa, tsb, tc, p, pair_tiles, stream);
 }
 
 // Column tile of the two-CTA kernel for a mode and N; 0 = not applicable.
@@ -137,6 +198,7 @@ static int pick_bn2(int64_t N) {
     return ((N % 192 == 0 || padded * 10 <= N * 11) && g_force_bn != 128) ? 192 : 128;
   }
   if (g_force_bn == 128) return 128;
+  if (g_force_bn == kBN3) return (wide && N % 256 == 0) ? 256 : ((N % 192 == 0) ? 192 : 128);   // 384 did not apply
   if (g_force_bn == 192) return (N % 192 == 0) ? 192 : 128;
   if (g_force_bn == 256) return (wide && N % 256 == 0) ? 256 : 128;
   if (wide && N % 256 == 0) return 256;
@@ -152,9 +214,11 @@ static int run2(const void* a, int64_t a_rows, int64_t a_cols, const void* b, in
   if (rc) return rc;
   rc = make_tmap_u8(&tb, b, b_rows, b_cols, BK, bn / 2);
   if (rc) return rc;
-  rc = make_tmap(&tsa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, p.sfa, sfa_tiles, 128, 128, 4, CU_TENSOR_MAP_SWIZZLE_NONE);
+  rc = make_tmap(&tsa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, p.sfa, sfa_tiles, 128, 128, kSfGroup2,
+                 CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc) return rc;
-  rc = make_tmap(&tsb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, p.sfb, sfb_tiles, 128, 128, 4, CU_TENSOR_MAP_SWIZZLE_NONE);
+  rc = make_tmap(&tsb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, p.sfb, sfb_tiles, 128, 128, kSfGroup2,
+                 CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc) return rc;
   // upper bound of pair tiles: varlen-M: every expert may add one half-empty pair
   int64_t pair_tiles;
@@ -172,6 +236,7 @@ template <int MODE>
 static int run(const void* a, int64_t a_rows, int64_t a_cols, const void* b, int64_t b_rows, int64_t b_cols,
                GemmParams& p, int max_tiles_128, cudaStream_t stream) {
   if (p.E > kMaxExpertsSmem) return SMOE_ERR_SHAPE;
+  if (use_gemm3<MODE>(p)) return run3<MODE>(a, a_rows, a_cols, b, b_rows, b_cols, p, stream);
   {
     const int bn2 = pick_bn2<MODE>(p.N);
     const bool ok2 = bn2 != 0 && p.E <= kMaxExperts2 && (MODE != WGRAD || p.rows % 256 == 0);
@@ -244,6 +309,8 @@ int smoe_internal_gemm_knobs(int bn) {
   g_skip_store = ((bn >> 16) & 1) | (((bn >> 18) & 1) << 1);   // bit 16: no stores; bit 18: no epilogue (fused dgated)
   g_force_v1 = (bn >> 17) & 1;
   g_skip_store |= ((bn >> 19) & 0x1F) << 2;    // bits 19..23 -> timing-experiment bits 2..6 of GemmParams::debug_skip_store
+  g_stage_cut = (bn >> 24) & 3;                // bits 24..25: ring stages to leave unused
+  g_l2_prefetch = ((bn >> 26) & 0x1F) - 1;     // bits 26..30: L2 prefetch distance + 1 (0 = kernel default)
   return SMOE_OK;
 }
 
@@ -329,7 +396,7 @@ int smoe_gemm_wgrad(const void* a_t_fp8, const void* a_sf, const void* b_t_fp8, 
   p.rows = (int)M; p.N = (int)N; p.K = (int)TKp; p.E = (int)E;
   p.efo = efo; p.sfa = (const uint8_t*)a_sf; p.sfb = (const uint8_t*)b_sf;
   p.sfa_ktiles = (int)(TKp / 128); p.sfb_ktiles = (int)(TKp / 128);
-  p.c = c; p.accumulate = accumulate; p.status = status;
+  p.c = c; p.accumulate = accumulate; p.status = status; p.debug_skip_store = g_skip_store;
   return run<WGRAD>(a_t_fp8, M, TKp, b_t_fp8, N, TKp, p, (int)(E * (M / 128) * (N / 128)), (cudaStream_t)stream);
 }
 
@@ -342,7 +409,7 @@ int smoe_gemm_wgrad_mn(const void* a_fp8, const void* a_sf, const void* b_fp8, c
   p.rows = (int)M; p.N = (int)N; p.K = (int)TKp; p.E = (int)E;
   p.efo = efo; p.sfa = (const uint8_t*)a_sf; p.sfb = (const uint8_t*)b_sf;
   p.sfa_ktiles = (int)(TKp / 128); p.sfb_ktiles = (int)(TKp / 128);
-  p.c = c; p.accumulate = accumulate; p.status = status;
+  p.c = c; p.accumulate = accumulate; p.status = status; p.debug_skip_store = g_skip_store;
   p.a_mn = layout & 1; p.b_mn = (layout >> 1) & 1;
   return run<WGRAD>(a_fp8, p.a_mn ? TKp : M, p.a_mn ? M : TKp, b_fp8, p.b_mn ? TKp : N, p.b_mn ? N : TKp, p,
                     (int)(E * (M / 128) * (N / 128)), (cudaStream_t)stream);

@@ -53,6 +53,8 @@ struct GemmParams {
   uint8_t* y1s_col_sf;  // DGATEDQ out: ISA scales of y1s^T as a (N, TKp) operand (1x32 along TKp)
   int* status;          // device status word: 0 ok, else first failure code
   int debug_skip_store; // timing experiments only: drain TMEM but skip the global stores
+  int dbg_stage_cut;    // timing experiments only: use this many fewer ring stages
+  int l2_prefetch;      // K tiles ahead of the shared-memory ring at which operand tiles are prefetched into L2 (0 = off)
 };
 
 template <int BN>

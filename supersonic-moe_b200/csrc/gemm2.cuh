@@ -13,6 +13,8 @@ namespace smoe {
 constexpr int kEpiWarps2 = 8;
 constexpr int kThreads2 = 32 * (2 + kEpiWarps2);
 constexpr int kMaxExperts2 = 256;   // expert offsets cached in shared memory by the two-CTA kernel
+constexpr int kDefaultL2Prefetch = 0;
+constexpr int kSfGroup2 = 4;        // K tiles whose scales travel in one TMA copy (box rows of the scale tensor maps)
 
 // ---- cluster helpers -------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -49,6 +51,11 @@ __device__ __forceinline__ void tma_gather4_pair(uint32_t dst, const void* tmap,
       ::"r"(dst), "l"(tmap), "r"(bar_cluster), "r"(c0), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
       : "memory");
 }
+// Operand tile -> L2 only (no shared memory, no barrier): warms the line the ring will ask for a few K tiles later.
+__device__ __forceinline__ void tma_prefetch_l2_2d(const void* tmap, int c0, int c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tmap), "r"(c0), "r"(c1)
+               : "memory");
+}
 __device__ __forceinline__ void tmem_alloc2(uint32_t dst_smem, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols)
                : "memory");
@@ -66,6 +73,28 @@ __device__ __forceinline__ void mma_mxf8_pair(uint32_t d_tmem, uint64_t a_desc, 
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+// The same with the shared-memory descriptors given as (low word, high word): the high words are constants of the
+// kernel, only the low words (start address) move, so the issuing warp carries 32-bit values only.
+__device__ __forceinline__ void mma_mxf8_pair_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
+                                                 uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], da, db, %4, [%6], [%7], p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+__device__ __forceinline__ void tc_cp_sf_pair_lo(uint32_t dst_tmem, uint32_t src_lo, uint32_t src_hi) {
+  asm volatile(
+      "{\n\t.reg .b64 d;\n\t"
+      "mov.b64 d, {%1, %2};\n\t"
+      "tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], d;\n\t}"
+      ::"r"(dst_tmem), "r"(src_lo), "r"(src_hi)
       : "memory");
 }
 // completion of all MMAs issued so far -> one arrival on the barrier at this
@@ -110,13 +139,12 @@ struct Gemm2Smem {
   static constexpr int B_BYTES = (BN / 2) * BK;           // this CTA's half of the B tile
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int SFB_TILES = (BN == 128) ? 1 : 2;   // 128-row scale tiles covering the BN window
-  // Scales travel in their own ring: one slot holds the scales of kSfGroup consecutive K tiles
-  // (A: 4 x 512 B, B: 4 x 512 B per 128-row tile), fetched with one TMA copy per operand tile
-  // instead of one per K tile.
-  static constexpr int SF_GROUP = 4;
+  // Scales travel in their own ring: one slot holds the scales of SF_GROUP consecutive K tiles (A: SF_GROUP x 512 B,
+  // B: SF_GROUP x 512 B per 128-row tile), fetched with one TMA copy per operand tile instead of one per K tile.
+  // (A deeper ring of smaller groups - 5 slots of 2 K tiles - measured 10 % slower: the extra TMA copies and
+  // barrier traffic cost more than the longer prefetch distance gains.)
+  static constexpr int SF_GROUP = kSfGroup2;
   static constexpr int SF_SLOT_BYTES = SF_GROUP * 512 * (1 + SFB_TILES);
-  static constexpr int SF_SLOTS = 2;
-  static constexpr int SF_BYTES = ((SF_SLOTS * SF_SLOT_BYTES + 1023) / 1024) * 1024;
   // output staging per epilogue warp: PLAIN 2 KB (bf16 32x32), WGRAD 2 KB (f32 32x16),
   // DGATED 4 KB (dz) + 2 KB (y1s), GATED 2 KB (z e4m3 32x64) + 1 KB (y1 e4m3 32x32)
   // DGATEDQ 2 KB (dz e4m3 32x64) + 1 KB (y1s e4m3 32x32)
@@ -127,10 +155,15 @@ struct Gemm2Smem {
   static constexpr int EPI_WARPS = 4 * COL_GROUPS;
   static constexpr int THREADS = 32 * (2 + EPI_WARPS);
   static constexpr int EPI_BYTES = EPI_WARPS * EPI_BYTES_PER_WARP;
-  static constexpr int AUX_BYTES = 1024 + 2 * (kMaxExperts2 + 1) * 4;
-  static constexpr int STAGES_RAW = (227 * 1024 - 1024 - AUX_BYTES - EPI_BYTES - SF_BYTES) / STAGE_BYTES;
+  static constexpr int AUX_BYTES = 512 + 2 * (kMaxExperts2 + 1) * 4 + 8;      // barriers etc. + expert offsets
+  static constexpr int BUDGET = 227 * 1024 - 1024 - AUX_BYTES - EPI_BYTES;    // 1024: alignment slack
+  static constexpr int SF_SLOTS = 2;
+  static constexpr int STAGES_RAW = (BUDGET - SF_SLOTS * SF_SLOT_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int SF_BYTES = SF_SLOTS * SF_SLOT_BYTES;
   static constexpr int TOTAL = STAGES * STAGE_BYTES + SF_BYTES + EPI_BYTES + AUX_BYTES + 1024;
+  static_assert(TOTAL <= 227 * 1024, "shared memory budget");
+  static_assert((2 * STAGES + 4 + 2 * SF_SLOTS) * 8 <= 496, "barrier storage");
   static constexpr int ACC_STAGES = (BN == 256) ? 1 : 2;  // TMEM: 512 columns
   static constexpr int SF_COLS = 4 + 4 * SFB_TILES;
   static constexpr int SF_COL0 = ACC_STAGES * BN;
@@ -195,9 +228,9 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   uint8_t* epi = sfring + S::SF_BYTES;
   uint8_t* aux = epi + S::EPI_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(aux);     // full[S], empty[S], tfull[2], tempty[2], sffull[2], sfempty[2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux + 512);
-  volatile int* s_abort = reinterpret_cast<volatile int*>(aux + 516);
-  int* s_efo = reinterpret_cast<int*>(aux + 1024);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux + 496);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(aux + 500);
+  int* s_efo = reinterpret_cast<int*>(aux + 512);
   int* s_pairs = s_efo + (kMaxExperts2 + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -250,122 +283,167 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   const uint32_t sf_base = smem_u32(sfring);
   const int n_col_tiles = (p.N + BN - 1) / BN;
   const int n_total = (MODE == WGRAD) ? p.E * (p.rows / (2 * BM)) * n_col_tiles : s_pairs[p.E] * n_col_tiles;
+  const int nst = S::STAGES - p.dbg_stage_cut;       // ring stages in use (all of them outside timing experiments)
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer (both CTAs)
+    // Warp-uniform loops, one elected lane issues (see the MMA issuer below for why); only the gather path keeps
+    // per-lane state (four row indices each).
     if (lane == 0) {
       prefetch_tmap(&tmap_a); prefetch_tmap(&tmap_b); prefetch_tmap(&tmap_sfa); prefetch_tmap(&tmap_sfb);
     }
     const uint32_t full0 = map_to_cta(bar_full, 0);      // the leader's full barriers
     const uint32_t sffull0 = map_to_cta(bar_sffull, 0);
+    const int n_total_u = __shfl_sync(0xffffffffu, n_total, 0);
+    const bool a_mn = MODE == WGRAD && p.a_mn, b_mn = MODE == WGRAD && p.b_mn;
     int stage = 0, sfs = 0;
     uint32_t phase = 0, sfphase = 0;
     bool ok = true;
-    for (int tile = pair_id; tile < n_total && ok; tile += n_pairs_grid) {
-      const PairTile t = pair_tile<BN, MODE>(tile, rank, p, s_efo, s_pairs);
-      if (t.nkt == 0) continue;
+    const bool dbg_noload = (p.debug_skip_store & 4) != 0;   // timing experiment: operands fetched for one ring pass only
+    int dbg_filled = 0;
+    for (int tile = pair_id; tile < n_total_u && ok; tile += n_pairs_grid) {
+      const PairTile tl = pair_tile<BN, MODE>(tile, rank, p, s_efo, s_pairs);
+      const int nkt = __shfl_sync(0xffffffffu, tl.nkt, 0);
+      if (nkt == 0) continue;
+      const int kt0 = __shfl_sync(0xffffffffu, tl.kt0, 0);
+      const int valid = __shfl_sync(0xffffffffu, tl.valid, 0);
+      const int m0 = __shfl_sync(0xffffffffu, tl.m0, 0);
+      const int n0 = __shfl_sync(0xffffffffu, tl.n0, 0);
+      const int te = __shfl_sync(0xffffffffu, tl.e, 0);
       int4 rows4 = make_int4(0, 0, 0, 0);
-      if (GATHER && t.valid) rows4 = *reinterpret_cast<const int4*>(p.a_idx + t.m0 + 4 * lane);
-      const int b_base = (MODE == WGRAD) ? t.n0 : t.e * p.N + t.n0;
+      if (GATHER && valid) rows4 = *reinterpret_cast<const int4*>(p.a_idx + m0 + 4 * lane);
+      const int b_base = (MODE == WGRAD) ? n0 : te * p.N + n0;
       const int b_row = b_base + rank * (BN / 2);
       // rows of the A-scale tensor are 512-byte tiles: (row tile, k tile)
-      int sfa_tile = t.m0 / 128;
-      if (!t.valid) sfa_tile = 0;                        // phantom half: any in-range tile will do
+      const int sfa_tile = valid ? m0 / 128 : 0;         // phantom half: any in-range tile will do
       const int sfb_tile = b_base / 128;                 // first 128-row scale tile touching the BN window
-      for (int kt = t.kt0; kt < t.kt0 + t.nkt; ++kt) {
-        if (((kt - t.kt0) & (S::SF_GROUP - 1)) == 0) {
+      const int a_row = valid ? m0 : 0;
+      for (int kt = kt0; kt < kt0 + nkt; ++kt) {
+        if (((kt - kt0) & (S::SF_GROUP - 1)) == 0) {
           // scales of the next SF_GROUP K tiles: rows [tile*ktiles + kt, +SF_GROUP) of the 512-byte-row scale
           // tensors (rows past this operand tile's K range are fetched too and never used)
-          if (lane == 0) ok = mbar_wait(bar_sfempty + 8 * sfs, sfphase ^ 1);
-          ok = __shfl_sync(0xffffffff, ok, 0);
+          ok = __all_sync(0xffffffffu, mbar_wait(bar_sfempty + 8 * sfs, sfphase ^ 1));
           if (!ok) break;
-          if (lane == 0) {
+          if (elect_one()) {
             const uint32_t sffull = sffull0 + 8 * sfs;
             const uint32_t dst = sf_base + sfs * S::SF_SLOT_BYTES;
             if (rank == 0) mbar_expect_tx(bar_sffull + 8 * sfs, S::SF_TX_BYTES);
             tma_load_2d_pair(dst, &tmap_sfa, sffull, 0, sfa_tile * p.sfa_ktiles + kt);
 #pragma unroll
             for (int j = 0; j < S::SFB_TILES; ++j)
-              tma_load_2d_pair(dst + 2048 * (1 + j), &tmap_sfb, sffull, 0, (sfb_tile + j) * p.sfb_ktiles + kt);
+              tma_load_2d_pair(dst + S::SF_GROUP * 512 * (1 + j), &tmap_sfb, sffull, 0,
+                               (sfb_tile + j) * p.sfb_ktiles + kt);
           }
           if (++sfs == S::SF_SLOTS) { sfs = 0; sfphase ^= 1; }
         }
-        if (lane == 0) ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1);
-        ok = __shfl_sync(0xffffffff, ok, 0);
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * stage, phase ^ 1));
         if (!ok) break;
         const uint32_t full = full0 + 8 * stage;
         const uint32_t a_dst = smem_base + stage * S::STAGE_BYTES;
         const uint32_t b_dst = a_dst + S::A_BYTES;
-        if (lane == 0) {
-          if (rank == 0) mbar_expect_tx(bar_full + 8 * stage, S::TX_BYTES);
-          if (MODE == WGRAD && p.a_mn) tma_load_2d_pair(a_dst, &tmap_a, full, t.m0, kt * BK);
-          else if (!GATHER) tma_load_2d_pair(a_dst, &tmap_a, full, kt * BK, t.valid ? t.m0 : 0);
-          if (MODE == WGRAD && p.b_mn) tma_load_2d_pair(b_dst, &tmap_b, full, b_row, kt * BK);
-          else tma_load_2d_pair(b_dst, &tmap_b, full, kt * BK, b_row);
+        if (dbg_noload && dbg_filled >= nst) {
+          if (rank == 0 && elect_one()) mbar_arrive(bar_full + 8 * stage);
+        } else {
+          ++dbg_filled;
+          if (elect_one()) {
+            if (rank == 0) mbar_expect_tx(bar_full + 8 * stage, S::TX_BYTES);
+            if (a_mn) tma_load_2d_pair(a_dst, &tmap_a, full, m0, kt * BK);
+            else if (!GATHER) tma_load_2d_pair(a_dst, &tmap_a, full, kt * BK, a_row);
+            if (b_mn) tma_load_2d_pair(b_dst, &tmap_b, full, b_row, kt * BK);
+            else tma_load_2d_pair(b_dst, &tmap_b, full, kt * BK, b_row);
+            const int kp = kt + p.l2_prefetch;
+            if (p.l2_prefetch > 0 && kp < kt0 + nkt) {
+              if (a_mn) tma_prefetch_l2_2d(&tmap_a, m0, kp * BK);
+              else if (!GATHER) tma_prefetch_l2_2d(&tmap_a, kp * BK, a_row);
+              if (b_mn) tma_prefetch_l2_2d(&tmap_b, b_row, kp * BK);
+              else tma_prefetch_l2_2d(&tmap_b, kp * BK, b_row);
+            }
+          }
+          if (GATHER) {
+            __syncwarp();
+            tma_gather4_pair(a_dst + lane * 4 * BK, &tmap_a, full, kt * BK, rows4.x, rows4.y, rows4.z, rows4.w);
+          }
         }
-        if (GATHER) {
-          __syncwarp();
-          tma_gather4_pair(a_dst + lane * 4 * BK, &tmap_a, full, kt * BK, rows4.x, rows4.y, rows4.z, rows4.w);
-        }
-        if (++stage == S::STAGES) { stage = 0; phase ^= 1; }
+        if (++stage == nst) { stage = 0; phase ^= 1; }
       }
     }
     if (!ok && lane == 0) { *s_abort = 1; atomicCAS(p.status, 0, 201); }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
-    if (rank == 0 && elect_one()) {
+    // The whole warp walks the loops in lock step and one elected lane issues.  Every loop-carried value (stage,
+    // phases, descriptor words) is then the same in all lanes, which lets the compiler keep the operands of the
+    // tcgen05 instructions in uniform registers; with the loops inside a single-lane branch each operand had to be
+    // moved over per instruction, and the issue rate of this one thread - not the tensor pipe, the operand loads or
+    // the accumulator drain - bounded the kernel (900-1000 clocks per K tile where the MMAs need 512).
+    if (rank == 0) {
       // WGRAD may take either operand MN-major: [K rows, M or N bytes] tiles instead of [M or N rows, K bytes]
       const bool a_mn = MODE == WGRAD && p.a_mn, b_mn = MODE == WGRAD && p.b_mn;
       const uint32_t idesc = make_idesc_mxf8(2 * BM, BN) | (a_mn ? 1u << 15 : 0u) | (b_mn ? 1u << 16 : 0u);
-      const uint32_t a_step = a_mn ? 256u : 2u, b_step = b_mn ? 256u : 2u;   // descriptor units of 16 bytes per 32 K
+      const uint32_t idesc_kb[4] = {idesc_with_sf_ids(idesc, 0, 0), idesc_with_sf_ids(idesc, 1, 1),
+                                    idesc_with_sf_ids(idesc, 2, 2), idesc_with_sf_ids(idesc, 3, 3)};
+      // operand descriptors (see make_desc_kmajor_sw128 / make_desc_mnmajor_sw128): the high word - 1024-byte group
+      // stride, version, 128-byte swizzle - is a constant; the low word is the start address in 16-byte units plus
+      // the leading byte offset field, and moves by 32 bytes (K-major) or 4096 bytes (MN-major) per 32-wide K block
+      const uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+      const uint32_t sf_hi = (128u >> 4) | (1u << 14);
+      const uint32_t a_step = a_mn ? 256u : 2u, b_step = b_mn ? 256u : 2u;
+      const uint32_t a_lo0 = ((smem_base & 0x3FFFF) >> 4) | ((a_mn ? (uint32_t)(S::A_BYTES >> 4) : 1u) << 16);
+      const uint32_t b_lo0 = (((smem_base + S::A_BYTES) & 0x3FFFF) >> 4) | ((b_mn ? (uint32_t)(S::B_BYTES >> 4) : 1u) << 16);
+      const uint32_t sf_lo0 = (sf_base & 0x3FFFF) >> 4;
+      const int n_total_u = __shfl_sync(0xffffffffu, n_total, 0);
+      const bool skip_sf_cp = (p.debug_skip_store & 16) != 0;
       int stage = 0, as = 0, sfs = 0;
       uint32_t phase = 0, aphase = 0, sfphase = 0;
       bool ok = true;
-      for (int tile = pair_id; tile < n_total && ok; tile += n_pairs_grid) {
+      for (int tile = pair_id; tile < n_total_u && ok; tile += n_pairs_grid) {
         const PairTile t = pair_tile<BN, MODE>(tile, 0, p, s_efo, s_pairs);
-        if (t.nkt == 0) continue;
-        ok = mbar_wait(bar_tempty + 8 * as, aphase ^ 1);
+        const int nkt = __shfl_sync(0xffffffffu, t.nkt, 0);
+        if (nkt == 0) continue;
+        const int n0 = __shfl_sync(0xffffffffu, t.n0, 0);
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_tempty + 8 * as, aphase ^ 1));
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + as * BN;
         // BN = 192: an odd column tile starts 64 rows into its first 128-row scale tile
-        const uint32_t sfb_shift = (BN == 192) ? (((t.n0 / BN) & 1) ? 2u : 0u) : 0u;
-        for (int k = 0; k < t.nkt; ++k) {
+        const uint32_t sfb_shift = (BN == 192) ? (((n0 / BN) & 1) ? 2u : 0u) : 0u;
+        for (int k = 0; k < nkt; ++k) {
           const int kg = k & (S::SF_GROUP - 1);
           if (kg == 0) {
-            ok = mbar_wait(bar_sffull + 8 * sfs, sfphase);
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_sffull + 8 * sfs, sfphase));
             if (!ok) break;
           }
-          ok = mbar_wait(bar_full + 8 * stage, phase);
+          ok = __all_sync(0xffffffffu, mbar_wait(bar_full + 8 * stage, phase));
           if (!ok) break;
-          tc_fence_after();
-          const uint32_t a_src = smem_base + stage * S::STAGE_BYTES;
-          const uint32_t b_src = a_src + S::A_BYTES;
-          const uint32_t sf_src = sf_base + sfs * S::SF_SLOT_BYTES + kg * 512;
+          const uint32_t a_lo = a_lo0 + stage * (S::STAGE_BYTES >> 4);
+          const uint32_t b_lo = b_lo0 + stage * (S::STAGE_BYTES >> 4);
+          const uint32_t sf_lo = sf_lo0 + ((sfs * S::SF_SLOT_BYTES + kg * 512) >> 4);
           const uint32_t sfa_t = tmem_base + S::SF_COL0 + stage * S::SF_COLS;
           const uint32_t sfb_t = sfa_t + 4;
-          tc_cp_sf_pair(sfa_t, make_desc_sf(sf_src));
+          const bool sf_done = (kg == S::SF_GROUP - 1 || k == nkt - 1);      // last use of this scale slot
+          if (elect_one()) {
+            if (!skip_sf_cp) {
+              tc_cp_sf_pair_lo(sfa_t, sf_lo, sf_hi);
 #pragma unroll
-          for (int j = 0; j < S::SFB_TILES; ++j) tc_cp_sf_pair(sfb_t + 4 * j, make_desc_sf(sf_src + 2048 * (1 + j)));
-          const uint64_t a_desc = a_mn ? make_desc_mnmajor_sw128(a_src, S::A_BYTES) : make_desc_kmajor_sw128(a_src);
-          const uint64_t b_desc = b_mn ? make_desc_mnmajor_sw128(b_src, S::B_BYTES) : make_desc_kmajor_sw128(b_src);
+              for (int j = 0; j < S::SFB_TILES; ++j)
+                tc_cp_sf_pair_lo(sfb_t + 4 * j, sf_lo + ((S::SF_GROUP * 512 * (1 + j)) >> 4), sf_hi);
+            }
 #pragma unroll
-          for (int kb = 0; kb < BK / 32; ++kb) {
-            mma_mxf8_pair(d_tmem, a_desc + a_step * kb, b_desc + b_step * kb, idesc_with_sf_ids(idesc, kb, kb), sfa_t,
-                          sfb_t + sfb_shift, (k | kb) != 0);
+            for (int kb = 0; kb < BK / 32; ++kb)
+              mma_mxf8_pair_lo(d_tmem, a_lo + a_step * kb, b_lo + b_step * kb, desc_hi, idesc_kb[kb], sfa_t,
+                               sfb_t + sfb_shift, (k | kb) != 0);
+            tc_commit_pair(bar_empty + 8 * stage, 3);
+            if (sf_done) tc_commit_pair(bar_sfempty + 8 * sfs, 3);
           }
-          tc_commit_pair(bar_empty + 8 * stage, 3);
-          if (++stage == S::STAGES) { stage = 0; phase ^= 1; }
-          if (kg == S::SF_GROUP - 1 || k == t.nkt - 1) {      // last use of this scale slot
-            tc_commit_pair(bar_sfempty + 8 * sfs, 3);
+          if (++stage == nst) { stage = 0; phase ^= 1; }
+          if (sf_done) {
             if (++sfs == S::SF_SLOTS) { sfs = 0; sfphase ^= 1; }
           }
         }
         if (!ok) break;
-        tc_commit_pair(bar_tfull + 8 * as, 3);
+        if (elect_one()) tc_commit_pair(bar_tfull + 8 * as, 3);
         if (++as == S::ACC_STAGES) { as = 0; aphase ^= 1; }
       }
-      if (!ok) { *s_abort = 1; atomicCAS(p.status, 0, 202); }
+      if (!ok && lane == 0) { *s_abort = 1; atomicCAS(p.status, 0, 202); }
     }
     __syncwarp();
   } else {
@@ -411,7 +489,9 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + as * BN + half * COLS_PER_WARP;
 
       bool released = false;
-      if (MODE == PLAIN) {
+      if (p.debug_skip_store & 8) {
+        // timing experiment: the accumulator is handed back untouched
+      } else if (MODE == PLAIN) {
         // Drain the whole row segment into registers (bf16-packed), hand the accumulator back to the
         // MMA warp, then stage and store.  32 columns of bf16 = 64-byte rows, SWIZZLE_64B, 2 x 2 KB.
         constexpr int NC = COLS_PER_WARP / 32;

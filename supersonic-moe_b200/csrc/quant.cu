@@ -479,9 +479,9 @@ int smoe_quant_rows_scatter(const void* x_bf16, int64_t T, int64_t K, const int3
                             const int32_t* s_scatter_idx, const int32_t* valid_rows, int64_t rows, void* q,
                             void* isa_scales, void* stream) {
   if (T < 0 || rows < 0 || K <= 0 || K % 128 || K > 16384) return SMOE_ERR_SHAPE;
+  if (rows == 0) return SMOE_OK;      // nothing routed: not an error, and the (empty) buffers may be null
   if (!naept || !s_rev || !s_scatter_idx || !isa_scales) return SMOE_ERR_ARG;
   if (((uintptr_t)x_bf16 & 15) || ((uintptr_t)q & 15)) return SMOE_ERR_ALIGN;
-  if (rows == 0) return SMOE_OK;
   const int row_bytes = (int)((K + 4 * (K / 128) + 15) & ~(int64_t)15);
   const int warps = row_bytes * 8 <= 48 * 1024 ? 8 : (row_bytes * 4 <= 48 * 1024 ? 4 : 2);
   const int token_blocks = (int)((T + warps - 1) / warps);
@@ -496,9 +496,9 @@ int smoe_quant_rows_scatter(const void* x_bf16, int64_t T, int64_t K, const int3
 int smoe_quant_rows_gather(const void* x_bf16, const int32_t* idx, const int32_t* valid_rows, int64_t rows, int64_t K,
                            void* q, void* isa_scales, void* stream) {
   if (rows < 0 || K <= 0 || K % 128) return SMOE_ERR_SHAPE;
+  if (rows == 0) return SMOE_OK;      // nothing routed: not an error, and the (empty) buffers may be null
   if (!idx || !isa_scales) return SMOE_ERR_ARG;
   if (((uintptr_t)x_bf16 & 15) || ((uintptr_t)q & 7)) return SMOE_ERR_ALIGN;
-  if (rows == 0) return SMOE_OK;
   int64_t blocks = (rows + 7) / 8;
   if (blocks > 148 * 16) blocks = 148 * 16;
   quant_rows_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>((const uint4*)x_bf16, rows, (int)K, (uint2*)q,
@@ -520,8 +520,8 @@ int smoe_gather_scales_isa(const void* raw_scales, const int32_t* idx, int64_t r
 int smoe_gather_rows_fp8(const void* q, const void* raw_scales, const int32_t* idx, const int32_t* valid_rows,
                          int64_t rows, int64_t K, void* q_out, void* isa_out, void* stream) {
   if (rows < 0 || K <= 0 || K % 128) return SMOE_ERR_SHAPE;
+  if (rows == 0) return SMOE_OK;      // nothing routed: not an error, and the (empty) buffers may be null
   if (((uintptr_t)q & 15) || ((uintptr_t)q_out & 15) || ((uintptr_t)raw_scales & 3)) return SMOE_ERR_ALIGN;
-  if (rows == 0) return SMOE_OK;
   const int threads = K / 16 >= 256 ? 256 : (int)((K / 16 + 31) / 32 * 32);
   gather_rows_kernel<<<(unsigned)rows, threads, 0, (cudaStream_t)stream>>>(
       (const uint4*)q, (const uint8_t*)raw_scales, idx, valid_rows, (int)K, (uint4*)q_out, (uint8_t*)isa_out);
@@ -541,8 +541,8 @@ int smoe_quant_cols_t(const void* src_bf16, const int32_t* idx, int64_t rows, in
 int smoe_requant_cols_t(const void* src_fp8, const void* src_scales, const int32_t* idx, int64_t rows, int64_t dim,
                         void* q_t, void* isa, void* stream) {
   if (rows < 0 || rows % 128 || dim <= 0 || dim % 64) return SMOE_ERR_SHAPE;
+  if (rows == 0) return SMOE_OK;      // nothing routed: not an error, and the (empty) buffers may be null
   if (!src_scales) return SMOE_ERR_ARG;
-  if (rows == 0) return SMOE_OK;
   dim3 grid((unsigned)(rows / CT_ROWS), (unsigned)(dim / CT_COLS));
   quant_cols_kernel<false, true><<<grid, 256, 0, (cudaStream_t)stream>>>(
       src_fp8, (const uint8_t*)src_scales, idx, rows, (int)dim, (uint8_t*)q_t, (uint8_t*)isa, nullptr, nullptr);
@@ -563,8 +563,8 @@ int smoe_quant_iso32(const void* x_bf16, int64_t rows, int64_t cols, void* q, vo
 int smoe_quant_dual_gather(const void* x_bf16, const int32_t* idx, const int32_t* valid_rows, int64_t rows, int64_t K,
                            void* q_row, void* row_isa, void* q_col, void* col_isa, void* stream) {
   if (rows < 0 || rows % 128 || K <= 0 || K % 256) return SMOE_ERR_SHAPE;
+  if (rows == 0) return SMOE_OK;      // nothing routed: not an error, and the (empty) buffers may be null
   if (!q_col || !col_isa || ((q_row == nullptr) != (row_isa == nullptr))) return SMOE_ERR_ARG;
-  if (rows == 0) return SMOE_OK;
   const int64_t tasks = (rows / 32) * (K / 256);
   const unsigned blocks = (unsigned)((tasks + 3) / 4);
   if (q_row)
@@ -581,8 +581,8 @@ int smoe_scatter_rows_fp8(const void* q, const void* raw_scales, int64_t T, int6
                           const int32_t* s_rev, const int32_t* s_scatter_idx, const int32_t* valid_rows, int64_t rows,
                           void* q_out, void* isa_out, void* stream) {
   if (T < 0 || rows < 0 || K <= 0 || K % 128) return SMOE_ERR_SHAPE;
+  if (rows == 0) return SMOE_OK;      // nothing routed: not an error, and the (empty) buffers may be null
   if (((uintptr_t)q & 15) || ((uintptr_t)q_out & 15) || ((uintptr_t)raw_scales & 3)) return SMOE_ERR_ALIGN;
-  if (rows == 0) return SMOE_OK;
   const int token_blocks = (int)((T + 7) / 8);
   const int pad_blocks = 148;
   scatter_rows_fp8_kernel<<<(unsigned)(token_blocks + pad_blocks), 256, 0, (cudaStream_t)stream>>>(

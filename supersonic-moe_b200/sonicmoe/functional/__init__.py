@@ -95,6 +95,22 @@ def _mn_wgrad_ok(E: int, M: int, N: int) -> bool:
     return E <= 256 and M % 256 == 0 and N % 256 == 0
 
 
+def _wide_wgrad_ok(E: int, M: int, N: int) -> bool:
+    """Shapes the 256 x 384 weight-gradient kernel takes (fewest operand bytes per MMA): its A operand may stay
+    [TKp, M], its B operand must be K-major, i.e. the column quantizer writes it transposed [N, TKp]."""
+    return E <= 256 and M % 256 == 0 and N % 384 == 0
+
+
+def _col_operand(src, idx, TKp, valid_rows, E, M, N):
+    """Column-quantised (1x32 along the routed rows) B operand of a weight-gradient GEMM from bf16 `src` rows
+    gathered by `idx`: (payload, ISA scales for (N, TKp), payload_is_rows_major)."""
+    if _mn_wgrad_ok(E, M, N) and not _wide_wgrad_ok(E, M, N):
+        _, _, q, sf = ops.quant_dual_gather(src, idx, TKp, valid_rows, with_rows=False)
+        return q, sf, True
+    q_t, sf = ops.quant_cols_t(src, idx, TKp)
+    return q_t, sf, False
+
+
 def _wgrad(a, a_sf, a_rows_tk, b, b_sf, b_rows_tk, efo, out, accumulate):
     """out[e] (+)= A_e^T B_e over expert e's rows; either operand is [dim, TKp] or, *_rows_tk, [TKp, dim]."""
     if a_rows_tk or b_rows_tk:
@@ -325,14 +341,10 @@ class _UpProjection(torch.autograd.Function):
         TKp = dz_q.shape[0]
         dw1 = None
         if ctx.needs_input_grad[1]:
-            mn = _mn_wgrad_ok(E, N2, H)
             if ctx.x_is_fp8:     # x is e4m3 + raw scales: dequantise, then column-wise re-quantise
                 xc, x_sf, xc_rows = *ops.requant_cols_t(x, x_raw, x_gather_idx, TKp), False
-            elif mn:             # column scales, payload left [TKp, H]
-                _, _, xc, x_sf = ops.quant_dual_gather(x, x_gather_idx, TKp, efo[-1:], with_rows=False)
-                xc_rows = True
-            else:
-                xc, x_sf, xc_rows = *ops.quant_cols_t(x, x_gather_idx, TKp), False
+            else:                # column scales; payload [TKp, H] or transposed, whichever the GEMM runs fastest on
+                xc, x_sf, xc_rows = _col_operand(x, x_gather_idx, TKp, efo[-1:], E, N2, H)
             mg, base = _grad_target(w1, (E, N2, H))
             out = mg if mg is not None else torch.empty(E, N2, H, dtype=torch.float32, device=dz_q.device)
             # a row-major dz payload (32x32-block scales) doubles as the MN-major weight-gradient operand
@@ -428,6 +440,7 @@ class _DownProjection(torch.autograd.Function):
             if USE_TMA_GATHER:
                 dout_q, dout_raw, _ = ops.quant_rows(dout, raw=True)
         y1s_q = dout_c = None
+        dout_c_rows = False
         w2t_q, w2t_sf = weight_fp8(w2, True)
         if USE_TMA_GATHER:
             a_sf = ops.gather_scales_isa(dout_raw, x_gather_idx, TKp, H)
@@ -440,7 +453,7 @@ class _DownProjection(torch.autograd.Function):
                 # in a second, gathered pass (93 us); the one-pass dual kernel measured 209 us there
                 dg_q, a_sf = ops.quant_rows_scatter(dout, naept, s_rev, s_scatter_idx, TKp, efo[-1:])
                 if ctx.needs_input_grad[2] and _mn_wgrad_ok(E, I, H):
-                    _, _, dout_c, dout_sf = ops.quant_dual_gather(dout, x_gather_idx, TKp, efo[-1:], with_rows=False)
+                    dout_c, dout_sf, dout_c_rows = _col_operand(dout, x_gather_idx, TKp, efo[-1:], E, I, H)
             if FUSE_DGATED_QUANT and _mn_wgrad_ok(E, I, H):
                 # dz / y1s never exist in bf16: the epilogue emits the e4m3 operands of dgrad, dw1 and dw2,
                 # row-major; the weight-gradient GEMMs read them MN-major (needs 256-multiples of I and H)
@@ -464,7 +477,8 @@ class _DownProjection(torch.autograd.Function):
             mg, base = _grad_target(w2, (E, I, H))
             out = mg if mg is not None else torch.empty(E, I, H, dtype=torch.float32, device=s.device)
             _wgrad(y1s_q if y1s_q is not None else y1s_t, y1s_sf, y1s_q is not None,
-                   dout_c if dout_c is not None else dout_t, dout_sf, dout_c is not None, efo, out, mg is not None)
+                   dout_c if dout_c is not None else dout_t, dout_sf, dout_c is not None and dout_c_rows, efo, out,
+                   mg is not None)
             if mg is not None:
                 _after_accumulate(base)
             else:

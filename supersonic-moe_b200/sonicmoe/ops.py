@@ -60,17 +60,26 @@ def _timed(fn):
     return wrapper
 
 
+def _dev_index(device) -> int:
+    """Ordinal of a CUDA device given as a device, a string or an int; "cuda" without an ordinal means the current
+    device (so that "cuda" and "cuda:0" name the same status word)."""
+    d = torch.device(device) if not isinstance(device, int) else torch.device("cuda", device)
+    if d.type != "cuda":
+        raise RuntimeError("sonicmoe kernels need CUDA tensors (no CPU fallback)")
+    return d.index if d.index is not None else torch.cuda.current_device()
+
+
 def status_word(device) -> torch.Tensor:
     """Per-device int32 word the GEMM kernels write a failure code into (0 = ok)."""
-    key = torch.device(device).index
+    key = _dev_index(device)
     if key not in _status:
-        _status[key] = torch.zeros(1, dtype=_I32, device=device)
+        _status[key] = torch.zeros(1, dtype=_I32, device=torch.device("cuda", key))
     return _status[key]
 
 
 def _raise_status(device, code):
     status_word(device).zero_()
-    raise RuntimeError(f"sonicmoe GEMM kernel reported device failure code {code} on {torch.device(device)} "
+    raise RuntimeError(f"sonicmoe GEMM kernel reported device failure code {code} on cuda:{_dev_index(device)} "
                        "(a bounded wait inside a kernel ran out; results of that step are invalid)")
 
 
@@ -90,10 +99,9 @@ _posted = {}     # device index -> [(pinned int32 tensor, event), ...] not yet l
 
 def post_status(device):
     """Enqueue, on the current stream, a copy of the status word to the host (no-op while a graph is captured)."""
-    device = torch.device(device)
-    if device.type != "cuda" or torch.cuda.is_current_stream_capturing():
+    if torch.device(device).type != "cuda" or torch.cuda.is_current_stream_capturing():
         return
-    q = _posted.setdefault(device.index, [])
+    q = _posted.setdefault(_dev_index(device), [])
     if len(q) >= 8:           # nobody polls (e.g. a forward-only loop through the raw Functions): keep the newest
         del q[:-4]
     host = torch.empty(1, dtype=_I32, pin_memory=True)
@@ -105,8 +113,9 @@ def post_status(device):
 
 def poll_status(device):
     """Look at the posted copies that have arrived; raise on a recorded failure.  Never waits."""
-    device = torch.device(device)
-    q = _posted.get(device.index)
+    if torch.device(device).type != "cuda":
+        return
+    q = _posted.get(_dev_index(device))
     while q and q[0][1].query():
         host, _ = q.pop(0)
         code = int(host[0])

@@ -22,7 +22,7 @@ REPORT = []                                # every gate() call of the session: w
 
 
 def stats(got, ref):
-    got, ref = got.detach().float().cpu().flatten(), ref.detach().float().cpu().flatten()
+    got, ref = got.detach().double().cpu().flatten(), ref.detach().double().cpu().flatten()
     cos = float((got * ref).sum() / (got.norm() * ref.norm()).clamp(min=1e-30))
     rr = float((got - ref).norm() / ref.norm().clamp(min=1e-30))
     return cos, rr

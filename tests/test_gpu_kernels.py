@@ -292,7 +292,8 @@ def test_topk_metadata_with_undersized_buffers_stays_in_bounds(ops):
     efo, xg, ss, sr, na = e(E + 1), e(TKp), e(TKp), e(TK), e(N + 1)
     sc, si, cnt = torch.full((TKp + 64,), -77.0, device=dev), e(TK), e(E)
     ws = torch.empty(lib.smoe_topk_metadata_workspace(N, E), dtype=torch.uint8, device=dev)
-    check(lib.smoe_topk_metadata(idx.to(dev).data_ptr(), probs.to(dev).data_ptr(), N, K, E, 128, TK, TKp, 0, 0,
+    idx_d, probs_d = idx.to(dev), probs.to(dev)
+    check(lib.smoe_topk_metadata(idx_d.data_ptr(), probs_d.data_ptr(), N, K, E, 128, TK, TKp, 0, 0,
                                  efo.data_ptr(), xg.data_ptr(), ss.data_ptr(), sr.data_ptr(), na.data_ptr(),
                                  sc.data_ptr(), si.data_ptr(), cnt.data_ptr(), ws.data_ptr(),
                                  torch.cuda.current_stream().cuda_stream), "topk_metadata")
@@ -331,9 +332,11 @@ def stats(got, ref):
     return cos, rr
 
 
-@pytest.mark.parametrize("bn", [128, 192, 256, 128 | (1 << 17), 256 | (1 << 17)])
+# 384 = the 256 x 384 double-accumulator kernel (N % 384 == 0; other N fall back); bit 17 = the single-CTA kernel
+@pytest.mark.parametrize("bn", [128, 192, 256, 384, 128 | (1 << 17), 256 | (1 << 17)])
 @pytest.mark.parametrize("tiles,N,K", [([1, 0, 2, 1], 256, 128), ([3, 2, 0, 0, 4, 1, 1, 2], 512, 1024),
-                                        ([40, 30, 50, 28], 1536, 768), ([5, 4, 0, 7], 768, 256)])
+                                        ([40, 30, 50, 28], 1536, 768), ([5, 4, 0, 7], 768, 256), ([6, 5], 384, 512),
+                                        ([3, 0, 1], 768, 640)])
 def test_gemm_varlen_m(ops, bn, tiles, N, K):
     from sonicmoe._lib import lib
     g = torch.Generator().manual_seed(sum(tiles) + N + K)
@@ -484,8 +487,9 @@ def test_gemm_dgated(ops, T, H, I, tiles, mode):
     assert (dz.cpu()[s == 0] == 0).all() and (y1s.cpu()[s == 0] == 0).all()
 
 
-@pytest.mark.parametrize("bn", [128, 192, 256, 128 | (1 << 17), 256 | (1 << 17)])
-@pytest.mark.parametrize("M,N,tiles", [(128, 256, [1, 0, 2, 1]), (512, 768, [3, 2, 0, 0, 4, 1, 1, 2]), (768, 384, [2, 1, 3])])
+@pytest.mark.parametrize("bn", [128, 192, 256, 384, 128 | (1 << 17), 256 | (1 << 17)])
+@pytest.mark.parametrize("M,N,tiles", [(128, 256, [1, 0, 2, 1]), (512, 768, [3, 2, 0, 0, 4, 1, 1, 2]), (768, 384, [2, 1, 3]),
+                                       (256, 1152, [5, 0, 9, 4])])
 def test_gemm_wgrad(ops, bn, M, N, tiles):
     from sonicmoe._lib import lib
     g = torch.Generator().manual_seed(M + N)
