@@ -247,12 +247,19 @@ class TorchMoEBaseline(torch.nn.Module):
         self.w1 = torch.nn.Parameter((torch.randn(E, 2 * I, H, generator=g) * std).to(dtype))
         self.w2 = torch.nn.Parameter((torch.randn(E, H, I, generator=g) * std).to(dtype))
 
+    def experts_only(self, x, sel, gates):
+        """The expert compute on pre-routed inputs (sel [T,K] expert ids, gates [T,K]): the region the reference's
+        own benchmark times; the router linear / top-k stay outside."""
+        return self._experts(x, sel.flatten().long(), gates.type_as(x))
+
     def forward(self, x):
-        T = x.shape[0]
         logits = F.linear(x, self.router)
         vals, sel = logits.topk(self.K, dim=-1)
         gates = F.softmax(vals.float(), dim=-1).type_as(x)
-        sel = sel.flatten()
+        return self._experts(x, sel.flatten(), gates), logits
+
+    def _experts(self, x, sel, gates):
+        T = x.shape[0]
         with torch.no_grad():
             _, order = sel.sort(stable=True)
             freq = sel.bincount(minlength=self.E)
@@ -264,4 +271,4 @@ class TorchMoEBaseline(torch.nn.Module):
         h = torch.cat([F.linear(h[e], self.w2[e]) for e in range(self.E)], dim=0)
         h = h * batch_gates.unsqueeze(-1)
         out = torch.zeros(T, self.H, dtype=torch.float32).index_add(0, fan_in, h.float())
-        return out.to(x.dtype), logits
+        return out.to(x.dtype)
