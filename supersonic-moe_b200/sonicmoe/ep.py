@@ -35,6 +35,20 @@ import torch.distributed as dist
 USE_PEER_COMBINE = os.getenv("SONIC_MOE_EP_PEER", "0") == "1"
 
 
+_COMM_STREAMS: dict = {}
+
+
+def _comm_stream(device) -> "torch.cuda.Stream":
+    """The one stream per device on which the expert-parallel exchanges run (same issue order on every rank)."""
+    key = torch.device(device).index
+    if key is None:
+        key = torch.cuda.current_device()
+    st = _COMM_STREAMS.get(key)
+    if st is None:
+        st = _COMM_STREAMS[key] = torch.cuda.Stream(device=torch.device("cuda", key))
+    return st
+
+
 class PeerArena:
     """A bf16 [rows, H] buffer per rank that every rank of the group has mapped.  Allocation and mapping are
     collective calls; the size is derived from quantities all ranks share."""
@@ -143,11 +157,32 @@ class DispatchPlan:
         off[1:] = goes.sum(dim=0).cumsum(0)
         self.copy_off = off.to(torch.int32).contiguous()
 
-    def a2a(self, send: torch.Tensor, reverse: bool = False) -> torch.Tensor:
-        """Rows travel to their destination (or, reversed, back to their source)."""
+    def a2a(self, send: torch.Tensor, reverse: bool = False, after=None) -> torch.Tensor:
+        """Rows travel to their destination (or, reversed, back to their source).
+
+        On CUDA every exchange of a plan is issued, in program order, on one communication stream.  It starts once
+        `after` (an event: "the payload is complete") has happened - or, without one, once everything given to the
+        current stream so far has run - and the current stream resumes when the exchange is done.  Kernels that
+        were enqueued on the current stream AFTER `after` was recorded therefore run underneath the exchange: that
+        is how the weight-gradient GEMMs overlap the return exchange of dx in the backward."""
         s, r = (self.recv_counts, self.send_counts) if reverse else (self.send_counts, self.recv_counts)
-        out = send.new_empty((sum(r),) + tuple(send.shape[1:]))
-        dist.all_to_all_single(out, send.contiguous(), output_split_sizes=r, input_split_sizes=s, group=self.group)
+        send = send.contiguous()
+        if not send.is_cuda:
+            out = send.new_empty((sum(r),) + tuple(send.shape[1:]))
+            dist.all_to_all_single(out, send, output_split_sizes=r, input_split_sizes=s, group=self.group)
+            return out
+        cur = torch.cuda.current_stream(send.device)
+        comm = _comm_stream(send.device)
+        if after is not None:
+            comm.wait_event(after)
+        else:
+            comm.wait_stream(cur)
+        with torch.cuda.stream(comm):
+            out = send.new_empty((sum(r),) + tuple(send.shape[1:]))
+            dist.all_to_all_single(out, send, output_split_sizes=r, input_split_sizes=s, group=self.group)
+        send.record_stream(comm)
+        out.record_stream(cur)
+        cur.wait_stream(comm)
         return out
 
     def pull_and_sum(self, arena: "PeerArena") -> torch.Tensor:
@@ -221,7 +256,11 @@ class _Dispatch(torch.autograd.Function):
                     arena.view(dx_recv.shape[0]).copy_(dx_recv)
                 dx = plan.pull_and_sum(arena).to(ctx.x_dtype)
             else:
-                dx = plan.sum_copies(plan.a2a(dx_recv.contiguous(), reverse=True)).to(ctx.x_dtype)
+                # dx_recv was complete before the weight-gradient GEMMs were enqueued: the exchange waits for that
+                # moment only, so those GEMMs run underneath it
+                from .functional import take_result_ready
+                ready = take_result_ready(dx_recv) if dx_recv.is_cuda else None
+                dx = plan.sum_copies(plan.a2a(dx_recv.contiguous(), reverse=True, after=ready)).to(ctx.x_dtype)
         if ctx.needs_input_grad[1] and dp_recv is not None:
             back = plan.a2a(dp_recv.contiguous().float(), reverse=True)
             # a slot lives on exactly one rank: every other copy contributes an exact zero

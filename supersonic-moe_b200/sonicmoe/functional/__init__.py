@@ -88,6 +88,10 @@ USE_TMA_GATHER = os.getenv("SONIC_MOE_TMA_GATHER", "0") == "1"
 # GemmDGated emits the e4m3 operands of the three GEMMs that follow it (dgrad, dw1, dw2) straight from its
 # epilogue instead of bf16 dz / y1s plus separate quantizer passes (same bytes either way).
 FUSE_DGATED_QUANT = os.getenv("SONIC_MOE_FUSE_DGATED_QUANT", "1") == "1"
+# With a main_grad accumulator the dw2 GEMM is run by _UpProjection.backward after dx (see there); "0" keeps it in
+# _DownProjection.backward (needed only if a caller differentiates with respect to w2 alone, so that the first
+# Function's backward never runs).
+_DEFER_DW2 = os.getenv("SONIC_MOE_DEFER_DW2", "1") == "1"
 
 
 def _mn_wgrad_ok(E: int, M: int, N: int) -> bool:
@@ -198,6 +202,26 @@ def _after_accumulate(base):
     hook = getattr(base, "_apply_backward_hook", None)
     if hook is not None:
         hook()
+
+
+# "This tensor is complete on the stream that produced it": an event per freshly produced dx, recorded BEFORE the
+# weight-gradient GEMMs are enqueued.  A consumer on another stream (the expert-parallel return exchange on its
+# communication stream) waits for that event instead of for everything the compute stream has been given.
+_RESULT_READY: dict = {}
+
+
+def note_result_ready(t: torch.Tensor):
+    if t.is_cuda and not torch.cuda.is_current_stream_capturing():
+        if len(_RESULT_READY) >= 16:
+            _RESULT_READY.pop(next(iter(_RESULT_READY)))
+        ev = torch.cuda.Event()
+        ev.record()
+        _RESULT_READY[t.data_ptr()] = ev
+
+
+def take_result_ready(t: torch.Tensor):
+    """The event recorded when `t` was produced, or None (then the consumer orders itself after the whole stream)."""
+    return _RESULT_READY.pop(t.data_ptr(), None)
 
 
 # Where the next layer call should put its two token-side results (forward output, dx).  The expert-parallel layer
@@ -312,7 +336,10 @@ class _UpProjection(torch.autograd.Function):
             z_q, z_sc, y1_q, y1_sf = ops.gemm_gated(xg_q, None, a_sf, w1_q, w1_sf, efo, TKp)
             del xg_q
         out_buf, ctx.dx_buf = _take_placement()
-        link = {"y1": (y1_q, y1_sf), "z": (z_q, z_sc), "out_buf": out_buf}
+        link = {"y1": (y1_q, y1_sf), "z": (z_q, z_sc), "out_buf": out_buf,
+                # whether a backward of this Function will run (it then also runs the weight-gradient GEMM that
+                # _DownProjection.backward hands over)
+                "up_runs_backward": bool(ctx.needs_input_grad[0] or ctx.needs_input_grad[1])}
         cfg = fp8_config if fp8_config is not None else get_active_config()
         if cfg is not None and cfg.resolve_recompute_z() and not is_inference:
             # keep what regenerates z instead of z itself; the backward re-runs this GEMM and gets the same bytes
@@ -339,6 +366,22 @@ class _UpProjection(torch.autograd.Function):
         dz_q, dz_rsf, dz_t, dz_csf = link.pop("dz")
         E, N2, H = w1.shape
         TKp = dz_q.shape[0]
+        # dx first: it is what an enclosing exchange (the expert-parallel return all-to-all) waits for, and the
+        # weight gradients that follow on this stream then run underneath that exchange (the reference opens the
+        # same slot for dw1: sonicmoe/functional/__init__.py:278-311)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            w1t_q, w1t_sf = weight_fp8(w1, True)
+            dx_exp = ops.gemm_varlen_m(dz_q, dz_rsf, w1t_q, w1t_sf, efo)
+            buf = ctx.dx_buf if (ctx.dx_buf is not None and ctx.x_dtype == torch.bfloat16) else None
+            dx = ops.combine(dx_exp, s_rev, naept, None, ctx.T, out=buf)
+            del dx_exp
+            if dx.dtype != ctx.x_dtype:
+                dx = dx.to(ctx.x_dtype)
+            note_result_ready(dx)
+        deferred_dw2 = link.pop("dw2_job", None)
+        if deferred_dw2 is not None:
+            deferred_dw2()
         dw1 = None
         if ctx.needs_input_grad[1]:
             if ctx.x_is_fp8:     # x is e4m3 + raw scales: dequantise, then column-wise re-quantise
@@ -353,14 +396,6 @@ class _UpProjection(torch.autograd.Function):
                 _after_accumulate(base)
             else:
                 dw1 = out.to(w1.dtype)
-        dx = None
-        if ctx.needs_input_grad[0]:
-            w1t_q, w1t_sf = weight_fp8(w1, True)
-            dx_exp = ops.gemm_varlen_m(dz_q, dz_rsf, w1t_q, w1t_sf, efo)
-            buf = ctx.dx_buf if (ctx.dx_buf is not None and ctx.x_dtype == torch.bfloat16) else None
-            dx = ops.combine(dx_exp, s_rev, naept, None, ctx.T, out=buf)
-            if dx.dtype != ctx.x_dtype:
-                dx = dx.to(ctx.x_dtype)
         ops.post_status(dz_q.device)      # last kernels of the layer's backward: let the next call see their status
         return (dx, dw1) + (None,) * 15
 
@@ -475,13 +510,22 @@ class _DownProjection(torch.autograd.Function):
                 else:
                     dout_t, dout_sf = ops.quant_cols_t(dout, x_gather_idx, TKp)
             mg, base = _grad_target(w2, (E, I, H))
-            out = mg if mg is not None else torch.empty(E, I, H, dtype=torch.float32, device=s.device)
-            _wgrad(y1s_q if y1s_q is not None else y1s_t, y1s_sf, y1s_q is not None,
-                   dout_c if dout_c is not None else dout_t, dout_sf, dout_c is not None and dout_c_rows, efo, out,
-                   mg is not None)
-            if mg is not None:
+            a_op, a_rows = (y1s_q, True) if y1s_q is not None else (y1s_t, False)
+            b_op, b_rows = (dout_c, dout_c_rows) if dout_c is not None else (dout_t, False)
+            if mg is not None and link.get("up_runs_backward") and _DEFER_DW2:
+                # accumulation into main_grad returns no tensor: the GEMM is handed to _UpProjection.backward, which
+                # runs it after dx so that it, too, lies underneath an enclosing exchange of dx
+                def dw2_job(a_op=a_op, a_rows=a_rows, b_op=b_op, b_rows=b_rows, sf_a=y1s_sf, sf_b=dout_sf, mg=mg,
+                            base=base, efo=efo):
+                    _wgrad(a_op, sf_a, a_rows, b_op, sf_b, b_rows, efo, mg, True)
+                    _after_accumulate(base)
+                link["dw2_job"] = dw2_job
+            elif mg is not None:
+                _wgrad(a_op, y1s_sf, a_rows, b_op, dout_sf, b_rows, efo, mg, True)
                 _after_accumulate(base)
             else:
+                out = torch.empty(E, I, H, dtype=torch.float32, device=s.device)
+                _wgrad(a_op, y1s_sf, a_rows, b_op, dout_sf, b_rows, efo, out, False)
                 dw2 = out.transpose(1, 2).to(w2.dtype)
         if dz is not None:
             link["dz"] = ops.quant_iso32(dz)
