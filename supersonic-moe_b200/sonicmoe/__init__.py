@@ -17,9 +17,12 @@ from .functional import (  # noqa: F401
     drop_weight_fp8,
     enable_fp8,
     enable_quack_gemm,
+    general_routing_router_metadata,
+    moe_general_routing_inputs,
     moe_TC_softmax_topk_layer,
     precompute_weight_fp8,
 )
 from .interface import run_sonic_moe  # noqa: F401
 from .moe import MoE  # noqa: F401
 from .quack_utils import pack_blockscaled_1x32_scales  # noqa: F401
+from .routing import token_rounding_routing  # noqa: F401

@@ -601,3 +601,62 @@ def moe_TC_softmax_topk_layer(x, router_w, w1, b1, w2, b2, K, stream_id, activat
                               md["x_gather_idx"], md["s_scatter_idx"], md["s_reverse_scatter_idx"], md["naept"],
                               False, activation_type, fp8_protocol, None, None, scores, md["score_src_idx"])
     return o, logits, md["counts"]
+
+
+# ----------------------------------------------------------------------------
+# general routing: a list of (token, expert, score) pairs instead of a [T,K] table
+# ----------------------------------------------------------------------------
+_MAX_PAIRS_PER_TOKEN = 16        # lanes per token the routing-metadata kernel handles
+
+
+def _pairs_to_table(router_scores_selected, sorted_selected_T, selected_E, T):
+    """(score, token, expert) pairs, sorted by token -> padded tables idx [T,Kmax] (-1 = no pair) and scores
+    [T,Kmax]; the scatter into the score table is differentiable with respect to the pair scores."""
+    tok = sorted_selected_T.long()
+    per_tok = torch.bincount(tok, minlength=T)
+    kmax = int(per_tok.max()) if tok.numel() else 1
+    if kmax > _MAX_PAIRS_PER_TOKEN:
+        raise NotImplementedError(f"a token routed to {kmax} experts: at most {_MAX_PAIRS_PER_TOKEN} are supported")
+    kmax = max(kmax, 1)
+    first = torch.cumsum(per_tok, 0) - per_tok
+    lane = torch.arange(tok.numel(), device=tok.device) - first[tok]
+    idx = torch.full((T, kmax), -1, dtype=torch.int32, device=tok.device)
+    idx[tok, lane] = selected_E.to(torch.int32)
+    scores = torch.zeros(T, kmax, dtype=torch.float32, device=tok.device).index_put((tok, lane),
+                                                                                  router_scores_selected.float())
+    return idx, scores
+
+
+def general_routing_router_metadata(router_scores_selected, sorted_selected_T, selected_E, T: int, E: int):
+    """Routing metadata for an arbitrary list of (token, expert) pairs sorted by token - same outputs as the
+    reference's function of this name (sonicmoe/functional/__init__.py:740-773): (expert_frequency,
+    expert_frequency_offset [E+1], x_gather_idx, s_scatter_idx, s_reverse_scatter_idx,
+    num_activated_expert_per_token_offset [T+1]), all unpadded (alignment 1)."""
+    idx, scores = _pairs_to_table(router_scores_selected.detach(), sorted_selected_T, selected_E, T)
+    n = int(sorted_selected_T.numel())
+    md = ops.topk_metadata(idx, scores, E, alignment=1, TK_alloc=n, TKp_alloc=n, lane_order=1, pad_mode=1)
+    return (md["counts"], md["efo"], md["x_gather_idx"], md["s_scatter_idx"], md["s_reverse_scatter_idx"],
+            md["naept"])
+
+
+def moe_general_routing_inputs(x, router_scores, token_indices, expert_indices, w1, b1, w2, b2, E, stream_id,
+                               activation_type=ActivationType.SWIGLU, is_inference_mode_enabled=False):
+    """MoE layer on an explicit routing: pair i sends token `token_indices[i]` (ascending) to expert
+    `expert_indices[i]` with weight `router_scores[i]`; a token may have any number of pairs up to 16 (what a
+    token-rounding or expert-choice router produces).  x [T,H]; w1 [2I,H,E] and w2 [H,I,E] views of the
+    expert-major parameters, as in `moe_TC_softmax_topk_layer`.  Returns (o [T,H], expert_frequency [E] int32);
+    differentiable with respect to x, router_scores, w1 and w2.  Call sites in the reference:
+    benchmarks/moe-token-rounding.py:103-118, tools/introspect.py:1511-1514."""
+    from ..interface import run_sonic_moe
+    _require_fp8()
+    require_swiglu(activation_type)
+    if b1 is not None or b2 is not None:
+        raise NotImplementedError("expert biases are not supported on the MXFP8 path")
+    T = x.shape[0]
+    w1_e, w2_e = _expert_major(w1), _expert_major(w2)
+    idx, scores = _pairs_to_table(router_scores, token_indices, expert_indices, T)
+    counts = ops.count_cumsum(expert_indices.to(torch.int32).contiguous(), E, do_cumsum=False) if E % 4 == 0 \
+        else torch.bincount(expert_indices.long(), minlength=E).to(torch.int32)
+    o = run_sonic_moe(x, idx, scores, idx.shape[1], E, w1_e, w2_e, fp8=True, activation_type=activation_type,
+                      sync_free_sizing=True)
+    return o, counts

@@ -10,6 +10,25 @@ from .enums import ActivationType
 from .functional import _DownProjection, _UpProjection, enable_fp8, place_results
 
 
+def scale_bytes(fp8_scale: torch.Tensor, H: int) -> torch.Tensor:
+    """The 1x32 ue8m0 scales of an FP8 payload as one byte per group, u8 [N, H/32], from any of the formats the
+    reference's dispatch delivers (sonicmoe/quack_utils/blockscaled_fp8_gemm.py:535-550, interface.py:135-187):
+    uint8 / float8_e8m0fnu [N, H/32]; int32 [N, H/128] - four scale bytes per word, the compact form DeepEP
+    transports as opaque int32; int32 [N, H/32] - one word per group."""
+    groups = H // 32
+    if fp8_scale.dtype == torch.uint8 and fp8_scale.shape[-1] == groups:
+        return fp8_scale.contiguous()
+    if fp8_scale.dtype == torch.int32 and fp8_scale.shape[-1] * 4 == groups:
+        return fp8_scale.contiguous().view(torch.uint8)           # little-endian: byte j of a row is group j
+    if fp8_scale.dtype == torch.int32 and fp8_scale.shape[-1] == groups:
+        return fp8_scale.to(torch.uint8)
+    if getattr(torch, "float8_e8m0fnu", None) is not None and fp8_scale.dtype == torch.float8_e8m0fnu \
+            and fp8_scale.shape[-1] == groups:
+        return fp8_scale.contiguous().view(torch.uint8)
+    raise ValueError(f"fp8_scale {fp8_scale.dtype} {tuple(fp8_scale.shape)} is none of the 1x32 ue8m0 formats for "
+                     f"H={H}: u8/e8m0 [N,{groups}], int32 [N,{groups // 4}] (packed words) or int32 [N,{groups}]")
+
+
 def run_sonic_moe(hidden_states, topk_indices, topk_scores, K, E, w1, w2, fp8=False, tokens_per_expert=None,
                   fp8_scale=None, fp8_combine_grad_handle=None, fp8_config=None, release_fp8_weights=False,
                   activation_type=ActivationType.SWIGLU, sync_free_sizing=False, grad_holder=None, out=None,
@@ -46,7 +65,7 @@ def run_sonic_moe(hidden_states, topk_indices, topk_scores, K, E, w1, w2, fp8=Fa
     stream_id = torch.cuda.current_stream().cuda_stream
     payload = None
     if fp8_scale is not None:
-        payload = (hidden_states.view(torch.uint8), fp8_scale)
+        payload = (hidden_states.view(torch.uint8), scale_bytes(fp8_scale, hidden_states.shape[1]))
         hidden_states = grad_holder if grad_holder is not None else torch.empty(
             (), dtype=torch.bfloat16, device=hidden_states.device).expand(N, hidden_states.shape[1])
     need_router_grad = topk_scores.requires_grad

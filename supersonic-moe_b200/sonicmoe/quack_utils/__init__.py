@@ -15,9 +15,24 @@ def quantize_and_pack_activation(x: torch.Tensor):
     return q.view(torch.float8_e4m3fn), isa
 
 
-def quantize_activation_blockscaled_fast(x: torch.Tensor):
-    """bf16 [M,K] -> (e4m3 [M,K], raw ue8m0 scales [M,K/32]) (blockscaled_fp8_gemm.py:518-596)."""
+def quantize_activation_blockscaled_fast(x: torch.Tensor, group_size: int = 32, scale_dtype=None,
+                                         pack_scale_words: bool = False):
+    """bf16 [M,K] -> (e4m3 [M,K], ue8m0 scales) (blockscaled_fp8_gemm.py:518-596).  Scales: u8 [M,K/32] by default;
+    `pack_scale_words`: int32 [M,K/128], four scale bytes per word (the compact form an FP8 dispatch transports);
+    `scale_dtype=torch.int32`: int32 [M,K/32], one word per group."""
+    if group_size != 32:
+        raise NotImplementedError("1x32 groups only")
+    want_i32 = str(scale_dtype) in ("torch.int32", "int32")
+    if pack_scale_words and want_i32:
+        raise ValueError("pack_scale_words and an explicit int32 scale_dtype are mutually exclusive")
     q, raw, _ = ops.quant_rows(x.contiguous(), raw=True, isa=False)
+    if pack_scale_words:
+        if raw.shape[1] % 4:
+            raise ValueError(f"pack_scale_words requires the number of 1x32 groups to be divisible by 4, got "
+                             f"{raw.shape[1]} for K={x.shape[1]}")
+        raw = raw.view(torch.int32)
+    elif want_i32:
+        raw = raw.to(torch.int32)
     return q.view(torch.float8_e4m3fn), raw
 
 

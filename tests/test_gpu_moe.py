@@ -563,3 +563,81 @@ def test_reference_bench_distribution_meets_the_published_tolerance_as_it_stands
         gate(name, got, ref, em, strict=True, report=report)
     print("\n" + "\n".join(f"refdist {T}x{H}x{I} E{E} K{K} {n}: gpu cos {a:.5f} rrmse {b:.5f} | emulation "
                            f"{c:.5f} {d:.5f} | gpu vs emulation {e:.5f} {f:.5f}" for n, a, b, c, d, e, f in report))
+
+
+@pytest.mark.parametrize("routing", ["down", "up", "nr"])
+def test_token_rounding_router_through_general_routing(sm, routing):
+    """`token_rounding_routing` -> `moe_general_routing_inputs`: every expert's row count is a multiple of 128, so the
+    padded layout has no pad row at all, and out / dx / dscores / dw1 / dw2 meet both oracles
+    (reference: benchmarks/moe-token-rounding.py:103-181)."""
+    from parity_util import gate
+    T, H, I, E, K = 1024, 512, 256, 16, 4
+    x, dy, w1, w2, wr, _ = make_layer(T, H, I, E, K, 81)
+    logits = torch.nn.functional.linear(x.float(), wr.float())
+    s, tok, exp = sm.token_rounding_routing(logits.to(DEV), K, 128, routing)
+    counts = torch.bincount(exp.long(), minlength=E).cpu()
+    assert bool((counts % 128 == 0).all()) and int(counts.sum()) == tok.numel()
+    # the same pairs as a padded table for the oracles
+    from sonicmoe.functional import _pairs_to_table, general_routing_router_metadata
+    idx, sc = _pairs_to_table(s.cpu(), tok.cpu(), exp.cpu(), T)
+    md = R.topk_metadata(idx, sc, E, 128)
+    assert md["real_TKp"] == md["real_TK"] == tok.numel(), "no pad rows"
+    gold = OM.moe_fp32(x, w1, w2, md, dy)
+    emu = OM.moe_fp8_emulated(x, w1, w2, md, dy)
+    xd = x.to(DEV).requires_grad_(True)
+    sd = s.detach().clone().requires_grad_(True)
+    moe = sm.MoE(E, K, H, I, sm.ActivationType.SWIGLU, add_bias=False, std=0.02).to(DEV).to(torch.bfloat16)
+    with torch.no_grad():
+        moe.c_fc.weight.copy_(w1)
+        moe.c_proj.weight.copy_(w2)
+    with sm.enable_fp8():
+        o, freq = sm.moe_general_routing_inputs(xd, sd, tok, exp, moe.c_fc.weight.permute(1, 2, 0), None,
+                                                moe.c_proj.weight.permute(1, 2, 0), None, E, 0,
+                                                sm.ActivationType.SWIGLU, False)
+    o.backward(dy.to(DEV))
+    torch.cuda.synchronize()
+    sm.ops.check_status(DEV)
+    assert torch.equal(freq.cpu().long(), counts)
+    tk = md["real_TK"]
+    # pair i of the (token-sorted) list <-> table slot (token, lane): the oracle's ds is token-major over the table
+    flat = torch.zeros(idx.numel())
+    ds_pairs = lambda r: flat.clone().index_put_((md["score_src_idx"][:tk].long(),), r["ds"][:tk].float())[
+        (idx.flatten() >= 0)]
+    for name, got, ref, em in [("out", o, gold["o"], emu["o"]), ("dx", xd.grad, gold["dx"], emu["dx"]),
+                               ("ds", sd.grad, ds_pairs(gold), ds_pairs(emu)),
+                               ("dw1", moe.c_fc.weight.grad, gold["dw1"], emu["dw1"]),
+                               ("dw2", moe.c_proj.weight.grad, gold["dw2"], emu["dw2_IH"].transpose(1, 2))]:
+        gate(f"token-rounding {routing} {name}", got, ref, em, strict=False)
+    # the unpadded metadata of the reference's general-routing helper: a permutation sorted by expert, tokens
+    # ascending inside an expert, and its inverse
+    freq2, efo, xg, ss, srev, naept = general_routing_router_metadata(s, tok, exp, T, E)
+    n = tok.numel()
+    assert torch.equal(freq2.cpu().long(), counts) and int(efo[-1]) == n and int(naept[-1]) == n
+    e_sorted = exp.cpu()[ss.cpu().long()]
+    assert bool((e_sorted[1:] >= e_sorted[:-1]).all())
+    assert torch.equal(xg.cpu()[:n], tok.cpu()[ss.cpu().long()])
+    assert torch.equal(ss.cpu()[srev.cpu().long()], torch.arange(n, dtype=torch.int32))
+
+
+def test_fp8_payload_scale_formats(sm):
+    """An FP8 dispatch payload with its scales as u8 [N,H/32], as compact int32 words [N,H/128] (four ue8m0 bytes per
+    word) or as int32 [N,H/32] gives bit-identical results (reference: blockscaled_fp8_gemm.py:535-550)."""
+    from sonicmoe.quack_utils import quantize_activation_blockscaled_fast as quant
+    T, H, I, E, K = 512, 512, 256, 8, 4
+    x, dy, w1, w2, _, _ = make_layer(T, H, I, E, K, 91)
+    idx, scores = masked_routing(T, E, K, E, 92)
+    w1d, w2d = w1.to(DEV), w2.to(DEV)
+    xd = x.to(DEV)
+    q, raw = quant(xd)
+    q2, words = quant(xd, pack_scale_words=True)
+    q3, wide = quant(xd, scale_dtype=torch.int32)
+    assert words.dtype == torch.int32 and tuple(words.shape) == (T, H // 128)
+    assert wide.dtype == torch.int32 and tuple(wide.shape) == (T, H // 32)
+    assert torch.equal(q.view(torch.uint8), q2.view(torch.uint8)) and torch.equal(words.view(torch.uint8), raw)
+    run = lambda sc: sm.run_sonic_moe(q, idx.to(DEV), scores.to(DEV), K, E, w1d, w2d, fp8=True, fp8_scale=sc)
+    base = run(raw)
+    assert torch.equal(base, run(words)) and torch.equal(base, run(wide))
+    ref = sm.run_sonic_moe(xd, idx.to(DEV), scores.to(DEV), K, E, w1d, w2d, fp8=True)
+    assert torch.equal(base, ref)                      # same bytes as quantising inside the layer
+    with pytest.raises(ValueError):
+        run(raw[:, :-1].contiguous())
