@@ -239,6 +239,24 @@ int smoe_gemm_wgrad_mn(const void* a_fp8, const void* a_sf, const void* b_fp8, c
                        float* c, int64_t M, int64_t N, int64_t TKp, int64_t E, int accumulate, int layout,
                        int32_t* status, void* stream);
 
+/* ---- gated activations outside the GEMM epilogues ----------------------------
+ * The fused epilogues of smoe_gemm_gated / smoe_gemm_dgated* carry SwiGLU.  For the reference's other gated
+ * activations (sonicmoe/enums.py:18-33; mapped to quack.activation.reglu / geglu in quack_utils/gemm_gated.py:171-177)
+ * the projections run as plain GEMMs (smoe_gemm_varlen_m) and these two HBM-bound kernels do the epilogues' work.
+ * act: 0 = swiglu, 1 = reglu (relu(g) * u), 2 = geglu (tanh-approximated gelu(g) * u); gate / up interleaved. */
+
+/* z bf16 [rows,2I] -> z e4m3 [rows,2I] + raw 1x32 scales [rows,2I/32] (amax floor 1e-4) and y1 = bf16(act(g)*u) ->
+ * e4m3 [rows,I] + ISA scales for (rows,I): what the epilogue of gemm_gated emits
+ * (sonicmoe/quack_utils/_gated_epilogues.py:1331-1513).  I % 32 == 0. */
+int smoe_glu_fwd(const void* z_bf16, int64_t rows, int64_t I, int act, void* z_fp8, void* z_scales, void* y1_fp8,
+                 void* y1_sf, void* stream);
+
+/* D bf16 [rows,I] (= dout . W2 per expert) against the saved e4m3 z: dz bf16 [rows,2I] (interleaved), y1s = s*y bf16
+ * [rows,I], ds_rows[row] = sum_j y_j D_j: what the epilogue of gemm_dgated emits
+ * (sonicmoe/quack_utils/_gated_epilogues.py:2864-3000). */
+int smoe_glu_bwd(const void* d_bf16, const void* z_fp8, const void* z_scales, const float* s, int64_t rows, int64_t I,
+                 int act, void* dz_bf16, void* y1s_bf16, float* ds_rows, void* stream);
+
 /* ---- combine / router ------------------------------------------------------ */
 
 /* o[t,:] = sum_j w * y[s_rev[naept[t]+j], :] in ascending j, f32 accumulate, bf16 store; w = scores[naept[t]+j]

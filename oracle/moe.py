@@ -54,10 +54,43 @@ def router_backward(scores: torch.Tensor, idx: torch.Tensor, dscores: torch.Tens
 # ----------------------------------------------------------------------------
 # expert math helpers (interleaved layout: even rows of w1[e] = gate, odd = up)
 # ----------------------------------------------------------------------------
+GELU_C0, GELU_C1 = 0.7978845608028654, 0.044715        # sqrt(2/pi); the tanh approximation of GELU
+
+
 def swiglu(z: torch.Tensor) -> torch.Tensor:
     g, u = z[..., 0::2], z[..., 1::2]
     sig = 1.0 / (1.0 + torch.exp(-g))
     return (g * sig) * u
+
+
+def glu(z: torch.Tensor, act: str = "swiglu") -> torch.Tensor:
+    """act(gate) * up on interleaved columns: swiglu, reglu = relu(g)*u, geglu = gelu_tanh(g)*u
+    (the reference maps the names to quack.activation.swiglu / reglu / geglu, quack_utils/gemm_gated.py:171-177)."""
+    if act == "swiglu":
+        return swiglu(z)
+    g, u = z[..., 0::2], z[..., 1::2]
+    if act == "reglu":
+        return torch.relu(g) * u
+    if act == "geglu":
+        return (0.5 * g * (1.0 + torch.tanh(GELU_C0 * (g + GELU_C1 * g ** 3)))) * u
+    raise ValueError(act)
+
+
+def dglu(z: torch.Tensor, dy: torch.Tensor, act: str = "swiglu"):
+    """-> (dz interleaved, y = act(g)*u) for upstream dy with respect to y."""
+    if act == "swiglu":
+        return dswiglu(z, dy)
+    g, u = z[..., 0::2], z[..., 1::2]
+    if act == "reglu":
+        a, da = torch.relu(g), (g > 0).to(z.dtype)
+    elif act == "geglu":
+        t = torch.tanh(GELU_C0 * (g + GELU_C1 * g ** 3))
+        a = 0.5 * g * (1.0 + t)
+        da = 0.5 * (1.0 + t) + 0.5 * g * (1.0 - t * t) * GELU_C0 * (1.0 + 3.0 * GELU_C1 * g * g)
+    else:
+        raise ValueError(act)
+    dz = torch.stack([da * u * dy, a * dy], dim=-1).reshape(z.shape)
+    return dz, a * u
 
 
 def dswiglu(z: torch.Tensor, dy: torch.Tensor):
@@ -98,7 +131,7 @@ def combine(y2: torch.Tensor, md: dict, N: int, weighted: bool) -> torch.Tensor:
 # ----------------------------------------------------------------------------
 # fp32 gold
 # ----------------------------------------------------------------------------
-def moe_fp32(x, w1, w2, md: dict, dy=None):
+def moe_fp32(x, w1, w2, md: dict, dy=None, act: str = "swiglu"):
     """x [N,H], w1 [E,2I,H], w2 [E,H,I] (any float dtype, promoted to fp32),
     md = oracle.routing.topk_metadata(...).  Returns dict(o, and with dy: dx, dw1,
     dw2, ds (token-major, length TK))."""
@@ -112,7 +145,7 @@ def moe_fp32(x, w1, w2, md: dict, dy=None):
     y2 = torch.zeros(TKp, H)
     for e, a, b in _segments(efo):
         z[a:b] = x[xg[a:b]] @ w1[e].T
-    y1 = swiglu(z)
+    y1 = glu(z, act)
     for e, a, b in _segments(efo):
         y2[a:b] = y1[a:b] @ w2[e].T
     out = dict(o=combine(y2, md, N, True), z=z, y1=y1, y2=y2)
@@ -123,7 +156,7 @@ def moe_fp32(x, w1, w2, md: dict, dy=None):
     D = torch.zeros(TKp, I2 // 2)
     for e, a, b in _segments(efo):
         D[a:b] = dout[a:b] @ w2[e]
-    dz, y = dswiglu(z, s.unsqueeze(1) * D)
+    dz, y = dglu(z, s.unsqueeze(1) * D, act)
     ds_row = (y * D).sum(dim=1)
     y1s = s.unsqueeze(1) * y
     dw1 = torch.zeros_like(w1)
@@ -159,7 +192,7 @@ def _deq_w(qs):
     return Q.dequant_rows(q.reshape(E * N, K), s.reshape(E * N, K // 32)).reshape(E, N, K)
 
 
-def moe_fp8_emulated(x, w1, w2, md: dict, dy=None, y1_bf16_rne: bool = True):
+def moe_fp8_emulated(x, w1, w2, md: dict, dy=None, y1_bf16_rne: bool = True, act: str = "swiglu"):
     """x, dy bf16 [N,H]; w1 [E,2I,H], w2 [E,H,I] bf16.  All outputs of the FP8 path
     plus every quantised intermediate (bytes and scale bytes)."""
     N, H = x.shape
@@ -178,7 +211,7 @@ def moe_fp8_emulated(x, w1, w2, md: dict, dy=None, y1_bf16_rne: bool = True):
     z = torch.zeros(TKp, I2)
     for e, a, b in _segments(efo):
         z[a:b] = xd[xg[a:b]] @ W1[e].T
-    y1 = swiglu(z)
+    y1 = glu(z, act)
     if y1_bf16_rne:
         y1 = Q.bf16_rne(y1)
     zq, zs = Q.row_quant(z, amax_floor=1e-4)
@@ -201,7 +234,7 @@ def moe_fp8_emulated(x, w1, w2, md: dict, dy=None, y1_bf16_rne: bool = True):
     for e, a, b in _segments(efo):
         D[a:b] = dd[xg[a:b]] @ W2T[e].T
     zd = Q.dequant_rows(zq, zs)
-    dz, y = dswiglu(zd, s.unsqueeze(1) * D)
+    dz, y = dglu(zd, s.unsqueeze(1) * D, act)
     ds_row = (y * D).sum(dim=1)
     y1s = (s.unsqueeze(1) * y).to(torch.bfloat16)
     dz = dz.to(torch.bfloat16)

@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 OUT = os.path.join(HERE, "sonicmoe", "libsmoe_b200.so")
-SOURCES = ["routing.cu", "quant.cu", "combine.cu", "ep_plan.cu", "ep_peer.cu", "gemm.cu"]
+SOURCES = ["routing.cu", "quant.cu", "combine.cu", "glu.cu", "ep_plan.cu", "ep_peer.cu", "gemm.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-I", INCLUDE, "-I", CSRC]
 

@@ -77,7 +77,7 @@ class SonicMoEMlpNode:
     experts            per-expert modules with `up_gate_proj.weight [H, 2I]` and `down_proj.weight [I, H]`
     n_experts          local experts E
     hidden_size, intermediate_size
-    activation_type    SwiGLU only in this build
+    activation_type    SwiGLU (fused GEMM epilogues), ReGLU or GEGLU (plain GEMMs + activation kernels)
     stream_id          kept for signature compatibility (work runs on the current stream)
 
     Training-loop contract (mlp_node_v2.py:655-679):
@@ -95,8 +95,8 @@ class SonicMoEMlpNode:
         self._E, self._H, self._I = n_experts, hidden_size, intermediate_size
         if isinstance(activation_type, str):
             activation_type = ActivationType(activation_type)
-        if activation_type != ActivationType.SWIGLU:
-            raise NotImplementedError(f"activation {activation_type}: only SwiGLU is built")
+        from ..enums import activation_code
+        activation_code(activation_type)          # SwiGLU, ReGLU, GEGLU; raises for anything else
         self._activation_type = activation_type
         self._stream_id = stream_id
         self._w_cache: dict = {}

@@ -26,7 +26,7 @@ import torch.nn.functional as F
 
 from .. import ops
 from ..config import get_active_config
-from ..enums import ActivationType, require_swiglu
+from ..enums import ActivationType, activation_code, require_swiglu
 
 # ----------------------------------------------------------------------------
 # flags (API kept; a single compute path sits behind them)
@@ -296,6 +296,16 @@ class Fp8CombineGradHandle:
         return p
 
 
+def _up_projection(xg_q, a_sf, w1_q, w1_sf, efo, TKp, act):
+    """z = x_sorted . W1^T, y1 = act(gate) * up; z and y1 leave as MXFP8.  SwiGLU: one GEMM with the activation and
+    both quantizers in its epilogue; ReGLU / GEGLU: a plain GEMM to bf16 z, then the stand-alone activation kernel
+    (rows beyond the last expert's segment hold whatever the allocator left: they are never read downstream)."""
+    if act == 0:
+        return ops.gemm_gated(xg_q, None, a_sf, w1_q, w1_sf, efo, TKp)
+    z = ops.gemm_varlen_m(xg_q, a_sf, w1_q, w1_sf, efo)
+    return ops.glu_fwd(z, act)
+
+
 class _UpProjection(torch.autograd.Function):
     @classmethod
     def apply(cls, x, w1, b1, expert_frequency_offset, total_expert_freq, K, stream_id, x_gather_idx, s_scatter_idx,
@@ -312,7 +322,7 @@ class _UpProjection(torch.autograd.Function):
                 activation_type, is_inference, low_precision_postact, prequant_payload, fp8_config):
         ctx.set_materialize_grads(False)   # an unused output must not be handed a zero-filled [TKp, I] gradient
         _require_fp8()
-        require_swiglu(activation_type)
+        act = activation_code(activation_type)
         if b1 is not None:
             raise NotImplementedError("expert biases are not supported on the MXFP8 path")
         E, N2, H = w1.shape
@@ -322,10 +332,10 @@ class _UpProjection(torch.autograd.Function):
             # x arrives as e4m3 bytes + raw 1x32 ue8m0 scales (expert-parallel dispatch payload)
             x_q, x_raw = prequant_payload[0], prequant_payload[1]
             x_q = x_q.view(torch.uint8)
-        elif USE_TMA_GATHER:
+        elif USE_TMA_GATHER and act == 0:
             x_q, x_raw, _ = ops.quant_rows(x.contiguous(), raw=True)
         w1_q, w1_sf = weight_fp8(w1, False)
-        if USE_TMA_GATHER:
+        if USE_TMA_GATHER and act == 0:
             a_sf = ops.gather_scales_isa(x_raw, x_gather_idx, TKp, H)
             z_q, z_sc, y1_q, y1_sf = ops.gemm_gated(x_q, x_gather_idx, a_sf, w1_q, w1_sf, efo, TKp)
         else:
@@ -333,10 +343,10 @@ class _UpProjection(torch.autograd.Function):
                 xg_q, a_sf = ops.scatter_rows_fp8(x_q, x_raw, naept, s_rev, s_scatter_idx, TKp, efo[-1:])
             else:      # quantise straight into expert-sorted order
                 xg_q, a_sf = ops.quant_rows_scatter(x.contiguous(), naept, s_rev, s_scatter_idx, TKp, efo[-1:])
-            z_q, z_sc, y1_q, y1_sf = ops.gemm_gated(xg_q, None, a_sf, w1_q, w1_sf, efo, TKp)
+            z_q, z_sc, y1_q, y1_sf = _up_projection(xg_q, a_sf, w1_q, w1_sf, efo, TKp, act)
             del xg_q
         out_buf, ctx.dx_buf = _take_placement()
-        link = {"y1": (y1_q, y1_sf), "z": (z_q, z_sc), "out_buf": out_buf,
+        link = {"y1": (y1_q, y1_sf), "z": (z_q, z_sc), "out_buf": out_buf, "act": act,
                 # whether a backward of this Function will run (it then also runs the weight-gradient GEMM that
                 # _DownProjection.backward hands over)
                 "up_runs_backward": bool(ctx.needs_input_grad[0] or ctx.needs_input_grad[1])}
@@ -345,7 +355,7 @@ class _UpProjection(torch.autograd.Function):
             # keep what regenerates z instead of z itself; the backward re-runs this GEMM and gets the same bytes
             link["z"] = None
             link["z_recompute"] = (x if prequant_payload is None else None, x_q, x_raw, w1, efo, x_gather_idx,
-                                   s_scatter_idx, s_rev, naept, TKp)
+                                   s_scatter_idx, s_rev, naept, TKp, act)
             del z_q, z_sc
         ctx.link = link
         ctx.T = x.shape[0]
@@ -403,10 +413,10 @@ class _UpProjection(torch.autograd.Function):
 def _recompute_z(args):
     """z as e4m3 + raw scales, regenerated from the up-projection's inputs (same kernels, same bytes as the
     forward produced; the re-computed y1 is discarded)."""
-    x, x_q, x_raw, w1, efo, x_gather_idx, s_scatter_idx, s_rev, naept, TKp = args
+    x, x_q, x_raw, w1, efo, x_gather_idx, s_scatter_idx, s_rev, naept, TKp, act = args
     H = w1.shape[2]
     w1_q, w1_sf = weight_fp8(w1, False)
-    if USE_TMA_GATHER:
+    if USE_TMA_GATHER and act == 0:
         if x_q is None:
             x_q, x_raw, _ = ops.quant_rows(x.contiguous(), raw=True)
         a_sf = ops.gather_scales_isa(x_raw, x_gather_idx, TKp, H)
@@ -416,7 +426,7 @@ def _recompute_z(args):
             xg_q, a_sf = ops.scatter_rows_fp8(x_q, x_raw, naept, s_rev, s_scatter_idx, TKp, efo[-1:])
         else:
             xg_q, a_sf = ops.quant_rows_scatter(x.contiguous(), naept, s_rev, s_scatter_idx, TKp, efo[-1:])
-        z_q, z_sc, _, _ = ops.gemm_gated(xg_q, None, a_sf, w1_q, w1_sf, efo, TKp)
+        z_q, z_sc, _, _ = _up_projection(xg_q, a_sf, w1_q, w1_sf, efo, TKp, act)
     return z_q, z_sc
 
 
@@ -472,12 +482,13 @@ class _DownProjection(torch.autograd.Function):
             if dout.dtype != torch.bfloat16:
                 dout = dout.to(torch.bfloat16)
             dout_q = dout_raw = None
-            if USE_TMA_GATHER:
+            if USE_TMA_GATHER and link.get("act", 0) == 0:
                 dout_q, dout_raw, _ = ops.quant_rows(dout, raw=True)
         y1s_q = dout_c = None
         dout_c_rows = False
+        act = link.get("act", 0)
         w2t_q, w2t_sf = weight_fp8(w2, True)
-        if USE_TMA_GATHER:
+        if USE_TMA_GATHER and act == 0:
             a_sf = ops.gather_scales_isa(dout_raw, x_gather_idx, TKp, H)
             dz, y1s, dsp = ops.gemm_dgated(dout_q, x_gather_idx, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, TKp)
         else:
@@ -489,7 +500,13 @@ class _DownProjection(torch.autograd.Function):
                 dg_q, a_sf = ops.quant_rows_scatter(dout, naept, s_rev, s_scatter_idx, TKp, efo[-1:])
                 if ctx.needs_input_grad[2] and _mn_wgrad_ok(E, I, H):
                     dout_c, dout_sf, dout_c_rows = _col_operand(dout, x_gather_idx, TKp, efo[-1:], E, I, H)
-            if FUSE_DGATED_QUANT and _mn_wgrad_ok(E, I, H):
+            if act != 0:
+                # ReGLU / GEGLU: D from a plain GEMM, then the stand-alone activation-gradient kernel; dz / y1s in bf16
+                # take the separate quantizers below
+                D = ops.gemm_varlen_m(dg_q, a_sf, w2t_q, w2t_sf, efo)
+                dz, y1s, dsp = ops.glu_bwd(D, z_q, z_sc, s, act)
+                del D
+            elif FUSE_DGATED_QUANT and _mn_wgrad_ok(E, I, H):
                 # dz / y1s never exist in bf16: the epilogue emits the e4m3 operands of dgrad, dw1 and dw2,
                 # row-major; the weight-gradient GEMMs read them MN-major (needs 256-multiples of I and H)
                 dz_q, dz_rsf, dz_csf, y1s_q, y1s_sf, dsp = ops.gemm_dgated_fused(
@@ -586,7 +603,7 @@ def moe_TC_softmax_topk_layer(x, router_w, w1, b1, w2, b2, K, stream_id, activat
     parameters (rows of w1 interleaved gate0, up0, gate1, ...).  Returns (o [T,H], router_logits [T,E],
     expert_frequency [E] int32); differentiable w.r.t. x, router_w, w1, w2."""
     _require_fp8()
-    require_swiglu(activation_type)
+    activation_code(activation_type)
     ops.poll_status(x.device)         # a device-side failure of an earlier pass surfaces here, without a sync
     T, H = x.shape
     E = router_w.shape[0]
@@ -649,7 +666,7 @@ def moe_general_routing_inputs(x, router_scores, token_indices, expert_indices, 
     benchmarks/moe-token-rounding.py:103-118, tools/introspect.py:1511-1514."""
     from ..interface import run_sonic_moe
     _require_fp8()
-    require_swiglu(activation_type)
+    activation_code(activation_type)
     if b1 is not None or b2 is not None:
         raise NotImplementedError("expert biases are not supported on the MXFP8 path")
     T = x.shape[0]

@@ -436,6 +436,39 @@ def gemm_wgrad_mn(a, a_sf, b, b_sf, efo, out, accumulate, a_rowmajor_tk, b_rowma
     return out
 
 
+# ---------------------------------------------------------------- gated activations outside the GEMMs
+@_timed
+def glu_fwd(z, act):
+    """z bf16 [rows,2I] -> (z_q [rows,2I], z_sc raw [rows,2I/32], y1_q [rows,I], y1_sf ISA); act 0 swiglu, 1 reglu,
+    2 geglu."""
+    _cuda(z)
+    assert z.dtype == torch.bfloat16 and z.ndim == 2
+    rows, N = z.shape
+    I = N // 2
+    dev = z.device
+    z_q = torch.empty(rows, N, dtype=_U8, device=dev)
+    z_sc = torch.empty(rows, N // 32, dtype=_U8, device=dev)
+    y1_q = torch.empty(rows, I, dtype=_U8, device=dev)
+    y1_sf = torch.empty(isa_bytes(rows, I), dtype=_U8, device=dev)
+    check(lib.smoe_glu_fwd(_p(z), rows, I, int(act), _p(z_q), _p(z_sc), _p(y1_q), _p(y1_sf), _stream()), "glu_fwd")
+    return z_q, z_sc, y1_q, y1_sf
+
+
+@_timed
+def glu_bwd(D, z_q, z_sc, s, act):
+    """D bf16 [rows,I], saved z (e4m3 + raw scales), row scores -> (dz bf16 [rows,2I], y1s bf16 [rows,I],
+    ds partial f32 [1, rows])."""
+    _cuda(D, z_q, z_sc, s)
+    rows, I = D.shape
+    dev = D.device
+    dz = torch.empty(rows, 2 * I, dtype=torch.bfloat16, device=dev)
+    y1s = torch.empty(rows, I, dtype=torch.bfloat16, device=dev)
+    dsp = torch.empty(1, rows, dtype=torch.float32, device=dev)
+    check(lib.smoe_glu_bwd(_p(D), _p(z_q), _p(z_sc), _p(s), rows, I, int(act), _p(dz), _p(y1s), _p(dsp), _stream()),
+          "glu_bwd")
+    return dz, y1s, dsp
+
+
 # ---------------------------------------------------------------- token side
 @_timed
 def combine(y, s_rev, naept, scores, T, out=None):

@@ -641,3 +641,36 @@ def test_fp8_payload_scale_formats(sm):
     assert torch.equal(base, ref)                      # same bytes as quantising inside the layer
     with pytest.raises(ValueError):
         run(raw[:, :-1].contiguous())
+
+
+@pytest.mark.parametrize("act", ["reglu", "geglu", "swiglu"])
+def test_other_gated_activations_match_oracles(sm, act):
+    """ReGLU and GEGLU (reference: sonicmoe/enums.py:18-33) run as plain GEMMs + stand-alone activation kernels;
+    SwiGLU through the same module path for comparison.  Both oracles take the activation by name."""
+    from parity_util import gate
+    T, H, I, E, K = 1024, 512, 256, 8, 4
+    x, dy, w1, w2, _, _ = make_layer(T, H, I, E, K, 101)
+    w1 = (w1.float() * 4).to(torch.bfloat16)          # gate values of order one, so the activations differ visibly
+    idx, scores = masked_routing(T, E, K, E, 102)
+    md = R.topk_metadata(idx, scores, E, 128)
+    gold = OM.moe_fp32(x, w1, w2, md, dy, act=act)
+    emu = OM.moe_fp8_emulated(x, w1, w2, md, dy, act=act)
+    xd = x.to(DEV).requires_grad_(True)
+    sd = scores.to(DEV).requires_grad_(True)
+    w1d, w2d = w1.to(DEV).requires_grad_(True), w2.to(DEV).requires_grad_(True)
+    out = sm.run_sonic_moe(xd, idx.to(DEV), sd, K, E, w1d, w2d, fp8=True, activation_type=sm.ActivationType(act))
+    out.backward(dy.to(DEV))
+    torch.cuda.synchronize()
+    sm.ops.check_status(DEV)
+    tk = md["real_TK"]
+    ds_of = lambda r: torch.zeros(T * K).index_put_((md["score_src_idx"][:tk].long(),), r["ds"][:tk].float())
+    for name, got, ref, em in [("out", out, gold["o"], emu["o"]), ("dx", xd.grad, gold["dx"], emu["dx"]),
+                               ("ds", sd.grad.flatten(), ds_of(gold), ds_of(emu)),
+                               ("dw1", w1d.grad, gold["dw1"], emu["dw1"]),
+                               ("dw2", w2d.grad, gold["dw2"], emu["dw2_IH"].transpose(1, 2))]:
+        gate(f"{act} {name}", got, ref, em, strict=False)
+    if act != "swiglu":
+        sw = OM.moe_fp32(x, w1, w2, md, dy, act="swiglu")["o"]
+        assert stats(gold["o"], sw)[1] > 0.05, "the test data must tell the activations apart"
+    with pytest.raises(NotImplementedError):
+        sm.run_sonic_moe(xd, idx.to(DEV), sd, K, E, w1d, w2d, fp8=True, activation_type=sm.ActivationType.SITU_GLU)
