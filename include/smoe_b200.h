@@ -192,7 +192,10 @@ int smoe_gemm_varlen_m(const void* a_fp8, const void* a_sf, const void* b_fp8, c
 /* Up-projection: z = x[a_idx] . W1[e]^T (N = 2I, K = H), y1 = swiglu(z) on interleaved gate/up columns;
  * z -> e4m3 [rows,N] + raw scales [rows,N/32] (amax floor 1e-4), y1 -> bf16 RNE -> e4m3 [rows,N/2] + ISA scales.
  * a_idx == NULL: x_fp8 is already in expert-sorted row order ([rows,K]) and is loaded as plain TMA tiles;
- * a_idx != NULL: rows are fetched by index with TMA gather4 and no gathered copy exists.
+ * a_idx != NULL: x_fp8 is the un-gathered [T,K] activation and row p of the GEMM is x_fp8[a_idx[p]], fetched inside
+ * the kernel by four cp.async load warps per CTA (as the reference's gather_A does,
+ * sonicmoe/quack_utils/gemm_sm100_fp8_zeromat.py:60-67) - no gathered copy exists; a_sf holds the scales already in
+ * expert-sorted ISA layout (smoe_gather_scales_isa).
  * Replaces gemm_gated (sonicmoe/quack_utils/sm100_funcs.py:207-455, gemm_sm100_fp8_zeromat.py:379-406,
  * _gated_epilogues.py:1331-1513).  N % 256 == 0. */
 int smoe_gemm_gated(const void* x_fp8, int64_t T, const int32_t* a_idx, const void* a_sf, const void* w1_fp8,
@@ -221,6 +224,14 @@ int smoe_gemm_dgated_fused(const void* dout_fp8, const void* a_sf, const void* w
                            void* dz_row_sf, void* dz_col_sf, void* y1s_q, void* y1s_col_sf, float* ds_partial,
                            int64_t rows, int64_t N, int64_t K, int64_t E, int32_t* status, void* stream);
 int64_t smoe_gemm_dgated_fused_partials(int64_t N);
+
+/* The same with the A rows fetched by index inside the kernel: dout_fp8 is the un-gathered [T,K] e4m3 gradient, row p
+ * of the GEMM is dout_fp8[a_idx[p]] (cp.async load warps, see smoe_gemm_gated); a_sf as above, expert-sorted. */
+int smoe_gemm_dgated_fused_gather(const void* dout_fp8, int64_t T, const int32_t* a_idx, const void* a_sf,
+                                  const void* w2t_fp8, const void* w2t_sf, const int32_t* efo, const void* z_fp8,
+                                  const void* z_scales, const float* s, void* dz_q, void* dz_row_sf, void* dz_col_sf,
+                                  void* y1s_q, void* y1s_col_sf, float* ds_partial, int64_t rows, int64_t N,
+                                  int64_t K, int64_t E, int32_t* status, void* stream);
 
 /* Weight gradient: C[e] (M x N, f32) (+)= A_t[:, seg_e] . B_t[:, seg_e]^T with A_t e4m3 [M,TKp], B_t e4m3 [N,TKp]
  * and ISA scales for (M,TKp) / (N,TKp).  Replaces wgrad_gemm_varlen_k

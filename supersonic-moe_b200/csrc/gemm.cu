@@ -60,6 +60,7 @@ static int make_tmap(CUtensorMap* m, CUtensorMapDataType dt, int esize, const vo
 static int g_force_bn = 0;
 static int g_skip_store = 0;
 static int g_force_v1 = 0;
+static int g_force_gather4 = 0;     // A rows by index: TMA gather4 instead of the cp.async load warps
 static int g_stage_cut = 0;
 static int g_l2_prefetch = -1;     // -1: the kernel's default
 
@@ -114,12 +115,12 @@ struct OutMaps {
   CUtensorMap c, c2, c3;
 };
 
-template <int BN, int MODE>
+template <int BN, int MODE, bool CPG = false>
 static int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa, const CUtensorMap& tsb,
                    const OutMaps& om, const GemmParams& p, int64_t max_pair_tiles, cudaStream_t stream) {
-  using S = Gemm2Smem<BN, MODE>;
+  using S = Gemm2Smem<BN, MODE, CPG>;
   static bool attr_set[kMaxDevices] = {};
-  auto kern = gemm2_mxf8_kernel<BN, MODE>;
+  auto kern = gemm2_mxf8_kernel<BN, MODE, CPG>;
   if (!ensure_smem_attr(kern, S::TOTAL, attr_set)) return SMOE_ERR_LAUNCH;
   int64_t pairs = sm_count() / 2;
   if (max_pair_tiles < pairs) pairs = max_pair_tiles;
@@ -224,6 +225,18 @@ static int run2(const void* a, int64_t a_rows, int64_t a_cols, const void* b, in
   int64_t pair_tiles;
   if (MODE == WGRAD) pair_tiles = (int64_t)p.E * (p.rows / 256) * (p.N / bn);
   else pair_tiles = ((int64_t)p.rows / 256 + p.E) * ((p.N + bn - 1) / bn);
+  // indexed A rows: cp.async load warps (GATED / DGATED / DGATEDQ), unless the test knob asks for TMA gather4
+  constexpr bool CAN_CPG = (MODE == GATED || MODE == DGATED || MODE == DGATEDQ);
+  if (CAN_CPG && gather && !g_force_gather4) {
+    constexpr int MC = CAN_CPG ? MODE : GATED;
+    p.a_src = a;
+    if (bn == 256) {
+      constexpr int M256 = (MC == GATED) ? GATED : GATED;       // of the gather modes only GATED runs 256 columns
+      return launch2<256, M256, true>(ta, tb, tsa, tsb, om, p, pair_tiles, stream);
+    }
+    if (bn == 192) return launch2<192, MC, true>(ta, tb, tsa, tsb, om, p, pair_tiles, stream);
+    return launch2<128, MC, true>(ta, tb, tsa, tsb, om, p, pair_tiles, stream);
+  }
   if (bn == 256) {
     constexpr int M256 = (MODE == PLAIN || MODE == WGRAD || MODE == GATED) ? MODE : PLAIN;   // only the wide modes reach here
     return launch2<256, M256>(ta, tb, tsa, tsb, om, p, pair_tiles, stream);
@@ -309,6 +322,7 @@ int smoe_internal_gemm_knobs(int bn) {
   g_skip_store = ((bn >> 16) & 1) | (((bn >> 18) & 1) << 1);   // bit 16: no stores; bit 18: no epilogue (fused dgated)
   g_force_v1 = (bn >> 17) & 1;
   g_skip_store |= ((bn >> 19) & 0x1F) << 2;    // bits 19..23 -> timing-experiment bits 2..6 of GemmParams::debug_skip_store
+  g_force_gather4 = (bn >> 31) & 1;            // bit 31: indexed A rows through TMA gather4
   g_stage_cut = (bn >> 24) & 3;                // bits 24..25: ring stages to leave unused
   g_l2_prefetch = ((bn >> 26) & 0x1F) - 1;     // bits 26..30: L2 prefetch distance + 1 (0 = kernel default)
   return SMOE_OK;
@@ -360,21 +374,41 @@ int smoe_gemm_dgated(const void* dout_fp8, int64_t T, const int* a_idx, const vo
   return run<DGATED>(dout_fp8, T, K, w2t_fp8, E * N, K, p, (int)((rows / 128) * (N / 128)), (cudaStream_t)stream);
 }
 
-int smoe_gemm_dgated_fused(const void* dout_fp8, const void* a_sf, const void* w2t_fp8, const void* w2t_sf,
-                           const int* efo, const void* z_fp8, const void* z_scales, const float* s, void* dz_q,
-                           void* dz_row_sf, void* dz_col_sf, void* y1s_q, void* y1s_col_sf, float* ds_partial,
-                           int64_t rows, int64_t N, int64_t K, int64_t E, int* status, void* stream) {
+static int dgated_fused_impl(const void* dout_fp8, int64_t a_rows, const int* a_idx, const void* a_sf,
+                             const void* w2t_fp8, const void* w2t_sf, const int* efo, const void* z_fp8,
+                             const void* z_scales, const float* s, void* dz_q, void* dz_row_sf, void* dz_col_sf,
+                             void* y1s_q, void* y1s_col_sf, float* ds_partial, int64_t rows, int64_t N, int64_t K,
+                             int64_t E, int* status, void* stream) {
   if (rows < 0 || rows % 128 || N % 128 || K % 128 || E <= 0) return SMOE_ERR_SHAPE;
   if (rows == 0) return SMOE_OK;
   GemmParams p{};
   p.rows = (int)rows; p.N = (int)N; p.K = (int)K; p.E = (int)E;
-  p.efo = efo; p.a_idx = nullptr; p.sfa = (const uint8_t*)a_sf; p.sfb = (const uint8_t*)w2t_sf;
+  p.efo = efo; p.a_idx = a_idx; p.sfa = (const uint8_t*)a_sf; p.sfb = (const uint8_t*)w2t_sf;
   p.sfa_ktiles = (int)(K / 128); p.sfb_ktiles = (int)(K / 128);
   p.z_fp8 = (uint8_t*)const_cast<void*>(z_fp8); p.z_sc = (uint8_t*)const_cast<void*>(z_scales);
   p.s = s; p.dz = dz_q; p.y1s = y1s_q; p.ds_partial = ds_partial; p.status = status;
   p.dz_row_sf = (uint8_t*)dz_row_sf; p.dz_col_sf = (uint8_t*)dz_col_sf; p.y1s_col_sf = (uint8_t*)y1s_col_sf;
   p.debug_skip_store = g_skip_store;
-  return run<DGATEDQ>(dout_fp8, rows, K, w2t_fp8, E * N, K, p, (int)((rows / 128) * (N / 128)), (cudaStream_t)stream);
+  return run<DGATEDQ>(dout_fp8, a_rows, K, w2t_fp8, E * N, K, p, (int)((rows / 128) * (N / 128)),
+                      (cudaStream_t)stream);
+}
+
+int smoe_gemm_dgated_fused(const void* dout_fp8, const void* a_sf, const void* w2t_fp8, const void* w2t_sf,
+                           const int* efo, const void* z_fp8, const void* z_scales, const float* s, void* dz_q,
+                           void* dz_row_sf, void* dz_col_sf, void* y1s_q, void* y1s_col_sf, float* ds_partial,
+                           int64_t rows, int64_t N, int64_t K, int64_t E, int* status, void* stream) {
+  return dgated_fused_impl(dout_fp8, rows, nullptr, a_sf, w2t_fp8, w2t_sf, efo, z_fp8, z_scales, s, dz_q, dz_row_sf,
+                           dz_col_sf, y1s_q, y1s_col_sf, ds_partial, rows, N, K, E, status, stream);
+}
+
+int smoe_gemm_dgated_fused_gather(const void* dout_fp8, int64_t T, const int* a_idx, const void* a_sf,
+                                  const void* w2t_fp8, const void* w2t_sf, const int* efo, const void* z_fp8,
+                                  const void* z_scales, const float* s, void* dz_q, void* dz_row_sf, void* dz_col_sf,
+                                  void* y1s_q, void* y1s_col_sf, float* ds_partial, int64_t rows, int64_t N,
+                                  int64_t K, int64_t E, int* status, void* stream) {
+  if (rows > 0 && (T <= 0 || a_idx == nullptr)) return SMOE_ERR_ARG;
+  return dgated_fused_impl(dout_fp8, T, a_idx, a_sf, w2t_fp8, w2t_sf, efo, z_fp8, z_scales, s, dz_q, dz_row_sf,
+                           dz_col_sf, y1s_q, y1s_col_sf, ds_partial, rows, N, K, E, status, stream);
 }
 
 int64_t smoe_gemm_dgated_fused_partials(int64_t N) {

@@ -32,6 +32,7 @@ struct GemmParams {
   int E;
   const int* efo;   // [E+1] padded expert row offsets (device)
   const int* a_idx; // [TKp] row gather indices for A (GATED / DGATED), else null
+  const void* a_src; // the un-gathered A ([T, K] e4m3) the cp.async load warps read through a_idx
   const uint8_t* sfa;   // ISA-packed scales of A'
   const uint8_t* sfb;   // ISA-packed scales of B
   int sfa_ktiles;   // number of 128-wide K tiles in the SFA layout

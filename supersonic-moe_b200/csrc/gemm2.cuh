@@ -133,8 +133,12 @@ __device__ __forceinline__ float warp_max_abs(float x) {
   return r;
 }
 
-template <int BN, int MODE>
+// CPG: the rows of A are gathered by index inside the kernel with cp.async (four extra load warps per CTA) instead of
+// arriving as TMA tiles of a pre-gathered copy.
+template <int BN, int MODE, bool CPG = false>
 struct Gemm2Smem {
+  static constexpr int GATHER_WARPS = CPG ? 4 : 0;        // load warps; one more warp forwards "rows have landed"
+  static constexpr int EXTRA_WARPS = CPG ? GATHER_WARPS + 1 : 0;
   static constexpr int A_BYTES = BM * BK;                 // this CTA's 128 rows
   static constexpr int B_BYTES = (BN / 2) * BK;           // this CTA's half of the B tile
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -153,7 +157,7 @@ struct Gemm2Smem {
   // 192-column gated tiles measured slower than two: 646 vs 619 us up-projection, 412 vs 385 us fused dgated.)
   static constexpr int COL_GROUPS = 2;
   static constexpr int EPI_WARPS = 4 * COL_GROUPS;
-  static constexpr int THREADS = 32 * (2 + EPI_WARPS);
+  static constexpr int THREADS = 32 * (2 + EPI_WARPS + EXTRA_WARPS);
   static constexpr int EPI_BYTES = EPI_WARPS * EPI_BYTES_PER_WARP;
   static constexpr int AUX_BYTES = 512 + 2 * (kMaxExperts2 + 1) * 4 + 8;      // barriers etc. + expert offsets
   static constexpr int BUDGET = 227 * 1024 - 1024 - AUX_BYTES - EPI_BYTES;    // 1024: alignment slack
@@ -163,12 +167,14 @@ struct Gemm2Smem {
   static constexpr int SF_BYTES = SF_SLOTS * SF_SLOT_BYTES;
   static constexpr int TOTAL = STAGES * STAGE_BYTES + SF_BYTES + EPI_BYTES + AUX_BYTES + 1024;
   static_assert(TOTAL <= 227 * 1024, "shared memory budget");
-  static_assert((2 * STAGES + 4 + 2 * SF_SLOTS) * 8 <= 496, "barrier storage");
+  static_assert((3 * STAGES + 4 + 2 * SF_SLOTS) * 8 <= 496, "barrier storage");
   static constexpr int ACC_STAGES = (BN == 256) ? 1 : 2;  // TMEM: 512 columns
   static constexpr int SF_COLS = 4 + 4 * SFB_TILES;
   static constexpr int SF_COL0 = ACC_STAGES * BN;
   static_assert(SF_COL0 + STAGES * SF_COLS <= 512, "TMEM budget");
-  static constexpr uint32_t TX_BYTES = 2u * (A_BYTES + B_BYTES);        // both CTAs' A and B per stage
+  // bytes the TMA copies of one stage credit to the full barrier: both CTAs' B, and A unless the load warps bring it
+  static constexpr uint32_t TX_BYTES = 2u * ((CPG ? 0 : A_BYTES) + B_BYTES);
+  static constexpr uint32_t FULL_ARRIVALS = CPG ? 3 : 1;    // the producer's expect_tx (+ both CTAs' forwarders)
   static constexpr uint32_t SF_TX_BYTES = 2u * SF_SLOT_BYTES;            // both CTAs' scales per group
 };
 
@@ -214,14 +220,14 @@ __device__ __forceinline__ PairTile pair_tile(int tile, int rank, const GemmPara
   return t;
 }
 
-template <int BN, int MODE>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((Gemm2Smem<BN, MODE>::THREADS), 1)
+template <int BN, int MODE, bool CPG = false>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((Gemm2Smem<BN, MODE, CPG>::THREADS), 1)
 gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                   const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                   const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_c2,
                   const __grid_constant__ CUtensorMap tmap_c3, const GemmParams p) {
-  using S = Gemm2Smem<BN, MODE>;
-  const bool GATHER = p.a_idx != nullptr;   // rows of A fetched by index (TMA gather4) vs. a plain tile
+  using S = Gemm2Smem<BN, MODE, CPG>;
+  const bool GATHER = !CPG && p.a_idx != nullptr;   // rows of A fetched by index with TMA gather4 vs. a plain tile
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sfring = smem + S::STAGES * S::STAGE_BYTES;
@@ -244,6 +250,7 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   const uint32_t bar_tempty = bar_tfull + 8 * 2;
   const uint32_t bar_sffull = bar_tempty + 8 * 2;
   const uint32_t bar_sfempty = bar_sffull + 8 * S::SF_SLOTS;
+  const uint32_t bar_landed = bar_sfempty + 8 * S::SF_SLOTS;    // CPG: this CTA's gathered rows of a stage are in place
 
   for (int i = threadIdx.x; i <= p.E; i += blockDim.x) s_efo[i] = p.efo[i];
   __syncthreads();
@@ -255,8 +262,9 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     }
     s_pairs[p.E] = acc;
     for (int s = 0; s < S::STAGES; ++s) {
-      mbar_init(bar_full + 8 * s, 1);        // leader's: its own producer arms it; both CTAs' copies credit it
+      mbar_init(bar_full + 8 * s, S::FULL_ARRIVALS);   // leader's: its producer arms it, both CTAs' copies credit it
       mbar_init(bar_empty + 8 * s, 1);       // one commit arrival per use, in each CTA
+      if (CPG) mbar_init(bar_landed + 8 * s, 32 * S::GATHER_WARPS);   // one arrival per load thread
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_tfull + 8 * s, 1);                   // commit arrival, in each CTA
@@ -341,20 +349,20 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const uint32_t full = full0 + 8 * stage;
         const uint32_t a_dst = smem_base + stage * S::STAGE_BYTES;
         const uint32_t b_dst = a_dst + S::A_BYTES;
-        if (dbg_noload && dbg_filled >= nst) {
+        if (!CPG && dbg_noload && dbg_filled >= nst) {
           if (rank == 0 && elect_one()) mbar_arrive(bar_full + 8 * stage);
         } else {
           ++dbg_filled;
           if (elect_one()) {
             if (rank == 0) mbar_expect_tx(bar_full + 8 * stage, S::TX_BYTES);
             if (a_mn) tma_load_2d_pair(a_dst, &tmap_a, full, m0, kt * BK);
-            else if (!GATHER) tma_load_2d_pair(a_dst, &tmap_a, full, kt * BK, a_row);
+            else if (!GATHER && !CPG) tma_load_2d_pair(a_dst, &tmap_a, full, kt * BK, a_row);
             if (b_mn) tma_load_2d_pair(b_dst, &tmap_b, full, b_row, kt * BK);
             else tma_load_2d_pair(b_dst, &tmap_b, full, kt * BK, b_row);
             const int kp = kt + p.l2_prefetch;
             if (p.l2_prefetch > 0 && kp < kt0 + nkt) {
               if (a_mn) tma_prefetch_l2_2d(&tmap_a, m0, kp * BK);
-              else if (!GATHER) tma_prefetch_l2_2d(&tmap_a, kp * BK, a_row);
+              else if (!GATHER && !CPG) tma_prefetch_l2_2d(&tmap_a, kp * BK, a_row);
               if (b_mn) tma_prefetch_l2_2d(&tmap_b, b_row, kp * BK);
               else tma_prefetch_l2_2d(&tmap_b, kp * BK, b_row);
             }
@@ -446,6 +454,79 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       if (!ok && lane == 0) { *s_abort = 1; atomicCAS(p.status, 0, 202); }
     }
     __syncwarp();
+  } else if (CPG && warp >= 2 + S::EPI_WARPS && warp < 2 + S::EPI_WARPS + S::GATHER_WARPS) {
+    // ------------------------------------------------------------ A-row load warps (both CTAs)
+    // Four warps bring this CTA's 128 rows of A, row r of the tile = row a_idx[m0 + r] of the un-gathered e4m3
+    // activation, with 16-byte cp.async copies into the 128-byte-swizzled stage (chunk c of row r lands at chunk
+    // c ^ (r & 7)).  A warp instruction covers four rows x 128 bytes = four full cache lines.  A thread never waits
+    // for its copies: cp.async.mbarrier.arrive makes the stage's "landed" barrier count it once they are done, so
+    // the warps run ahead as far as the ring has free stages.
+    const int gw = warp - (2 + S::EPI_WARPS);           // rows [32 gw, 32 gw + 32) of the tile
+    const int sub = lane >> 3, ch = lane & 7;
+    const int n_total_u = __shfl_sync(0xffffffffu, n_total, 0);
+    const uint8_t* xq = reinterpret_cast<const uint8_t*>(p.a_src);
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = pair_id; tile < n_total_u && ok; tile += n_pairs_grid) {
+      const PairTile tl = pair_tile<BN, MODE>(tile, rank, p, s_efo, s_pairs);
+      const int nkt = __shfl_sync(0xffffffffu, tl.nkt, 0);
+      if (nkt == 0) continue;
+      const int valid = __shfl_sync(0xffffffffu, tl.valid, 0);
+      const int m0 = __shfl_sync(0xffffffffu, tl.m0, 0);
+      const uint8_t* src[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int r = gw * 32 + i * 4 + sub;
+        const int64_t row = valid ? (int64_t)p.a_idx[m0 + r] : 0;
+        src[i] = xq + row * p.K + ch * 16;
+      }
+      for (int kt = 0; kt < nkt; ++kt) {
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * stage, phase ^ 1));
+        if (!ok) break;
+        const uint32_t a_dst = smem_base + stage * S::STAGE_BYTES + gw * 32 * BK;
+        if (valid) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rr = i * 4 + sub;                   // row within this warp's 32; (gw * 32 + rr) & 7 == rr & 7
+            const uint32_t dst = a_dst + rr * BK + ((ch ^ (rr & 7)) << 4);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src[i] + (size_t)kt * BK)
+                         : "memory");
+          }
+        }
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar_landed + 8 * stage) : "memory");
+        if (++stage == nst) { stage = 0; phase ^= 1; }
+      }
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");      // nothing of this thread is in flight when the CTA exits
+    if (!ok && lane == 0) { *s_abort = 1; atomicCAS(p.status, 0, 204); }
+  } else if (CPG && warp == 2 + S::EPI_WARPS + S::GATHER_WARPS) {
+    // ------------------------------------------------------------ forwarder (both CTAs): when this CTA's rows of a
+    // stage have landed, make them visible to the async proxy (the MMA reads shared memory through it) and count
+    // this CTA in on the leader's full barrier of that stage
+    // Lane l serves ring stage l: the stages are forwarded independently of one another, so the wake-up, the proxy
+    // fence and the remote arrival of one stage overlap those of the others (a single thread walking the stages in
+    // order forwarded one K tile per ~0.8 us and throttled the whole kernel).
+    const uint32_t full0 = map_to_cta(bar_full, 0);
+    const int n_total_u = __shfl_sync(0xffffffffu, n_total, 0);
+    int total_kt = 0;                                     // K tiles this CTA pair will run
+    for (int tile = pair_id; tile < n_total_u; tile += n_pairs_grid) {
+      const PairTile tl = pair_tile<BN, MODE>(tile, rank, p, s_efo, s_pairs);
+      total_kt += __shfl_sync(0xffffffffu, tl.nkt, 0);
+    }
+    bool ok = true;
+    if (lane < nst) {
+      uint32_t ph = 0;
+      for (int n = lane; n < total_kt; n += nst) {
+        ok = mbar_wait(bar_landed + 8 * lane, ph);
+        if (!ok) break;
+        fence_proxy_async_smem();
+        mbar_arrive_cluster(full0 + 8 * lane);
+        ph ^= 1;
+      }
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok && lane == 0) { *s_abort = 1; atomicCAS(p.status, 0, 205); }
   } else {
     // ------------------------------------------------------------ epilogue (8 or 12 warps per CTA)
     const int q = warp & 3;                       // TMEM lane quadrant of this warp

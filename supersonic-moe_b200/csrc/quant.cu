@@ -383,109 +383,6 @@ quant_cols_kernel(const void* __restrict__ src_, const uint8_t* __restrict__ src
   }
 }
 
-// ------------------------------------------------------------------ columns, pipelined
-// The hot instance of the column quantizer - bf16 source rows gathered by idx, one scale per column and 32 rows,
-// e4m3 written transposed - as a persistent kernel that keeps the next tile's gathered loads (and the row indices
-// of the tile after that) in flight while the current tile is quantised and written: the one-tile-per-block
-// version above spends most of its time in the dependent idx -> row load chain.  Tiles are walked row tile
-// fastest, so that the blocks resident at any moment read the same 128-byte column slice of the source rows and
-// the K-fold re-read of a token (once per expert it is routed to) is served by L2.
-__global__ void __launch_bounds__(256)
-quant_cols_pipe_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ idx, int64_t rows, int dim,
-                       uint8_t* __restrict__ q_t, uint8_t* __restrict__ col_isa) {
-  __shared__ __nv_bfloat16 s_in[2][CT_ROWS][CT_PITCH];
-  __shared__ __align__(16) uint8_t s_out[CT_COLS][CT_ROWS + 16];
-  __shared__ __align__(4) uint8_t s_scb[CT_COLS][4];
-  const int tid = threadIdx.x;
-  const int64_t n_rt = rows / CT_ROWS;
-  const int64_t n_tiles = n_rt * (dim / CT_COLS);
-  const int rr = tid >> 3, cc = (tid & 7) * 8;          // load: 8 threads x 16 bytes cover one 64-column row
-  const int c = tid & 63, g = tid >> 6;                 // compute: column, 32-row group
-
-  auto rows_of = [&](int64_t t, int64_t (&srow)[4]) {
-    const int64_t r0 = (t % n_rt) * CT_ROWS;
-#pragma unroll
-    for (int pass = 0; pass < 4; ++pass) {
-      const int64_t r = r0 + pass * 32 + rr;
-      srow[pass] = idx ? (int64_t)idx[r] : r;
-    }
-  };
-  auto load = [&](int64_t t, const int64_t (&srow)[4], uint4 (&v)[4]) {
-    const int c0 = (int)(t / n_rt) * CT_COLS;
-#pragma unroll
-    for (int pass = 0; pass < 4; ++pass) v[pass] = *reinterpret_cast<const uint4*>(src + srow[pass] * dim + c0 + cc);
-  };
-  auto stash = [&](int buf, const uint4 (&v)[4]) {
-#pragma unroll
-    for (int pass = 0; pass < 4; ++pass) {
-      uint32_t* d = reinterpret_cast<uint32_t*>(&s_in[buf][pass * 32 + rr][cc]);
-      d[0] = v[pass].x; d[1] = v[pass].y; d[2] = v[pass].z; d[3] = v[pass].w;
-    }
-  };
-
-  int64_t t = blockIdx.x;
-  if (t >= n_tiles) return;
-  int64_t srow_next[4];
-  uint4 v_next[4];
-  rows_of(t, srow_next);
-  load(t, srow_next, v_next);
-  stash(0, v_next);
-  int64_t t1 = t + gridDim.x, t2 = t1 + gridDim.x;
-  if (t1 < n_tiles) {
-    rows_of(t1, srow_next);
-    load(t1, srow_next, v_next);
-  }
-  if (t2 < n_tiles) rows_of(t2, srow_next);
-  __syncthreads();
-  int buf = 0;
-  for (; t < n_tiles; t = t1, t1 = t2, t2 += gridDim.x) {
-    // ---- quantise tile t from s_in[buf]
-    float v[32];
-    float amax = 0.f;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      v[i] = __bfloat162float(s_in[buf][g * 32 + i][c]);
-      amax = fmaxf(amax, fabsf(v[i]));
-    }
-    const int e = q_e8m0_of(amax);
-    const float qs = q_scale_of(e);
-    uint32_t w[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) w[i] = q_pack4(v[4 * i] * qs, v[4 * i + 1] * qs, v[4 * i + 2] * qs, v[4 * i + 3] * qs);
-    uint4* so = reinterpret_cast<uint4*>(&s_out[c][g * 32]);
-    so[0] = make_uint4(w[0], w[1], w[2], w[3]);
-    so[1] = make_uint4(w[4], w[5], w[6], w[7]);
-    s_scb[c][g] = (uint8_t)e;
-    __syncthreads();
-    // ---- write tile t; the loads of tile t1 are still in flight
-    const int64_t r0 = (t % n_rt) * CT_ROWS;
-    const int c0 = (int)(t / n_rt) * CT_COLS;
-    {
-      const int oc = tid >> 3, seg = (tid & 7) * 16;
-#pragma unroll
-      for (int pass = 0; pass < 2; ++pass) {
-        const int col = pass * 32 + oc;
-        *reinterpret_cast<uint4*>(q_t + (size_t)(c0 + col) * rows + r0 + seg) =
-            *reinterpret_cast<const uint4*>(&s_out[col][seg]);
-      }
-    }
-    if (tid < CT_COLS) {
-      const size_t col = c0 + tid;
-      *reinterpret_cast<uint32_t*>(col_isa + isa_offset(col, (size_t)(r0 >> 5), (size_t)(rows >> 7))) =
-          *reinterpret_cast<const uint32_t*>(&s_scb[tid][0]);
-    }
-    // ---- tile t1 lands in the other buffer; tile t2's loads start
-    if (t1 < n_tiles) stash(buf ^ 1, v_next);
-    if (t2 < n_tiles) {
-      load(t2, srow_next, v_next);
-      const int64_t t3 = t2 + gridDim.x;
-      if (t3 < n_tiles) rows_of(t3, srow_next);
-    }
-    __syncthreads();
-    buf ^= 1;
-  }
-}
-
 }  // namespace smoe
 
 using namespace smoe;
@@ -635,14 +532,9 @@ int smoe_quant_cols_t(const void* src_bf16, const int32_t* idx, int64_t rows, in
                       void* stream) {
   if (rows < 0 || rows % 128 || dim <= 0 || dim % 64) return SMOE_ERR_SHAPE;
   if (rows == 0) return SMOE_OK;
-  if (((uintptr_t)src_bf16 & 15) || ((uintptr_t)q_t & 15)) return SMOE_ERR_ALIGN;
-  const int64_t tiles = (rows / CT_ROWS) * (dim / CT_COLS);
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int64_t grid = tiles < (int64_t)sms * 4 ? tiles : (int64_t)sms * 4;     // 4 resident blocks per SM (44 KB each)
-  quant_cols_pipe_kernel<<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)src_bf16, idx, rows, (int)dim, (uint8_t*)q_t, (uint8_t*)isa);
+  dim3 grid((unsigned)(rows / CT_ROWS), (unsigned)(dim / CT_COLS));
+  quant_cols_kernel<false, false><<<grid, 256, 0, (cudaStream_t)stream>>>(src_bf16, nullptr, idx, rows, (int)dim,
+                                                                          (uint8_t*)q_t, (uint8_t*)isa, nullptr, nullptr);
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }
 

@@ -80,11 +80,15 @@ def _require_fp8():
             "use_fp8=True / fp8=True, or activate SonicMoEConfig(use_fp8=True) (the BF16 GEMM path is out of scope)")
 
 
-# How the up-projection and GemmDGated read their gathered A rows:
-#   False  rows are gathered once into an expert-sorted e4m3 buffer and loaded as plain TMA tiles (default:
-#          one tiled copy per 16 KB; measured far faster than per-row fetches on B200)
-#   True   rows are fetched inside the GEMM with TMA gather4 (4 rows of 128 bytes per copy, no gathered buffer)
-USE_TMA_GATHER = os.getenv("SONIC_MOE_TMA_GATHER", "0") == "1"
+# How the up-projection and GemmDGated get their A rows (row p of the GEMM = activation row x_gather_idx[p]):
+#   "copy"     the row quantizer writes an expert-sorted e4m3 copy [TKp,H], loaded as plain TMA tiles
+#   "cpasync"  the activation is quantised once as [T,H]; four load warps per CTA fetch the rows by index inside the
+#              GEMM (no [TKp,H] copy is written or read); only the scales are gathered (1/32 of the bytes)
+# ("1" in SONIC_MOE_TMA_GATHER is the older spelling of in-kernel gathering)
+A_GATHER = os.getenv("SONIC_MOE_A_GATHER", "cpasync" if os.getenv("SONIC_MOE_TMA_GATHER", "0") == "1" else "copy")
+if A_GATHER not in ("copy", "cpasync"):
+    raise ValueError(f"SONIC_MOE_A_GATHER={A_GATHER!r}: expected 'copy' or 'cpasync'")
+USE_TMA_GATHER = A_GATHER == "cpasync"          # in-kernel gathering of A rows
 # GemmDGated emits the e4m3 operands of the three GEMMs that follow it (dgrad, dw1, dw2) straight from its
 # epilogue instead of bf16 dz / y1s plus separate quantizer passes (same bytes either way).
 FUSE_DGATED_QUANT = os.getenv("SONIC_MOE_FUSE_DGATED_QUANT", "1") == "1"
@@ -490,7 +494,15 @@ class _DownProjection(torch.autograd.Function):
         w2t_q, w2t_sf = weight_fp8(w2, True)
         if USE_TMA_GATHER and act == 0:
             a_sf = ops.gather_scales_isa(dout_raw, x_gather_idx, TKp, H)
-            dz, y1s, dsp = ops.gemm_dgated(dout_q, x_gather_idx, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, TKp)
+            if dout is not None and ctx.needs_input_grad[2] and _mn_wgrad_ok(E, I, H):
+                dout_c, dout_sf, dout_c_rows = _col_operand(dout, x_gather_idx, TKp, efo[-1:], E, I, H)
+            if FUSE_DGATED_QUANT and _mn_wgrad_ok(E, I, H):
+                dz_q, dz_rsf, dz_csf, y1s_q, y1s_sf, dsp = ops.gemm_dgated_fused(
+                    dout_q, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, TKp, a_idx=x_gather_idx)
+                link["dz"] = (dz_q, dz_rsf, None, dz_csf)
+                dz = y1s = None
+            else:
+                dz, y1s, dsp = ops.gemm_dgated(dout_q, x_gather_idx, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, TKp)
         else:
             if dout_q is not None:
                 dg_q, a_sf = ops.scatter_rows_fp8(dout_q, dout_raw, naept, s_rev, s_scatter_idx, TKp, efo[-1:])

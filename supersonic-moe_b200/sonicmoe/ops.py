@@ -386,11 +386,12 @@ def gemm_dgated(dout_q, a_idx, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, rows):
 
 
 @_timed
-def gemm_dgated_fused(dg_q, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, rows):
-    """GemmDGated with fused operand quantizers.  dg_q u8 [rows,H] (expert-sorted), w2t_q u8 [E,I,H] ->
+def gemm_dgated_fused(dg_q, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, rows, a_idx=None):
+    """GemmDGated with fused operand quantizers.  dg_q u8 [rows,H] (expert-sorted) - or, with a_idx, the un-gathered
+    [T,H] whose rows the kernel fetches by index - w2t_q u8 [E,I,H] ->
     (dz_q [rows,2I], dz ISA scales for (rows,2I), dz ISA scales for (2I,rows), y1s_q [rows,I], y1s ISA scales for
     (I,rows), ds_partial).  dz_q / y1s_q stay row-major; gemm_wgrad_mn takes them as they are."""
-    _cuda(dg_q, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s)
+    _cuda(dg_q, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, a_idx)
     K = dg_q.shape[1]
     E, N, _ = w2t_q.shape
     dev = dg_q.device
@@ -401,6 +402,12 @@ def gemm_dgated_fused(dg_q, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, rows):
     dz_csf = torch.empty(isa_bytes(2 * N, rows), dtype=_U8, device=dev)
     y1s_sf = torch.empty(isa_bytes(N, rows), dtype=_U8, device=dev)
     dsp = torch.zeros(parts, rows, dtype=torch.float32, device=dev)
+    if a_idx is not None:
+        check(lib.smoe_gemm_dgated_fused_gather(_p(dg_q), dg_q.shape[0], _p(a_idx), _p(a_sf), _p(w2t_q), _p(w2t_sf),
+                                                _p(efo), _p(z_q), _p(z_sc), _p(s), _p(dz_q), _p(dz_rsf), _p(dz_csf),
+                                                _p(y1s_q), _p(y1s_sf), _p(dsp), rows, N, K, E,
+                                                _p(status_word(dev)), _stream()), "gemm_dgated_fused_gather")
+        return dz_q, dz_rsf, dz_csf, y1s_q, y1s_sf, dsp
     check(lib.smoe_gemm_dgated_fused(_p(dg_q), _p(a_sf), _p(w2t_q), _p(w2t_sf), _p(efo), _p(z_q), _p(z_sc), _p(s),
                                      _p(dz_q), _p(dz_rsf), _p(dz_csf), _p(y1s_q), _p(y1s_sf), _p(dsp),
                                      rows, N, K, E, _p(status_word(dev)), _stream()), "gemm_dgated_fused")

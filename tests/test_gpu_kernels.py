@@ -376,14 +376,18 @@ def gated_inputs(T, H, I, tiles, seed):
 
 GATED_SHAPES = [(300, 256, 128, [1, 2, 0, 1]), (2000, 1024, 512, [5, 3, 9, 0, 0, 2, 1, 4]),
                 (1000, 512, 768, [3, 1, 2])]
-# A rows: "tma_gather" = fetched by index inside the GEMM (TMA gather4); "gathered" = expert-sorted copy, tiled TMA;
-# the "_1cta" variants run the single-CTA kernel
-GATHER_MODES = ["tma_gather", "gathered", "tma_gather_1cta", "gathered_1cta"]
+# A rows: "tma_gather" = fetched by index inside the GEMM (two-CTA kernel: cp.async load warps; with "4": TMA gather4;
+# single-CTA kernel: TMA gather4); "gathered" = expert-sorted copy, tiled TMA; the "_1cta" variants run the
+# single-CTA kernel
+GATHER_MODES = ["tma_gather", "tma_gather4", "gathered", "tma_gather_1cta", "gathered_1cta"]
 
 
 def _force(mode):
     from sonicmoe._lib import lib
-    lib.smoe_internal_gemm_knobs((1 << 17) if mode.endswith("_1cta") else 0)
+    bits = (1 << 17) if mode.endswith("_1cta") else 0
+    if mode == "tma_gather4":
+        bits |= -(1 << 31)            # bit 31 of a 32-bit int
+    lib.smoe_internal_gemm_knobs(bits)
 
 
 @pytest.mark.parametrize("T,H,I,tiles", GATED_SHAPES)
@@ -616,6 +620,21 @@ def test_gemm_dgated_fused_quantizers_match_separate_kernels(ops, T, H, I, tiles
     # ds partials are summed over column tiles of different widths in the two kernels: fp32 re-association only
     a, b = f_dsp.sum(0)[:n], dsp.sum(0)[:n]
     assert torch.equal(a, b) or torch.allclose(a, b, rtol=1e-5, atol=1e-5 * float(b.abs().max()))
+    # rows fetched by index inside the kernel (cp.async load warps) instead of the gathered copy: the same bits
+    lib.smoe_internal_gemm_knobs(bn)
+    try:
+        g_out = ops.gemm_dgated_fused(dq.to(DEV), *args, a_idx=a_idx.to(DEV))
+        torch.cuda.synchronize()
+        ops.check_status(DEV)
+    finally:
+        lib.smoe_internal_gemm_knobs(0)
+    for name, got, want in zip(("dz_q", "dz_rsf", "dz_csf", "y1s_q", "y1s_sf"), g_out[:5],
+                               (f_dzq, f_rsf, f_csf, f_yq, f_ysf)):
+        if got.ndim == 2:
+            assert torch.equal(got[:n], want[:n]), name
+    assert torch.equal(Q.unpack_isa(g_out[1].cpu(), rows, 2 * I)[:n], Q.unpack_isa(f_rsf.cpu(), rows, 2 * I)[:n])
+    assert torch.equal(Q.unpack_isa(g_out[4].cpu(), I, rows)[:, :n // 32], Q.unpack_isa(f_ysf.cpu(), I, rows)[:, :n // 32])
+    assert torch.equal(g_out[5].sum(0)[:n], f_dsp.sum(0)[:n])
 
 
 @pytest.mark.parametrize("T,K,E,world", [(333, 4, 16, 4), (1000, 8, 8, 8), (64, 2, 6, 2)])

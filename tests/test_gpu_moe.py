@@ -674,3 +674,41 @@ def test_other_gated_activations_match_oracles(sm, act):
         assert stats(gold["o"], sw)[1] > 0.05, "the test data must tell the activations apart"
     with pytest.raises(NotImplementedError):
         sm.run_sonic_moe(xd, idx.to(DEV), sd, K, E, w1d, w2d, fp8=True, activation_type=sm.ActivationType.SITU_GLU)
+
+
+def test_in_kernel_row_gather_writes_no_gathered_copy_and_gives_the_same_bits(sm):
+    """SONIC_MOE_A_GATHER=cpasync: x and dout are quantised once as [T,H] and the GEMMs fetch their rows by index
+    (four cp.async load warps per CTA) - no expert-sorted [TKp,H] copy is written or read - with results bit-identical
+    to the gathered-copy path."""
+    import sonicmoe.functional as Fn
+    T, H, I, E, K = 1024, 512, 256, 8, 4
+    x, dy, w1, w2, _, _ = make_layer(T, H, I, E, K, 111)
+    idx, scores = masked_routing(T, E, K, 6, 112)          # two experts remote: masked slots, pad rows
+    w1d, w2d = w1[:6].contiguous().to(DEV), w2[:6].contiguous().to(DEV)
+
+    def run(mode):
+        prev = (Fn.A_GATHER, Fn.USE_TMA_GATHER)
+        Fn.A_GATHER, Fn.USE_TMA_GATHER = mode, mode == "cpasync"
+        rec = []
+        sm.ops.set_recorder(rec)
+        try:
+            xd = x.to(DEV).requires_grad_(True)
+            sd = scores.to(DEV).requires_grad_(True)
+            a, b = w1d.detach().requires_grad_(True), w2d.detach().requires_grad_(True)
+            out = sm.run_sonic_moe(xd, idx.to(DEV), sd, K, 6, a, b, fp8=True)
+            out.backward(dy.to(DEV))
+            torch.cuda.synchronize()
+            sm.ops.check_status(DEV)
+        finally:
+            sm.ops.set_recorder(None)
+            Fn.A_GATHER, Fn.USE_TMA_GATHER = prev
+        return (out.detach(), xd.grad, sd.grad, a.grad, b.grad), [n for n, _, _ in rec]
+
+    base, ops_copy = run("copy")
+    got, ops_cp = run("cpasync")
+    assert "quant_rows_scatter" in ops_copy
+    assert not {"quant_rows_scatter", "gather_rows_fp8", "scatter_rows_fp8", "quant_rows_gather"} & set(ops_cp)
+    # x and dout are quantised once each as [T,H] (the other quant_rows calls are the weight copies of either mode)
+    assert ops_cp.count("quant_rows") == ops_copy.count("quant_rows") + 2 and ops_cp.count("gather_scales_isa") == 2
+    for name, a, b in zip(("out", "dx", "ds", "dw1", "dw2"), base, got):
+        assert torch.equal(a, b), name
