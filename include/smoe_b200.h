@@ -287,6 +287,12 @@ int smoe_gather_scores(const float* scores, const int32_t* s_scatter_idx, int64_
 int smoe_ds_finalize(const float* ds_partial, int64_t partials, int64_t rows, const int32_t* s_rev, int64_t TK,
                      const int32_t* real_tk, float* ds_tm, const int32_t* src_idx, float* scatter_out, void* stream);
 
+/* *pinned_host_word = *status, written by a one-thread kernel on `stream`: `status` is the device word the GEMM entry
+ * points report failures in, `pinned_host_word` page-locked host memory the device can address (cudaHostAlloc /
+ * torch pin_memory).  Lets a host poll for device-side failures without a synchronisation and without a memcpy that
+ * would queue behind bulk transfers.  No counterpart in the reference, whose kernels report nothing. */
+int smoe_status_post(const int32_t* status, int32_t* pinned_host_word, void* stream);
+
 /* top-K of each row of logits [T,E] (f32) and softmax over the K selected values.
  * Replaces _softmax_topk_fwd (sonicmoe/functional/forward.py:217-236, topk_softmax.py). */
 int smoe_topk_softmax(const float* logits, int64_t T, int64_t E, int64_t K, float* scores, int32_t* idx, void* stream);

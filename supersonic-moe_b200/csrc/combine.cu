@@ -149,6 +149,10 @@ topk_softmax_bwd_kernel(const float* __restrict__ scores, const int* __restrict_
   }
 }
 
+// One thread copies the device status word into pinned, device-visible host memory: a kernel store instead of a
+// device-to-host memcpy, so that it never queues behind large copies on a copy engine.
+__global__ void status_post_kernel(const int* __restrict__ status, volatile int* host_word) { *host_word = *status; }
+
 }  // namespace smoe
 
 using namespace smoe;
@@ -181,6 +185,12 @@ int smoe_ds_finalize(const float* ds_partial, int64_t partials, int64_t rows, co
   if (scatter_out && !src_idx) return SMOE_ERR_ARG;
   ds_finalize_kernel<<<(unsigned)((TK + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
       ds_partial, (int)partials, rows, s_rev, TK, real_tk, ds_tm, src_idx, scatter_out);
+  return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
+}
+
+int smoe_status_post(const int32_t* status, int32_t* pinned_host_word, void* stream) {
+  if (!status || !pinned_host_word) return SMOE_ERR_ARG;
+  status_post_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(status, pinned_host_word);
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }
 

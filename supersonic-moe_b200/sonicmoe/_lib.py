@@ -48,6 +48,7 @@ SIGNATURES = {
     "smoe_combine": (_I, [_P, _P, _P, _P, _P, _L, _L, _P]),
     "smoe_gather_scores": (_I, [_P, _P, _L, _P, _P]),
     "smoe_ds_finalize": (_I, [_P, _L, _L, _P, _L, _P, _P, _P, _P, _P]),
+    "smoe_status_post": (_I, [_P, _P, _P]),
     "smoe_topk_softmax": (_I, [_P, _L, _L, _L, _P, _P, _P]),
     "smoe_topk_softmax_bwd": (_I, [_P, _P, _P, _L, _L, _L, _P, _P]),
 }

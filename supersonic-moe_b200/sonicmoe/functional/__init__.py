@@ -152,13 +152,26 @@ def weight_fp8(w: torch.Tensor, transposed: bool):
     if hit is not None and hit[0] == ver and hit[3]() is base:
         return hit[1], hit[2]
     with torch.no_grad():
-        src = w.detach().transpose(1, 2) if transposed else w.detach()
-        src = src.contiguous()
+        src = w.detach()
         if src.dtype != torch.bfloat16:
             src = src.to(torch.bfloat16)
+        src = src.contiguous()
         E, N, K = src.shape
-        q, _, sf = ops.quant_rows(src.view(E * N, K), raw=False, isa=True)
-        q = q.view(E, N, K)
+        if transposed and N % 128 == 0 and K % 128 == 0:
+            # W^T quantised row-wise (1x32 along N) is W quantised column-wise (32 consecutive rows of W) with the
+            # bytes written transposed: the column quantizer reads W as it lies and no transposed bf16 copy is made
+            # (the reference reads each weight once for both orientations, blockscaled_fp8_gemm.py:4243-4315)
+            q = torch.empty(E, K, N, dtype=torch.uint8, device=src.device)
+            per = ops.isa_bytes(K, N)
+            sf = torch.empty(E * per, dtype=torch.uint8, device=src.device)
+            for e in range(E):
+                ops.quant_cols_t(src[e], None, N, out=(q[e], sf[e * per:(e + 1) * per]))
+        else:
+            if transposed:
+                src = src.transpose(1, 2).contiguous()
+                E, N, K = src.shape
+            q, _, sf = ops.quant_rows(src.view(E * N, K), raw=False, isa=True)
+            q = q.view(E, N, K)
     if len(_WEIGHT_CACHE) >= _WEIGHT_CACHE_MAX:
         _WEIGHT_CACHE.pop(next(iter(_WEIGHT_CACHE)))
     _WEIGHT_CACHE[key] = (ver, q, sf, weakref.ref(base))

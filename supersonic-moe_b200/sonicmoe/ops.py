@@ -90,37 +90,35 @@ def check_status(device):
         _raise_status(device, s)
 
 
-# The layer reads the status word without ever waiting for the GPU: the end of a forward / backward enqueues a
-# 4-byte copy of the word into pinned host memory plus an event; the next entry into the layer looks at the copies
-# whose event has completed and raises if one is non-zero.  A failure therefore surfaces one call late at the
-# latest, and a healthy run pays one tiny copy per pass and no synchronisation.
-_posted = {}     # device index -> [(pinned int32 tensor, event), ...] not yet looked at
+# The layer reads the status word without ever waiting for the GPU: the end of a forward / backward launches a
+# one-thread kernel that stores the word into pinned host memory (a kernel store, not a memcpy: it cannot queue behind
+# bulk transfers on a copy engine); the next entry into the layer looks at that host word and raises if it is
+# non-zero.  The word is sticky on the device, so a failure surfaces at the latest one call after the pass whose
+# post saw it, and a healthy run pays one tiny launch per pass and no synchronisation.
+_posted = {}     # device index -> pinned int32[1] mirror of the device status word
 
 
 def post_status(device):
-    """Enqueue, on the current stream, a copy of the status word to the host (no-op while a graph is captured)."""
+    """Enqueue, on the current stream, the store of the status word into its pinned host mirror (no-op while a graph
+    is captured)."""
     if torch.device(device).type != "cuda" or torch.cuda.is_current_stream_capturing():
         return
-    q = _posted.setdefault(_dev_index(device), [])
-    if len(q) >= 8:           # nobody polls (e.g. a forward-only loop through the raw Functions): keep the newest
-        del q[:-4]
-    host = torch.empty(1, dtype=_I32, pin_memory=True)
-    host.copy_(status_word(device), non_blocking=True)
-    ev = torch.cuda.Event()
-    ev.record()
-    q.append((host, ev))
+    key = _dev_index(device)
+    host = _posted.get(key)
+    if host is None:
+        host = _posted[key] = torch.zeros(1, dtype=_I32).pin_memory()
+    check(lib.smoe_status_post(_p(status_word(device)), host.data_ptr(), _stream()), "status_post")
 
 
 def poll_status(device):
-    """Look at the posted copies that have arrived; raise on a recorded failure.  Never waits."""
+    """Look at the host mirror of the status word; raise on a recorded failure.  Never waits."""
     if torch.device(device).type != "cuda":
         return
-    q = _posted.get(_dev_index(device))
-    while q and q[0][1].query():
-        host, _ = q.pop(0)
+    host = _posted.get(_dev_index(device))
+    if host is not None:
         code = int(host[0])
         if code != 0:
-            q.clear()
+            host[0] = 0
             _raise_status(device, code)
 
 
@@ -297,13 +295,19 @@ def scatter_rows_fp8(q, raw, naept, s_rev, s_scatter_idx, rows, valid_rows=None)
 
 
 @_timed
-def quant_cols_t(src, idx, rows):
-    """bf16 [T,dim] (rows gathered by idx, or None) -> (e4m3 bytes [dim, rows], ISA scales for (dim, rows))."""
+def quant_cols_t(src, idx, rows, out=None):
+    """bf16 [T,dim] (rows gathered by idx, or None) -> (e4m3 bytes [dim, rows], ISA scales for (dim, rows)); `out` =
+    (q_t, isa) places the results in caller-owned buffers (slices of a stacked tensor)."""
     _cuda(src, idx)
     assert src.dtype == torch.bfloat16
     dim = src.shape[1]
-    q_t = torch.empty(dim, rows, dtype=_U8, device=src.device)
-    isa = torch.empty(isa_bytes(dim, rows), dtype=_U8, device=src.device)
+    if out is not None:
+        q_t, isa = out
+        _cuda(q_t, isa)
+        assert q_t.dtype == _U8 and tuple(q_t.shape) == (dim, rows) and isa.numel() == isa_bytes(dim, rows)
+    else:
+        q_t = torch.empty(dim, rows, dtype=_U8, device=src.device)
+        isa = torch.empty(isa_bytes(dim, rows), dtype=_U8, device=src.device)
     check(lib.smoe_quant_cols_t(_p(src), _p(idx), rows, dim, _p(q_t), _p(isa), _stream()), "quant_cols_t")
     return q_t, isa
 

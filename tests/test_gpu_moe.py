@@ -14,6 +14,7 @@ import pytest
 import torch
 
 from oracle import moe as OM
+from oracle import quant as Q
 from oracle import routing as R
 
 pytestmark = pytest.mark.gpu
@@ -712,3 +713,23 @@ def test_in_kernel_row_gather_writes_no_gathered_copy_and_gives_the_same_bits(sm
     assert ops_cp.count("quant_rows") == ops_copy.count("quant_rows") + 2 and ops_cp.count("gather_scales_isa") == 2
     for name, a, b in zip(("out", "dx", "ds", "dw1", "dw2"), base, got):
         assert torch.equal(a, b), name
+
+
+def test_transposed_weight_copy_without_a_transposed_bf16_tensor(sm):
+    """`weight_fp8(w, transposed=True)` quantises W^T row-wise by running the column quantizer over W as it lies:
+    same bytes and scale bytes as transposing first and quantising rows."""
+    from sonicmoe.functional import clear_weight_cache, weight_fp8
+    g = torch.Generator().manual_seed(121)
+    for E, N, K in ((4, 256, 128), (3, 384, 256), (2, 128, 384)):
+        w = (torch.randn(E, N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+        clear_weight_cache()
+        q, sf = weight_fp8(w, True)
+        wt = w.transpose(1, 2).contiguous()
+        rq, _, rsf = sm.ops.quant_rows(wt.view(E * K, N), raw=False, isa=True)
+        assert tuple(q.shape) == (E, K, N) and torch.equal(q.view(E * K, N), rq)
+        got = torch.stack([Q.unpack_isa(sf.cpu()[e * sm.ops.isa_bytes(K, N):(e + 1) * sm.ops.isa_bytes(K, N)], K, N)
+                           for e in range(E)])
+        assert torch.equal(sf, rsf)                      # per-expert ISA blocks concatenated = the (E*K, N) layout
+        assert torch.equal(got, Q.unpack_isa(rsf.cpu(), E * K, N).view(E, K, N // 32))
+        oq, osc = Q.row_quant(wt.view(E * K, N).float().cpu())
+        assert torch.equal(q.view(E * K, N).cpu(), oq) and torch.equal(got.view(E * K, N // 32), osc)
