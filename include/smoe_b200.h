@@ -155,7 +155,8 @@ int smoe_gather_rows_fp8(const void* q, const void* raw_scales, const int32_t* i
 
 /* Same result in scatter form (pad rows zero instead of a copy of row idx[r]): every source row is read once and
  * written to its positions s_rev[naept[t] .. naept[t+1]); used for the e4m3 payload an expert-parallel dispatch
- * delivers, where a received row feeds several local experts. */
+ * delivers, where a received row feeds several local experts.  isa_out (and then raw_scales) may be null: payload
+ * only, for a caller that already holds the packed scales (deepep_topk_to_sonic_metadata_with_scales). */
 int smoe_scatter_rows_fp8(const void* q, const void* raw_scales, int64_t T, int64_t K, const int32_t* naept,
                           const int32_t* s_rev, const int32_t* s_scatter_idx, const int32_t* valid_rows, int64_t rows,
                           void* q_out, void* isa_out, void* stream);
@@ -179,6 +180,15 @@ int smoe_requant_cols_t(const void* src_fp8, const void* src_scales, const int32
  * (sonicmoe/quack_utils/blockscaled_fp8_gemm.py:2052-2198).  rows % 128 == 0, cols % 128 == 0. */
 int smoe_quant_iso32(const void* x_bf16, int64_t rows, int64_t cols, void* q, void* row_isa, void* q_t, void* col_isa,
                      void* stream);
+/* q_t may be null: the row-major payload then serves both orientations (with 32x32-block scales the transposed
+ * bytes are the transposed quantisation), which is the reference's single-buffer ISO32 weight cache
+ * (sonicmoe/quack_utils/blockscaled_fp8_gemm.py:3765-3856): a weight [N,K] is kept once, K-major for the forward
+ * GEMM (row_isa) and read MN-major by smoe_gemm_varlen_m_bt for the activation gradient (col_isa). */
+
+/* dst[b][c][r] = src[b][r][c] over a batch of [rows, cols] byte matrices (rows, cols multiples of 64, batch <=
+ * 65535).  Makes the transient K-major copy of an ISO32 weight for a GEMM that cannot read it MN-major (the
+ * reference does the same for w2 in its backward, sonicmoe/functional/__init__.py:2160). */
+int smoe_transpose_u8(const void* src, int64_t batch, int64_t rows, int64_t cols, void* dst, void* stream);
 
 /* ---- grouped GEMMs (tcgen05 block-scaled) --------------------------------- */
 
@@ -188,6 +198,14 @@ int smoe_quant_iso32(const void* x_bf16, int64_t rows, int64_t cols, void* q, vo
  * (sonicmoe/quack_utils/sm100_funcs.py:784-807, blockscaled_fp8_gemm.py:4563-4748). */
 int smoe_gemm_varlen_m(const void* a_fp8, const void* a_sf, const void* b_fp8, const void* b_sf, const int32_t* efo,
                        void* c_bf16, int64_t rows, int64_t N, int64_t K, int64_t E, int32_t* status, void* stream);
+
+/* The same product with B stored [E,K,N] (N contiguous, "MN-major"): B[e] is read as it lies in a weight kept once
+ * for both orientations; b_sf = ISA scales for (E*N, K) as above.  Replaces the zero-copy `.permute(0,2,1)` view the
+ * reference hands its GEMM in ISO32 mode (sonicmoe/quack_utils/blockscaled_fp8_gemm.py:3822-3840).  256-column
+ * two-CTA tiles only: N % 256 == 0, E <= 256, else SMOE_ERR_SHAPE. */
+int smoe_gemm_varlen_m_bt(const void* a_fp8, const void* a_sf, const void* b_kn_fp8, const void* b_sf,
+                          const int32_t* efo, void* c_bf16, int64_t rows, int64_t N, int64_t K, int64_t E,
+                          int32_t* status, void* stream);
 
 /* Up-projection: z = x[a_idx] . W1[e]^T (N = 2I, K = H), y1 = swiglu(z) on interleaved gate/up columns;
  * z -> e4m3 [rows,N] + raw scales [rows,N/32] (amax floor 1e-4), y1 -> bf16 RNE -> e4m3 [rows,N/2] + ISA scales.

@@ -174,10 +174,23 @@ def moe_fp32(x, w1, w2, md: dict, dy=None, act: str = "swiglu"):
 # ----------------------------------------------------------------------------
 # FP8 frontier dataflow, emulated
 # ----------------------------------------------------------------------------
-def quantize_weights(w1, w2):
+def quantize_weights(w1, w2, iso32: bool = False):
     """Four row-wise 1x32 layouts (blockscaled_fp8_gemm.py:4363-4406):
     W1 (E,2I,H) scales along H; W1T (E,H,2I) along 2I; W2 (E,H,I) along I;
-    W2T (E,I,H) along H.  Returns dict name -> (bytes, raw scales), flattened over E."""
+    W2T (E,I,H) along H.  Returns dict name -> (bytes, raw scales), flattened over E.
+    `iso32`: one scale per 32x32 block and ONE payload per weight, its transpose being the byte transpose
+    (blockscaled_fp8_gemm.py:3765-3856); expressed here in the same (bytes, 1x32 raw scales) form."""
+    if iso32:
+        def iq(w):
+            E, N, K = w.shape
+            q, s = Q.iso32_quant(w.reshape(E * N, K))                    # s: [E*N/32, K/32]
+            q, s = q.reshape(E, N, K), s.reshape(E, N // 32, K // 32)
+            rows = s.repeat_interleave(32, dim=1)                        # [E, N, K/32]
+            cols = s.transpose(1, 2).repeat_interleave(32, dim=1)        # [E, K, N/32]
+            return (q, rows.contiguous()), (q.transpose(1, 2).contiguous(), cols.contiguous())
+        (a, at), (b, bt) = iq(w1), iq(w2)
+        return dict(w1=a, w1t=at, w2=b, w2t=bt)
+
     def rq(w):
         E, N, K = w.shape
         q, s = Q.row_quant(w.reshape(E * N, K))
@@ -192,7 +205,8 @@ def _deq_w(qs):
     return Q.dequant_rows(q.reshape(E * N, K), s.reshape(E * N, K // 32)).reshape(E, N, K)
 
 
-def moe_fp8_emulated(x, w1, w2, md: dict, dy=None, y1_bf16_rne: bool = True, act: str = "swiglu"):
+def moe_fp8_emulated(x, w1, w2, md: dict, dy=None, y1_bf16_rne: bool = True, act: str = "swiglu",
+                     iso32_weight: bool = False):
     """x, dy bf16 [N,H]; w1 [E,2I,H], w2 [E,H,I] bf16.  All outputs of the FP8 path
     plus every quantised intermediate (bytes and scale bytes)."""
     N, H = x.shape
@@ -201,7 +215,7 @@ def moe_fp8_emulated(x, w1, w2, md: dict, dy=None, y1_bf16_rne: bool = True, act
     efo, xg = md["efo"], md["x_gather_idx"].long()
     TKp = xg.shape[0]
     s = md["topk_scores"][md["s_scatter_idx"].long()]
-    wq = quantize_weights(w1, w2)
+    wq = quantize_weights(w1, w2, iso32_weight)
     W1, W1T, W2, W2T = (_deq_w(wq[k]) for k in ("w1", "w1t", "w2", "w2t"))
     r = dict(wq=wq)
 

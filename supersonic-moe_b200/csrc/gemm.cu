@@ -154,6 +154,7 @@ static bool use_gemm3(const GemmParams& p) {
   if (g_force_v1 || (g_force_bn != 0 && g_force_bn != kBN3)) return false;
   if (p.N % kBN3 != 0 || p.E > kMaxExperts2) return false;
   if (MODE == WGRAD && (p.rows % 256 != 0 || p.b_mn)) return false;
+  if (MODE == PLAIN && p.b_mn) return false;      // a 192-byte MN-major slice is not a swizzle atom
   return true;
 }
 
@@ -258,8 +259,10 @@ static int run(const void* a, int64_t a_rows, int64_t a_cols, const void* b, int
       int rc = SMOE_OK;
       const int64_t sfa_tiles = (MODE == WGRAD) ? (int64_t)(p.rows / 128) * p.sfa_ktiles
                                                 : (int64_t)(p.rows / 128) * p.sfa_ktiles;
-      const int64_t sfb_tiles = (MODE == WGRAD) ? (int64_t)(p.N / 128) * p.sfb_ktiles : (b_rows / 128) * p.sfb_ktiles;
-      if (MODE == WGRAD && (p.a_mn || p.b_mn) && bn2 != 256) return SMOE_ERR_SHAPE;
+      const int64_t sfb_tiles = (MODE == WGRAD) ? (int64_t)(p.N / 128) * p.sfb_ktiles
+                                : (MODE == PLAIN && p.b_mn) ? ((int64_t)p.E * p.N / 128) * p.sfb_ktiles
+                                                            : (b_rows / 128) * p.sfb_ktiles;
+      if ((MODE == WGRAD || MODE == PLAIN) && (p.a_mn || p.b_mn) && bn2 != 256) return SMOE_ERR_SHAPE;
       if (MODE == PLAIN) {
         rc = make_tmap(&om.c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.c, p.rows, p.N, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B);
         om.c2 = om.c;
@@ -290,7 +293,7 @@ static int run(const void* a, int64_t a_rows, int64_t a_cols, const void* b, int
     }
   }
   if (MODE == DGATEDQ) return SMOE_ERR_SHAPE;     // fused-quantizer epilogue exists in the two-CTA kernel only
-  if (MODE == WGRAD && (p.a_mn || p.b_mn)) return SMOE_ERR_SHAPE;   // so do MN-major operands
+  if ((MODE == WGRAD || MODE == PLAIN) && (p.a_mn || p.b_mn)) return SMOE_ERR_SHAPE;   // so do MN-major operands
   constexpr int M1 = (MODE == DGATEDQ) ? DGATED : MODE;
   const int bn = pick_bn(p.N);
   CUtensorMap ta, tb;
@@ -338,6 +341,19 @@ int smoe_gemm_varlen_m(const void* a_fp8, const void* a_sf, const void* b_fp8, c
   p.sfa_ktiles = (int)(K / 128); p.sfb_ktiles = (int)(K / 128);
   p.c = c_bf16; p.status = status; p.debug_skip_store = g_skip_store;
   return run<PLAIN>(a_fp8, rows, K, b_fp8, E * N, K, p, (int)((rows / 128) * (N / 128)), (cudaStream_t)stream);
+}
+
+int smoe_gemm_varlen_m_bt(const void* a_fp8, const void* a_sf, const void* b_kn_fp8, const void* b_sf, const int* efo,
+                          void* c_bf16, int64_t rows, int64_t N, int64_t K, int64_t E, int* status, void* stream) {
+  if (rows < 0 || rows % 128 || N % 256 || K % 128 || E <= 0 || E > kMaxExperts2) return SMOE_ERR_SHAPE;
+  if (rows == 0) return SMOE_OK;
+  GemmParams p{};
+  p.rows = (int)rows; p.N = (int)N; p.K = (int)K; p.E = (int)E;
+  p.efo = efo; p.sfa = (const uint8_t*)a_sf; p.sfb = (const uint8_t*)b_sf;
+  p.sfa_ktiles = (int)(K / 128); p.sfb_ktiles = (int)(K / 128);
+  p.c = c_bf16; p.status = status; p.debug_skip_store = g_skip_store;
+  p.b_mn = 1;                                      // B of expert e = rows [e*K, (e+1)*K) of an [E*K, N] matrix
+  return run<PLAIN>(a_fp8, rows, K, b_kn_fp8, E * K, N, p, (int)((rows / 128) * (N / 128)), (cudaStream_t)stream);
 }
 
 int smoe_gemm_gated(const void* x_fp8, int64_t T, const int* a_idx, const void* a_sf, const void* w1_fp8,

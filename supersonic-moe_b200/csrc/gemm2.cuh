@@ -303,7 +303,8 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     const uint32_t full0 = map_to_cta(bar_full, 0);      // the leader's full barriers
     const uint32_t sffull0 = map_to_cta(bar_sffull, 0);
     const int n_total_u = __shfl_sync(0xffffffffu, n_total, 0);
-    const bool a_mn = MODE == WGRAD && p.a_mn, b_mn = MODE == WGRAD && p.b_mn;
+    // MN-major operands: both of a weight gradient, or the B of a PLAIN product whose weights lie [E, K, N]
+    const bool a_mn = MODE == WGRAD && p.a_mn, b_mn = (MODE == WGRAD || MODE == PLAIN) && p.b_mn;
     int stage = 0, sfs = 0;
     uint32_t phase = 0, sfphase = 0;
     bool ok = true;
@@ -321,7 +322,9 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       int4 rows4 = make_int4(0, 0, 0, 0);
       if (GATHER && valid) rows4 = *reinterpret_cast<const int4*>(p.a_idx + m0 + 4 * lane);
       const int b_base = (MODE == WGRAD) ? n0 : te * p.N + n0;
-      const int b_row = b_base + rank * (BN / 2);
+      const bool b_mn_plain = MODE == PLAIN && b_mn;       // B of expert te = rows [te*K, (te+1)*K) of an [E*K, N] matrix
+      const int b_row = (b_mn_plain ? n0 : b_base) + rank * (BN / 2);
+      const int b_k0 = b_mn_plain ? te * p.K : 0;
       // rows of the A-scale tensor are 512-byte tiles: (row tile, k tile)
       const int sfa_tile = valid ? m0 / 128 : 0;         // phantom half: any in-range tile will do
       const int sfb_tile = b_base / 128;                 // first 128-row scale tile touching the BN window
@@ -357,13 +360,13 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             if (rank == 0) mbar_expect_tx(bar_full + 8 * stage, S::TX_BYTES);
             if (a_mn) tma_load_2d_pair(a_dst, &tmap_a, full, m0, kt * BK);
             else if (!GATHER && !CPG) tma_load_2d_pair(a_dst, &tmap_a, full, kt * BK, a_row);
-            if (b_mn) tma_load_2d_pair(b_dst, &tmap_b, full, b_row, kt * BK);
+            if (b_mn) tma_load_2d_pair(b_dst, &tmap_b, full, b_row, b_k0 + kt * BK);
             else tma_load_2d_pair(b_dst, &tmap_b, full, kt * BK, b_row);
             const int kp = kt + p.l2_prefetch;
             if (p.l2_prefetch > 0 && kp < kt0 + nkt) {
               if (a_mn) tma_prefetch_l2_2d(&tmap_a, m0, kp * BK);
               else if (!GATHER && !CPG) tma_prefetch_l2_2d(&tmap_a, kp * BK, a_row);
-              if (b_mn) tma_prefetch_l2_2d(&tmap_b, b_row, kp * BK);
+              if (b_mn) tma_prefetch_l2_2d(&tmap_b, b_row, b_k0 + kp * BK);
               else tma_prefetch_l2_2d(&tmap_b, kp * BK, b_row);
             }
           }
@@ -385,7 +388,7 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     // the accumulator drain - bounded the kernel (900-1000 clocks per K tile where the MMAs need 512).
     if (rank == 0) {
       // WGRAD may take either operand MN-major: [K rows, M or N bytes] tiles instead of [M or N rows, K bytes]
-      const bool a_mn = MODE == WGRAD && p.a_mn, b_mn = MODE == WGRAD && p.b_mn;
+      const bool a_mn = MODE == WGRAD && p.a_mn, b_mn = (MODE == WGRAD || MODE == PLAIN) && p.b_mn;
       const uint32_t idesc = make_idesc_mxf8(2 * BM, BN) | (a_mn ? 1u << 15 : 0u) | (b_mn ? 1u << 16 : 0u);
       const uint32_t idesc_kb[4] = {idesc_with_sf_ids(idesc, 0, 0), idesc_with_sf_ids(idesc, 1, 1),
                                     idesc_with_sf_ids(idesc, 2, 2), idesc_with_sf_ids(idesc, 3, 3)};

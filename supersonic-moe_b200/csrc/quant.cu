@@ -242,6 +242,7 @@ scatter_rows_fp8_kernel(const uint4* __restrict__ q, const uint8_t* __restrict__
         }
       }
     }
+    if (isa == nullptr) return;                          // payload only: the caller already holds the packed scales
     for (int kt = lane; kt < k_tiles; kt += 32) {
       const uint32_t word = *reinterpret_cast<const uint32_t*>(raw + t * groups + kt * 4);
       for (int j = beg; j < end; ++j)
@@ -255,10 +256,31 @@ scatter_rows_fp8_kernel(const uint4* __restrict__ q, const uint8_t* __restrict__
     for (int64_t row = w0; row < m_end; row += nwarps) {
       if (s_scatter[row] < real_tk) continue;
       for (int c = lane; c < k16; c += 32) out[row * k16 + c] = make_uint4(0, 0, 0, 0);
+      if (isa == nullptr) continue;
       for (int kt = lane; kt < k_tiles; kt += 32)
         *reinterpret_cast<uint32_t*>(isa + isa_offset(row, (size_t)kt * 4, k_tiles)) = 0u;
     }
   }
+}
+
+// ------------------------------------------------------------------ byte transpose
+// dst[b][c][r] = src[b][r][c] for a batch of [rows, cols] byte matrices, 64 x 64 tiles through shared memory.  With
+// one scale per 32x32 block the transposed bytes of an e4m3 matrix ARE its transposed quantisation.
+__global__ void __launch_bounds__(256)
+transpose_u8_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int rows, int cols) {
+  __shared__ __align__(16) uint8_t s[64][64 + 16];
+  const size_t base = (size_t)blockIdx.z * rows * cols;
+  const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+  const int tr = threadIdx.x >> 2, seg = (threadIdx.x & 3) * 16;
+  *reinterpret_cast<uint4*>(&s[tr][seg]) =
+      *reinterpret_cast<const uint4*>(src + base + (size_t)(r0 + tr) * cols + c0 + seg);
+  __syncthreads();
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    w[i] = (uint32_t)s[seg + 4 * i][tr] | ((uint32_t)s[seg + 4 * i + 1][tr] << 8) |
+           ((uint32_t)s[seg + 4 * i + 2][tr] << 16) | ((uint32_t)s[seg + 4 * i + 3][tr] << 24);
+  *reinterpret_cast<uint4*>(dst + base + (size_t)(c0 + tr) * rows + r0 + seg) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
 // ------------------------------------------------------------------ columns
@@ -342,8 +364,9 @@ quant_cols_kernel(const void* __restrict__ src_, const uint8_t* __restrict__ src
   atomicOr(&s_sc[c], (uint32_t)e << (8 * g));   // distinct bits per thread: order-free
   __syncthreads();
 
-  // transposed bytes: 8 threads x 16 bytes cover one 128-byte row of s_out
-  {
+  // transposed bytes: 8 threads x 16 bytes cover one 128-byte row of s_out (skipped when the caller of the 32x32
+  // form wants the row-major payload only)
+  if (!ISO || q_t != nullptr) {
     const int cc = tid >> 3, seg = (tid & 7) * 16;
 #pragma unroll
     for (int pass = 0; pass < 2; ++pass) {
@@ -560,6 +583,17 @@ int smoe_quant_iso32(const void* x_bf16, int64_t rows, int64_t cols, void* q, vo
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }
 
+int smoe_transpose_u8(const void* src, int64_t batch, int64_t rows, int64_t cols, void* dst, void* stream) {
+  if (batch < 0 || rows < 0 || cols < 0 || rows % 64 || cols % 64 || batch > 65535) return SMOE_ERR_SHAPE;
+  if (batch == 0 || rows == 0 || cols == 0) return SMOE_OK;
+  if (!src || !dst) return SMOE_ERR_ARG;
+  if (((uintptr_t)src & 15) || ((uintptr_t)dst & 15)) return SMOE_ERR_ALIGN;
+  dim3 grid((unsigned)(cols / 64), (unsigned)(rows / 64), (unsigned)batch);
+  if (grid.y > 65535) return SMOE_ERR_SHAPE;
+  transpose_u8_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const uint8_t*)src, (uint8_t*)dst, (int)rows, (int)cols);
+  return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
+}
+
 int smoe_quant_dual_gather(const void* x_bf16, const int32_t* idx, const int32_t* valid_rows, int64_t rows, int64_t K,
                            void* q_row, void* row_isa, void* q_col, void* col_isa, void* stream) {
   if (rows < 0 || rows % 128 || K <= 0 || K % 256) return SMOE_ERR_SHAPE;
@@ -583,6 +617,7 @@ int smoe_scatter_rows_fp8(const void* q, const void* raw_scales, int64_t T, int6
   if (T < 0 || rows < 0 || K <= 0 || K % 128) return SMOE_ERR_SHAPE;
   if (rows == 0) return SMOE_OK;      // nothing routed: not an error, and the (empty) buffers may be null
   if (((uintptr_t)q & 15) || ((uintptr_t)q_out & 15) || ((uintptr_t)raw_scales & 3)) return SMOE_ERR_ALIGN;
+  if (isa_out != nullptr && raw_scales == nullptr) return SMOE_ERR_ARG;
   const int token_blocks = (int)((T + 7) / 8);
   const int pad_blocks = 148;
   scatter_rows_fp8_kernel<<<(unsigned)(token_blocks + pad_blocks), 256, 0, (cudaStream_t)stream>>>(

@@ -35,6 +35,8 @@ SIGNATURES = {
     "smoe_requant_cols_t": (_I, [_P, _P, _P, _L, _L, _P, _P, _P]),
     "smoe_quant_iso32": (_I, [_P, _L, _L, _P, _P, _P, _P, _P]),
     "smoe_gemm_varlen_m": (_I, [_P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P, _P]),
+    "smoe_gemm_varlen_m_bt": (_I, [_P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P, _P]),
+    "smoe_transpose_u8": (_I, [_P, _L, _L, _L, _P, _P]),
     "smoe_gemm_gated": (_I, [_P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P, _P]),
     "smoe_gemm_dgated": (_I, [_P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P, _P]),
     "smoe_gemm_dgated_partials": (_L, [_L]),

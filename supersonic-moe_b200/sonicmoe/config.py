@@ -4,12 +4,17 @@ frontier path - so the flags that selected other backends are accepted and
 recorded but do not switch code paths."""
 from __future__ import annotations
 
+import os
 import threading
 from contextlib import contextmanager
 from dataclasses import dataclass
 from typing import Optional
 
 _tls = threading.local()
+
+
+def _env_bool(name: str) -> bool:
+    return os.getenv(name, "").strip().lower() in ("1", "true", "yes", "on")
 
 
 def get_active_config() -> Optional["SonicMoEConfig"]:
@@ -51,6 +56,21 @@ class SonicMoEConfig:
         (sonicmoe/config.py:154-170, functional/__init__.py:884-903,2047-2053 of the reference): trades one extra
         up-projection per step for TKp x 2I bytes (+ scales) of saved activations per layer."""
         return bool(self.recompute_z)
+
+    def resolve_iso32_weight(self) -> bool:
+        """One FP8 buffer per weight, quantised with one scale per 32x32 block and read in both orientations,
+        instead of two 1x32 copies (sonicmoe/config.py:208-211; env SONIC_MOE_FP8_ISO32_WEIGHT, default off)."""
+        if self.iso32_weight is not None:
+            return bool(self.iso32_weight)
+        return _env_bool("SONIC_MOE_FP8_ISO32_WEIGHT")
+
+    def resolve_stagewise_memory(self) -> bool:
+        """Memory-lean ordering of the backward (every operand is produced right before its one consumer and freed
+        right after) plus a per-stage record of allocated / peak bytes (sonicmoe/config.py:203-206; env
+        SONIC_MOE_STAGEWISE_MEMORY, default off)."""
+        if self.stagewise_memory is not None:
+            return bool(self.stagewise_memory)
+        return _env_bool("SONIC_MOE_STAGEWISE_MEMORY")
 
     @contextmanager
     def activate(self):

@@ -178,11 +178,109 @@ def weight_fp8(w: torch.Tensor, transposed: bool):
     return q, sf
 
 
-def precompute_weight_fp8(w1: torch.Tensor, w2: torch.Tensor):
-    """Fill the four cached layouts: W1 (E,2I,H), W1^T (E,H,2I), W2 (E,H,I), W2^T (E,I,H)."""
+def _iso32_ok(w: torch.Tensor) -> bool:
+    return w.shape[1] % 128 == 0 and w.shape[2] % 128 == 0
+
+
+def weight_fp8_iso32(w: torch.Tensor):
+    """w [E,N,K] bf16 -> (e4m3 bytes [E,N,K], ISA scales for (E*N, K), ISA scales for (E*K, N)) with ONE scale per
+    32x32 block: the one payload is W K-major for the forward GEMM and, read N-contiguous, W^T for the backward
+    one, so half the FP8 weight memory of the two 1x32 copies (the reference's ISO32 weight cache,
+    sonicmoe/quack_utils/blockscaled_fp8_gemm.py:3765-3856; coarser scales: one per 1024 values instead of 32)."""
+    base = _base_of(w)
+    key = (w.data_ptr(), tuple(w.shape), tuple(w.stride()), "iso32", w.device.index)
+    ver = base._version
+    hit = _WEIGHT_CACHE.get(key)
+    if hit is not None and hit[0] == ver and hit[3]() is base:
+        return hit[1], hit[2][0], hit[2][1]
+    with torch.no_grad():
+        src = w.detach()
+        if src.dtype != torch.bfloat16:
+            src = src.to(torch.bfloat16)
+        src = src.contiguous()
+        E, N, K = src.shape
+        q = torch.empty(E, N, K, dtype=torch.uint8, device=src.device)
+        per_r, per_c = ops.isa_bytes(N, K), ops.isa_bytes(K, N)
+        row_sf = torch.empty(E * per_r, dtype=torch.uint8, device=src.device)
+        col_sf = torch.empty(E * per_c, dtype=torch.uint8, device=src.device)
+        for e in range(E):
+            ops.quant_iso32(src[e], out=(q[e], row_sf[e * per_r:(e + 1) * per_r], col_sf[e * per_c:(e + 1) * per_c]))
+    if len(_WEIGHT_CACHE) >= _WEIGHT_CACHE_MAX:
+        _WEIGHT_CACHE.pop(next(iter(_WEIGHT_CACHE)))
+    _WEIGHT_CACHE[key] = (ver, q, (row_sf, col_sf), weakref.ref(base))
+    return q, row_sf, col_sf
+
+
+def _weight_operand(w: torch.Tensor, transposed: bool, iso32: bool):
+    """(payload, ISA scales, stored_kn) of W (or W^T) as the B operand of a GEMM.  `stored_kn`: the payload is the
+    single ISO32 buffer, which holds the wanted operand [E, K', N'] with N' contiguous - the caller reads it through
+    `_gemm_plain` (MN-major B) or makes a transient byte transpose."""
+    if iso32 and _iso32_ok(w):
+        q, row_sf, col_sf = weight_fp8_iso32(w)
+        return (q, col_sf, True) if transposed else (q, row_sf, False)
+    q, sf = weight_fp8(w, transposed)
+    return q, sf, False
+
+
+def _gemm_plain(a_q, a_sf, b_q, b_sf, stored_kn, efo):
+    """rows grouped by expert x B[e]^T -> bf16.  `stored_kn`: B lies [E, K, N] (see `_weight_operand`)."""
+    if not stored_kn:
+        return ops.gemm_varlen_m(a_q, a_sf, b_q, b_sf, efo)
+    E, K, N = b_q.shape
+    if N % 256 == 0 and E <= 256:
+        return ops.gemm_varlen_m_bt(a_q, a_sf, b_q, b_sf, efo)
+    return ops.gemm_varlen_m(a_q, a_sf, ops.transpose_u8(b_q), b_sf, efo)     # transient K-major copy
+
+
+def _modes(fp8_config):
+    """(iso32_weight, stagewise_memory) of this call: an explicit config wins, then the active one, then the
+    environment."""
+    cfg = fp8_config if fp8_config is not None else get_active_config()
+    if cfg is None:
+        from ..config import SonicMoEConfig
+        cfg = SonicMoEConfig()
+    return cfg.resolve_iso32_weight(), cfg.resolve_stagewise_memory()
+
+
+# Per-stage memory record of the memory-lean mode (reference: _log_stage_memory, functional/__init__.py:726-737):
+# (stage, bytes allocated, peak bytes allocated since the previous record); each record synchronises the device.
+STAGE_MEMORY_LOG: list = []
+
+
+def _log_stage_memory(enabled: bool, stage: str):
+    if not enabled or torch.cuda.is_current_stream_capturing():
+        return
+    torch.cuda.synchronize()
+    STAGE_MEMORY_LOG.append((stage, torch.cuda.memory_allocated(), torch.cuda.max_memory_allocated()))
+    if len(STAGE_MEMORY_LOG) > 4096:
+        del STAGE_MEMORY_LOG[:2048]
+    torch.cuda.reset_peak_memory_stats()
+
+
+_GATED_OUTPUT_PAYLOAD_ATTR = "_sonic_preallocated_gated_outputs"
+
+
+def attach_preallocated_gated_outputs(packed_scales: torch.Tensor, outputs):
+    """Carry the four per-call up-projection outputs (pre-activation, post-activation, raw pre-activation scales,
+    post-activation ISA scales: what `deepep_topk_to_sonic_metadata_with_scales` allocates) on the packed-scales
+    tensor of the prequantised payload, so that they need not be explicit autograd inputs
+    (sonicmoe/functional/__init__.py:505-513)."""
+    if len(outputs) != 4:
+        raise ValueError(f"expected four gated outputs, got {len(outputs)}")
+    setattr(packed_scales, _GATED_OUTPUT_PAYLOAD_ATTR, tuple(outputs))
+    return packed_scales
+
+
+def precompute_weight_fp8(w1: torch.Tensor, w2: torch.Tensor, iso32_weight: bool | None = None):
+    """Fill the cached layouts: W1 (E,2I,H), W1^T (E,H,2I), W2 (E,H,I), W2^T (E,I,H) - or, in ISO32 mode, the one
+    buffer per weight."""
+    iso = _modes(None)[0] if iso32_weight is None else iso32_weight
     for w in (w1, w2):
-        weight_fp8(w, False)
-        weight_fp8(w, True)
+        if iso and _iso32_ok(w):
+            weight_fp8_iso32(w)
+        else:
+            weight_fp8(w, False)
+            weight_fp8(w, True)
 
 
 def clear_weight_cache():
@@ -196,7 +294,7 @@ def clear_weight_cache():
 def drop_weight_fp8(*weights: torch.Tensor):
     """Forget the cached FP8 copies (both orientations) of the given weights only."""
     for w in weights:
-        for transposed in (False, True):
+        for transposed in (False, True, "iso32"):
             _WEIGHT_CACHE.pop((w.data_ptr(), tuple(w.shape), tuple(w.stride()), transposed, w.device.index), None)
 
 
@@ -313,12 +411,12 @@ class Fp8CombineGradHandle:
         return p
 
 
-def _up_projection(xg_q, a_sf, w1_q, w1_sf, efo, TKp, act):
+def _up_projection(xg_q, a_sf, w1_q, w1_sf, efo, TKp, act, out=None):
     """z = x_sorted . W1^T, y1 = act(gate) * up; z and y1 leave as MXFP8.  SwiGLU: one GEMM with the activation and
     both quantizers in its epilogue; ReGLU / GEGLU: a plain GEMM to bf16 z, then the stand-alone activation kernel
     (rows beyond the last expert's segment hold whatever the allocator left: they are never read downstream)."""
     if act == 0:
-        return ops.gemm_gated(xg_q, None, a_sf, w1_q, w1_sf, efo, TKp)
+        return ops.gemm_gated(xg_q, None, a_sf, w1_q, w1_sf, efo, TKp, out=out)
     z = ops.gemm_varlen_m(xg_q, a_sf, w1_q, w1_sf, efo)
     return ops.glu_fwd(z, act)
 
@@ -344,26 +442,44 @@ class _UpProjection(torch.autograd.Function):
             raise NotImplementedError("expert biases are not supported on the MXFP8 path")
         E, N2, H = w1.shape
         TKp = int(TKp)
-        x_q = x_raw = None
+        x_q = x_raw = packed_sf = gated_out = None
         if prequant_payload is not None:
-            # x arrives as e4m3 bytes + raw 1x32 ue8m0 scales (expert-parallel dispatch payload)
+            # x arrives as e4m3 bytes + raw 1x32 ue8m0 scales (expert-parallel dispatch payload); a third element is
+            # the scales already gathered to expert-sorted rows in the ISA layout, and may carry the four
+            # up-projection outputs allocated with the metadata (attach_preallocated_gated_outputs)
             x_q, x_raw = prequant_payload[0], prequant_payload[1]
             x_q = x_q.view(torch.uint8)
+            if len(prequant_payload) > 2 and prequant_payload[2] is not None:
+                packed_sf = prequant_payload[2]
+                gated_out = getattr(packed_sf, _GATED_OUTPUT_PAYLOAD_ATTR, None)
+                if gated_out is not None:      # (pre-activation, post-activation, z scales, y1 scales) -> op order
+                    gated_out = (gated_out[0], gated_out[2], gated_out[1], gated_out[3])
+                packed_sf = packed_sf.view(torch.uint8).reshape(-1)
+                if packed_sf.numel() != ops.isa_bytes(TKp, H):
+                    raise ValueError(f"packed scales hold {packed_sf.numel()} bytes, ({TKp}, {H}) needs "
+                                     f"{ops.isa_bytes(TKp, H)}")
         elif USE_TMA_GATHER and act == 0:
             x_q, x_raw, _ = ops.quant_rows(x.contiguous(), raw=True)
-        w1_q, w1_sf = weight_fp8(w1, False)
+        iso32, stagewise = _modes(fp8_config)
+        w1_q, w1_sf, _ = _weight_operand(w1, False, iso32)
         if USE_TMA_GATHER and act == 0:
-            a_sf = ops.gather_scales_isa(x_raw, x_gather_idx, TKp, H)
-            z_q, z_sc, y1_q, y1_sf = ops.gemm_gated(x_q, x_gather_idx, a_sf, w1_q, w1_sf, efo, TKp)
+            a_sf = packed_sf if packed_sf is not None else ops.gather_scales_isa(x_raw, x_gather_idx, TKp, H)
+            z_q, z_sc, y1_q, y1_sf = ops.gemm_gated(x_q, x_gather_idx, a_sf, w1_q, w1_sf, efo, TKp, out=gated_out)
         else:
-            if x_q is not None:
+            if x_q is not None and packed_sf is not None:
+                xg_q, _ = ops.scatter_rows_fp8(x_q, None, naept, s_rev, s_scatter_idx, TKp, efo[-1:],
+                                               with_scales=False)
+                a_sf = packed_sf
+            elif x_q is not None:
                 xg_q, a_sf = ops.scatter_rows_fp8(x_q, x_raw, naept, s_rev, s_scatter_idx, TKp, efo[-1:])
             else:      # quantise straight into expert-sorted order
                 xg_q, a_sf = ops.quant_rows_scatter(x.contiguous(), naept, s_rev, s_scatter_idx, TKp, efo[-1:])
-            z_q, z_sc, y1_q, y1_sf = _up_projection(xg_q, a_sf, w1_q, w1_sf, efo, TKp, act)
+            z_q, z_sc, y1_q, y1_sf = _up_projection(xg_q, a_sf, w1_q, w1_sf, efo, TKp, act, out=gated_out)
             del xg_q
+        _log_stage_memory(stagewise, "forward: after up-projection")
         out_buf, ctx.dx_buf = _take_placement()
-        link = {"y1": (y1_q, y1_sf), "z": (z_q, z_sc), "out_buf": out_buf, "act": act,
+        link = {"y1": (y1_q, y1_sf), "z": (z_q, z_sc), "out_buf": out_buf, "act": act, "iso32": iso32,
+                "stagewise": stagewise,
                 # whether a backward of this Function will run (it then also runs the weight-gradient GEMM that
                 # _DownProjection.backward hands over)
                 "up_runs_backward": bool(ctx.needs_input_grad[0] or ctx.needs_input_grad[1])}
@@ -372,7 +488,7 @@ class _UpProjection(torch.autograd.Function):
             # keep what regenerates z instead of z itself; the backward re-runs this GEMM and gets the same bytes
             link["z"] = None
             link["z_recompute"] = (x if prequant_payload is None else None, x_q, x_raw, w1, efo, x_gather_idx,
-                                   s_scatter_idx, s_rev, naept, TKp, act)
+                                   s_scatter_idx, s_rev, naept, TKp, act, iso32)
             del z_q, z_sc
         ctx.link = link
         ctx.T = x.shape[0]
@@ -398,14 +514,16 @@ class _UpProjection(torch.autograd.Function):
         # same slot for dw1: sonicmoe/functional/__init__.py:278-311)
         dx = None
         if ctx.needs_input_grad[0]:
-            w1t_q, w1t_sf = weight_fp8(w1, True)
-            dx_exp = ops.gemm_varlen_m(dz_q, dz_rsf, w1t_q, w1t_sf, efo)
+            w1t_q, w1t_sf, kn = _weight_operand(w1, True, link.get("iso32", False))
+            dx_exp = _gemm_plain(dz_q, dz_rsf, w1t_q, w1t_sf, kn, efo)
+            del w1t_q, w1t_sf
             buf = ctx.dx_buf if (ctx.dx_buf is not None and ctx.x_dtype == torch.bfloat16) else None
             dx = ops.combine(dx_exp, s_rev, naept, None, ctx.T, out=buf)
             del dx_exp
             if dx.dtype != ctx.x_dtype:
                 dx = dx.to(ctx.x_dtype)
             note_result_ready(dx)
+            _log_stage_memory(link.get("stagewise", False), "backward: after dx")
         deferred_dw2 = link.pop("dw2_job", None)
         if deferred_dw2 is not None:
             deferred_dw2()
@@ -423,16 +541,19 @@ class _UpProjection(torch.autograd.Function):
                 _after_accumulate(base)
             else:
                 dw1 = out.to(w1.dtype)
-        ops.post_status(dz_q.device)      # last kernels of the layer's backward: let the next call see their status
+            del xc, x_sf
+        del dz_q, dz_rsf, dz_t, dz_csf
+        _log_stage_memory(link.get("stagewise", False), "backward: after dw1")
+        ops.post_status(x.device)      # last kernels of the layer's backward: let the next call see their status
         return (dx, dw1) + (None,) * 15
 
 
 def _recompute_z(args):
     """z as e4m3 + raw scales, regenerated from the up-projection's inputs (same kernels, same bytes as the
     forward produced; the re-computed y1 is discarded)."""
-    x, x_q, x_raw, w1, efo, x_gather_idx, s_scatter_idx, s_rev, naept, TKp, act = args
+    x, x_q, x_raw, w1, efo, x_gather_idx, s_scatter_idx, s_rev, naept, TKp, act, iso32 = args
     H = w1.shape[2]
-    w1_q, w1_sf = weight_fp8(w1, False)
+    w1_q, w1_sf, _ = _weight_operand(w1, False, iso32)
     if USE_TMA_GATHER and act == 0:
         if x_q is None:
             x_q, x_raw, _ = ops.quant_rows(x.contiguous(), raw=True)
@@ -468,9 +589,12 @@ class _DownProjection(torch.autograd.Function):
             raise NotImplementedError("expert biases are not supported on the MXFP8 path")
         link = _handoff_take(z)
         y1_q, y1_sf = link.pop("y1")
-        w2_q, w2_sf = weight_fp8(w2, False)
+        w2_q, w2_sf, _ = _weight_operand(w2, False, link.get("iso32", False))
         y2 = ops.gemm_varlen_m(y1_q, y1_sf, w2_q, w2_sf, efo)
+        del y1_q, y1_sf
         o = ops.combine(y2, s_rev, naept, topk_scores, int(T), out=link.pop("out_buf", None))
+        del y2
+        _log_stage_memory(link.get("stagewise", False), "forward: after down-projection")
         ops.post_status(o.device)
         ctx.link = link
         ctx.T = int(T)
@@ -504,10 +628,18 @@ class _DownProjection(torch.autograd.Function):
         y1s_q = dout_c = None
         dout_c_rows = False
         act = link.get("act", 0)
-        w2t_q, w2t_sf = weight_fp8(w2, True)
+        stagewise = link.get("stagewise", False)
+        # memory-lean order: the column-quantised copy of dout is made after GemmDGated has run and z and the
+        # gathered dout rows are freed, and dw2 runs (and frees its operands) before dx_expanded is allocated
+        early_cols = not stagewise
+        w2t_q, w2t_sf, kn = _weight_operand(w2, True, link.get("iso32", False))
+        if kn:
+            # GemmDGated reads B K-major only (its 192-column slices are no MN-major swizzle atoms): a transient
+            # byte-transposed copy, freed after the GEMM (the reference does the same, functional/__init__.py:2160)
+            w2t_q = ops.transpose_u8(w2t_q)
         if USE_TMA_GATHER and act == 0:
             a_sf = ops.gather_scales_isa(dout_raw, x_gather_idx, TKp, H)
-            if dout is not None and ctx.needs_input_grad[2] and _mn_wgrad_ok(E, I, H):
+            if early_cols and dout is not None and ctx.needs_input_grad[2] and _mn_wgrad_ok(E, I, H):
                 dout_c, dout_sf, dout_c_rows = _col_operand(dout, x_gather_idx, TKp, efo[-1:], E, I, H)
             if FUSE_DGATED_QUANT and _mn_wgrad_ok(E, I, H):
                 dz_q, dz_rsf, dz_csf, y1s_q, y1s_sf, dsp = ops.gemm_dgated_fused(
@@ -523,7 +655,7 @@ class _DownProjection(torch.autograd.Function):
                 # row scales in scatter form (each token read once: 68 us on T=8192, H=3072, K=8), column scales
                 # in a second, gathered pass (93 us); the one-pass dual kernel measured 209 us there
                 dg_q, a_sf = ops.quant_rows_scatter(dout, naept, s_rev, s_scatter_idx, TKp, efo[-1:])
-                if ctx.needs_input_grad[2] and _mn_wgrad_ok(E, I, H):
+                if early_cols and ctx.needs_input_grad[2] and _mn_wgrad_ok(E, I, H):
                     dout_c, dout_sf, dout_c_rows = _col_operand(dout, x_gather_idx, TKp, efo[-1:], E, I, H)
             if act != 0:
                 # ReGLU / GEGLU: D from a plain GEMM, then the stand-alone activation-gradient kernel; dz / y1s in bf16
@@ -541,20 +673,24 @@ class _DownProjection(torch.autograd.Function):
             else:
                 dz, y1s, dsp = ops.gemm_dgated(dg_q, None, a_sf, w2t_q, w2t_sf, efo, z_q, z_sc, s, TKp)
             del dg_q
-        del z_q, z_sc
+        del z_q, z_sc, w2t_q, w2t_sf, a_sf
+        _log_stage_memory(stagewise, "backward: after GemmDGated")
         dw2 = None
         if ctx.needs_input_grad[2]:
             if y1s is not None:
                 y1s_t, y1s_sf = ops.quant_cols_t(y1s, None, TKp)
+                del y1s
             if dout_c is None:
                 if dout is None:
                     dout_t, dout_sf = ops.requant_cols_t(dout_q, dout_raw, x_gather_idx, TKp)
+                elif _mn_wgrad_ok(E, I, H):
+                    dout_c, dout_sf, dout_c_rows = _col_operand(dout, x_gather_idx, TKp, efo[-1:], E, I, H)
                 else:
                     dout_t, dout_sf = ops.quant_cols_t(dout, x_gather_idx, TKp)
             mg, base = _grad_target(w2, (E, I, H))
             a_op, a_rows = (y1s_q, True) if y1s_q is not None else (y1s_t, False)
             b_op, b_rows = (dout_c, dout_c_rows) if dout_c is not None else (dout_t, False)
-            if mg is not None and link.get("up_runs_backward") and _DEFER_DW2:
+            if mg is not None and link.get("up_runs_backward") and _DEFER_DW2 and not stagewise:
                 # accumulation into main_grad returns no tensor: the GEMM is handed to _UpProjection.backward, which
                 # runs it after dx so that it, too, lies underneath an enclosing exchange of dx
                 def dw2_job(a_op=a_op, a_rows=a_rows, b_op=b_op, b_rows=b_rows, sf_a=y1s_sf, sf_b=dout_sf, mg=mg,
@@ -569,6 +705,8 @@ class _DownProjection(torch.autograd.Function):
                 out = torch.empty(E, I, H, dtype=torch.float32, device=s.device)
                 _wgrad(a_op, y1s_sf, a_rows, b_op, dout_sf, b_rows, efo, out, False)
                 dw2 = out.transpose(1, 2).to(w2.dtype)
+            del a_op, b_op, y1s_q, dout_c
+            _log_stage_memory(stagewise, "backward: after dw2")
         if dz is not None:
             link["dz"] = ops.quant_iso32(dz)
         else:      # the gradient edge of z still needs a tensor of its shape; its contents are never read

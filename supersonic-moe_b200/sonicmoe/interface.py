@@ -6,8 +6,9 @@ from __future__ import annotations
 import torch
 
 from . import ops
-from .enums import ActivationType
-from .functional import _DownProjection, _UpProjection, enable_fp8, place_results
+from .enums import ActivationType, activation_code
+from .functional import (_DownProjection, _UpProjection, attach_preallocated_gated_outputs, enable_fp8,
+                         place_results)
 
 
 def scale_bytes(fp8_scale: torch.Tensor, H: int) -> torch.Tensor:
@@ -65,7 +66,23 @@ def run_sonic_moe(hidden_states, topk_indices, topk_scores, K, E, w1, w2, fp8=Fa
     stream_id = torch.cuda.current_stream().cuda_stream
     payload = None
     if fp8_scale is not None:
-        payload = (hidden_states.view(torch.uint8), scale_bytes(fp8_scale, hidden_states.shape[1]))
+        H = hidden_states.shape[1]
+        raw = scale_bytes(fp8_scale, H)
+        payload = (hidden_states.view(torch.uint8), raw)
+        gated_n = int(w1.shape[1])
+        if activation_code(activation_type) == 0 and gated_n % 256 == 0 and H % 128 == 0 \
+                and hidden_states.dtype in (torch.float8_e4m3fn, torch.uint8):
+            # the scales gathered to expert-sorted rows and the four outputs of the up-projection are made together
+            # with the metadata and travel with the payload (reference: interface.py:136-188,254-262; the output
+            # allocation sits in its metadata op, deepep_topk_metadata_cuda/kernel.cu:982-1019)
+            TKp_alloc = md["TKp_alloc"]
+            packed = ops.gather_scales_isa(raw, md["x_gather_idx"], TKp_alloc, H)
+            dev = hidden_states.device
+            outs = (torch.empty(TKp_alloc, gated_n, dtype=hidden_states.dtype, device=dev),
+                    torch.empty(TKp_alloc, gated_n // 2, dtype=hidden_states.dtype, device=dev),
+                    torch.empty(TKp_alloc, gated_n // 32, dtype=torch.uint8, device=dev),
+                    torch.empty(TKp_alloc // 128, gated_n // 256, 512, dtype=torch.uint8, device=dev))
+            payload = (payload[0], raw, attach_preallocated_gated_outputs(packed, outs))
         hidden_states = grad_holder if grad_holder is not None else torch.empty(
             (), dtype=torch.bfloat16, device=hidden_states.device).expand(N, hidden_states.shape[1])
     need_router_grad = topk_scores.requires_grad

@@ -282,13 +282,16 @@ def gather_rows_fp8(q, raw, idx, rows, valid_rows=None):
 
 
 @_timed
-def scatter_rows_fp8(q, raw, naept, s_rev, s_scatter_idx, rows, valid_rows=None):
+def scatter_rows_fp8(q, raw, naept, s_rev, s_scatter_idx, rows, valid_rows=None, with_scales=True):
     """q u8 [T,K], raw scales u8 [T,K/32] -> (rows in expert-sorted order [rows,K], ISA scales of (rows,K)); each
-    source row is read once and written to all its positions; pad rows are zero."""
+    source row is read once and written to all its positions; pad rows are zero.  `with_scales=False`: payload
+    only (the second result is None), for a caller that already holds the packed scales."""
     _cuda(q, raw, naept, s_rev, s_scatter_idx, valid_rows)
     T, K = q.shape
     out = torch.empty(rows, K, dtype=_U8, device=q.device)
-    isa = torch.empty(isa_bytes(rows, K), dtype=_U8, device=q.device)
+    isa = torch.empty(isa_bytes(rows, K), dtype=_U8, device=q.device) if with_scales else None
+    if not with_scales:
+        raw = None
     check(lib.smoe_scatter_rows_fp8(_p(q), _p(raw), T, K, _p(naept), _p(s_rev), _p(s_scatter_idx), _p(valid_rows),
                                     rows, _p(out), _p(isa), _stream()), "scatter_rows_fp8")
     return out, isa
@@ -325,18 +328,36 @@ def requant_cols_t(src_q, src_raw, idx, rows):
 
 
 @_timed
-def quant_iso32(x):
-    """bf16 [rows, cols] -> (q [rows,cols], row ISA, q_t [cols,rows], col ISA)."""
+def quant_iso32(x, transposed_payload=True, out=None):
+    """bf16 [rows, cols] -> (q [rows,cols], row ISA, q_t [cols,rows] or None, col ISA); one scale per 32x32 block.
+    `out` = (q, row ISA, col ISA) buffers to fill (then no transposed payload is written)."""
     _cuda(x)
-    assert x.dtype == torch.bfloat16
+    assert x.dtype == torch.bfloat16 and x.is_contiguous()
     rows, cols = x.shape
     dev = x.device
-    q = torch.empty(rows, cols, dtype=_U8, device=dev)
-    q_t = torch.empty(cols, rows, dtype=_U8, device=dev)
-    ri = torch.empty(isa_bytes(rows, cols), dtype=_U8, device=dev)
-    ci = torch.empty(isa_bytes(cols, rows), dtype=_U8, device=dev)
+    if out is not None:
+        q, ri, ci = out
+        q_t = None
+        assert q.is_contiguous() and q.numel() == rows * cols and ri.numel() == isa_bytes(rows, cols) \
+            and ci.numel() == isa_bytes(cols, rows)
+    else:
+        q = torch.empty(rows, cols, dtype=_U8, device=dev)
+        q_t = torch.empty(cols, rows, dtype=_U8, device=dev) if transposed_payload else None
+        ri = torch.empty(isa_bytes(rows, cols), dtype=_U8, device=dev)
+        ci = torch.empty(isa_bytes(cols, rows), dtype=_U8, device=dev)
     check(lib.smoe_quant_iso32(_p(x), rows, cols, _p(q), _p(ri), _p(q_t), _p(ci), _stream()), "quant_iso32")
     return q, ri, q_t, ci
+
+
+@_timed
+def transpose_u8(src):
+    """u8 [B, R, C] -> u8 [B, C, R] (R, C multiples of 64)."""
+    _cuda(src)
+    assert src.dtype == _U8 and src.is_contiguous() and src.dim() == 3
+    B, R, C = src.shape
+    dst = torch.empty(B, C, R, dtype=_U8, device=src.device)
+    check(lib.smoe_transpose_u8(_p(src), B, R, C, _p(dst), _stream()), "transpose_u8")
+    return dst
 
 
 # ---------------------------------------------------------------- GEMMs
@@ -353,18 +374,42 @@ def gemm_varlen_m(a_q, a_sf, b_q, b_sf, efo):
 
 
 @_timed
-def gemm_gated(x_q, a_idx, a_sf, w1_q, w1_sf, efo, rows):
-    """x_q u8 [T,H], w1_q u8 [E,2I,H] -> z_q [rows,2I], z_sc [rows,2I/32], y1_q [rows,I], y1_sf (ISA)."""
+def gemm_varlen_m_bt(a_q, a_sf, b_kn_q, b_sf, efo):
+    """a_q u8 [rows,K], b_kn_q u8 [E,K,N] (B[e] stored N-contiguous), b_sf ISA scales for (E*N, K) -> bf16 [rows,N]."""
+    _cuda(a_q, a_sf, b_kn_q, b_sf, efo)
+    rows, K = a_q.shape
+    E, Kb, N = b_kn_q.shape
+    assert Kb == K
+    c = torch.empty(rows, N, dtype=torch.bfloat16, device=a_q.device)
+    check(lib.smoe_gemm_varlen_m_bt(_p(a_q), _p(a_sf), _p(b_kn_q), _p(b_sf), _p(efo), _p(c), rows, N, K, E,
+                                    _p(status_word(a_q.device)), _stream()), "gemm_varlen_m_bt")
+    return c
+
+
+@_timed
+def gemm_gated(x_q, a_idx, a_sf, w1_q, w1_sf, efo, rows, out=None):
+    """x_q u8 [T,H], w1_q u8 [E,2I,H] -> z_q [rows,2I], z_sc [rows,2I/32], y1_q [rows,I], y1_sf (ISA).
+    `out` = those four as buffers allocated by the caller (any one-byte dtype; sizes checked)."""
     _cuda(x_q, a_idx, a_sf, w1_q, w1_sf, efo)
     if a_idx is None and x_q.shape[0] != rows:
         raise ValueError("gemm_gated without a_idx needs x_q in expert-sorted order [rows, K]")
     T, K = x_q.shape
     E, N, _ = w1_q.shape
     dev = x_q.device
-    z_q = torch.empty(rows, N, dtype=_U8, device=dev)
-    z_sc = torch.empty(rows, N // 32, dtype=_U8, device=dev)
-    y1_q = torch.empty(rows, N // 2, dtype=_U8, device=dev)
-    y1_sf = torch.empty(isa_bytes(rows, N // 2), dtype=_U8, device=dev)
+    if out is not None:
+        z_q, z_sc, y1_q, y1_sf = (t.view(_U8) for t in out)
+        _cuda(z_q, z_sc, y1_q, y1_sf)
+        want = (rows * N, rows * (N // 32), rows * (N // 2), isa_bytes(rows, N // 2))
+        got = (z_q.numel(), z_sc.numel(), y1_q.numel(), y1_sf.numel())
+        if got != want:
+            raise ValueError(f"gemm_gated: pre-allocated outputs hold {got} bytes, the call needs {want}")
+        z_q, z_sc, y1_q = z_q.view(rows, N), z_sc.view(rows, N // 32), y1_q.view(rows, N // 2)
+        y1_sf = y1_sf.view(-1)
+    else:
+        z_q = torch.empty(rows, N, dtype=_U8, device=dev)
+        z_sc = torch.empty(rows, N // 32, dtype=_U8, device=dev)
+        y1_q = torch.empty(rows, N // 2, dtype=_U8, device=dev)
+        y1_sf = torch.empty(isa_bytes(rows, N // 2), dtype=_U8, device=dev)
     check(lib.smoe_gemm_gated(_p(x_q), T, _p(a_idx), _p(a_sf), _p(w1_q), _p(w1_sf), _p(efo), _p(z_q), _p(z_sc),
                               _p(y1_q), _p(y1_sf), rows, N, K, E, _p(status_word(dev)), _stream()), "gemm_gated")
     return z_q, z_sc, y1_q, y1_sf

@@ -696,3 +696,80 @@ def test_ep_combine_pull_on_one_gpu_with_local_stand_ins_for_the_peers(ops, T, K
             i = int(copy_pos[c]); r = int(send_rank[i])
             want[t] += bufs[r][first_row[r] + i - plan.send_off[r]].float().cpu()
     assert torch.equal(out.cpu(), want.to(torch.bfloat16))
+
+
+def test_transpose_u8_and_plain_gemm_with_b_stored_kn(ops):
+    """`transpose_u8` is a byte transpose; `gemm_varlen_m_bt` reads B[e] stored [K,N] (the single ISO32 weight
+    buffer) and gives the bits of the K-major GEMM on the byte-transposed copy, and the dequantised fp32 product."""
+    g = torch.Generator().manual_seed(77)
+    t = torch.randint(0, 256, (3, 128, 192), generator=g, dtype=torch.uint8).to(DEV)
+    assert torch.equal(ops.transpose_u8(t), t.transpose(1, 2).contiguous())
+    for E, N, K, seg in ((4, 256, 384, (256, 0, 128, 384)), (2, 768, 256, (384, 128))):
+        rows = sum(seg)
+        efo = torch.tensor([0] + list(torch.tensor(seg).cumsum(0)), dtype=torch.int32, device=DEV)
+        a = torch.randn(rows, K, generator=g).to(torch.bfloat16).to(DEV)
+        # B logical [E, N, K]; stored as W [E, K, N] quantised with 32x32-block scales
+        w = (torch.randn(E, K, N, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
+        a_q, _, a_sf = ops.quant_rows(a, raw=False, isa=True)
+        q = torch.empty(E, K, N, dtype=torch.uint8, device=DEV)
+        per_r, per_c = ops.isa_bytes(K, N), ops.isa_bytes(N, K)
+        rsf = torch.empty(E * per_r, dtype=torch.uint8, device=DEV)
+        csf = torch.empty(E * per_c, dtype=torch.uint8, device=DEV)
+        for e in range(E):
+            qq, ri, qt, ci = ops.quant_iso32(w[e])
+            ops.quant_iso32(w[e], out=(q[e], rsf[e * per_r:(e + 1) * per_r], csf[e * per_c:(e + 1) * per_c]))
+            assert torch.equal(q[e], qq) and torch.equal(qt, qq.t().contiguous())
+            assert torch.equal(rsf[e * per_r:(e + 1) * per_r], ri) and torch.equal(csf[e * per_c:(e + 1) * per_c], ci)
+        got = ops.gemm_varlen_m_bt(a_q, a_sf, q, csf, efo)
+        ref = ops.gemm_varlen_m(a_q, a_sf, ops.transpose_u8(q), csf, efo)
+        torch.cuda.synchronize()
+        ops.check_status(DEV)
+        assert torch.equal(got, ref)
+        # dequantised fp32 product
+        aq, asc = Q.row_quant(a.float().cpu())
+        ad = Q.dequant_rows(aq, asc)
+        want = torch.zeros(rows, N)
+        for e in range(E):
+            wq, ws = Q.iso32_quant(w[e].float().cpu())
+            wd = Q.e4m3_bytes_to_f32(wq) * Q.dequant_scale_from_e8m0(ws).repeat_interleave(32, 0).repeat_interleave(32, 1)
+            lo, hi = int(efo[e]), int(efo[e + 1])
+            want[lo:hi] = ad[lo:hi] @ wd
+        gd, wd64 = got.double().cpu(), want.double()
+        cos = float((gd * wd64).sum() / (gd.norm() * wd64.norm()))
+        assert cos > 0.99999, cos
+
+
+def test_payload_only_scatter_and_caller_owned_gated_outputs(ops):
+    """`scatter_rows_fp8(with_scales=False)` writes the same payload bytes; `gemm_gated(out=...)` fills the
+    caller's buffers with the same bytes and rejects buffers of the wrong size."""
+    g = torch.Generator().manual_seed(78)
+    T, H, N2, E, K = 256, 256, 512, 4, 2
+    idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32).to(DEV)
+    probs = torch.rand(T, K, generator=g).to(DEV)
+    md = ops.topk_metadata(idx, probs, E)
+    TKp = md["TKp_alloc"]
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16).to(DEV)
+    q, raw, _ = ops.quant_rows(x, raw=True)
+    full, isa = ops.scatter_rows_fp8(q, raw, md["naept"], md["s_reverse_scatter_idx"], md["s_scatter_idx"], TKp,
+                                     md["efo"][-1:])
+    only, none = ops.scatter_rows_fp8(q, raw, md["naept"], md["s_reverse_scatter_idx"], md["s_scatter_idx"], TKp,
+                                      md["efo"][-1:], with_scales=False)
+    n = int(md["efo"][-1])
+    assert none is None and torch.equal(full[:n], only[:n])
+    w = (torch.randn(E, N2, H, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    wq, _, wsf = ops.quant_rows(w.view(E * N2, H), raw=False, isa=True)
+    wq = wq.view(E, N2, H)
+    ref = ops.gemm_gated(full, None, isa, wq, wsf, md["efo"], TKp)
+    bufs = (torch.zeros(TKp, N2, dtype=torch.float8_e4m3fn, device=DEV),
+            torch.zeros(TKp, N2 // 32, dtype=torch.uint8, device=DEV),
+            torch.zeros(TKp, N2 // 2, dtype=torch.float8_e4m3fn, device=DEV),
+            torch.zeros(TKp // 128, N2 // 256, 512, dtype=torch.uint8, device=DEV))
+    got = ops.gemm_gated(full, None, isa, wq, wsf, md["efo"], TKp, out=bufs)
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    assert got[0].data_ptr() == bufs[0].data_ptr() and got[3].data_ptr() == bufs[3].data_ptr()
+    nb = n // 128 * (N2 // 2 // 128) * 512
+    assert torch.equal(ref[0][:n], got[0][:n]) and torch.equal(ref[1][:n], got[1][:n])
+    assert torch.equal(ref[2][:n], got[2][:n]) and torch.equal(ref[3][:nb], got[3][:nb])
+    with pytest.raises(ValueError):
+        ops.gemm_gated(full, None, isa, wq, wsf, md["efo"], TKp, out=(bufs[0], bufs[1], bufs[2], bufs[3][:-1]))

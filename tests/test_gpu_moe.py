@@ -733,3 +733,183 @@ def test_transposed_weight_copy_without_a_transposed_bf16_tensor(sm):
         assert torch.equal(got, Q.unpack_isa(rsf.cpu(), E * K, N).view(E, K, N // 32))
         oq, osc = Q.row_quant(wt.view(E * K, N).float().cpu())
         assert torch.equal(q.view(E * K, N).cpu(), oq) and torch.equal(got.view(E * K, N // 32), osc)
+
+
+def _layer_run(sm, x, dy, w1, w2, idx, scores, K, E, cfg=None, main_grad=False):
+    xd = x.to(DEV).requires_grad_(True)
+    sd = scores.to(DEV).requires_grad_(True)
+    w1d, w2d = w1.to(DEV).requires_grad_(True), w2.to(DEV).requires_grad_(True)
+    if main_grad:
+        w1d.main_grad = torch.zeros(w1.shape, dtype=torch.float32, device=DEV)
+        w2d.main_grad = torch.zeros(w2.shape[0], w2.shape[2], w2.shape[1], dtype=torch.float32, device=DEV)
+    out = sm.run_sonic_moe(xd, idx.to(DEV), sd, K, E, w1d, w2d, fp8=True, fp8_config=cfg)
+    out.backward(dy.to(DEV))
+    torch.cuda.synchronize()
+    sm.ops.check_status(DEV)
+    if main_grad:
+        return out.detach(), xd.grad, sd.grad, w1d.main_grad, w2d.main_grad
+    return out.detach(), xd.grad, sd.grad, w1d.grad, w2d.grad
+
+
+@pytest.mark.parametrize("T,H,I,E,K,seed", [(1024, 512, 256, 8, 4, 131), (512, 384, 256, 4, 2, 132)])
+def test_iso32_weight_cache_one_buffer_per_weight(sm, T, H, I, E, K, seed):
+    """`SonicMoEConfig(iso32_weight=True)`: each weight is quantised once with one scale per 32x32 block; the forward
+    GEMMs read that buffer K-major and the activation-gradient GEMM reads the same bytes MN-major (H % 256 == 0) or
+    through a transient byte transpose.  Half the cached FP8 weight bytes, results equal to the CPU emulation of
+    the same dataflow, and inside the reference's FP8 thresholds against fp32 (tests/ops/test_moe_module.py:56-61:
+    RRMSE < 0.10, cosine > 0.99)."""
+    import sonicmoe.functional as Fn
+    x, dy, w1, w2, _, _ = make_layer(T, H, I, E, K, seed)
+    idx, scores = masked_routing(T, E, K, E, seed + 1)
+    md = R.topk_metadata(idx, scores, E, 128)
+    gold = OM.moe_fp32(x, w1, w2, md, dy)
+    emu = OM.moe_fp8_emulated(x, w1, w2, md, dy, iso32_weight=True)
+
+    def cached_bytes():
+        return sum(v[1].numel() for v in Fn._WEIGHT_CACHE.values())
+
+    Fn.clear_weight_cache()
+    base = _layer_run(sm, x, dy, w1, w2, idx, scores, K, E)
+    two_copies = cached_bytes()
+    Fn.clear_weight_cache()
+    rec = []
+    sm.ops.set_recorder(rec)
+    try:
+        got = _layer_run(sm, x, dy, w1, w2, idx, scores, K, E, sm.SonicMoEConfig(use_fp8=True, iso32_weight=True))
+    finally:
+        sm.ops.set_recorder(None)
+    names = [n for n, _, _ in rec]
+    assert cached_bytes() * 2 == two_copies
+    assert all(k[3] == "iso32" for k in Fn._WEIGHT_CACHE)
+    fused = H % 256 == 0 and I % 256 == 0            # else dz takes the stand-alone 32x32-block quantizer once
+    assert names.count("quant_iso32") == 2 * E + (0 if fused else 1) and "quant_rows" not in names
+    assert ("gemm_varlen_m_bt" in names) == (H % 256 == 0) and names.count("transpose_u8") == (1 if H % 256 == 0 else 2)
+    ds_ref, ds_emu = torch.zeros(T * K), torch.zeros(T * K)
+    ds_ref[md["score_src_idx"][:md["real_TK"]].long()] = gold["ds"][:md["real_TK"]]
+    ds_emu[md["score_src_idx"][:md["real_TK"]].long()] = emu["ds"][:md["real_TK"]]
+    refs = dict(out=(gold["o"], emu["o"]), dx=(gold["dx"], emu["dx"]), ds=(ds_ref, ds_emu),
+                dw1=(gold["dw1"], emu["dw1"]), dw2=(gold["dw2"], emu["dw2_IH"].transpose(1, 2)))
+    for (name, (g, e)), t in zip(refs.items(), got):
+        t = t.flatten() if name == "ds" else t
+        c, r = stats(t, e)
+        assert c >= 0.9995 and r <= 0.03, f"{name} vs emulation: cos {c:.5f} rrmse {r:.5f}"
+        c, r = stats(t, g)
+        assert c >= 0.99 and r <= 0.10, f"{name} vs fp32: cos {c:.5f} rrmse {r:.5f}"
+    # the environment switch selects the same path
+    import os
+    os.environ["SONIC_MOE_FP8_ISO32_WEIGHT"] = "1"
+    try:
+        env = _layer_run(sm, x, dy, w1, w2, idx, scores, K, E)
+    finally:
+        del os.environ["SONIC_MOE_FP8_ISO32_WEIGHT"]
+    for a, b in zip(got, env):
+        assert torch.equal(a, b)
+    # coarser scales: the scale bytes differ from the 1x32 copy's (the layer's results may still coincide bit for bit:
+    # a power-of-two scale twice as large costs an e4m3 value nothing until it turns subnormal)
+    w1d = w1.to(DEV)
+    q32, rsf32, _ = Fn.weight_fp8_iso32(w1d)
+    q1, sf1 = Fn.weight_fp8(w1d, False)
+    assert not torch.equal(rsf32, sf1)
+    for a, b in zip(base, got):
+        c, r = stats(b, a)
+        assert c >= 0.9999 and r <= 0.02
+    Fn.clear_weight_cache()
+
+
+def test_stagewise_memory_same_bits_lower_backward_peak_and_a_stage_record(sm):
+    """`SonicMoEConfig(stagewise_memory=True)`: the backward makes each operand right before its one consumer and
+    frees it right after (dout's column-quantised copy after GemmDGated has released z and the gathered rows; dw2
+    before dx_expanded is allocated).  Bit-identical results, a lower peak, and a per-stage memory record."""
+    import sonicmoe.functional as Fn
+    T, H, I, E, K = 4096, 1024, 512, 8, 4
+    x, dy, w1, w2, _, _ = make_layer(T, H, I, E, K, 141)
+    idx, scores = masked_routing(T, E, K, E, 142)
+
+    def run(cfg):
+        _layer_run(sm, x, dy, w1, w2, idx, scores, K, E, cfg, main_grad=True)      # warm the weight cache
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats()
+        before = torch.cuda.memory_allocated()
+        res = _layer_run(sm, x, dy, w1, w2, idx, scores, K, E, cfg, main_grad=True)
+        return res, torch.cuda.max_memory_allocated() - before
+
+    base, peak_default = run(None)
+    del Fn.STAGE_MEMORY_LOG[:]
+    lean, peak_lean = run(sm.SonicMoEConfig(use_fp8=True, stagewise_memory=True))
+    for name, a, b in zip(("out", "dx", "ds", "dw1", "dw2"), base, lean):
+        assert torch.equal(a, b), name
+    stages = [s for s, _, _ in Fn.STAGE_MEMORY_LOG]
+    for want in ("forward: after up-projection", "forward: after down-projection", "backward: after GemmDGated",
+                 "backward: after dw2", "backward: after dx", "backward: after dw1"):
+        assert want in stages, (want, stages)
+    assert stages.index("backward: after dw2") < stages.index("backward: after dx")
+    TKp = T * K + E * 128
+    # the default holds dout's column copy and y1s (TKp*(H+I) bytes) while dx_expanded (2*TKp*H) is live
+    assert peak_lean < peak_default - TKp * I // 2, (peak_lean, peak_default)
+
+
+def test_metadata_with_scales_and_preallocated_gated_outputs(sm):
+    """`deepep_topk_to_sonic_metadata_with_scales`: the ten metadata values, the payload's scales gathered to
+    expert-sorted rows in the ISA layout (u8 and compact int32 carriers give the same bytes), and the four
+    up-projection outputs allocated for the call; a payload carrying them makes `_UpProjection` write there."""
+    from sonicmoe.ernie_compat import deepep_topk_to_sonic_metadata, deepep_topk_to_sonic_metadata_with_scales
+    from sonicmoe.functional import attach_preallocated_gated_outputs
+    from sonicmoe.quack_utils import quantize_activation_blockscaled_fast as quant
+    T, H, I, E, K = 512, 512, 256, 8, 4
+    x, dy, w1, w2, _, _ = make_layer(T, H, I, E, K, 151)
+    idx, scores = masked_routing(T, E, K, 6, 152)
+    idx_d, sc_d = idx.to(DEV), scores.to(DEV)
+    counts = torch.bincount(idx[idx >= 0].long(), minlength=6).tolist()
+    q, raw = quant(x.to(DEV))
+    _, words = quant(x.to(DEV), pack_scale_words=True)
+    base = deepep_topk_to_sonic_metadata(idx_d, sc_d, counts, 6)
+    res = deepep_topk_to_sonic_metadata_with_scales(idx_d, sc_d, counts, 6, raw, H)
+    assert len(res) == 11
+    for a, b in zip(base, res[:10]):
+        assert (torch.equal(a, b) if isinstance(a, torch.Tensor) else a == b)
+    TKp = res[6]
+    want = Q.gather_scales_to_isa(raw.cpu(), base[1].cpu(), H)
+    assert torch.equal(res[10].cpu().view(-1), want.view(-1))
+    res_w = deepep_topk_to_sonic_metadata_with_scales(idx_d, sc_d, counts, 6, words, H, gated_output_prototype=q,
+                                                      gated_n=2 * I)
+    assert len(res_w) == 15 and torch.equal(res_w[10], res[10])
+    pre, post, zs, ps = res_w[11:]
+    assert pre.dtype == q.dtype and tuple(pre.shape) == (TKp, 2 * I) and tuple(post.shape) == (TKp, I)
+    assert zs.dtype == torch.uint8 and tuple(zs.shape) == (TKp, 2 * I // 32)
+    assert tuple(ps.shape) == (TKp // 128, 2 * I // 256, 512)
+    bf = deepep_topk_to_sonic_metadata_with_scales(idx_d, sc_d, counts, 6, raw, H, gated_output_prototype=q,
+                                                   gated_n=2 * I, gated_preact_bf16=True,
+                                                   gated_allocate_z_scale=False)
+    assert bf[11].dtype == torch.bfloat16 and bf[13].numel() == 0
+    with pytest.raises(ValueError):
+        deepep_topk_to_sonic_metadata_with_scales(idx_d, sc_d, counts, 6, raw, H, gated_n=2 * I)
+    with pytest.raises(ValueError):
+        deepep_topk_to_sonic_metadata_with_scales(idx_d, sc_d, counts, 6, raw, H, gated_output_prototype=q, gated_n=384)
+    with pytest.raises(ValueError):
+        deepep_topk_to_sonic_metadata_with_scales(idx_d, sc_d, counts, 6, raw[:-1], H)
+    with pytest.raises(ValueError):
+        deepep_topk_to_sonic_metadata_with_scales(idx_d, sc_d, counts, 6, raw, H, gated_output_prototype=x.to(DEV),
+                                                  gated_n=2 * I)
+    # the up-projection writes into the buffers the payload carries
+    w1d = w1[:6].contiguous().to(DEV)
+    for t in (pre, post, zs, ps):
+        t.view(torch.uint8).fill_(0x55)
+    payload = (q, raw, attach_preallocated_gated_outputs(res_w[10], (pre, post, zs, ps)))
+    holder = torch.empty((), dtype=torch.bfloat16, device=DEV).expand(T, H)
+    with sm.enable_fp8(True):
+        sm.functional._UpProjection.apply(holder, w1d, None, res_w[0], TKp, K, 0, res_w[1], res_w[2], res_w[3],
+                                          res_w[4], True, sm.ActivationType.SWIGLU, True, False, payload, None)
+    link = sm.functional._HANDOFF.popitem()[1]
+    assert link["z"][0].data_ptr() == pre.data_ptr() and link["y1"][0].data_ptr() == post.data_ptr()
+    assert link["z"][1].data_ptr() == zs.data_ptr() and link["y1"][1].data_ptr() == ps.data_ptr()
+    with sm.enable_fp8(True):
+        sm.functional._UpProjection.apply(holder, w1d, None, res_w[0], TKp, K, 0, res_w[1], res_w[2], res_w[3],
+                                          res_w[4], True, sm.ActivationType.SWIGLU, True, False, (q, raw), None)
+    ref = sm.functional._HANDOFF.popitem()[1]
+    n = int(res_w[0][-1])                               # rows of the experts' segments (the rest is never written)
+    assert torch.equal(ref["z"][0][:n], pre.view(torch.uint8)[:n])
+    assert torch.equal(ref["y1"][0][:n], post.view(torch.uint8)[:n])
+    nb = n // 128 * (I // 128) * 512                    # the ISA scale tiles of those rows
+    assert torch.equal(ref["z"][1][:n], zs[:n]) and torch.equal(ref["y1"][1][:nb], ps.view(-1)[:nb])
+    torch.cuda.synchronize()
+    sm.ops.check_status(DEV)
