@@ -537,7 +537,10 @@ def _measure(args, cname, world, rank, dev, dist, sonicmoe, ops, strong, extra=F
         "dtype": "fp8_e4m3 (ue8m0 1x32 scales), f32 accumulate", "data": "synthetic",
         "config": dict(config_keys(cname, cfg, world, T, scaling),
                        **({"ep_return_exchange": "peer memory (SONIC_MOE_EP_PEER=1)" if os.getenv("SONIC_MOE_EP_PEER", "0")
-                           == "1" else "nccl all_to_all"} if world > 1 else {})),
+                           == "1" else "nccl all_to_all",
+                           "ep_dispatch": "rows fetched from the sources' mapped memory (pull kernel)"
+                           if os.getenv("SONIC_MOE_EP_DISPATCH", "pull") == "pull" else "nccl all_to_all"}
+                          if world > 1 else {})),
         "mfu_fp8_of_4.5PF": round(F / (ms * 1e-3) / FP8_PEAK_NOMINAL / world, 4),
         "tflops": round(F / (ms * 1e-3) / 1e12, 1),
         "tokens_per_s": round(T_job / (ms * 1e-3), 1),

@@ -106,6 +106,20 @@ int smoe_ep_combine_pull(const void* const* peer_bases, const int32_t* first_row
                          int64_t world, const int32_t* copy_pos, const int32_t* copy_off, const int32_t* send_rank,
                          void* out_bf16, int64_t T, int64_t H, void* stream);
 
+/* Dispatch over NVLink peer memory: this rank fetches the rows addressed to it straight from the sources' buffers
+ * (peer_bases[s]: rank s's buffer as mapped into this process; the same byte layout on every rank: e4m3 tokens [T,H]
+ * at off_q, raw 1x32 scales [T,H/32] at off_raw, the token of every outgoing row [n_send] int32 at off_tok, its local
+ * expert ids [n_send,K] int32 at off_idx, the tokens' probabilities [T,K] f32 at off_probs).  recv_counts[s] rows
+ * come from rank s, starting at row src_off[s] of its send order; they land in q_out / raw_out / idx_out / p_out in
+ * the order an all-to-all delivers them (sources ascending).  idx_out and p_out may both be null (payload only: the
+ * gradient's dispatch in the backward).  The caller orders "every rank has written its buffer" before the call on
+ * the stream.  Plain loads, no multicast, no wait in the kernel.  No counterpart in the reference (DeepEP's dispatch
+ * plays this role outside it).  H % 128 == 0, K <= 32, world <= 16. */
+int smoe_ep_dispatch_pull(const void* const* peer_bases, const int32_t* recv_counts, const int32_t* src_off,
+                          int64_t world, int64_t off_q, int64_t off_raw, int64_t off_tok, int64_t off_idx,
+                          int64_t off_probs, int64_t H, int64_t K, void* q_out, void* raw_out, int32_t* idx_out,
+                          float* p_out, void* stream);
+
 /* ---- MXFP8 1x32 ue8m0 quantizers ------------------------------------------ */
 
 /* Row-wise: x bf16 [M,K] -> e4m3 [M,K] + raw scales [M,K/32] and/or ISA-packed scales

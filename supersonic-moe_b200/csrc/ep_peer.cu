@@ -65,9 +65,89 @@ ep_combine_pull_kernel(PeerTable tab, const int* __restrict__ copy_pos, const in
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Dispatch over peer memory: every rank leaves its quantised tokens (e4m3 [T,H] + raw 1x32 scales [T,H/32]), their
+// probabilities [T,K] and its send lists (token and local expert ids of every outgoing row, grouped by destination
+// rank) in a buffer all ranks have mapped; the destination then fetches the rows addressed to it straight from the
+// sources, in the order an all-to-all would deliver them (sources ascending, each in its send order).  One warp per
+// received row, plain 16-byte loads over NVLink, no staging copy of the outgoing rows, no wait inside the kernel.
+struct PullTable {
+  const uint8_t* base[kMaxPeers];   // rank s's buffer as mapped into this process
+  int recv_off[kMaxPeers + 1];      // first received row that comes from rank s (prefix of the receive counts)
+  int src_off[kMaxPeers];           // where the segment addressed to this rank starts in rank s's send order
+};
+
+struct PullLayout {                 // byte offsets inside every rank's buffer (the same on all ranks)
+  int64_t q, raw, tok, idx, probs;
+};
+
+__global__ void __launch_bounds__(256)
+ep_dispatch_pull_kernel(PullTable tab, PullLayout lay, int world, int H, int K, int n_recv, uint4* __restrict__ q_out,
+                        uint32_t* __restrict__ raw_out, int* __restrict__ idx_out, float* __restrict__ p_out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= n_recv) return;
+  int s = 0;
+  while (s + 1 < world && tab.recv_off[s + 1] <= row) ++s;
+  const int64_t j = tab.src_off[s] + (row - tab.recv_off[s]);      // row of rank s's send order
+  const uint8_t* base = tab.base[s];
+  const int64_t tok = reinterpret_cast<const int*>(base + lay.tok)[j];
+  const int h16 = H >> 4, words = H >> 7;                          // 16-byte pieces of a row; 4-byte scale words
+  const uint4* src = reinterpret_cast<const uint4*>(base + lay.q) + tok * h16;
+  uint4* dst = q_out + row * h16;
+  for (int c0 = 0; c0 < h16; c0 += 32 * 8) {                       // eight remote loads in flight per lane
+    uint4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int c = c0 + u * 32 + lane;
+      if (c < h16) v[u] = src[c];
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int c = c0 + u * 32 + lane;
+      if (c < h16) dst[c] = v[u];
+    }
+  }
+  const uint32_t* rsrc = reinterpret_cast<const uint32_t*>(base + lay.raw) + tok * words;
+  for (int c = lane; c < words; c += 32) raw_out[row * words + c] = rsrc[c];
+  if (idx_out != nullptr && lane < K) {
+    idx_out[row * K + lane] = reinterpret_cast<const int*>(base + lay.idx)[j * K + lane];
+    p_out[row * K + lane] = reinterpret_cast<const float*>(base + lay.probs)[tok * K + lane];
+  }
+}
+
 }  // namespace smoe
 
 extern "C" {
+
+int smoe_ep_dispatch_pull(const void* const* peer_bases, const int32_t* recv_counts, const int32_t* src_off,
+                          int64_t world, int64_t off_q, int64_t off_raw, int64_t off_tok, int64_t off_idx,
+                          int64_t off_probs, int64_t H, int64_t K, void* q_out, void* raw_out, int32_t* idx_out,
+                          float* p_out, void* stream) {
+  if (world <= 0 || world > smoe::kMaxPeers || H <= 0 || H % 128 || K <= 0 || K > 32) return SMOE_ERR_SHAPE;
+  if ((idx_out == nullptr) != (p_out == nullptr)) return SMOE_ERR_ARG;
+  if ((off_q | off_raw | off_tok | off_idx | off_probs) & 15) return SMOE_ERR_ALIGN;
+  smoe::PullTable tab{};
+  int64_t n = 0;
+  for (int r = 0; r < world; ++r) {
+    if (recv_counts[r] < 0 || src_off[r] < 0) return SMOE_ERR_ARG;
+    if ((uintptr_t)peer_bases[r] & 15) return SMOE_ERR_ALIGN;
+    tab.base[r] = (const uint8_t*)peer_bases[r];
+    tab.recv_off[r] = (int)n;
+    tab.src_off[r] = src_off[r];
+    n += recv_counts[r];
+  }
+  tab.recv_off[world] = (int)n;
+  if (n == 0) return SMOE_OK;
+  if (n > INT32_MAX) return SMOE_ERR_SHAPE;
+  if (!q_out || !raw_out) return SMOE_ERR_ARG;
+  if (((uintptr_t)q_out & 15) || ((uintptr_t)raw_out & 3)) return SMOE_ERR_ALIGN;
+  smoe::PullLayout lay{off_q, off_raw, off_tok, off_idx, off_probs};
+  const int64_t blocks = (n + 7) / 8;
+  smoe::ep_dispatch_pull_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+      tab, lay, (int)world, (int)H, (int)K, (int)n, (uint4*)q_out, (uint32_t*)raw_out, idx_out, p_out);
+  return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
+}
 
 int smoe_ep_combine_pull(const void* const* peer_bases, const int32_t* first_row, const int32_t* send_off,
                          int64_t world, const int32_t* copy_pos, const int32_t* copy_off, const int32_t* send_rank,

@@ -33,6 +33,13 @@ import torch.distributed as dist
 # each other's memory (torch symmetric memory).  Default: NCCL all-to-all + a local reduction, which measured
 # faster on 4 GPUs (5.03 vs 5.48 ms per step on the reference-shape layer).
 USE_PEER_COMBINE = os.getenv("SONIC_MOE_EP_PEER", "0") == "1"
+# SONIC_MOE_EP_DISPATCH=pull: the two FP8 dispatch exchanges (x in the forward, dout in the backward) are fetched by
+# the destination rank straight from the sources' quantised tokens over NVLink (csrc/ep_peer.cu) - no gathered copy
+# of the outgoing rows, no all-to-all, no packing of scales / ids / probabilities into a side exchange; "nccl": the
+# rows are gathered and travel through NCCL all-to-alls.  Needs the same peer mapping as above.
+DISPATCH = os.getenv("SONIC_MOE_EP_DISPATCH", "pull")
+if DISPATCH not in ("pull", "nccl"):
+    raise ValueError(f"SONIC_MOE_EP_DISPATCH={DISPATCH!r}: expected 'pull' or 'nccl'")
 
 
 _COMM_STREAMS: dict = {}
@@ -73,6 +80,72 @@ class PeerArena:
         dist.all_reduce(self.token, group=self.group)
 
 
+def _align256(n: int) -> int:
+    return (n + 255) // 256 * 256
+
+
+class DispatchArena:
+    """One byte buffer per rank, mapped by every rank of the group, from which the peers fetch what this rank sends:
+    two payload slots (x in the forward, dout in the backward: e4m3 [T,H] + raw scales [T,H/32]), the tokens'
+    probabilities [T,K] f32, and the send lists (token [n_send] and local expert ids [n_send,K] of every outgoing
+    row).  The layout is a function of (T capacity, H, K, world) only, hence the same on all ranks."""
+
+    def __init__(self, group, t_cap: int, H: int, K: int, world: int, device):
+        import torch.distributed._symmetric_memory as symm
+        self.t_cap, self.H, self.K, self.world = t_cap, H, K, world
+        cap = t_cap * min(K, world)
+        at = 0
+        self.off_q, self.off_raw = [], []
+        for _ in range(2):
+            self.off_q.append(at)
+            at += _align256(t_cap * H)
+            self.off_raw.append(at)
+            at += _align256(t_cap * (H // 32))
+        self.off_probs = at
+        at += _align256(t_cap * K * 4)
+        self.off_tok = at
+        at += _align256(cap * 4)
+        self.off_idx = at
+        at += _align256(cap * K * 4)
+        self.buf = symm.empty(at, dtype=torch.uint8, device=device)
+        self.hdl = symm.rendezvous(self.buf, group.group_name)
+        self.ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+        self.token = torch.zeros(1, dtype=torch.float32, device=device)
+        self.group = group
+
+    def fits(self, T: int, H: int, K: int, world: int) -> bool:
+        return T <= self.t_cap and (H, K, world) == (self.H, self.K, self.world)
+
+    def payload(self, slot: int, T: int):
+        """(q [T,H], raw [T,H/32]) views of payload slot `slot`."""
+        H = self.H
+        q = self.buf[self.off_q[slot]: self.off_q[slot] + T * H].view(T, H)
+        raw = self.buf[self.off_raw[slot]: self.off_raw[slot] + T * (H // 32)].view(T, H // 32)
+        return q, raw
+
+    def publish_lists(self, plan: "DispatchPlan", probs=None):
+        """This rank's send lists (and, in the forward, its tokens' probabilities) into the mapped buffer."""
+        n, K = plan.n_send, self.K
+        if n:
+            self.buf[self.off_tok: self.off_tok + n * 4].view(torch.int32).copy_(plan.send_tok_i32)
+            self.buf[self.off_idx: self.off_idx + n * K * 4].view(torch.int32).view(n, K).copy_(plan.send_idx)
+        if probs is not None and plan.T:
+            self.buf[self.off_probs: self.off_probs + plan.T * K * 4].view(torch.float32).view(plan.T, K).copy_(probs)
+
+    def layout(self, slot: int):
+        return (self.off_q[slot], self.off_raw[slot], self.off_tok, self.off_idx, self.off_probs)
+
+    def everyone_has_written(self):
+        """Stream-ordered: returns (on the stream) once every rank's earlier work on its stream is done."""
+        dist.all_reduce(self.token, group=self.group)
+
+    def pull(self, plan: "DispatchPlan", slot: int, with_meta: bool):
+        from . import ops
+        self.everyone_has_written()
+        return ops.ep_dispatch_pull(self.ptrs, plan.recv_counts, plan.src_seg_off, self.layout(slot), self.H, self.K,
+                                    self.buf.device, with_meta=with_meta)
+
+
 class DispatchPlan:
     """Who goes where, built from the top-k indices of this rank's tokens.
 
@@ -110,6 +183,8 @@ class DispatchPlan:
         self.n_send, self.n_recv = sum(self.send_counts), sum(self.recv_counts)
         # where this rank's rows start inside rank r's receive order (sources ascending), and the send offsets
         self.first_row_at = [sum(int(M[s][r]) for s in range(me)) for r in range(world)]
+        # where the segment addressed to this rank starts inside rank s's send order (destinations ascending)
+        self.src_seg_off = [sum(int(M[s][r]) for r in range(me)) for s in range(world)]
         self.send_off = [sum(self.send_counts[:r]) for r in range(world)]
         self.max_recv_rows = max(sum(int(M[s][r]) for s in range(world)) for r in range(world))
         self.tokens_all = [int(M[s][-1]) for s in range(world)]
@@ -230,6 +305,16 @@ class _Dispatch(torch.autograd.Function):
         tok, K, H = plan.send_tok, plan.K, x.shape[1]
         # the wide payload travels as it is (no repacking copies); scales, expert ids and probabilities share
         # one narrow exchange
+        disp = getattr(plan, "disp", None)
+        if fp8 and disp is not None:
+            # peers fetch this rank's rows from its quantised tokens in place; this rank fetches what is addressed to it
+            from . import ops
+            ops.quant_rows(x.contiguous(), raw=True, out=disp.payload(0, plan.T))
+            disp.publish_lists(plan, probs.detach().float())
+            q_recv, raw_recv, idx_recv, p_recv = disp.pull(plan, 0, True)
+            holder = torch.empty((), dtype=x.dtype, device=x.device).expand(plan.n_recv, H)
+            ctx.mark_non_differentiable(q_recv, raw_recv, idx_recv)
+            return holder, p_recv, q_recv, raw_recv, idx_recv
         meta = [plan.send_idx, probs.float()[tok]]
         if fp8:
             from . import ops
@@ -286,6 +371,14 @@ class _Combine(torch.autograd.Function):
     def backward(ctx, dout):
         plan, tok = ctx.plan, ctx.plan.send_tok
         dout = dout.contiguous()
+        disp = getattr(plan, "disp", None)
+        if ctx.handle is not None and disp is not None:
+            from . import ops
+            ops.quant_rows(dout.to(torch.bfloat16), raw=True, out=disp.payload(1, plan.T))
+            disp.publish_lists(plan)      # a later forward of the same layer may have replaced the lists since
+            q_recv, raw_recv, _, _ = disp.pull(plan, 1, False)
+            ctx.handle.put(q_recv, raw_recv)
+            return torch.empty((), dtype=dout.dtype, device=dout.device).expand(plan.n_recv, dout.shape[1]), None, None
         if ctx.handle is not None:
             from . import ops
             q, raw, _ = ops.quant_rows(dout.to(torch.bfloat16), raw=True)
@@ -306,6 +399,25 @@ class ExpertParallelMoE:
         self._arena = None
         self._peer_ok = USE_PEER_COMBINE and expert_fn is None      # read at construction
         self._place = None
+        self._disp = None
+        self._disp_ok = DISPATCH == "pull" and expert_fn is None and payload == "fp8"
+
+    def _dispatch_arena_for(self, plan: DispatchPlan, H: int, device):
+        """The mapped buffer the peers fetch this rank's rows from, (re)allocated collectively when the largest token
+        count of any rank (known to all ranks from the plan) outgrows it."""
+        group = self.group if self.group is not None else dist.group.WORLD
+        world = dist.get_world_size(group)
+        if not self._disp_ok or device.type != "cuda" or world < 2 or H % 128 or plan.K > 32:
+            return None
+        need = max(plan.tokens_all)
+        if self._disp is None or not self._disp.fits(need, H, plan.K, world):
+            try:
+                self._disp = DispatchArena(group, need, H, plan.K, world, device)
+            except Exception as exc:      # no peer mapping on this system: every rank fails alike
+                import warnings
+                warnings.warn(f"expert-parallel peer-memory dispatch unavailable ({exc!r}); using NCCL all-to-all")
+                self._disp_ok, self._disp = False, None
+        return self._disp
 
     def _arena_for(self, plan: DispatchPlan, H: int, device):
         """The mapped buffer for this call's partial rows, (re)allocated collectively when the largest receive
@@ -341,6 +453,7 @@ class ExpertParallelMoE:
         self.last_rows_received = plan.n_recv
         fp8 = self.payload == "fp8"
         self.tokens_per_local_expert = plan.tokens_per_local_expert
+        plan.disp = self._dispatch_arena_for(plan, x.shape[1], x.device) if fp8 else None
         rows, probs, q, raw, local_idx = _Dispatch.apply(x, topk_scores, plan, fp8)
         handle = None
         if fp8:
@@ -427,6 +540,7 @@ def parity_against_single_gpu(group=None, device=None, T=1024, H=512, I=256, K=4
     res = dict(out=st(out, mine[0]), dx=st(xd.grad, mine[1]), ds=st(sd.grad, mine[2]), dw1=st(w1_grad, dw1_ref),
                dw2=st(w2_grad, dw2_ref))
     res["used_peer"] = ep._arena is not None
+    res["used_pull_dispatch"] = ep._disp is not None
     res["rows_received"] = int(ep.last_rows_received)
     return res
 

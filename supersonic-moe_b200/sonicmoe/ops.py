@@ -203,13 +203,43 @@ def ep_combine_pull(peer_ptrs, first_row, send_off, copy_pos, copy_off, send_ran
     return out
 
 
+@_timed
+def ep_dispatch_pull(peer_ptrs, recv_counts, src_off, layout, H, K, device, with_meta=True):
+    """Fetch the rows addressed to this rank straight from the sources' mapped buffers (peer_ptrs: their device
+    addresses in this process; recv_counts / src_off: host ints per source; layout: byte offsets (q, raw, tok, idx,
+    probs) inside every buffer) -> (e4m3 rows [n,H], raw scales [n,H/32], local expert ids [n,K] | None,
+    probabilities [n,K] | None), sources ascending."""
+    import ctypes
+    world = len(peer_ptrs)
+    n = int(sum(recv_counts))
+    q = torch.empty(n, H, dtype=_U8, device=device)
+    raw = torch.empty(n, H // 32, dtype=_U8, device=device)
+    idx = torch.empty(n, K, dtype=_I32, device=device) if with_meta else None
+    p = torch.empty(n, K, dtype=torch.float32, device=device) if with_meta else None
+    bases = (ctypes.c_void_p * world)(*[int(v) for v in peer_ptrs])
+    rc = (ctypes.c_int32 * world)(*[int(v) for v in recv_counts])
+    so = (ctypes.c_int32 * world)(*[int(v) for v in src_off])
+    oq, oraw, otok, oidx, oprobs = (int(v) for v in layout)
+    check(lib.smoe_ep_dispatch_pull(bases, rc, so, world, oq, oraw, otok, oidx, oprobs, H, K, _p(q), _p(raw), _p(idx),
+                                    _p(p), _stream()), "ep_dispatch_pull")
+    return q, raw, idx, p
+
+
 # ---------------------------------------------------------------- quantizers
 @_timed
-def quant_rows(x, raw=True, isa=False):
-    """bf16 [M,K] -> (e4m3 bytes [M,K] u8, raw scales [M,K/32] u8 | None, ISA scales u8 | None)."""
+def quant_rows(x, raw=True, isa=False, out=None):
+    """bf16 [M,K] -> (e4m3 bytes [M,K] u8, raw scales [M,K/32] u8 | None, ISA scales u8 | None).  `out` = (q, raw)
+    u8 buffers of those shapes to fill instead of fresh allocations."""
     _cuda(x)
     assert x.dtype == torch.bfloat16 and x.ndim == 2
     M, K = x.shape
+    if out is not None:
+        q, r = out
+        _cuda(q, r)
+        assert q.dtype == _U8 and tuple(q.shape) == (M, K) and r.dtype == _U8 and tuple(r.shape) == (M, K // 32)
+        i = torch.empty(isa_bytes(M, K), dtype=_U8, device=x.device) if isa else None
+        check(lib.smoe_quant_rows(_p(x), M, K, _p(q), _p(r), _p(i), _stream()), "quant_rows")
+        return q, r, i
     q = torch.empty(M, K, dtype=_U8, device=x.device)
     r = torch.empty(M, K // 32, dtype=_U8, device=x.device) if raw else None
     i = torch.empty(isa_bytes(M, K), dtype=_U8, device=x.device) if isa else None

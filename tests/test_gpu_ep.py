@@ -19,7 +19,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, q, peer, starve):
+def _worker(rank, world, port, q, peer, starve, dispatch="pull"):
     try:
         import datetime
         import torch.distributed as dist
@@ -30,7 +30,10 @@ def _worker(rank, world, port, q, peer, starve):
                                 timeout=datetime.timedelta(seconds=120))
         import sonicmoe.ep as ep_mod
         ep_mod.USE_PEER_COMBINE = peer          # return exchanges over mapped peer memory vs NCCL all-to-all
+        ep_mod.DISPATCH = "pull" if dispatch == "both" else dispatch   # FP8 rows fetched from the peers vs all-to-all
         res = ep_mod.parity_against_single_gpu(dist.group.WORLD, dev, starve_last_rank=starve)
+        if dispatch == "both":
+            res["modes_bit_identical"] = _same_bits_either_dispatch(ep_mod, dev, rank, world)
         q.put((rank, res))
         dist.barrier()
         dist.destroy_process_group()
@@ -39,12 +42,49 @@ def _worker(rank, world, port, q, peer, starve):
         raise
 
 
-def _launch(world, peer, starve):
+def _same_bits_either_dispatch(ep_mod, dev, rank, world):
+    """The same expert-parallel step, twice each way and interleaved (forward A, forward B, backward A, backward
+    B on one layer object): rows fetched from the peers' memory give the bits of the NCCL all-to-all path."""
+    import torch.distributed as dist
+    T, H, I, K, El = 768, 512, 256, 4, 4
+    E = El * world
+    g = torch.Generator().manual_seed(900 + rank)
+    gw = torch.Generator().manual_seed(899)
+    w1 = (torch.randn(E, 2 * I, H, generator=gw) * 0.02).to(torch.bfloat16)[rank * El:(rank + 1) * El].contiguous()
+    w2 = (torch.randn(E, H, I, generator=gw) * 0.02).to(torch.bfloat16)[rank * El:(rank + 1) * El].contiguous()
+    batches = []
+    for _ in range(2):
+        x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+        dy = torch.randn(T, H, generator=g).to(torch.bfloat16)
+        vals, idx = torch.randn(T, E, generator=g).topk(K, dim=-1)
+        batches.append((x, dy, torch.softmax(vals, -1), idx.to(torch.int32)))
+
+    def run(mode):
+        ep_mod.DISPATCH = mode
+        layer = ep_mod.ExpertParallelMoE(E, K, dist.group.WORLD)
+        w1d, w2d = w1.to(dev).requires_grad_(True), w2.to(dev).requires_grad_(True)
+        live = []
+        for x, dy, sc, idx in batches:          # both forwards before either backward
+            xd, sd = x.to(dev).requires_grad_(True), sc.to(dev).requires_grad_(True)
+            live.append((layer(xd, idx.to(dev), sd, w1d, w2d), xd, sd, dy))
+        outs = []
+        for out, xd, sd, dy in live:
+            out.backward(dy.to(dev))
+            outs += [out.detach(), xd.grad, sd.grad]
+        torch.cuda.synchronize(dev)
+        assert (layer._disp is not None) == (mode == "pull")
+        return outs + [w1d.grad, w2d.grad]
+
+    a, b = run("nccl"), run("pull")
+    return all(torch.equal(u, v) for u, v in zip(a, b))
+
+
+def _launch(world, peer, starve, dispatch="pull"):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q, peer, starve)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, peer, starve, dispatch)) for r in range(world)]
     for p in procs:
         p.start()
     results = {}
@@ -76,6 +116,7 @@ def test_ep_two_gpus_matches_single_gpu_layer(peer):
     from sonicmoe.ep import PARITY_LIMITS
     for rank, res in _launch(2, peer, False).items():
         assert res.pop("used_peer") == peer, "the requested return-exchange path was not the one that ran"
+        assert res.pop("used_pull_dispatch") is True
         assert res.pop("rows_received") > 0
         for name, (cos, rr) in res.items():
             cmin, rmax = PARITY_LIMITS[name]
@@ -92,7 +133,24 @@ def test_ep_rank_that_receives_no_tokens():
     results = _launch(2, False, True)
     assert results[1]["rows_received"] == 0 and results[0]["rows_received"] > 0
     for rank, res in results.items():
+        res.pop("used_peer"), res.pop("rows_received"), res.pop("used_pull_dispatch")
+        for name, (cos, rr) in res.items():
+            cmin, rmax = PARITY_LIMITS[name]
+            assert cos > cmin and rr < rmax, (rank, name, cos, rr)
+
+
+def test_ep_dispatch_through_nccl_and_both_dispatch_paths_give_the_same_bits():
+    """SONIC_MOE_EP_DISPATCH=nccl (rows gathered and sent through all-to-alls) still matches the single-GPU layer, and
+    the default (rows fetched by the destination from the sources' mapped memory) reproduces it bit for bit, also
+    with two forwards of one layer in flight before their backwards."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from sonicmoe.ep import PARITY_LIMITS
+    for rank, res in _launch(2, False, False, "nccl").items():
+        assert res.pop("used_pull_dispatch") is False
         res.pop("used_peer"), res.pop("rows_received")
         for name, (cos, rr) in res.items():
             cmin, rmax = PARITY_LIMITS[name]
             assert cos > cmin and rr < rmax, (rank, name, cos, rr)
+    for rank, res in _launch(2, False, False, "both").items():
+        assert res["modes_bit_identical"] is True, rank
