@@ -113,10 +113,12 @@ int smoe_ep_combine_pull(const void* const* peer_bases, const int32_t* first_row
  * come from rank s, starting at row src_off[s] of its send order; they land in q_out / raw_out / idx_out / p_out in
  * the order an all-to-all delivers them (sources ascending).  idx_out and p_out may both be null (payload only: the
  * gradient's dispatch in the backward).  The caller orders "every rank has written its buffer" before the call on
- * the stream.  Plain loads, no multicast, no wait in the kernel.  No counterpart in the reference (DeepEP's dispatch
- * plays this role outside it).  H % 128 == 0, K <= 32, world <= 16. */
+ * the stream.  `rank` (this rank's index among the sources) only sets where the grid starts: with the next rank's
+ * rows, so that the ranks do not all read from the same source at the same time.  Plain loads, no multicast, no
+ * wait in the kernel.  No counterpart in the reference (DeepEP's dispatch plays this role outside it).
+ * H % 128 == 0, K <= 32, world <= 16. */
 int smoe_ep_dispatch_pull(const void* const* peer_bases, const int32_t* recv_counts, const int32_t* src_off,
-                          int64_t world, int64_t off_q, int64_t off_raw, int64_t off_tok, int64_t off_idx,
+                          int64_t world, int64_t rank, int64_t off_q, int64_t off_raw, int64_t off_tok, int64_t off_idx,
                           int64_t off_probs, int64_t H, int64_t K, void* q_out, void* raw_out, int32_t* idx_out,
                           float* p_out, void* stream);
 

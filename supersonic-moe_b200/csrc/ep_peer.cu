@@ -82,11 +82,17 @@ struct PullLayout {                 // byte offsets inside every rank's buffer (
 };
 
 __global__ void __launch_bounds__(256)
-ep_dispatch_pull_kernel(PullTable tab, PullLayout lay, int world, int H, int K, int n_recv, uint4* __restrict__ q_out,
-                        uint32_t* __restrict__ raw_out, int* __restrict__ idx_out, float* __restrict__ p_out) {
+ep_dispatch_pull_kernel(PullTable tab, PullLayout lay, int world, int H, int K, int n_recv, int rot,
+                        uint4* __restrict__ q_out, uint32_t* __restrict__ raw_out, int* __restrict__ idx_out,
+                        float* __restrict__ p_out) {
   const int lane = threadIdx.x & 31;
-  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  // The grid walks the received rows starting at `rot` (the first row that comes from the NEXT rank) and wraps
+  // around: rank r begins with source r+1, so at any moment the ranks read from different sources instead of all
+  // draining rank 0's links first.
+  int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= n_recv) return;
+  row += rot;
+  if (row >= n_recv) row -= n_recv;
   int s = 0;
   while (s + 1 < world && tab.recv_off[s + 1] <= row) ++s;
   const int64_t j = tab.src_off[s] + (row - tab.recv_off[s]);      // row of rank s's send order
@@ -121,10 +127,11 @@ ep_dispatch_pull_kernel(PullTable tab, PullLayout lay, int world, int H, int K, 
 extern "C" {
 
 int smoe_ep_dispatch_pull(const void* const* peer_bases, const int32_t* recv_counts, const int32_t* src_off,
-                          int64_t world, int64_t off_q, int64_t off_raw, int64_t off_tok, int64_t off_idx,
+                          int64_t world, int64_t rank, int64_t off_q, int64_t off_raw, int64_t off_tok, int64_t off_idx,
                           int64_t off_probs, int64_t H, int64_t K, void* q_out, void* raw_out, int32_t* idx_out,
                           float* p_out, void* stream) {
   if (world <= 0 || world > smoe::kMaxPeers || H <= 0 || H % 128 || K <= 0 || K > 32) return SMOE_ERR_SHAPE;
+  if (rank < 0 || rank >= world) return SMOE_ERR_ARG;
   if ((idx_out == nullptr) != (p_out == nullptr)) return SMOE_ERR_ARG;
   if ((off_q | off_raw | off_tok | off_idx | off_probs) & 15) return SMOE_ERR_ALIGN;
   smoe::PullTable tab{};
@@ -144,8 +151,10 @@ int smoe_ep_dispatch_pull(const void* const* peer_bases, const int32_t* recv_cou
   if (((uintptr_t)q_out & 15) || ((uintptr_t)raw_out & 3)) return SMOE_ERR_ALIGN;
   smoe::PullLayout lay{off_q, off_raw, off_tok, off_idx, off_probs};
   const int64_t blocks = (n + 7) / 8;
+  const int rot = tab.recv_off[(rank + 1) % world];     // == n when the ranks after this one send nothing: wraps to 0
   smoe::ep_dispatch_pull_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
-      tab, lay, (int)world, (int)H, (int)K, (int)n, (uint4*)q_out, (uint32_t*)raw_out, idx_out, p_out);
+      tab, lay, (int)world, (int)H, (int)K, (int)n, rot >= n ? 0 : rot, (uint4*)q_out, (uint32_t*)raw_out, idx_out,
+      p_out);
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }
 

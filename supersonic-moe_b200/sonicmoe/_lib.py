@@ -24,7 +24,7 @@ SIGNATURES = {
     "smoe_ep_plan_dest": (_I, [_P, _L, _L, _L, _L, _P, _P, _P]),
     "smoe_ep_plan_send_idx": (_I, [_P, _P, _P, _L, _L, _L, _L, _P, _P, _P]),
     "smoe_ep_combine_pull": (_I, [_P, _P, _P, _L, _P, _P, _P, _P, _L, _L, _P]),
-    "smoe_ep_dispatch_pull": (_I, [_P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _P, _P, _P, _P, _P]),
+    "smoe_ep_dispatch_pull": (_I, [_P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _P, _P, _P, _P, _P]),
     "smoe_quant_rows": (_I, [_P, _L, _L, _P, _P, _P, _P]),
     "smoe_quant_rows_gather": (_I, [_P, _P, _P, _L, _L, _P, _P, _P]),
     "smoe_quant_dual_gather": (_I, [_P, _P, _P, _L, _L, _P, _P, _P, _P, _P]),

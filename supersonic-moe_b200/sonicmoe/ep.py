@@ -142,8 +142,8 @@ class DispatchArena:
     def pull(self, plan: "DispatchPlan", slot: int, with_meta: bool):
         from . import ops
         self.everyone_has_written()
-        return ops.ep_dispatch_pull(self.ptrs, plan.recv_counts, plan.src_seg_off, self.layout(slot), self.H, self.K,
-                                    self.buf.device, with_meta=with_meta)
+        return ops.ep_dispatch_pull(self.ptrs, plan.recv_counts, plan.src_seg_off, dist.get_rank(self.group),
+                                    self.layout(slot), self.H, self.K, self.buf.device, with_meta=with_meta)
 
 
 class DispatchPlan:

@@ -204,7 +204,7 @@ def ep_combine_pull(peer_ptrs, first_row, send_off, copy_pos, copy_off, send_ran
 
 
 @_timed
-def ep_dispatch_pull(peer_ptrs, recv_counts, src_off, layout, H, K, device, with_meta=True):
+def ep_dispatch_pull(peer_ptrs, recv_counts, src_off, rank, layout, H, K, device, with_meta=True):
     """Fetch the rows addressed to this rank straight from the sources' mapped buffers (peer_ptrs: their device
     addresses in this process; recv_counts / src_off: host ints per source; layout: byte offsets (q, raw, tok, idx,
     probs) inside every buffer) -> (e4m3 rows [n,H], raw scales [n,H/32], local expert ids [n,K] | None,
@@ -220,7 +220,7 @@ def ep_dispatch_pull(peer_ptrs, recv_counts, src_off, layout, H, K, device, with
     rc = (ctypes.c_int32 * world)(*[int(v) for v in recv_counts])
     so = (ctypes.c_int32 * world)(*[int(v) for v in src_off])
     oq, oraw, otok, oidx, oprobs = (int(v) for v in layout)
-    check(lib.smoe_ep_dispatch_pull(bases, rc, so, world, oq, oraw, otok, oidx, oprobs, H, K, _p(q), _p(raw), _p(idx),
+    check(lib.smoe_ep_dispatch_pull(bases, rc, so, world, int(rank), oq, oraw, otok, oidx, oprobs, H, K, _p(q), _p(raw), _p(idx),
                                     _p(p), _stream()), "ep_dispatch_pull")
     return q, raw, idx, p
 
