@@ -536,8 +536,10 @@ def _measure(args, cname, world, rank, dev, dist, sonicmoe, ops, strong, extra=F
         "vs_baseline": round(us / PUBLISHED_US[cname], 4) if (world == 1 and cname in PUBLISHED_US) else None,
         "dtype": "fp8_e4m3 (ue8m0 1x32 scales), f32 accumulate", "data": "synthetic",
         "config": dict(config_keys(cname, cfg, world, T, scaling),
-                       **({"ep_return_exchange": "peer memory (SONIC_MOE_EP_PEER=1)" if os.getenv("SONIC_MOE_EP_PEER", "0")
-                           == "1" else "nccl all_to_all",
+                       **({"ep_return_exchange": {"1": "peer memory, both directions (SONIC_MOE_EP_PEER=1)",
+                                                  "fwd": "forward: peer-memory pull fused with the reduction; backward "
+                                                         "(dx): nccl all_to_all under the weight gradients",
+                                                  "0": "nccl all_to_all"}[os.getenv("SONIC_MOE_EP_PEER", "fwd")],
                            "ep_dispatch": "rows fetched from the sources' mapped memory (pull kernel)"
                            if os.getenv("SONIC_MOE_EP_DISPATCH", "pull") == "pull" else "nccl all_to_all"}
                           if world > 1 else {})),

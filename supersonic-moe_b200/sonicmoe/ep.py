@@ -28,11 +28,20 @@ import os
 import torch
 import torch.distributed as dist
 
-# SONIC_MOE_EP_PEER=1: the two bf16 return exchanges (forward combine, backward dx) read the partial rows straight
-# from the owners' memory over NVLink, fused with the per-token reduction (csrc/ep_peer.cu); needs ranks that can map
-# each other's memory (torch symmetric memory).  Default: NCCL all-to-all + a local reduction, which measured
-# faster on 4 GPUs (5.03 vs 5.48 ms per step on the reference-shape layer).
-USE_PEER_COMBINE = os.getenv("SONIC_MOE_EP_PEER", "0") == "1"
+# SONIC_MOE_EP_PEER: how the two bf16 return exchanges (forward combine, backward dx) travel.
+#   "fwd" (default)  the forward's return reads the partial rows straight from the owners' memory over NVLink, fused
+#                    with the per-token reduction (csrc/ep_peer.cu); the backward's (dx) is an NCCL all-to-all on the
+#                    communication stream, where it runs underneath the weight-gradient GEMMs
+#   "1"              both read peer memory (the dx return then follows the weight gradients: nothing hides it)
+#   "0"              both are NCCL all-to-alls followed by a local reduction
+# Reading peer memory needs ranks that can map each other's memory (torch symmetric memory); if that fails the
+# layer warns once and uses NCCL.  Measured on the reference-shape layer, first-10-step medians: 8 GPUs 5.37 ms
+# ("fwd") against 5.55 ("0"); 2 GPUs 3.86 ("1") against 3.92 ("0").
+_PEER_MODE = os.getenv("SONIC_MOE_EP_PEER", "fwd")
+if _PEER_MODE not in ("0", "1", "fwd"):
+    raise ValueError(f"SONIC_MOE_EP_PEER={_PEER_MODE!r}: expected '0', '1' or 'fwd'")
+USE_PEER_COMBINE = _PEER_MODE in ("1", "fwd")
+PEER_COMBINE_BACKWARD = _PEER_MODE == "1"
 # SONIC_MOE_EP_DISPATCH=pull: the two FP8 dispatch exchanges (x in the forward, dout in the backward) are fetched by
 # the destination rank straight from the sources' quantised tokens over NVLink (csrc/ep_peer.cu) - no gathered copy
 # of the outgoing rows, no all-to-all, no packing of scales / ids / probabilities into a side exchange; "nccl": the
@@ -335,7 +344,7 @@ class _Dispatch(torch.autograd.Function):
         plan = ctx.plan
         dx = dp = None
         if ctx.needs_input_grad[0] and dx_recv is not None:
-            arena = getattr(plan, "arena", None)
+            arena = getattr(plan, "arena", None) if getattr(plan, "arena_backward", True) else None
             if arena is not None:       # the choice of path must not depend on this rank's data: all ranks pull
                 if dx_recv.numel() and not arena.holds(dx_recv):    # normally already where the peers read it
                     arena.view(dx_recv.shape[0]).copy_(dx_recv)
@@ -398,6 +407,7 @@ class ExpertParallelMoE:
         self.expert_fn = expert_fn or self._sonic_experts
         self._arena = None
         self._peer_ok = USE_PEER_COMBINE and expert_fn is None      # read at construction
+        self._peer_backward = PEER_COMBINE_BACKWARD
         self._place = None
         self._disp = None
         self._disp_ok = DISPATCH == "pull" and expert_fn is None and payload == "fp8"
@@ -444,7 +454,7 @@ class ExpertParallelMoE:
             holder, qbytes = rows
             return run_sonic_moe(qbytes, local_idx, probs, self.K, self.El, w1, w2, fp8=True, fp8_scale=fp8_scale,
                                  fp8_combine_grad_handle=handle, tokens_per_expert=counts, grad_holder=holder,
-                                 out=self._place, dx_out=self._place)
+                                 out=self._place, dx_out=self._place if self._peer_backward else None)
         return run_sonic_moe(rows, local_idx, probs, self.K, self.El, w1, w2, fp8=True, tokens_per_expert=counts)
 
     def __call__(self, x, topk_idx, topk_scores, w1, w2):
@@ -462,6 +472,7 @@ class ExpertParallelMoE:
             rows = (rows, q)
         arena = self._arena_for(plan, x.shape[1], x.device) if fp8 else None
         plan.arena = arena
+        plan.arena_backward = self._peer_backward
         # forward output and, later, dx of the local experts land in the mapped buffer (one region, used in turn)
         self._place = arena.view(plan.n_recv) if (arena is not None and plan.n_recv > 0) else None
         o_recv = self.expert_fn(rows, local_idx, probs, w1, w2, raw, handle)

@@ -29,7 +29,8 @@ def _worker(rank, world, port, q, peer, starve, dispatch="pull"):
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
                                 timeout=datetime.timedelta(seconds=120))
         import sonicmoe.ep as ep_mod
-        ep_mod.USE_PEER_COMBINE = peer          # return exchanges over mapped peer memory vs NCCL all-to-all
+        # return exchanges over mapped peer memory ("1": both, "fwd": the forward's only) vs NCCL all-to-all ("0")
+        ep_mod.USE_PEER_COMBINE, ep_mod.PEER_COMBINE_BACKWARD = peer in ("1", "fwd"), peer == "1"
         ep_mod.DISPATCH = "pull" if dispatch == "both" else dispatch   # FP8 rows fetched from the peers vs all-to-all
         res = ep_mod.parity_against_single_gpu(dist.group.WORLD, dev, starve_last_rank=starve)
         if dispatch == "both":
@@ -109,13 +110,13 @@ def _launch(world, peer, starve, dispatch="pull"):
     return results
 
 
-@pytest.mark.parametrize("peer", [False, True])
+@pytest.mark.parametrize("peer", ["0", "fwd", "1"])
 def test_ep_two_gpus_matches_single_gpu_layer(peer):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     from sonicmoe.ep import PARITY_LIMITS
     for rank, res in _launch(2, peer, False).items():
-        assert res.pop("used_peer") == peer, "the requested return-exchange path was not the one that ran"
+        assert res.pop("used_peer") == (peer != "0"), "the requested return-exchange path was not the one that ran"
         assert res.pop("used_pull_dispatch") is True
         assert res.pop("rows_received") > 0
         for name, (cos, rr) in res.items():
@@ -130,7 +131,7 @@ def test_ep_rank_that_receives_no_tokens():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     from sonicmoe.ep import PARITY_LIMITS
-    results = _launch(2, False, True)
+    results = _launch(2, "fwd", True)
     assert results[1]["rows_received"] == 0 and results[0]["rows_received"] > 0
     for rank, res in results.items():
         res.pop("used_peer"), res.pop("rows_received"), res.pop("used_pull_dispatch")
@@ -146,11 +147,11 @@ def test_ep_dispatch_through_nccl_and_both_dispatch_paths_give_the_same_bits():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     from sonicmoe.ep import PARITY_LIMITS
-    for rank, res in _launch(2, False, False, "nccl").items():
+    for rank, res in _launch(2, "0", False, "nccl").items():
         assert res.pop("used_pull_dispatch") is False
         res.pop("used_peer"), res.pop("rows_received")
         for name, (cos, rr) in res.items():
             cmin, rmax = PARITY_LIMITS[name]
             assert cos > cmin and rr < rmax, (rank, name, cos, rr)
-    for rank, res in _launch(2, False, False, "both").items():
+    for rank, res in _launch(2, "fwd", False, "both").items():
         assert res["modes_bit_identical"] is True, rank
