@@ -384,7 +384,7 @@ def _measure(args, cname, world, rank, dev, dist, sonicmoe, ops, strong, extra=F
         sub = dict(cfg, seed=cfg["seed"] + 1000 * (rank + 1), E=E)
         inp = make_inputs(sub, dev, T=T, weights=False)
         from sonicmoe.ep import ExpertParallelMoE
-        ep = ExpertParallelMoE(E, K, dist.group.WORLD)
+        ep = ExpertParallelMoE(E, K, dist.group.WORLD, capacity_tokens=T)
     else:
         El = E
         inp = make_inputs(cfg, dev, T=T)

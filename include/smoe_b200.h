@@ -122,6 +122,24 @@ int smoe_ep_dispatch_pull(const void* const* peer_bases, const int32_t* recv_cou
                           int64_t off_probs, int64_t H, int64_t K, void* q_out, void* raw_out, int32_t* idx_out,
                           float* p_out, void* stream);
 
+/* The two pull kernels without host-side counts.  Every rank additionally leaves, in its mapped buffer, the rows it
+ * sends to each rank (int32 [world] at off_counts) and the start of each destination's segment in its send order
+ * (int32 [world+1] at off_seg).  smoe_ep_tables (one warp) turns all ranks' copies into this rank's tables in device
+ * memory (`tables_out`: smoe_ep_tables_bytes() bytes); smoe_ep_dispatch_pull_dev walks `n_bound` rows (the capacity the
+ * outputs are allocated for), fetches the rows that exist and marks the others as routed nowhere (idx -1, probability
+ * 0, payload untouched); smoe_ep_combine_pull_dev is smoe_ep_combine_pull with its two offset tables read from
+ * `tables`.  With them a step needs no device-to-host read-back before its return exchange. */
+int64_t smoe_ep_tables_bytes(void);
+int smoe_ep_tables(const void* const* peer_bases, int64_t world, int64_t rank, int64_t off_counts, int64_t off_seg,
+                   void* tables_out, void* stream);
+int smoe_ep_dispatch_pull_dev(const void* const* peer_bases, const void* tables, int64_t world, int64_t rank,
+                              int64_t off_q, int64_t off_raw, int64_t off_tok, int64_t off_idx, int64_t off_probs,
+                              int64_t H, int64_t K, int64_t n_bound, void* q_out, void* raw_out, int32_t* idx_out,
+                              float* p_out, void* stream);
+int smoe_ep_combine_pull_dev(const void* const* peer_bases, const void* tables, int64_t world,
+                             const int32_t* copy_pos, const int32_t* copy_off, const int32_t* send_rank,
+                             void* out_bf16, int64_t T, int64_t H, void* stream);
+
 /* ---- MXFP8 1x32 ue8m0 quantizers ------------------------------------------ */
 
 /* Row-wise: x bf16 [M,K] -> e4m3 [M,K] + raw scales [M,K/32] and/or ISA-packed scales

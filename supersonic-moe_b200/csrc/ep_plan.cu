@@ -40,7 +40,7 @@ ep_send_idx_kernel(const int* __restrict__ idx, const int* __restrict__ send_tok
                    int64_t n_send, int K, int E, int El, int world, int* __restrict__ send_idx,
                    int* __restrict__ send_rank) {
   const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-  if (i >= n_send) return;
+  if (i >= n_send || i >= efo[world]) return;            // n_send may be an upper bound: the real count is efo[world]
   int r = 0;
   while (r + 1 < world && efo[r + 1] <= i) ++r;          // rows of rank r: [efo[r], efo[r+1])
   send_rank[i] = r;

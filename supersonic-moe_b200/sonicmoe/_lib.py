@@ -24,6 +24,10 @@ SIGNATURES = {
     "smoe_ep_plan_dest": (_I, [_P, _L, _L, _L, _L, _P, _P, _P]),
     "smoe_ep_plan_send_idx": (_I, [_P, _P, _P, _L, _L, _L, _L, _P, _P, _P]),
     "smoe_ep_combine_pull": (_I, [_P, _P, _P, _L, _P, _P, _P, _P, _L, _L, _P]),
+    "smoe_ep_tables_bytes": (_L, []),
+    "smoe_ep_tables": (_I, [_P, _L, _L, _L, _L, _P, _P]),
+    "smoe_ep_dispatch_pull_dev": (_I, [_P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L, _P, _P, _P, _P, _P]),
+    "smoe_ep_combine_pull_dev": (_I, [_P, _P, _L, _P, _P, _P, _P, _L, _L, _P]),
     "smoe_ep_dispatch_pull": (_I, [_P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _P, _P, _P, _P, _P]),
     "smoe_quant_rows": (_I, [_P, _L, _L, _P, _P, _P, _P]),
     "smoe_quant_rows_gather": (_I, [_P, _P, _P, _L, _L, _P, _P, _P]),

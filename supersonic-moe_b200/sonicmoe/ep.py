@@ -49,9 +49,35 @@ PEER_COMBINE_BACKWARD = _PEER_MODE == "1"
 DISPATCH = os.getenv("SONIC_MOE_EP_DISPATCH", "pull")
 if DISPATCH not in ("pull", "nccl"):
     raise ValueError(f"SONIC_MOE_EP_DISPATCH={DISPATCH!r}: expected 'pull' or 'nccl'")
+# SONIC_MOE_EP_SYNC_FREE=1 (default; needs the pull dispatch and the peer-memory forward return): the forward reads
+# nothing back from the device.  The counts travel to the host on a side stream and are looked at when the backward's
+# all-to-alls need them; until then both pull kernels take their offsets from tables built on the device and every
+# buffer is sized at world x capacity rows, rows that did not arrive being masked.
+SYNC_FREE = os.getenv("SONIC_MOE_EP_SYNC_FREE", "1") == "1"
 
 
 _COMM_STREAMS: dict = {}
+_READBACK_STREAMS: dict = {}
+_PINNED: dict = {}
+
+
+def _readback_stream(device) -> "torch.cuda.Stream":
+    """A side stream per device for small device-to-host copies that must not queue behind the compute stream."""
+    key = torch.device(device).index
+    st = _READBACK_STREAMS.get(key)
+    if st is None:
+        st = _READBACK_STREAMS[key] = torch.cuda.Stream(device=torch.device("cuda", key))
+    return st
+
+
+def _pinned_i64(shape):
+    """Pinned int64 host buffers, eight per shape used in turn (a plan reads its copy within the step it was made)."""
+    ring = _PINNED.setdefault(shape, [[], 0])
+    if len(ring[0]) < 8:
+        ring[0].append(torch.empty(shape, dtype=torch.int64).pin_memory())
+        return ring[0][-1]
+    ring[1] = (ring[1] + 1) % 8
+    return ring[0][ring[1]]
 
 
 def _comm_stream(device) -> "torch.cuda.Stream":
@@ -116,6 +142,11 @@ class DispatchArena:
         at += _align256(cap * 4)
         self.off_idx = at
         at += _align256(cap * K * 4)
+        self.off_counts = at                 # rows this rank sends to each rank, int32 [world]
+        at += 256
+        self.off_seg = at                    # start of each destination's segment in the send order, int32 [world+1]
+        at += 256
+        self.cap = cap
         self.buf = symm.empty(at, dtype=torch.uint8, device=device)
         self.hdl = symm.rendezvous(self.buf, group.group_name)
         self.ptrs = [int(p) for p in self.hdl.buffer_ptrs]
@@ -132,9 +163,25 @@ class DispatchArena:
         raw = self.buf[self.off_raw[slot]: self.off_raw[slot] + T * (H // 32)].view(T, H // 32)
         return q, raw
 
+    def _i32(self, off: int, n: int):
+        return self.buf[off: off + n * 4].view(torch.int32)
+
     def publish_lists(self, plan: "DispatchPlan", probs=None):
         """This rank's send lists (and, in the forward, its tokens' probabilities) into the mapped buffer."""
-        n, K = plan.n_send, self.K
+        K = self.K
+        if plan.deferred:
+            # no host-side count: the lists go out at their capacity together with the counts the peers need
+            cap = plan.send_tok_cap.numel()
+            if cap:
+                self._i32(self.off_tok, cap).copy_(plan.send_tok_cap)
+                self._i32(self.off_idx, cap * K).view(cap, K).copy_(plan.send_idx_cap)
+            self._i32(self.off_counts, self.world).copy_(plan.md_counts)
+            self._i32(self.off_seg, self.world + 1).copy_(plan.md_efo)
+            if probs is not None and plan.T:
+                self.buf[self.off_probs: self.off_probs + plan.T * K * 4].view(torch.float32).view(plan.T, K).copy_(
+                    probs)
+            return
+        n = plan.n_send
         if n:
             self.buf[self.off_tok: self.off_tok + n * 4].view(torch.int32).copy_(plan.send_tok_i32)
             self.buf[self.off_idx: self.off_idx + n * K * 4].view(torch.int32).view(n, K).copy_(plan.send_idx)
@@ -151,6 +198,12 @@ class DispatchArena:
     def pull(self, plan: "DispatchPlan", slot: int, with_meta: bool):
         from . import ops
         self.everyone_has_written()
+        if plan.deferred:
+            me = dist.get_rank(self.group)
+            # rebuilt after every barrier: a later forward of the same layer may have replaced the counts
+            plan.tables = ops.ep_tables(self.ptrs, me, self.off_counts, self.off_seg, self.buf.device)
+            return ops.ep_dispatch_pull_dev(self.ptrs, plan.tables, me, self.layout(slot), self.H, self.K,
+                                            plan.n_bound, self.buf.device, with_meta=with_meta)
         return ops.ep_dispatch_pull(self.ptrs, plan.recv_counts, plan.src_seg_off, dist.get_rank(self.group),
                                     self.layout(slot), self.H, self.K, self.buf.device, with_meta=with_meta)
 
@@ -165,27 +218,41 @@ class DispatchPlan:
                          copy_pos[copy_off[t]:copy_off[t+1]], ascending destination rank
     """
 
-    def __init__(self, idx: torch.Tensor, E: int, group, world: int | None = None):
+    # attributes that exist only once the counts have reached the host
+    _HOST_FIELDS = frozenset(("send_counts", "recv_counts", "tokens_per_local_expert", "n_send", "n_recv",
+                              "first_row_at", "src_seg_off", "send_off", "max_recv_rows", "tokens_all",
+                              "send_tok_i32", "send_idx", "send_rank", "send_tok", "copy_pos"))
+
+    def __init__(self, idx: torch.Tensor, E: int, group, world: int | None = None, deferred: bool = False):
+        """`deferred` (CUDA only): the counts are copied to the host on a side stream and read when first needed -
+        normally at the return exchange, long after they arrived - instead of right away, so building the plan does
+        not drain the GPU's work queue.  Until then only the capacity-sized device lists exist (`send_tok_cap`,
+        `send_idx_cap`, `copy_pos_cap`, `md_counts`, `md_efo`)."""
         world = dist.get_world_size(group) if world is None else world
         assert E % world == 0
         T, K = idx.shape
         self.T, self.K, self.El, self.E, self.group = T, K, E // world, E, group
+        self.world = world
+        self.deferred = bool(deferred) and idx.is_cuda
+        self._pending = None
         if idx.is_cuda:
             self._build_cuda(idx, world)
         else:
             self._build_torch(idx, world)
 
-    def _exchange_counts(self, rows_to, pairs, world):
-        """One small all-gather + ONE read-back gives every rank the whole picture: rows each rank sends to each
-        other rank, routed pairs per expert (summed over sources they size the expert-sorted buffers exactly) and
-        every rank's token count."""
-        me = dist.get_rank(self.group)
-        El = self.El
-        row = torch.cat([rows_to.reshape(-1).to(torch.int64), pairs.reshape(-1).to(torch.int64),
-                         torch.tensor([self.T], dtype=torch.int64, device=rows_to.device)])
-        parts = [torch.empty_like(row) for _ in range(world)]
-        dist.all_gather(parts, row.contiguous(), group=self.group)
-        M = torch.stack(parts).tolist()
+    def __getattr__(self, name):
+        # reached only when the attribute is missing: a host-side field of a plan whose counts are still in flight
+        if name in DispatchPlan._HOST_FIELDS and self.__dict__.get("_pending") is not None:
+            host, ready = self._pending
+            self._pending = None
+            ready.synchronize()
+            self._set_counts(host.tolist())
+            self._finish_cuda()
+            return self.__dict__[name]
+        raise AttributeError(name)
+
+    def _set_counts(self, M):
+        me, El, world = dist.get_rank(self.group), self.El, self.world
         self.send_counts = [int(v) for v in M[me][:world]]
         self.recv_counts = [int(M[s][me]) for s in range(world)]
         self.tokens_per_local_expert = [sum(int(M[s][world + me * El + j]) for s in range(world)) for j in range(El)]
@@ -197,6 +264,31 @@ class DispatchPlan:
         self.send_off = [sum(self.send_counts[:r]) for r in range(world)]
         self.max_recv_rows = max(sum(int(M[s][r]) for s in range(world)) for r in range(world))
         self.tokens_all = [int(M[s][-1]) for s in range(world)]
+
+    def _exchange_counts(self, rows_to, pairs, world):
+        """One small all-gather + ONE read-back gives every rank the whole picture: rows each rank sends to each
+        other rank, routed pairs per expert (summed over sources they size the expert-sorted buffers exactly) and
+        every rank's token count."""
+        row = torch.cat([rows_to.reshape(-1).to(torch.int64), pairs.reshape(-1).to(torch.int64),
+                         # (a fill kernel, not a host-to-device copy: a copy from pageable memory makes the host
+                         # wait for everything the stream has been given)
+                         torch.full((1,), self.T, dtype=torch.int64, device=rows_to.device)])
+        parts = [torch.empty_like(row) for _ in range(world)]
+        dist.all_gather(parts, row.contiguous(), group=self.group)
+        M = torch.stack(parts)
+        if not self.deferred:
+            self._set_counts(M.tolist())
+            return
+        dev = M.device
+        cur, side = torch.cuda.current_stream(dev), _readback_stream(dev)
+        side.wait_stream(cur)
+        host = _pinned_i64(tuple(M.shape))
+        with torch.cuda.stream(side):
+            host.copy_(M, non_blocking=True)
+            ready = torch.cuda.Event()
+            ready.record(side)
+        M.record_stream(side)
+        self._pending = (host, ready)
 
     def _build_cuda(self, idx, world):
         """The plan is the routing-metadata problem with destination ranks in the role of experts: one call of the
@@ -211,13 +303,31 @@ class DispatchPlan:
         # the probability operand of the metadata kernels is not needed here: any f32 buffer of the right size
         md = ops.topk_metadata(dest_u, dest_u.view(torch.float32), world, alignment=1, TK_alloc=cap,
                                TKp_alloc=cap + world)
+        self._idx, self._md = idx, md
+        self.md_counts, self.md_efo = md["counts"], md["efo"]
+        self.copy_off = md["naept"]
+        if self.deferred:
+            # capacity-sized lists, usable without any host-side count (rows beyond efo[world] are never read)
+            self.send_tok_cap = md["x_gather_idx"][:cap]
+            self.send_idx_cap, self.send_rank_cap = ops.ep_plan_send_idx(idx, self.send_tok_cap, md["efo"], cap,
+                                                                         self.E, world)
+            self.copy_pos_cap = md["s_reverse_scatter_idx"][:cap]
         self._exchange_counts(md["counts"], pairs, world)
-        n = self.n_send
+        if not self.deferred:
+            self._finish_cuda()
+
+    def _finish_cuda(self):
+        """The exactly-sized lists, once n_send is known on the host."""
+        from . import ops
+        n, md = self.n_send, self._md
         self.send_tok_i32 = md["x_gather_idx"][:n]
-        self.send_idx, self.send_rank = ops.ep_plan_send_idx(idx, self.send_tok_i32, md["efo"], n, self.E, world)
+        if self.deferred:
+            self.send_idx, self.send_rank = self.send_idx_cap[:n], self.send_rank_cap[:n]
+        else:
+            self.send_idx, self.send_rank = ops.ep_plan_send_idx(self._idx, self.send_tok_i32, md["efo"], n, self.E,
+                                                                 self.world)
         self.send_tok = self.send_tok_i32.long()
         self.copy_pos = md["s_reverse_scatter_idx"][:n]
-        self.copy_off = md["naept"]
 
     def _build_torch(self, idx, world):
         """Device-agnostic construction (CPU tensors, gloo)."""
@@ -273,6 +383,10 @@ class DispatchPlan:
         """[T, H]: every token's partial rows read from the owning ranks' arenas and added in ascending rank order."""
         from . import ops
         arena.everyone_has_written()
+        if self.deferred and self._pending is not None:
+            # counts still on their way to the host: offsets come from the tables the dispatch built on the device
+            return ops.ep_combine_pull_dev(arena.ptrs, self.tables, self.copy_pos_cap, self.copy_off,
+                                           self.send_rank_cap, self.T, arena.H, arena.buf.device)
         return ops.ep_combine_pull(arena.ptrs, self.first_row_at, self.send_off, self.copy_pos, self.copy_off,
                                    self.send_rank, self.T, arena.H, arena.buf.device)
 
@@ -311,9 +425,7 @@ class _Dispatch(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, probs, plan: DispatchPlan, fp8: bool):
         ctx.plan, ctx.x_dtype = plan, x.dtype
-        tok, K, H = plan.send_tok, plan.K, x.shape[1]
-        # the wide payload travels as it is (no repacking copies); scales, expert ids and probabilities share
-        # one narrow exchange
+        K, H = plan.K, x.shape[1]
         disp = getattr(plan, "disp", None)
         if fp8 and disp is not None:
             # peers fetch this rank's rows from its quantised tokens in place; this rank fetches what is addressed to it
@@ -321,9 +433,12 @@ class _Dispatch(torch.autograd.Function):
             ops.quant_rows(x.contiguous(), raw=True, out=disp.payload(0, plan.T))
             disp.publish_lists(plan, probs.detach().float())
             q_recv, raw_recv, idx_recv, p_recv = disp.pull(plan, 0, True)
-            holder = torch.empty((), dtype=x.dtype, device=x.device).expand(plan.n_recv, H)
+            holder = torch.empty((), dtype=x.dtype, device=x.device).expand(q_recv.shape[0], H)
             ctx.mark_non_differentiable(q_recv, raw_recv, idx_recv)
             return holder, p_recv, q_recv, raw_recv, idx_recv
+        # the wide payload travels as it is (no repacking copies); scales, expert ids and probabilities share
+        # one narrow exchange
+        tok = plan.send_tok
         meta = [plan.send_idx, probs.float()[tok]]
         if fp8:
             from . import ops
@@ -354,9 +469,11 @@ class _Dispatch(torch.autograd.Function):
                 # moment only, so those GEMMs run underneath it
                 from .functional import take_result_ready
                 ready = take_result_ready(dx_recv) if dx_recv.is_cuda else None
-                dx = plan.sum_copies(plan.a2a(dx_recv.contiguous(), reverse=True, after=ready)).to(ctx.x_dtype)
+                # (a bound-sized buffer of a plan with deferred counts: only the rows that arrived travel back)
+                dx = plan.sum_copies(plan.a2a(dx_recv[:plan.n_recv].contiguous(), reverse=True,
+                                              after=ready)).to(ctx.x_dtype)
         if ctx.needs_input_grad[1] and dp_recv is not None:
-            back = plan.a2a(dp_recv.contiguous().float(), reverse=True)
+            back = plan.a2a(dp_recv[:plan.n_recv].contiguous().float(), reverse=True)
             # a slot lives on exactly one rank: every other copy contributes an exact zero
             dp = torch.zeros(plan.T, plan.K, dtype=torch.float32, device=back.device).index_add_(0, plan.send_tok, back)
         return dx, dp, None, None
@@ -374,7 +491,7 @@ class _Combine(torch.autograd.Function):
             if o_recv.numel() and not arena.holds(o_recv):
                 arena.view(o_recv.shape[0]).copy_(o_recv)
             return plan.pull_and_sum(arena)
-        return plan.sum_copies(plan.a2a(o_recv.contiguous(), reverse=True))
+        return plan.sum_copies(plan.a2a(o_recv[:plan.n_recv].contiguous(), reverse=True))
 
     @staticmethod
     def backward(ctx, dout):
@@ -387,7 +504,8 @@ class _Combine(torch.autograd.Function):
             disp.publish_lists(plan)      # a later forward of the same layer may have replaced the lists since
             q_recv, raw_recv, _, _ = disp.pull(plan, 1, False)
             ctx.handle.put(q_recv, raw_recv)
-            return torch.empty((), dtype=dout.dtype, device=dout.device).expand(plan.n_recv, dout.shape[1]), None, None
+            return (torch.empty((), dtype=dout.dtype, device=dout.device).expand(q_recv.shape[0], dout.shape[1]), None,
+                    None)
         if ctx.handle is not None:
             from . import ops
             q, raw, _ = ops.quant_rows(dout.to(torch.bfloat16), raw=True)
@@ -402,7 +520,12 @@ class ExpertParallelMoE:
     `expert_fn(rows, local_idx, probs, w1, w2, fp8_scale, handle) -> [N,H]` is the per-rank expert compute; the
     default runs `run_sonic_moe` on the FP8 payload.  Tests on CPU pass `payload="bf16"` and an fp32 stand-in."""
 
-    def __init__(self, num_experts: int, top_k: int, group=None, payload: str = "fp8", expert_fn=None):
+    def __init__(self, num_experts: int, top_k: int, group=None, payload: str = "fp8", expert_fn=None,
+                 capacity_tokens: int | None = None):
+        """`capacity_tokens`: the largest number of tokens any rank will ever pass in one call.  With it the mapped
+        buffers are allocated on the first call and every call runs without reading counts back before its return
+        exchange; without it the first call reads the counts (and sizes the buffers from them) and later calls run
+        read-back-free as long as no rank's token count outgrows what the first call saw (a call that does raises)."""
         self.E, self.K, self.group, self.payload = num_experts, top_k, group, payload
         self.expert_fn = expert_fn or self._sonic_experts
         self._arena = None
@@ -411,70 +534,131 @@ class ExpertParallelMoE:
         self._place = None
         self._disp = None
         self._disp_ok = DISPATCH == "pull" and expert_fn is None and payload == "fp8"
+        self._capacity = capacity_tokens
+        self._sync_free = SYNC_FREE and self._disp_ok and self._peer_ok
+        self._plan = None
 
-    def _dispatch_arena_for(self, plan: DispatchPlan, H: int, device):
-        """The mapped buffer the peers fetch this rank's rows from, (re)allocated collectively when the largest token
-        count of any rank (known to all ranks from the plan) outgrows it."""
-        group = self.group if self.group is not None else dist.group.WORLD
+    @property
+    def last_rows_received(self) -> int:
+        """Rows the last call received (waits for that call's counts if they are still on their way to the host)."""
+        return 0 if self._plan is None else self._plan.n_recv
+
+    def _grp(self):
+        return self.group if self.group is not None else dist.group.WORLD
+
+    def _make_dispatch_arena(self, t_cap: int, H: int, K: int, device):
+        group = self._grp()
         world = dist.get_world_size(group)
-        if not self._disp_ok or device.type != "cuda" or world < 2 or H % 128 or plan.K > 32:
+        if not self._disp_ok or device.type != "cuda" or world < 2 or H % 128 or K > 32:
             return None
-        need = max(plan.tokens_all)
-        if self._disp is None or not self._disp.fits(need, H, plan.K, world):
+        if self._disp is None or not self._disp.fits(t_cap, H, K, world):
             try:
-                self._disp = DispatchArena(group, need, H, plan.K, world, device)
+                self._disp = DispatchArena(group, t_cap, H, K, world, device)
             except Exception as exc:      # no peer mapping on this system: every rank fails alike
                 import warnings
                 warnings.warn(f"expert-parallel peer-memory dispatch unavailable ({exc!r}); using NCCL all-to-all")
                 self._disp_ok, self._disp = False, None
         return self._disp
 
-    def _arena_for(self, plan: DispatchPlan, H: int, device):
-        """The mapped buffer for this call's partial rows, (re)allocated collectively when the largest receive
-        count of any rank (known to all ranks from the plan) outgrows it."""
-        if not self._peer_ok or device.type != "cuda" or dist.get_world_size(self.group) < 2:
+    def _make_arena(self, rows: int, H: int, device):
+        if not self._peer_ok or device.type != "cuda" or dist.get_world_size(self._grp()) < 2:
             return None
-        need = plan.max_recv_rows
-        if self._arena is None or self._arena.H != H or self._arena.rows < need:
-            rows = max(need, sum(plan.tokens_all))      # every rank sending everything to one rank always fits
+        if self._arena is None or self._arena.H != H or self._arena.rows < rows:
             try:
-                self._arena = PeerArena(self.group if self.group is not None else dist.group.WORLD, rows, H, device)
+                self._arena = PeerArena(self._grp(), rows, H, device)
             except Exception as exc:      # no peer mapping on this system: every rank fails alike
                 import warnings
                 warnings.warn(f"expert-parallel peer-memory combine unavailable ({exc!r}); using NCCL all-to-all")
                 self._peer_ok, self._arena = False, None
         return self._arena
 
+    def _dispatch_arena_for(self, plan: DispatchPlan, H: int, device):
+        """The mapped buffer the peers fetch this rank's rows from, (re)allocated collectively when the largest token
+        count of any rank (known to all ranks from the plan) outgrows it."""
+        return self._make_dispatch_arena(max(plan.tokens_all), H, plan.K, device)
+
+    def _arena_for(self, plan: DispatchPlan, H: int, device):
+        """The mapped buffer for this call's partial rows, (re)allocated collectively when the largest receive
+        count of any rank (known to all ranks from the plan) outgrows it."""
+        # world x the largest token count: every rank sending everything to one rank always fits
+        world = dist.get_world_size(self._grp())
+        return self._make_arena(max(plan.max_recv_rows, world * max(plan.tokens_all)), H, device)
+
+    def _ready_without_counts(self, T: int, H: int, K: int, device) -> bool:
+        """Whether this call can run on upper-bound sizes alone: both mapped buffers exist and are large enough for
+        `world x capacity` rows.  The capacity is a quantity all ranks share, so all ranks decide alike; a rank whose
+        own token count exceeds it cannot go on (the peers have no way to learn that in time) and raises."""
+        if not self._sync_free or device.type != "cuda":
+            return False
+        world = dist.get_world_size(self._grp())
+        if world < 2 or H % 128 or K > 32:
+            return False
+        if self._disp is None and self._capacity is not None:
+            # first call with a stated capacity: allocate now (collective calls, same arguments on every rank)
+            if self._make_dispatch_arena(self._capacity, H, K, device) is None:
+                self._sync_free = False
+                return False
+            if self._make_arena(world * self._capacity, H, device) is None:
+                self._sync_free = False
+                return False
+        if self._disp is None or self._arena is None:
+            return False                      # first call without a capacity: sizes come from the counts
+        if (H, K, world) != (self._disp.H, self._disp.K, self._disp.world) or self._arena.H != H \
+                or self._arena.rows < world * self._disp.t_cap:
+            return False
+        if T > self._disp.t_cap:
+            raise RuntimeError(f"expert-parallel layer: {T} tokens on this rank exceed the capacity of {self._disp.t_cap} "
+                               "the ranks agreed on; construct ExpertParallelMoE(capacity_tokens=...) with the largest "
+                               "per-rank token count, or set SONIC_MOE_EP_SYNC_FREE=0")
+        return True
+
     def _sonic_experts(self, rows, local_idx, probs, w1, w2, fp8_scale, handle):
         from .interface import run_sonic_moe
-        # the plan's count exchange already brought the routed pairs per local expert: the expert-sorted buffers
-        # are sized exactly instead of at the N*K upper bound, with no further read-back
-        counts = self.tokens_per_local_expert
+        plan = self._plan
         if fp8_scale is not None:
             holder, qbytes = rows
+            if plan is not None and plan.deferred:
+                # no counts on the host yet: expert-sorted buffers at the shape-only bound, rows that did not arrive
+                # are masked (-1) and cost nothing
+                return run_sonic_moe(qbytes, local_idx, probs, self.K, self.El, w1, w2, fp8=True, fp8_scale=fp8_scale,
+                                     fp8_combine_grad_handle=handle, sync_free_sizing=True, grad_holder=holder,
+                                     out=self._place, dx_out=self._place if self._peer_backward else None)
+            # the plan's count exchange already brought the routed pairs per local expert: the expert-sorted buffers
+            # are sized exactly instead of at the N*K upper bound, with no further read-back
             return run_sonic_moe(qbytes, local_idx, probs, self.K, self.El, w1, w2, fp8=True, fp8_scale=fp8_scale,
-                                 fp8_combine_grad_handle=handle, tokens_per_expert=counts, grad_holder=holder,
-                                 out=self._place, dx_out=self._place if self._peer_backward else None)
-        return run_sonic_moe(rows, local_idx, probs, self.K, self.El, w1, w2, fp8=True, tokens_per_expert=counts)
+                                 fp8_combine_grad_handle=handle, tokens_per_expert=self.tokens_per_local_expert,
+                                 grad_holder=holder, out=self._place,
+                                 dx_out=self._place if self._peer_backward else None)
+        return run_sonic_moe(rows, local_idx, probs, self.K, self.El, w1, w2, fp8=True,
+                             tokens_per_expert=self.tokens_per_local_expert)
 
     def __call__(self, x, topk_idx, topk_scores, w1, w2):
-        plan = DispatchPlan(topk_idx, self.E, self.group)
-        self.El = plan.El
-        self.last_rows_received = plan.n_recv
         fp8 = self.payload == "fp8"
-        self.tokens_per_local_expert = plan.tokens_per_local_expert
-        plan.disp = self._dispatch_arena_for(plan, x.shape[1], x.device) if fp8 else None
+        T, H = x.shape
+        deferred = fp8 and x.is_cuda and self._ready_without_counts(T, H, topk_idx.shape[1], x.device)
+        plan = DispatchPlan(topk_idx, self.E, self.group, deferred=deferred)
+        self._plan = plan
+        self.El = plan.El
+        if deferred:
+            plan.disp, arena = self._disp, self._arena
+            plan.n_bound = plan.world * self._disp.t_cap
+            self.tokens_per_local_expert = None
+        else:
+            self.tokens_per_local_expert = plan.tokens_per_local_expert
+            plan.disp = self._dispatch_arena_for(plan, H, x.device) if fp8 else None
         rows, probs, q, raw, local_idx = _Dispatch.apply(x, topk_scores, plan, fp8)
         handle = None
         if fp8:
             from .functional import Fp8CombineGradHandle
             handle = Fp8CombineGradHandle()
             rows = (rows, q)
-        arena = self._arena_for(plan, x.shape[1], x.device) if fp8 else None
+        if not deferred:
+            arena = self._arena_for(plan, H, x.device) if fp8 else None
         plan.arena = arena
         plan.arena_backward = self._peer_backward
         # forward output and, later, dx of the local experts land in the mapped buffer (one region, used in turn)
-        self._place = arena.view(plan.n_recv) if (arena is not None and plan.n_recv > 0) else None
+        n_rows = plan.n_bound if deferred else plan.n_recv
+        self._place = arena.view(n_rows) if (arena is not None and n_rows > 0) else None
         o_recv = self.expert_fn(rows, local_idx, probs, w1, w2, raw, handle)
         self._place = None
         return _Combine.apply(o_recv, plan, handle)
@@ -517,7 +701,9 @@ def parity_against_single_gpu(group=None, device=None, T=1024, H=512, I=256, K=4
     sd = scores.to(dev).requires_grad_(True)
     w1l = w1[lo:lo + El].contiguous().to(dev).requires_grad_(True)
     w2l = w2[lo:lo + El].contiguous().to(dev).requires_grad_(True)
-    ep = ExpertParallelMoE(E, K, group if group is not None else dist.group.WORLD)
+    # a stated capacity: the mapped buffers are allocated up front and this very first call already runs without
+    # reading counts back in its forward (the layer's steady-state path)
+    ep = ExpertParallelMoE(E, K, group if group is not None else dist.group.WORLD, capacity_tokens=T)
     out = ep(xd, idx.to(dev), sd, w1l, w2l)
     out.backward(dy.to(dev))
     torch.cuda.synchronize(dev)
@@ -552,6 +738,7 @@ def parity_against_single_gpu(group=None, device=None, T=1024, H=512, I=256, K=4
                dw2=st(w2_grad, dw2_ref))
     res["used_peer"] = ep._arena is not None
     res["used_pull_dispatch"] = ep._disp is not None
+    res["forward_without_readback"] = bool(ep._plan is not None and ep._plan.deferred)
     res["rows_received"] = int(ep.last_rows_received)
     return res
 

@@ -225,6 +225,47 @@ def ep_dispatch_pull(peer_ptrs, recv_counts, src_off, rank, layout, H, K, device
     return q, raw, idx, p
 
 
+def ep_tables(peer_ptrs, rank, off_counts, off_seg, device):
+    """This rank's receive / send offset tables, built on the device from the counts every rank left in its mapped
+    buffer -> opaque u8 tensor for `ep_dispatch_pull_dev` / `ep_combine_pull_dev`."""
+    import ctypes
+    world = len(peer_ptrs)
+    tab = torch.empty(int(lib.smoe_ep_tables_bytes()), dtype=_U8, device=device)
+    bases = (ctypes.c_void_p * world)(*[int(v) for v in peer_ptrs])
+    check(lib.smoe_ep_tables(bases, world, int(rank), int(off_counts), int(off_seg), _p(tab), _stream()), "ep_tables")
+    return tab
+
+
+@_timed
+def ep_dispatch_pull_dev(peer_ptrs, tables, rank, layout, H, K, n_bound, device, with_meta=True):
+    """`ep_dispatch_pull` with device-side counts: outputs have `n_bound` rows; rows beyond what arrived carry
+    idx -1 / probability 0 and an unwritten payload."""
+    import ctypes
+    world = len(peer_ptrs)
+    q = torch.empty(n_bound, H, dtype=_U8, device=device)
+    raw = torch.empty(n_bound, H // 32, dtype=_U8, device=device)
+    idx = torch.empty(n_bound, K, dtype=_I32, device=device) if with_meta else None
+    p = torch.empty(n_bound, K, dtype=torch.float32, device=device) if with_meta else None
+    bases = (ctypes.c_void_p * world)(*[int(v) for v in peer_ptrs])
+    oq, oraw, otok, oidx, oprobs = (int(v) for v in layout)
+    check(lib.smoe_ep_dispatch_pull_dev(bases, _p(tables), world, int(rank), oq, oraw, otok, oidx, oprobs, H, K,
+                                        n_bound, _p(q), _p(raw), _p(idx), _p(p), _stream()), "ep_dispatch_pull_dev")
+    return q, raw, idx, p
+
+
+@_timed
+def ep_combine_pull_dev(peer_ptrs, tables, copy_pos, copy_off, send_rank, T, H, device):
+    """`ep_combine_pull` with its offset tables read from device memory."""
+    import ctypes
+    _cuda(copy_pos, copy_off, send_rank)
+    world = len(peer_ptrs)
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=device)
+    bases = (ctypes.c_void_p * world)(*[int(p) for p in peer_ptrs])
+    check(lib.smoe_ep_combine_pull_dev(bases, _p(tables), world, _p(copy_pos), _p(copy_off), _p(send_rank), _p(out), T,
+                                       H, _stream()), "ep_combine_pull_dev")
+    return out
+
+
 # ---------------------------------------------------------------- quantizers
 @_timed
 def quant_rows(x, raw=True, isa=False, out=None):

@@ -74,6 +74,8 @@ def _same_bits_either_dispatch(ep_mod, dev, rank, world):
             outs += [out.detach(), xd.grad, sd.grad]
         torch.cuda.synchronize(dev)
         assert (layer._disp is not None) == (mode == "pull")
+        # the first call sized the mapped buffers from its counts; the second ran without reading any back
+        assert layer._plan.deferred == (mode == "pull")
         return outs + [w1d.grad, w2d.grad]
 
     a, b = run("nccl"), run("pull")
@@ -118,6 +120,8 @@ def test_ep_two_gpus_matches_single_gpu_layer(peer):
     for rank, res in _launch(2, peer, False).items():
         assert res.pop("used_peer") == (peer != "0"), "the requested return-exchange path was not the one that ran"
         assert res.pop("used_pull_dispatch") is True
+        # with both peer-memory paths on, the forward reads no counts back (they are looked at in the backward)
+        assert res.pop("forward_without_readback") == (peer != "0")
         assert res.pop("rows_received") > 0
         for name, (cos, rr) in res.items():
             cmin, rmax = PARITY_LIMITS[name]
@@ -135,6 +139,7 @@ def test_ep_rank_that_receives_no_tokens():
     assert results[1]["rows_received"] == 0 and results[0]["rows_received"] > 0
     for rank, res in results.items():
         res.pop("used_peer"), res.pop("rows_received"), res.pop("used_pull_dispatch")
+        assert res.pop("forward_without_readback") is True
         for name, (cos, rr) in res.items():
             cmin, rmax = PARITY_LIMITS[name]
             assert cos > cmin and rr < rmax, (rank, name, cos, rr)
@@ -148,7 +153,7 @@ def test_ep_dispatch_through_nccl_and_both_dispatch_paths_give_the_same_bits():
         pytest.skip("needs 2 GPUs")
     from sonicmoe.ep import PARITY_LIMITS
     for rank, res in _launch(2, "0", False, "nccl").items():
-        assert res.pop("used_pull_dispatch") is False
+        assert res.pop("used_pull_dispatch") is False and res.pop("forward_without_readback") is False
         res.pop("used_peer"), res.pop("rows_received")
         for name, (cos, rr) in res.items():
             cmin, rmax = PARITY_LIMITS[name]
