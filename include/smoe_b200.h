@@ -199,15 +199,17 @@ int smoe_scatter_rows_fp8(const void* q, const void* raw_scales, int64_t T, int6
  *   q_t  e4m3 [dim, rows]  (TRANSPOSED: the reduction dimension of the weight-gradient GEMM is contiguous)
  *   isa  ISA-packed scales for the logical (dim, rows) operand.
  * Replaces colwise_quantize_and_pack (sonicmoe/quack_utils/blockscaled_fp8_gemm.py:1517-1592,1824-1847);
- * same bytes and scale bytes, transposed storage.  rows % 128 == 0, dim % 64 == 0. */
-int smoe_quant_cols_t(const void* src_bf16, const int32_t* idx, int64_t rows, int64_t dim, void* q_t, void* isa,
-                      void* stream);
+ * same bytes and scale bytes, transposed storage.  rows % 128 == 0, dim % 64 == 0.  Row tiles at or beyond
+ * *valid_rows (device int, may be null) are left untouched: with buffers sized at an upper bound, only the rows of
+ * the experts' segments are ever read. */
+int smoe_quant_cols_t(const void* src_bf16, const int32_t* idx, const int32_t* valid_rows, int64_t rows, int64_t dim,
+                      void* q_t, void* isa, void* stream);
 
 /* Same, for a source that is already e4m3 with raw row-wise 1x32 scales [T,dim/32] (an FP8 dispatch payload):
  * dequantise, then column-wise re-quantise.  Replaces _dequant_colwise_quantize_and_pack_from_isa_kernel
  * (sonicmoe/quack_utils/blockscaled_fp8_gemm.py:5206-5359). */
-int smoe_requant_cols_t(const void* src_fp8, const void* src_scales, const int32_t* idx, int64_t rows, int64_t dim,
-                        void* q_t, void* isa, void* stream);
+int smoe_requant_cols_t(const void* src_fp8, const void* src_scales, const int32_t* idx, const int32_t* valid_rows,
+                        int64_t rows, int64_t dim, void* q_t, void* isa, void* stream);
 
 /* 32x32 block ("iso32") quantizer: dz bf16 [rows, cols] -> q e4m3 [rows, cols] + row-ISA scales for (rows, cols),
  * q_t e4m3 [cols, rows] + col-ISA scales for (cols, rows).  Replaces dual_quantize_varlen iso32

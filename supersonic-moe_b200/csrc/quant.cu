@@ -297,12 +297,15 @@ template <bool ISO, bool SRC_FP8>
 __global__ void __launch_bounds__(256)
 quant_cols_kernel(const void* __restrict__ src_, const uint8_t* __restrict__ src_scales,
                   const int* __restrict__ idx, int64_t rows, int dim, uint8_t* __restrict__ q_t,
-                  uint8_t* __restrict__ col_isa, uint8_t* __restrict__ q, uint8_t* __restrict__ row_isa) {
+                  uint8_t* __restrict__ col_isa, uint8_t* __restrict__ q, uint8_t* __restrict__ row_isa,
+                  const int* __restrict__ valid_rows) {
   __shared__ __nv_bfloat16 s_in[CT_ROWS][CT_PITCH];
   __shared__ __align__(16) uint8_t s_out[CT_COLS][CT_ROWS + 16];
   __shared__ uint32_t s_sc[CT_COLS];
   const int tid = threadIdx.x;
   const int64_t r0 = (int64_t)blockIdx.x * CT_ROWS;
+  // buffers sized at an upper bound: row tiles beyond the last expert's segment are never read by any GEMM
+  if (valid_rows != nullptr && r0 >= *valid_rows) return;
   const int c0 = blockIdx.y * CT_COLS;
   const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(src_);
 
@@ -551,24 +554,25 @@ int smoe_gather_rows_fp8(const void* q, const void* raw_scales, const int32_t* i
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }
 
-int smoe_quant_cols_t(const void* src_bf16, const int32_t* idx, int64_t rows, int64_t dim, void* q_t, void* isa,
-                      void* stream) {
+int smoe_quant_cols_t(const void* src_bf16, const int32_t* idx, const int32_t* valid_rows, int64_t rows, int64_t dim,
+                      void* q_t, void* isa, void* stream) {
   if (rows < 0 || rows % 128 || dim <= 0 || dim % 64) return SMOE_ERR_SHAPE;
   if (rows == 0) return SMOE_OK;
   dim3 grid((unsigned)(rows / CT_ROWS), (unsigned)(dim / CT_COLS));
-  quant_cols_kernel<false, false><<<grid, 256, 0, (cudaStream_t)stream>>>(src_bf16, nullptr, idx, rows, (int)dim,
-                                                                          (uint8_t*)q_t, (uint8_t*)isa, nullptr, nullptr);
+  quant_cols_kernel<false, false><<<grid, 256, 0, (cudaStream_t)stream>>>(
+      src_bf16, nullptr, idx, rows, (int)dim, (uint8_t*)q_t, (uint8_t*)isa, nullptr, nullptr, valid_rows);
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }
 
-int smoe_requant_cols_t(const void* src_fp8, const void* src_scales, const int32_t* idx, int64_t rows, int64_t dim,
-                        void* q_t, void* isa, void* stream) {
+int smoe_requant_cols_t(const void* src_fp8, const void* src_scales, const int32_t* idx, const int32_t* valid_rows,
+                        int64_t rows, int64_t dim, void* q_t, void* isa, void* stream) {
   if (rows < 0 || rows % 128 || dim <= 0 || dim % 64) return SMOE_ERR_SHAPE;
   if (rows == 0) return SMOE_OK;      // nothing routed: not an error, and the (empty) buffers may be null
   if (!src_scales) return SMOE_ERR_ARG;
   dim3 grid((unsigned)(rows / CT_ROWS), (unsigned)(dim / CT_COLS));
   quant_cols_kernel<false, true><<<grid, 256, 0, (cudaStream_t)stream>>>(
-      src_fp8, (const uint8_t*)src_scales, idx, rows, (int)dim, (uint8_t*)q_t, (uint8_t*)isa, nullptr, nullptr);
+      src_fp8, (const uint8_t*)src_scales, idx, rows, (int)dim, (uint8_t*)q_t, (uint8_t*)isa, nullptr, nullptr,
+      valid_rows);
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }
 
@@ -579,7 +583,7 @@ int smoe_quant_iso32(const void* x_bf16, int64_t rows, int64_t cols, void* q, vo
   dim3 grid((unsigned)(rows / CT_ROWS), (unsigned)(cols / CT_COLS));
   quant_cols_kernel<true, false><<<grid, 256, 0, (cudaStream_t)stream>>>(x_bf16, nullptr, nullptr, rows, (int)cols,
                                                                          (uint8_t*)q_t, (uint8_t*)col_isa, (uint8_t*)q,
-                                                                         (uint8_t*)row_isa);
+                                                                         (uint8_t*)row_isa, nullptr);
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }
 

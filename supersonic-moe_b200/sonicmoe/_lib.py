@@ -36,8 +36,8 @@ SIGNATURES = {
     "smoe_gather_scales_isa": (_I, [_P, _P, _L, _L, _P, _P]),
     "smoe_gather_rows_fp8": (_I, [_P, _P, _P, _P, _L, _L, _P, _P, _P]),
     "smoe_scatter_rows_fp8": (_I, [_P, _P, _L, _L, _P, _P, _P, _P, _L, _P, _P, _P]),
-    "smoe_quant_cols_t": (_I, [_P, _P, _L, _L, _P, _P, _P]),
-    "smoe_requant_cols_t": (_I, [_P, _P, _P, _L, _L, _P, _P, _P]),
+    "smoe_quant_cols_t": (_I, [_P, _P, _P, _L, _L, _P, _P, _P]),
+    "smoe_requant_cols_t": (_I, [_P, _P, _P, _P, _L, _L, _P, _P, _P]),
     "smoe_quant_iso32": (_I, [_P, _L, _L, _P, _P, _P, _P, _P]),
     "smoe_gemm_varlen_m": (_I, [_P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P, _P]),
     "smoe_gemm_varlen_m_bt": (_I, [_P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P, _P]),

@@ -115,7 +115,7 @@ def _col_operand(src, idx, TKp, valid_rows, E, M, N):
     if _mn_wgrad_ok(E, M, N) and not _wide_wgrad_ok(E, M, N):
         _, _, q, sf = ops.quant_dual_gather(src, idx, TKp, valid_rows, with_rows=False)
         return q, sf, True
-    q_t, sf = ops.quant_cols_t(src, idx, TKp)
+    q_t, sf = ops.quant_cols_t(src, idx, TKp, valid_rows=valid_rows)
     return q_t, sf, False
 
 
@@ -530,7 +530,7 @@ class _UpProjection(torch.autograd.Function):
         dw1 = None
         if ctx.needs_input_grad[1]:
             if ctx.x_is_fp8:     # x is e4m3 + raw scales: dequantise, then column-wise re-quantise
-                xc, x_sf, xc_rows = *ops.requant_cols_t(x, x_raw, x_gather_idx, TKp), False
+                xc, x_sf, xc_rows = *ops.requant_cols_t(x, x_raw, x_gather_idx, TKp, efo[-1:]), False
             else:                # column scales; payload [TKp, H] or transposed, whichever the GEMM runs fastest on
                 xc, x_sf, xc_rows = _col_operand(x, x_gather_idx, TKp, efo[-1:], E, N2, H)
             mg, base = _grad_target(w1, (E, N2, H))
@@ -678,15 +678,15 @@ class _DownProjection(torch.autograd.Function):
         dw2 = None
         if ctx.needs_input_grad[2]:
             if y1s is not None:
-                y1s_t, y1s_sf = ops.quant_cols_t(y1s, None, TKp)
+                y1s_t, y1s_sf = ops.quant_cols_t(y1s, None, TKp, valid_rows=efo[-1:])
                 del y1s
             if dout_c is None:
                 if dout is None:
-                    dout_t, dout_sf = ops.requant_cols_t(dout_q, dout_raw, x_gather_idx, TKp)
+                    dout_t, dout_sf = ops.requant_cols_t(dout_q, dout_raw, x_gather_idx, TKp, efo[-1:])
                 elif _mn_wgrad_ok(E, I, H):
                     dout_c, dout_sf, dout_c_rows = _col_operand(dout, x_gather_idx, TKp, efo[-1:], E, I, H)
                 else:
-                    dout_t, dout_sf = ops.quant_cols_t(dout, x_gather_idx, TKp)
+                    dout_t, dout_sf = ops.quant_cols_t(dout, x_gather_idx, TKp, valid_rows=efo[-1:])
             mg, base = _grad_target(w2, (E, I, H))
             a_op, a_rows = (y1s_q, True) if y1s_q is not None else (y1s_t, False)
             b_op, b_rows = (dout_c, dout_c_rows) if dout_c is not None else (dout_t, False)

@@ -369,10 +369,11 @@ def scatter_rows_fp8(q, raw, naept, s_rev, s_scatter_idx, rows, valid_rows=None,
 
 
 @_timed
-def quant_cols_t(src, idx, rows, out=None):
+def quant_cols_t(src, idx, rows, out=None, valid_rows=None):
     """bf16 [T,dim] (rows gathered by idx, or None) -> (e4m3 bytes [dim, rows], ISA scales for (dim, rows)); `out` =
-    (q_t, isa) places the results in caller-owned buffers (slices of a stacked tensor)."""
-    _cuda(src, idx)
+    (q_t, isa) places the results in caller-owned buffers (slices of a stacked tensor); `valid_rows` (device int):
+    row tiles at or beyond it are skipped."""
+    _cuda(src, idx, valid_rows)
     assert src.dtype == torch.bfloat16
     dim = src.shape[1]
     if out is not None:
@@ -382,18 +383,21 @@ def quant_cols_t(src, idx, rows, out=None):
     else:
         q_t = torch.empty(dim, rows, dtype=_U8, device=src.device)
         isa = torch.empty(isa_bytes(dim, rows), dtype=_U8, device=src.device)
-    check(lib.smoe_quant_cols_t(_p(src), _p(idx), rows, dim, _p(q_t), _p(isa), _stream()), "quant_cols_t")
+    check(lib.smoe_quant_cols_t(_p(src), _p(idx), _p(valid_rows), rows, dim, _p(q_t), _p(isa), _stream()),
+          "quant_cols_t")
     return q_t, isa
 
 
 @_timed
-def requant_cols_t(src_q, src_raw, idx, rows):
-    """e4m3 bytes [T,dim] + raw row scales [T,dim/32] -> (e4m3 [dim, rows], ISA scales for (dim, rows))."""
-    _cuda(src_q, src_raw, idx)
+def requant_cols_t(src_q, src_raw, idx, rows, valid_rows=None):
+    """e4m3 bytes [T,dim] + raw row scales [T,dim/32] -> (e4m3 [dim, rows], ISA scales for (dim, rows)); `valid_rows`
+    (device int): row tiles at or beyond it are skipped."""
+    _cuda(src_q, src_raw, idx, valid_rows)
     dim = src_q.shape[1]
     q_t = torch.empty(dim, rows, dtype=_U8, device=src_q.device)
     isa = torch.empty(isa_bytes(dim, rows), dtype=_U8, device=src_q.device)
-    check(lib.smoe_requant_cols_t(_p(src_q), _p(src_raw), _p(idx), rows, dim, _p(q_t), _p(isa), _stream()),
+    check(lib.smoe_requant_cols_t(_p(src_q), _p(src_raw), _p(idx), _p(valid_rows), rows, dim, _p(q_t), _p(isa),
+                                  _stream()),
           "requant_cols_t")
     return q_t, isa
 
