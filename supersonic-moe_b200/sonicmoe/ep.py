@@ -54,6 +54,13 @@ if DISPATCH not in ("pull", "nccl"):
 # all-to-alls need them; until then both pull kernels take their offsets from tables built on the device and every
 # buffer is sized at world x capacity rows, rows that did not arrive being masked.
 SYNC_FREE = os.getenv("SONIC_MOE_EP_SYNC_FREE", "1") == "1"
+# SONIC_MOE_EP_DX_RETURN=copy (default): the backward's return exchange (dx rows back to their sources) is a set of
+# plain device-to-device copies into the sources' mapped buffers, issued on the communication stream - the copy
+# engines move them over NVLink while the weight-gradient GEMMs keep every SM; "nccl": an all-to-all kernel, which
+# shares the SMs with those GEMMs (measured on 2 GPUs: dw2 309 us under the all-to-all kernel, 233 us alone).
+DX_RETURN = os.getenv("SONIC_MOE_EP_DX_RETURN", "copy")
+if DX_RETURN not in ("copy", "nccl"):
+    raise ValueError(f"SONIC_MOE_EP_DX_RETURN={DX_RETURN!r}: expected 'copy' or 'nccl'")
 
 
 _COMM_STREAMS: dict = {}
@@ -112,6 +119,29 @@ class PeerArena:
 
     def everyone_has_written(self):
         """Stream-ordered: returns (on the stream) once every rank's earlier work on its stream is done."""
+        dist.all_reduce(self.token, group=self.group)
+
+
+class ReturnArena:
+    """A bf16 [rows, H] buffer per rank, mapped by all ranks, that receives the rows this rank sent out when they
+    come back (in its send order): the owners copy them in with ordinary device-to-device copies."""
+
+    def __init__(self, group, rows: int, H: int, device):
+        import torch.distributed._symmetric_memory as symm
+        self.rows, self.H = rows, H
+        self.buf = symm.empty(rows * H, dtype=torch.bfloat16, device=device)
+        self.hdl = symm.rendezvous(self.buf, group.group_name)
+        self.token = torch.zeros(1, dtype=torch.float32, device=device)
+        self.group = group
+
+    def rows_of(self, rank: int, first: int, n: int) -> torch.Tensor:
+        """Rows [first, first + n) of rank `rank`'s buffer as a tensor of this process."""
+        return self.hdl.get_buffer(rank, (n, self.H), torch.bfloat16, first * self.H)
+
+    def mine(self, n: int) -> torch.Tensor:
+        return self.buf[: n * self.H].view(n, self.H)
+
+    def everyone_has_written(self):
         dist.all_reduce(self.token, group=self.group)
 
 
@@ -379,6 +409,28 @@ class DispatchPlan:
         cur.wait_stream(comm)
         return out
 
+    def return_by_copies(self, rows: torch.Tensor, ret: "ReturnArena", after=None) -> torch.Tensor:
+        """The reverse exchange of `a2a(rows, reverse=True)` as device-to-device copies: the rows received from
+        source s go back into s's mapped buffer at the place they have in s's send order.  Issued on the
+        communication stream after `after`; the current stream resumes once every rank's copies are done.  Returns
+        this rank's buffer rows [n_send, H] (its outgoing rows, returned)."""
+        cur = torch.cuda.current_stream(rows.device)
+        comm = _comm_stream(rows.device)
+        if after is not None:
+            comm.wait_event(after)
+        else:
+            comm.wait_stream(cur)
+        with torch.cuda.stream(comm):
+            at = 0
+            for s_rank, n in enumerate(self.recv_counts):
+                if n:
+                    ret.rows_of(s_rank, self.src_seg_off[s_rank], n).copy_(rows[at:at + n], non_blocking=True)
+                at += n
+            ret.everyone_has_written()
+        rows.record_stream(comm)
+        cur.wait_stream(comm)
+        return ret.mine(self.n_send)
+
     def pull_and_sum(self, arena: "PeerArena") -> torch.Tensor:
         """[T, H]: every token's partial rows read from the owning ranks' arenas and added in ascending rank order."""
         from . import ops
@@ -469,9 +521,13 @@ class _Dispatch(torch.autograd.Function):
                 # moment only, so those GEMMs run underneath it
                 from .functional import take_result_ready
                 ready = take_result_ready(dx_recv) if dx_recv.is_cuda else None
+                ret = getattr(plan, "ret", None)
                 # (a bound-sized buffer of a plan with deferred counts: only the rows that arrived travel back)
-                dx = plan.sum_copies(plan.a2a(dx_recv[:plan.n_recv].contiguous(), reverse=True,
-                                              after=ready)).to(ctx.x_dtype)
+                if ret is not None and dx_recv.is_cuda and dx_recv.dtype == torch.bfloat16:
+                    back = plan.return_by_copies(dx_recv[:plan.n_recv], ret, after=ready)
+                else:
+                    back = plan.a2a(dx_recv[:plan.n_recv].contiguous(), reverse=True, after=ready)
+                dx = plan.sum_copies(back).to(ctx.x_dtype)
         if ctx.needs_input_grad[1] and dp_recv is not None:
             back = plan.a2a(dp_recv[:plan.n_recv].contiguous().float(), reverse=True)
             # a slot lives on exactly one rank: every other copy contributes an exact zero
@@ -535,6 +591,8 @@ class ExpertParallelMoE:
         self._disp = None
         self._disp_ok = DISPATCH == "pull" and expert_fn is None and payload == "fp8"
         self._capacity = capacity_tokens
+        self._ret = None
+        self._ret_ok = DX_RETURN == "copy" and expert_fn is None and payload == "fp8"
         self._sync_free = SYNC_FREE and self._disp_ok and self._peer_ok
         self._plan = None
 
@@ -571,6 +629,18 @@ class ExpertParallelMoE:
                 warnings.warn(f"expert-parallel peer-memory combine unavailable ({exc!r}); using NCCL all-to-all")
                 self._peer_ok, self._arena = False, None
         return self._arena
+
+    def _make_return_arena(self, rows: int, H: int, device):
+        if not self._ret_ok or device.type != "cuda" or dist.get_world_size(self._grp()) < 2:
+            return None
+        if self._ret is None or self._ret.H != H or self._ret.rows < rows:
+            try:
+                self._ret = ReturnArena(self._grp(), rows, H, device)
+            except Exception as exc:      # no peer mapping on this system: every rank fails alike
+                import warnings
+                warnings.warn(f"expert-parallel return by peer copies unavailable ({exc!r}); using NCCL all-to-all")
+                self._ret_ok, self._ret = False, None
+        return self._ret
 
     def _dispatch_arena_for(self, plan: DispatchPlan, H: int, device):
         """The mapped buffer the peers fetch this rank's rows from, (re)allocated collectively when the largest token
@@ -656,6 +726,11 @@ class ExpertParallelMoE:
             arena = self._arena_for(plan, H, x.device) if fp8 else None
         plan.arena = arena
         plan.arena_backward = self._peer_backward
+        plan.ret = None
+        if fp8 and x.is_cuda and not (arena is not None and self._peer_backward):
+            # where this rank's outgoing rows land when dx comes back (sized from quantities all ranks share)
+            t_cap = self._disp.t_cap if deferred else max(plan.tokens_all)
+            plan.ret = self._make_return_arena(t_cap * min(plan.K, plan.world), H, x.device)
         # forward output and, later, dx of the local experts land in the mapped buffer (one region, used in turn)
         n_rows = plan.n_bound if deferred else plan.n_recv
         self._place = arena.view(n_rows) if (arena is not None and n_rows > 0) else None
@@ -739,6 +814,7 @@ def parity_against_single_gpu(group=None, device=None, T=1024, H=512, I=256, K=4
     res["used_peer"] = ep._arena is not None
     res["used_pull_dispatch"] = ep._disp is not None
     res["forward_without_readback"] = bool(ep._plan is not None and ep._plan.deferred)
+    res["dx_returned_by_copies"] = ep._ret is not None
     res["rows_received"] = int(ep.last_rows_received)
     return res
 

@@ -62,6 +62,7 @@ def _same_bits_either_dispatch(ep_mod, dev, rank, world):
 
     def run(mode):
         ep_mod.DISPATCH = mode
+        ep_mod.DX_RETURN = "copy" if mode == "pull" else "nccl"      # the all-NCCL data path against the default one
         layer = ep_mod.ExpertParallelMoE(E, K, dist.group.WORLD)
         w1d, w2d = w1.to(dev).requires_grad_(True), w2.to(dev).requires_grad_(True)
         live = []
@@ -122,6 +123,7 @@ def test_ep_two_gpus_matches_single_gpu_layer(peer):
         assert res.pop("used_pull_dispatch") is True
         # with both peer-memory paths on, the forward reads no counts back (they are looked at in the backward)
         assert res.pop("forward_without_readback") == (peer != "0")
+        assert res.pop("dx_returned_by_copies") == (peer != "1")      # "1" pulls dx from the owners instead
         assert res.pop("rows_received") > 0
         for name, (cos, rr) in res.items():
             cmin, rmax = PARITY_LIMITS[name]
@@ -139,6 +141,7 @@ def test_ep_rank_that_receives_no_tokens():
     assert results[1]["rows_received"] == 0 and results[0]["rows_received"] > 0
     for rank, res in results.items():
         res.pop("used_peer"), res.pop("rows_received"), res.pop("used_pull_dispatch")
+        assert res.pop("dx_returned_by_copies") is True
         assert res.pop("forward_without_readback") is True
         for name, (cos, rr) in res.items():
             cmin, rmax = PARITY_LIMITS[name]
@@ -154,7 +157,7 @@ def test_ep_dispatch_through_nccl_and_both_dispatch_paths_give_the_same_bits():
     from sonicmoe.ep import PARITY_LIMITS
     for rank, res in _launch(2, "0", False, "nccl").items():
         assert res.pop("used_pull_dispatch") is False and res.pop("forward_without_readback") is False
-        res.pop("used_peer"), res.pop("rows_received")
+        res.pop("used_peer"), res.pop("rows_received"), res.pop("dx_returned_by_copies")
         for name, (cos, rr) in res.items():
             cmin, rmax = PARITY_LIMITS[name]
             assert cos > cmin and rr < rmax, (rank, name, cos, rr)
