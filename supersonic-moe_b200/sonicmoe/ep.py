@@ -421,11 +421,18 @@ class DispatchPlan:
         else:
             comm.wait_stream(cur)
         with torch.cuda.stream(comm):
-            at = 0
-            for s_rank, n in enumerate(self.recv_counts):
-                if n:
-                    ret.rows_of(s_rank, self.src_seg_off[s_rank], n).copy_(rows[at:at + n], non_blocking=True)
+            starts, at = [], 0
+            for n in self.recv_counts:
+                starts.append(at)
                 at += n
+            me, world = dist.get_rank(self.group), self.world
+            for step in range(1, world + 1):
+                # rank r writes to r+1 first, then r+2, ...: at any moment every destination has one writer
+                s_rank = (me + step) % world
+                n = self.recv_counts[s_rank]
+                if n:
+                    ret.rows_of(s_rank, self.src_seg_off[s_rank], n).copy_(
+                        rows[starts[s_rank]:starts[s_rank] + n], non_blocking=True)
             ret.everyone_has_written()
         rows.record_stream(comm)
         cur.wait_stream(comm)
