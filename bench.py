@@ -342,6 +342,37 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def _write_timeline(path, step, d, rank, barrier):
+    """The GPU operations of one step (kernels, copies, memsets of every stream) in start order, as text: start,
+    duration, idle time since the previous operation ended, stream, name.  torch.profiler, not ncu (ncu is never put
+    around a multi-rank command); rank 0 writes the file."""
+    from torch.profiler import ProfilerActivity, profile
+    barrier()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(3):
+            step(d["x"], d["dy"], d["idx"], d["scores"])
+        torch.cuda.synchronize()
+    barrier()
+    if rank != 0:
+        return
+    ops_ = [e for e in prof.events() if e.device_type is not None and "cuda" in str(e.device_type).lower()]
+    ops_.sort(key=lambda e: e.time_range.start)
+    # the middle step: from the second to the third occurrence of the step's first kernel
+    first = ops_[0].name
+    marks = [i for i, e in enumerate(ops_) if e.name == first]
+    per = len(marks) // 3 if len(marks) >= 3 else 1
+    a, b = (marks[per], marks[2 * per]) if len(marks) >= 3 * per and per > 0 else (0, len(ops_))
+    t0 = ops_[a].time_range.start
+    prev_end = t0
+    with open(path, "w") as f:
+        f.write(f"step: {ops_[b - 1].time_range.end - t0:.1f} us, {b - a} GPU operations (start us, duration us, "
+                "idle us since the previous operation ended, name)\n")
+        for e in ops_[a:b]:
+            f.write(f"{e.time_range.start - t0:9.1f} {e.time_range.end - e.time_range.start:8.1f} "
+                    f"{e.time_range.start - prev_end:7.1f}  {e.name[:100]}\n")
+            prev_end = max(prev_end, e.time_range.end)
+
+
 def _ep_parity(dist, dev):
     """A small expert-parallel step against the single-GPU layer on the same tokens, on every rank, before anything
     is timed: {tensor: [min cosine over ranks, max relative RMS error over ranks]} plus the verdict."""
@@ -432,6 +463,8 @@ def _measure(args, cname, world, rank, dev, dist, sonicmoe, ops, strong, extra=F
     per_step = [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)]
     ms = total_ms / steps
 
+    if args.timeline:      # one more step under torch.profiler: every GPU operation with start, duration, gap
+        _write_timeline(args.timeline, step, d, rank, barrier)
     if args.lean:      # profiling runs: warm-up + timed steps only, nothing else launches
         sampler.stop()
         if rank == 0:
@@ -675,6 +708,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-extras", action="store_true", help="multi-GPU: skip the strong-scaling C4 / C5 runs")
     ap.add_argument("--lean", action="store_true", help="warm-up and timed steps only (for ncu captures)")
+    ap.add_argument("--timeline", default=None, metavar="FILE",
+                    help="also write the GPU operations of one step (torch.profiler) to FILE (rank 0)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
