@@ -143,7 +143,9 @@ static int launch3(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
   int64_t pairs = sm_count() / 2;
   if (max_pair_tiles < pairs) pairs = max_pair_tiles;
   if (pairs <= 0) return SMOE_OK;
-  kern<<<(unsigned)(2 * pairs), S::THREADS, S::TOTAL, stream>>>(ta, tb, tsa, tsb, tc, p);
+  GemmParams q = p;
+  q.dbg_stage_cut = g_stage_cut > 2 ? 2 : g_stage_cut;      // the head / tail schedule holds two stages
+  kern<<<(unsigned)(2 * pairs), S::THREADS, S::TOTAL, stream>>>(ta, tb, tsa, tsb, tc, q);
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }
 

@@ -119,6 +119,7 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   const int n_col_tiles = p.N / BN;
   const int n_total = (MODE == WGRAD) ? p.E * (p.rows / (2 * BM)) * n_col_tiles : s_pairs[p.E] * n_col_tiles;
   const bool a_mn = MODE == WGRAD && p.a_mn;
+  const int nst = S::STAGES - p.dbg_stage_cut;      // timing experiment: a shallower ring (0 in product use)
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer (both CTAs): warp-uniform loops, one
@@ -169,7 +170,7 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const uint32_t full = full0 + 8 * stage;
         const uint32_t a_dst = smem_base + stage * S::STAGE_BYTES;
         const uint32_t b_dst = a_dst + S::A_BYTES;
-        if (dbg_noload && dbg_filled >= S::STAGES) {
+        if (dbg_noload && dbg_filled >= nst) {
           if (rank == 0 && elect_one()) mbar_arrive(bar_full + 8 * stage);
         } else {
           ++dbg_filled;
@@ -181,7 +182,7 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             tma_load_2d_pair(b_dst + S::BH_BYTES, &tmap_b, full, kt * BK, b_row + HN);
           }
         }
-        if (++stage == S::STAGES) { stage = 0; phase ^= 1; }
+        if (++stage == nst) { stage = 0; phase ^= 1; }
       }
     }
     if (!ok && lane == 0) { *s_abort = 1; atomicCAS(p.status, 0, 201); }
@@ -260,7 +261,7 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           if (!both) {
             if ((k < J ? k : k - (nkt - J)) == 0) held0 = stage; else held1 = stage;
           }
-          if (++stage == S::STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == nst) { stage = 0; phase ^= 1; }
           if (sf_done) {
             if (++sfs == S::SF_SLOTS) { sfs = 0; sfphase ^= 1; }
           }
@@ -330,20 +331,26 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           if (!ok) break;
           tc_fence_after();
           if (!(p.debug_skip_store & 8)) {
+            // all of this warp's columns of the half in one go (one wait), the accumulator is handed back before
+            // the conversion: the drain is what the next tile's MMAs wait for
             const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + h * HN + grp * CPW;
+            uint32_t r[NC][32];
 #pragma unroll
-            for (int c = 0; c < NC; ++c) {
-              uint32_t r[32];
-              tmem_ld32(t_row + c * 32, r);
-              tmem_ld_wait();
+            for (int c = 0; c < NC; ++c) tmem_ld32(t_row + c * 32, r[c]);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * h);
+#pragma unroll
+            for (int c = 0; c < NC; ++c)
 #pragma unroll
               for (int i = 0; i < 16; ++i)
-                pk[h][c][i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-            }
+                pk[h][c][i] = pack_bf16x2(__uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1]));
+          } else {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * h);
           }
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * h);
         }
         if (!ok) break;
         if (t.valid && !(p.debug_skip_store & 8)) {
