@@ -145,6 +145,7 @@ static int launch3(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
   if (pairs <= 0) return SMOE_OK;
   GemmParams q = p;
   q.dbg_stage_cut = g_stage_cut > 2 ? 2 : g_stage_cut;      // the head / tail schedule holds two stages
+  q.l2_prefetch = g_l2_prefetch;                            // this kernel reads it as "length of the head / tail", -1 = default
   kern<<<(unsigned)(2 * pairs), S::THREADS, S::TOTAL, stream>>>(ta, tb, tsa, tsb, tc, q);
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }

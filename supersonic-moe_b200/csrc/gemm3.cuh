@@ -203,6 +203,8 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       int stage = 0, sfs = 0;
       uint32_t phase = 0, aphase = 0, sfphase = 0;
       bool ok = true;
+      // K tiles issued half-by-half at both ends of a tile (a timing experiment may shorten it)
+      const int JJ = (p.l2_prefetch >= 0 && p.l2_prefetch < kHeadTail3) ? p.l2_prefetch : kHeadTail3;
 
       // MMAs of K tile number k (of its tile) held in ring stage st, into accumulator half h
       auto issue_half = [&](int st, int k, int h) {
@@ -220,7 +222,7 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const PairTile t = pair_tile<BN, MODE>(tile, 0, p, s_efo, s_pairs);
         const int nkt = __shfl_sync(0xffffffffu, t.nkt, 0);
         if (nkt == 0) continue;
-        const int J = nkt >= 2 * kHeadTail3 ? kHeadTail3 : 0;
+        const int J = nkt >= 2 * JJ ? JJ : 0;
         int held0 = 0, held1 = 0;             // ring stages of the K tiles whose half-1 MMAs are still to come
         static_assert(kHeadTail3 == 2, "held0 / held1");
         ok = __all_sync(0xffffffffu, mbar_wait(bar_tempty, aphase ^ 1));
@@ -278,8 +280,10 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
               const int kfirst = head_end ? 0 : nkt - J;
               issue_half(held0, kfirst, 1);
               tc_commit_pair(bar_empty + 8 * held0, 3);
-              issue_half(held1, kfirst + 1, 1);
-              tc_commit_pair(bar_empty + 8 * held1, 3);
+              if (J == 2) {
+                issue_half(held1, kfirst + 1, 1);
+                tc_commit_pair(bar_empty + 8 * held1, 3);
+              }
             }
           }
         }
