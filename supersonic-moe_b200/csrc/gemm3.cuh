@@ -34,7 +34,8 @@ struct Gemm3Smem {
   static constexpr int SF_SLOTS = 2;
   static constexpr int SF_BYTES = SF_SLOTS * SF_SLOT_BYTES;
   static constexpr int EPI_WARPS = 8;                           // four TMEM lane quadrants x two column groups
-  static constexpr int THREADS = 32 * (2 + EPI_WARPS);
+  static constexpr int LEAD_WARPS = 3;                          // operand producer, MMA issuer, scale producer
+  static constexpr int THREADS = 32 * (LEAD_WARPS + EPI_WARPS);
   static constexpr int EPI_BUFS = 2;                            // staging buffers per warp, used in turn
   static constexpr int EPI_BYTES_PER_WARP = EPI_BUFS * 2048;    // bf16 32x32 or f32 32x16 per buffer
   static constexpr int EPI_BYTES = EPI_WARPS * EPI_BYTES_PER_WARP;
@@ -125,15 +126,14 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     // ------------------------------------------------------------ producer (both CTAs): warp-uniform loops, one
     // elected lane issues
     if (lane == 0) {
-      prefetch_tmap(&tmap_a); prefetch_tmap(&tmap_b); prefetch_tmap(&tmap_sfa); prefetch_tmap(&tmap_sfb);
+      prefetch_tmap(&tmap_a); prefetch_tmap(&tmap_b);
     }
     const uint32_t full0 = map_to_cta(bar_full, 0);
-    const uint32_t sffull0 = map_to_cta(bar_sffull, 0);
     const int n_total_u = __shfl_sync(0xffffffffu, n_total, 0);
     const bool dbg_noload = (p.debug_skip_store & 4) != 0;   // timing experiment: operands fetched for one ring pass only
     int dbg_filled = 0;
-    int stage = 0, sfs = 0;
-    uint32_t phase = 0, sfphase = 0;
+    int stage = 0;
+    uint32_t phase = 0;
     bool ok = true;
     for (int tile = pair_id; tile < n_total_u && ok; tile += n_pairs_grid) {
       const PairTile tl = pair_tile<BN, MODE>(tile, rank, p, s_efo, s_pairs);
@@ -146,25 +146,8 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       const int te = __shfl_sync(0xffffffffu, tl.e, 0);
       const int b_base = (MODE == WGRAD) ? n0 : te * p.N + n0;
       const int b_row = b_base + rank * (HN / 2);        // this CTA's 96 rows of half 0; half 1 lies HN rows further
-      const int sfa_tile = valid ? m0 / 128 : 0;         // phantom half: any in-range tile will do
-      const int sfb_tile = b_base / 128;                 // n0 is a multiple of 384, hence of 128
       const int a_row = valid ? m0 : 0;
       for (int kt = kt0; kt < kt0 + nkt; ++kt) {
-        if (((kt - kt0) & (S::SF_GROUP - 1)) == 0) {
-          ok = __all_sync(0xffffffffu, mbar_wait(bar_sfempty + 8 * sfs, sfphase ^ 1));
-          if (!ok) break;
-          if (elect_one()) {
-            const uint32_t sffull = sffull0 + 8 * sfs;
-            const uint32_t dst = sf_base + sfs * S::SF_SLOT_BYTES;
-            if (rank == 0) mbar_expect_tx(bar_sffull + 8 * sfs, S::SF_TX_BYTES);
-            tma_load_2d_pair(dst, &tmap_sfa, sffull, 0, sfa_tile * p.sfa_ktiles + kt);
-#pragma unroll
-            for (int j = 0; j < S::SFB_TILES; ++j)
-              tma_load_2d_pair(dst + S::SF_GROUP * 512 * (1 + j), &tmap_sfb, sffull, 0,
-                               (sfb_tile + j) * p.sfb_ktiles + kt);
-          }
-          if (++sfs == S::SF_SLOTS) { sfs = 0; sfphase ^= 1; }
-        }
         ok = __all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * stage, phase ^ 1));
         if (!ok) break;
         const uint32_t full = full0 + 8 * stage;
@@ -297,15 +280,55 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       if (!ok && lane == 0) { *s_abort = 1; atomicCAS(p.status, 0, 202); }
     }
     __syncwarp();
+  } else if (warp == 2) {
+    // ------------------------------------------------------------ scale producer (both CTAs).  A warp of its own:
+    // the scales of the next group of K tiles are requested as soon as a slot of their ring is free - up to two
+    // groups (eight K tiles) ahead of the MMAs - instead of when the operand ring gets there (two to four K tiles
+    // ahead, about the latency of the small copies while L2 is busy with the operands).
+    if (lane == 0) { prefetch_tmap(&tmap_sfa); prefetch_tmap(&tmap_sfb); }
+    const uint32_t sffull0 = map_to_cta(bar_sffull, 0);
+    const int n_total_u = __shfl_sync(0xffffffffu, n_total, 0);
+    int sfs = 0;
+    uint32_t sfphase = 0;
+    bool ok = true;
+    for (int tile = pair_id; tile < n_total_u && ok; tile += n_pairs_grid) {
+      const PairTile tl = pair_tile<BN, MODE>(tile, rank, p, s_efo, s_pairs);
+      const int nkt = __shfl_sync(0xffffffffu, tl.nkt, 0);
+      if (nkt == 0) continue;
+      const int kt0 = __shfl_sync(0xffffffffu, tl.kt0, 0);
+      const int valid = __shfl_sync(0xffffffffu, tl.valid, 0);
+      const int m0 = __shfl_sync(0xffffffffu, tl.m0, 0);
+      const int n0 = __shfl_sync(0xffffffffu, tl.n0, 0);
+      const int te = __shfl_sync(0xffffffffu, tl.e, 0);
+      const int b_base = (MODE == WGRAD) ? n0 : te * p.N + n0;
+      const int sfa_tile = valid ? m0 / 128 : 0;         // phantom half: any in-range tile will do
+      const int sfb_tile = b_base / 128;                 // n0 is a multiple of 384, hence of 128
+      for (int kt = kt0; kt < kt0 + nkt; kt += S::SF_GROUP) {
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_sfempty + 8 * sfs, sfphase ^ 1));
+        if (!ok) break;
+        if (elect_one()) {
+          const uint32_t sffull = sffull0 + 8 * sfs;
+          const uint32_t dst = sf_base + sfs * S::SF_SLOT_BYTES;
+          if (rank == 0) mbar_expect_tx(bar_sffull + 8 * sfs, S::SF_TX_BYTES);
+          tma_load_2d_pair(dst, &tmap_sfa, sffull, 0, sfa_tile * p.sfa_ktiles + kt);
+#pragma unroll
+          for (int j = 0; j < S::SFB_TILES; ++j)
+            tma_load_2d_pair(dst + S::SF_GROUP * 512 * (1 + j), &tmap_sfb, sffull, 0,
+                             (sfb_tile + j) * p.sfb_ktiles + kt);
+        }
+        if (++sfs == S::SF_SLOTS) { sfs = 0; sfphase ^= 1; }
+      }
+    }
+    if (!ok && lane == 0) { *s_abort = 1; atomicCAS(p.status, 0, 206); }
   } else {
     // ------------------------------------------------------------ epilogue: 8 warps per CTA, each owns 32 rows
     // (its TMEM lane quadrant) x 96 columns of each accumulator half
-    const int q = warp & 3;
-    const int grp = (warp - 2) >> 2;
+    const int q = warp & 3;                      // the TMEM lane quadrant a warp may read is its index modulo 4
+    const int grp = (warp - S::LEAD_WARPS) >> 2;
     const int row_in_tile = q * 32 + lane;
     constexpr int CPW = HN / 2;                 // columns per warp and half
     constexpr int NC = CPW / 32;                // 32-column chunks
-    const uint32_t stg = smem_u32(epi + (warp - 2) * S::EPI_BYTES_PER_WARP);
+    const uint32_t stg = smem_u32(epi + (warp - S::LEAD_WARPS) * S::EPI_BYTES_PER_WARP);
     const uint32_t tempty0 = map_to_cta(bar_tempty, 0);
     uint32_t aphase = 0;
     int buf = 0;
