@@ -157,7 +157,10 @@ struct Gemm2Smem {
   // 192-column gated tiles measured slower than two: 646 vs 619 us up-projection, 412 vs 385 us fused dgated.)
   static constexpr int COL_GROUPS = 2;
   static constexpr int EPI_WARPS = 4 * COL_GROUPS;
-  static constexpr int THREADS = 32 * (2 + EPI_WARPS + EXTRA_WARPS);
+  // the last warp brings the scales: a producer of its own, so that they are requested as soon as a slot of their
+  // ring is free (up to two groups of K tiles ahead of the MMAs) instead of when the operand ring gets there
+  static constexpr int SF_WARP = 2 + EPI_WARPS + EXTRA_WARPS;
+  static constexpr int THREADS = 32 * (SF_WARP + 1);
   static constexpr int EPI_BYTES = EPI_WARPS * EPI_BYTES_PER_WARP;
   static constexpr int AUX_BYTES = 512 + 2 * (kMaxExperts2 + 1) * 4 + 8;      // barriers etc. + expert offsets
   static constexpr int BUDGET = 227 * 1024 - 1024 - AUX_BYTES - EPI_BYTES;    // 1024: alignment slack
@@ -298,15 +301,14 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     // Warp-uniform loops, one elected lane issues (see the MMA issuer below for why); only the gather path keeps
     // per-lane state (four row indices each).
     if (lane == 0) {
-      prefetch_tmap(&tmap_a); prefetch_tmap(&tmap_b); prefetch_tmap(&tmap_sfa); prefetch_tmap(&tmap_sfb);
+      prefetch_tmap(&tmap_a); prefetch_tmap(&tmap_b);
     }
     const uint32_t full0 = map_to_cta(bar_full, 0);      // the leader's full barriers
-    const uint32_t sffull0 = map_to_cta(bar_sffull, 0);
     const int n_total_u = __shfl_sync(0xffffffffu, n_total, 0);
     // MN-major operands: both of a weight gradient, or the B of a PLAIN product whose weights lie [E, K, N]
     const bool a_mn = MODE == WGRAD && p.a_mn, b_mn = (MODE == WGRAD || MODE == PLAIN) && p.b_mn;
-    int stage = 0, sfs = 0;
-    uint32_t phase = 0, sfphase = 0;
+    int stage = 0;
+    uint32_t phase = 0;
     bool ok = true;
     const bool dbg_noload = (p.debug_skip_store & 4) != 0;   // timing experiment: operands fetched for one ring pass only
     int dbg_filled = 0;
@@ -325,28 +327,8 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       const bool b_mn_plain = MODE == PLAIN && b_mn;       // B of expert te = rows [te*K, (te+1)*K) of an [E*K, N] matrix
       const int b_row = (b_mn_plain ? n0 : b_base) + rank * (BN / 2);
       const int b_k0 = b_mn_plain ? te * p.K : 0;
-      // rows of the A-scale tensor are 512-byte tiles: (row tile, k tile)
-      const int sfa_tile = valid ? m0 / 128 : 0;         // phantom half: any in-range tile will do
-      const int sfb_tile = b_base / 128;                 // first 128-row scale tile touching the BN window
       const int a_row = valid ? m0 : 0;
       for (int kt = kt0; kt < kt0 + nkt; ++kt) {
-        if (((kt - kt0) & (S::SF_GROUP - 1)) == 0) {
-          // scales of the next SF_GROUP K tiles: rows [tile*ktiles + kt, +SF_GROUP) of the 512-byte-row scale
-          // tensors (rows past this operand tile's K range are fetched too and never used)
-          ok = __all_sync(0xffffffffu, mbar_wait(bar_sfempty + 8 * sfs, sfphase ^ 1));
-          if (!ok) break;
-          if (elect_one()) {
-            const uint32_t sffull = sffull0 + 8 * sfs;
-            const uint32_t dst = sf_base + sfs * S::SF_SLOT_BYTES;
-            if (rank == 0) mbar_expect_tx(bar_sffull + 8 * sfs, S::SF_TX_BYTES);
-            tma_load_2d_pair(dst, &tmap_sfa, sffull, 0, sfa_tile * p.sfa_ktiles + kt);
-#pragma unroll
-            for (int j = 0; j < S::SFB_TILES; ++j)
-              tma_load_2d_pair(dst + S::SF_GROUP * 512 * (1 + j), &tmap_sfb, sffull, 0,
-                               (sfb_tile + j) * p.sfb_ktiles + kt);
-          }
-          if (++sfs == S::SF_SLOTS) { sfs = 0; sfphase ^= 1; }
-        }
         ok = __all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * stage, phase ^ 1));
         if (!ok) break;
         const uint32_t full = full0 + 8 * stage;
@@ -530,6 +512,46 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     }
     ok = __all_sync(0xffffffffu, ok);
     if (!ok && lane == 0) { *s_abort = 1; atomicCAS(p.status, 0, 205); }
+  } else if (warp == S::SF_WARP) {
+    // ------------------------------------------------------------ scale producer (both CTAs)
+    if (lane == 0) { prefetch_tmap(&tmap_sfa); prefetch_tmap(&tmap_sfb); }
+    const uint32_t sffull0 = map_to_cta(bar_sffull, 0);
+    const int n_total_u = __shfl_sync(0xffffffffu, n_total, 0);
+    int sfs = 0;
+    uint32_t sfphase = 0;
+    bool ok = true;
+    for (int tile = pair_id; tile < n_total_u && ok; tile += n_pairs_grid) {
+      const PairTile tl = pair_tile<BN, MODE>(tile, rank, p, s_efo, s_pairs);
+      const int nkt = __shfl_sync(0xffffffffu, tl.nkt, 0);
+      if (nkt == 0) continue;
+      const int kt0 = __shfl_sync(0xffffffffu, tl.kt0, 0);
+      const int valid = __shfl_sync(0xffffffffu, tl.valid, 0);
+      const int m0 = __shfl_sync(0xffffffffu, tl.m0, 0);
+      const int n0 = __shfl_sync(0xffffffffu, tl.n0, 0);
+      const int te = __shfl_sync(0xffffffffu, tl.e, 0);
+      const int b_base = (MODE == WGRAD) ? n0 : te * p.N + n0;
+      // rows of the scale tensors are 512-byte tiles: (row tile, k tile)
+      const int sfa_tile = valid ? m0 / 128 : 0;         // phantom half: any in-range tile will do
+      const int sfb_tile = b_base / 128;                 // first 128-row scale tile touching the BN window
+      for (int kt = kt0; kt < kt0 + nkt; kt += S::SF_GROUP) {
+        // scales of the next SF_GROUP K tiles: rows [tile*ktiles + kt, +SF_GROUP) of the 512-byte-row scale
+        // tensors (rows past this operand tile's K range are fetched too and never used)
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_sfempty + 8 * sfs, sfphase ^ 1));
+        if (!ok) break;
+        if (elect_one()) {
+          const uint32_t sffull = sffull0 + 8 * sfs;
+          const uint32_t dst = sf_base + sfs * S::SF_SLOT_BYTES;
+          if (rank == 0) mbar_expect_tx(bar_sffull + 8 * sfs, S::SF_TX_BYTES);
+          tma_load_2d_pair(dst, &tmap_sfa, sffull, 0, sfa_tile * p.sfa_ktiles + kt);
+#pragma unroll
+          for (int j = 0; j < S::SFB_TILES; ++j)
+            tma_load_2d_pair(dst + S::SF_GROUP * 512 * (1 + j), &tmap_sfb, sffull, 0,
+                             (sfb_tile + j) * p.sfb_ktiles + kt);
+        }
+        if (++sfs == S::SF_SLOTS) { sfs = 0; sfphase ^= 1; }
+      }
+    }
+    if (!ok && lane == 0) { *s_abort = 1; atomicCAS(p.status, 0, 206); }
   } else {
     // ------------------------------------------------------------ epilogue (8 or 12 warps per CTA)
     const int q = warp & 3;                       // TMEM lane quadrant of this warp
