@@ -304,6 +304,18 @@ int smoe_gemm_wgrad_mn(const void* a_fp8, const void* a_sf, const void* b_fp8, c
                        float* c, int64_t M, int64_t N, int64_t TKp, int64_t E, int accumulate, int layout,
                        int32_t* status, void* stream);
 
+/* Two such products in ONE launch: c1[e] (+)= A1_e^T B1_e (M1 x N) and c2[e] (+)= A2_e^T B2_e (M2 x N) over the same
+ * expert segments - in the layer dw1 (A = dz, B = x) and dw2 (A = y1s, B = dout).  Run one after the other their
+ * tile counts (768 and 384 at the reference shape, on 74 CTA pairs) leave a partly filled last wave each; together
+ * they leave one.  256 x 384 kernel only: N % 384 == 0, M1, M2 % 256 == 0, E <= 256; both A operands stored
+ * [TKp, M] (a_rows_major_tk = 1) or both [M, TKp] (0); both B operands [N, TKp]; every output element still has a
+ * single writer.  The reference issues the two weight-gradient GEMMs separately
+ * (sonicmoe/quack_utils/sm100_funcs.py:947-976). */
+int smoe_gemm_wgrad_mn_pair(const void* a1_fp8, const void* a1_sf, const void* b1_fp8, const void* b1_sf, float* c1,
+                            int64_t M1, const void* a2_fp8, const void* a2_sf, const void* b2_fp8, const void* b2_sf,
+                            float* c2, int64_t M2, const int32_t* efo, int64_t N, int64_t TKp, int64_t E,
+                            int accumulate, int a_rows_major_tk, int32_t* status, void* stream);
+
 /* ---- gated activations outside the GEMM epilogues ----------------------------
  * The fused epilogues of smoe_gemm_gated / smoe_gemm_dgated* carry SwiGLU.  For the reference's other gated
  * activations (sonicmoe/enums.py:18-33; mapped to quack.activation.reglu / geglu in quack_utils/gemm_gated.py:171-177)

@@ -135,7 +135,8 @@ static int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
 // ---- two-CTA kernel with the 256 x 384 double-accumulator tile (PLAIN and WGRAD) ------------------------------
 template <int MODE>
 static int launch3(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa, const CUtensorMap& tsb,
-                   const CUtensorMap& tc, const GemmParams& p, int64_t max_pair_tiles, cudaStream_t stream) {
+                   const CUtensorMap& tc, const GemmParams& p, int64_t max_pair_tiles, cudaStream_t stream,
+                   const SecondMaps* second = nullptr) {
   using S = Gemm3Smem<MODE>;
   static bool attr_set[kMaxDevices] = {};
   auto kern = gemm3_mxf8_kernel<MODE>;
@@ -146,7 +147,8 @@ static int launch3(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
   GemmParams q = p;
   q.dbg_stage_cut = g_stage_cut > 2 ? 2 : g_stage_cut;      // the head / tail schedule holds two stages
   q.l2_prefetch = g_l2_prefetch;                            // this kernel reads it as "length of the head / tail", -1 = default
-  kern<<<(unsigned)(2 * pairs), S::THREADS, S::TOTAL, stream>>>(ta, tb, tsa, tsb, tc, q);
+  SecondMaps none{};
+  kern<<<(unsigned)(2 * pairs), S::THREADS, S::TOTAL, stream>>>(ta, tb, tsa, tsb, tc, second ? *second : none, q);
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
 }
 
@@ -189,6 +191,36 @@ static int run3(const void* a, int64_t a_rows, int64_t a_cols, const void* b, in
   if (rc) return rc;
   constexpr int M3 = (MODE == WGRAD) ? WGRAD : PLAIN;
   return launch3<M3>(ta, tb, tsa, tsb, tc, p, pair_tiles, stream);
+}
+
+// Two weight-gradient products in ONE launch of the 256 x 384 kernel: same N, same K range (TKp), same operand
+// layouts (A [TKp, M] or [M, TKp] for both; B K-major), own operands, scales and outputs.
+static int run3_wgrad_pair(const void* a1, const void* b1, GemmParams& p, const void* a2, const void* b2,
+                           const uint8_t* sfa2, const uint8_t* sfb2, int64_t TKp, cudaStream_t stream) {
+  CUtensorMap ta, tb, tsa, tsb, tc;
+  SecondMaps sm{};
+  const int64_t M1 = p.rows, M2 = p.rows2;
+  int rc = make_tmap_u8(&ta, a1, p.a_mn ? TKp : M1, p.a_mn ? M1 : TKp, BK, BM);
+  if (!rc) rc = make_tmap_u8(&sm.a, a2, p.a_mn ? TKp : M2, p.a_mn ? M2 : TKp, BK, BM);
+  if (!rc) rc = make_tmap_u8(&tb, b1, p.N, TKp, BK, kHN3 / 2);
+  if (!rc) rc = make_tmap_u8(&sm.b, b2, p.N, TKp, BK, kHN3 / 2);
+  if (rc) return rc;
+  const int64_t sfb_tiles = (int64_t)(p.N / 128) * p.sfb_ktiles;
+  rc = make_tmap(&tsa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, p.sfa, (int64_t)(M1 / 128) * p.sfa_ktiles, 128, 128, kSfGroup2,
+                 CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (!rc) rc = make_tmap(&sm.sfa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, sfa2, (int64_t)(M2 / 128) * p.sfa_ktiles, 128, 128,
+                          kSfGroup2, CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (!rc) rc = make_tmap(&tsb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, p.sfb, sfb_tiles, 128, 128, kSfGroup2,
+                          CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (!rc) rc = make_tmap(&sm.sfb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, sfb2, sfb_tiles, 128, 128, kSfGroup2,
+                          CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (!rc) rc = make_tmap(&tc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.c, (uint64_t)p.E * M1, p.N, 16, 32,
+                          CU_TENSOR_MAP_SWIZZLE_64B);
+  if (!rc) rc = make_tmap(&sm.c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.c2, (uint64_t)p.E * M2, p.N, 16, 32,
+                          CU_TENSOR_MAP_SWIZZLE_64B);
+  if (rc) return rc;
+  const int64_t pair_tiles = (int64_t)p.E * ((M1 + M2) / 256) * (p.N / kBN3);
+  return launch3<WGRAD>(ta, tb, tsa, tsb, tc, p, pair_tiles, stream, &sm);
 }
 
 // Column tile of the two-CTA kernel for a mode and N; 0 = not applicable.
@@ -466,6 +498,29 @@ int smoe_gemm_wgrad_mn(const void* a_fp8, const void* a_sf, const void* b_fp8, c
   p.a_mn = layout & 1; p.b_mn = (layout >> 1) & 1;
   return run<WGRAD>(a_fp8, p.a_mn ? TKp : M, p.a_mn ? M : TKp, b_fp8, p.b_mn ? TKp : N, p.b_mn ? N : TKp, p,
                     (int)(E * (M / 128) * (N / 128)), (cudaStream_t)stream);
+}
+
+/* dw_1 (+)= A1^T B1 and dw_2 (+)= A2^T B2 in one launch; see the header. */
+int smoe_gemm_wgrad_mn_pair(const void* a1_fp8, const void* a1_sf, const void* b1_fp8, const void* b1_sf, float* c1,
+                            int64_t M1, const void* a2_fp8, const void* a2_sf, const void* b2_fp8, const void* b2_sf,
+                            float* c2, int64_t M2, const int* efo, int64_t N, int64_t TKp, int64_t E, int accumulate,
+                            int a_rows_major_tk, int* status, void* stream) {
+  if (M1 <= 0 || M2 <= 0 || N <= 0 || M1 % 256 || M2 % 256 || N % kBN3 || TKp < 0 || TKp % 128 || E <= 0 ||
+      E > kMaxExperts2)
+    return SMOE_ERR_SHAPE;
+  if (g_force_v1 || (g_force_bn != 0 && g_force_bn != kBN3)) return SMOE_ERR_SHAPE;   // the tests' tile forcing
+  if (TKp == 0) {
+    const int rc = wgrad_nothing_routed(c1, M1, N, E, accumulate, (cudaStream_t)stream);
+    return rc ? rc : wgrad_nothing_routed(c2, M2, N, E, accumulate, (cudaStream_t)stream);
+  }
+  GemmParams p{};
+  p.rows = (int)M1; p.rows2 = (int)M2; p.N = (int)N; p.K = (int)TKp; p.E = (int)E;
+  p.efo = efo; p.sfa = (const uint8_t*)a1_sf; p.sfb = (const uint8_t*)b1_sf;
+  p.sfa_ktiles = (int)(TKp / 128); p.sfb_ktiles = (int)(TKp / 128);
+  p.c = c1; p.c2 = c2; p.accumulate = accumulate; p.status = status; p.debug_skip_store = g_skip_store;
+  p.a_mn = a_rows_major_tk ? 1 : 0;
+  return run3_wgrad_pair(a1_fp8, b1_fp8, p, a2_fp8, b2_fp8, (const uint8_t*)a2_sf, (const uint8_t*)b2_sf, TKp,
+                         (cudaStream_t)stream);
 }
 
 }  // extern "C"

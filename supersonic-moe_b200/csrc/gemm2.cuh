@@ -187,6 +187,7 @@ struct PairTile {
   int e;        // expert
   int kt0, nkt; // K-tile range
   int valid;    // 0: this CTA's half lies beyond its expert's rows - compute, store nothing
+  int prob;     // WGRAD with two products in one launch: which one this tile belongs to
 };
 
 // varlen-M: experts own ceil(n_e / 2) row pairs; s_pairs = exclusive prefix of that.
@@ -195,9 +196,16 @@ __device__ __forceinline__ PairTile pair_tile(int tile, int rank, const GemmPara
                                               const int* s_pairs) {
   PairTile t;
   const int n_tiles = (p.N + BN - 1) / BN;     // DGATEDQ may run a ragged last column tile
+  t.prob = 0;
   if (MODE == WGRAD) {
-    const int m_pairs = p.rows / (2 * BM);
-    const int per_e = m_pairs * n_tiles;
+    int m_pairs = p.rows / (2 * BM);
+    int per_e = m_pairs * n_tiles;
+    if (p.rows2 > 0 && tile >= p.E * per_e) {       // tiles of the second product follow those of the first
+      tile -= p.E * per_e;
+      t.prob = 1;
+      m_pairs = p.rows2 / (2 * BM);
+      per_e = m_pairs * n_tiles;
+    }
     t.e = tile / per_e;
     const int r = tile - t.e * per_e;
     t.m0 = (r / n_tiles) * 2 * BM + rank * BM;

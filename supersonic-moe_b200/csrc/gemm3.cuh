@@ -50,11 +50,19 @@ struct Gemm3Smem {
   static constexpr uint32_t SF_TX_BYTES = 2u * SF_SLOT_BYTES;
 };
 
+// Tensor maps of a second weight-gradient product that shares the launch (GemmParams::rows2 > 0): two products
+// whose tile counts are no multiples of the number of CTA pairs leave one partly filled last wave together instead
+// of one each.
+struct SecondMaps {
+  CUtensorMap a, b, sfa, sfb, c;
+};
+
 template <int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((Gemm3Smem<MODE>::THREADS), 1)
 gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                   const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
-                  const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
+                  const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ SecondMaps second,
+                  const GemmParams p) {
   static_assert(MODE == PLAIN || MODE == WGRAD, "the 384-wide tile exists for the plain and weight-gradient GEMMs");
   using S = Gemm3Smem<MODE>;
   constexpr int BN = kBN3, HN = kHN3;
@@ -118,7 +126,8 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t sf_base = smem_u32(sfring);
   const int n_col_tiles = p.N / BN;
-  const int n_total = (MODE == WGRAD) ? p.E * (p.rows / (2 * BM)) * n_col_tiles : s_pairs[p.E] * n_col_tiles;
+  const int n_total = (MODE == WGRAD) ? p.E * ((p.rows + p.rows2) / (2 * BM)) * n_col_tiles
+                                      : s_pairs[p.E] * n_col_tiles;
   const bool a_mn = MODE == WGRAD && p.a_mn;
   const int nst = S::STAGES - p.dbg_stage_cut;      // timing experiment: a shallower ring (0 in product use)
 
@@ -127,6 +136,7 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     // elected lane issues
     if (lane == 0) {
       prefetch_tmap(&tmap_a); prefetch_tmap(&tmap_b);
+      if (MODE == WGRAD && p.rows2 > 0) { prefetch_tmap(&second.a); prefetch_tmap(&second.b); }
     }
     const uint32_t full0 = map_to_cta(bar_full, 0);
     const int n_total_u = __shfl_sync(0xffffffffu, n_total, 0);
@@ -147,6 +157,9 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       const int b_base = (MODE == WGRAD) ? n0 : te * p.N + n0;
       const int b_row = b_base + rank * (HN / 2);        // this CTA's 96 rows of half 0; half 1 lies HN rows further
       const int a_row = valid ? m0 : 0;
+      const bool second_prob = MODE == WGRAD && __shfl_sync(0xffffffffu, tl.prob, 0) != 0;
+      const CUtensorMap* ta = second_prob ? &second.a : &tmap_a;
+      const CUtensorMap* tb = second_prob ? &second.b : &tmap_b;
       for (int kt = kt0; kt < kt0 + nkt; ++kt) {
         ok = __all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * stage, phase ^ 1));
         if (!ok) break;
@@ -159,10 +172,10 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           ++dbg_filled;
           if (elect_one()) {
             if (rank == 0) mbar_expect_tx(bar_full + 8 * stage, S::TX_BYTES);
-            if (a_mn) tma_load_2d_pair(a_dst, &tmap_a, full, m0, kt * BK);
-            else tma_load_2d_pair(a_dst, &tmap_a, full, kt * BK, a_row);
-            tma_load_2d_pair(b_dst, &tmap_b, full, kt * BK, b_row);
-            tma_load_2d_pair(b_dst + S::BH_BYTES, &tmap_b, full, kt * BK, b_row + HN);
+            if (a_mn) tma_load_2d_pair(a_dst, ta, full, m0, kt * BK);
+            else tma_load_2d_pair(a_dst, ta, full, kt * BK, a_row);
+            tma_load_2d_pair(b_dst, tb, full, kt * BK, b_row);
+            tma_load_2d_pair(b_dst + S::BH_BYTES, tb, full, kt * BK, b_row + HN);
           }
         }
         if (++stage == nst) { stage = 0; phase ^= 1; }
@@ -285,7 +298,10 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     // the scales of the next group of K tiles are requested as soon as a slot of their ring is free - up to two
     // groups (eight K tiles) ahead of the MMAs - instead of when the operand ring gets there (two to four K tiles
     // ahead, about the latency of the small copies while L2 is busy with the operands).
-    if (lane == 0) { prefetch_tmap(&tmap_sfa); prefetch_tmap(&tmap_sfb); }
+    if (lane == 0) {
+      prefetch_tmap(&tmap_sfa); prefetch_tmap(&tmap_sfb);
+      if (MODE == WGRAD && p.rows2 > 0) { prefetch_tmap(&second.sfa); prefetch_tmap(&second.sfb); }
+    }
     const uint32_t sffull0 = map_to_cta(bar_sffull, 0);
     const int n_total_u = __shfl_sync(0xffffffffu, n_total, 0);
     int sfs = 0;
@@ -303,6 +319,9 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       const int b_base = (MODE == WGRAD) ? n0 : te * p.N + n0;
       const int sfa_tile = valid ? m0 / 128 : 0;         // phantom half: any in-range tile will do
       const int sfb_tile = b_base / 128;                 // n0 is a multiple of 384, hence of 128
+      const bool second_prob = MODE == WGRAD && __shfl_sync(0xffffffffu, tl.prob, 0) != 0;
+      const CUtensorMap* tsa = second_prob ? &second.sfa : &tmap_sfa;
+      const CUtensorMap* tsb = second_prob ? &second.sfb : &tmap_sfb;
       for (int kt = kt0; kt < kt0 + nkt; kt += S::SF_GROUP) {
         ok = __all_sync(0xffffffffu, mbar_wait(bar_sfempty + 8 * sfs, sfphase ^ 1));
         if (!ok) break;
@@ -310,10 +329,10 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           const uint32_t sffull = sffull0 + 8 * sfs;
           const uint32_t dst = sf_base + sfs * S::SF_SLOT_BYTES;
           if (rank == 0) mbar_expect_tx(bar_sffull + 8 * sfs, S::SF_TX_BYTES);
-          tma_load_2d_pair(dst, &tmap_sfa, sffull, 0, sfa_tile * p.sfa_ktiles + kt);
+          tma_load_2d_pair(dst, tsa, sffull, 0, sfa_tile * p.sfa_ktiles + kt);
 #pragma unroll
           for (int j = 0; j < S::SFB_TILES; ++j)
-            tma_load_2d_pair(dst + S::SF_GROUP * 512 * (1 + j), &tmap_sfb, sffull, 0,
+            tma_load_2d_pair(dst + S::SF_GROUP * 512 * (1 + j), tsb, sffull, 0,
                              (sfb_tile + j) * p.sfb_ktiles + kt);
         }
         if (++sfs == S::SF_SLOTS) { sfs = 0; sfphase ^= 1; }
@@ -340,8 +359,9 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         if (MODE == WGRAD && !p.accumulate) {
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.c) +
-                                                    ((size_t)t.e * p.rows + grow) * p.N + t.n0 + h * HN + grp * CPW);
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(t.prob ? p.c2 : p.c) +
+                                                    ((size_t)t.e * (t.prob ? p.rows2 : p.rows) + grow) * p.N + t.n0 +
+                                                    h * HN + grp * CPW);
             for (int i = 0; i < CPW / 4; ++i) dst[i] = make_float4(0.f, 0.f, 0.f, 0.f);
           }
         }
@@ -434,10 +454,11 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-              const int crow = t.e * p.rows + t.m0 + q * 32;
+              const int crow = t.e * (t.prob ? p.rows2 : p.rows) + t.m0 + q * 32;
               const int ccol = t.n0 + h * HN + grp * CPW + c * 16;
-              if (p.accumulate) tma_reduce_add_2d(&tmap_c, sb, ccol, crow);
-              else tma_store_2d(&tmap_c, sb, ccol, crow);
+              const CUtensorMap* tc = t.prob ? &second.c : &tmap_c;
+              if (p.accumulate) tma_reduce_add_2d(tc, sb, ccol, crow);
+              else tma_store_2d(tc, sb, ccol, crow);
               bulk_commit_group();
             }
             buf ^= 1;

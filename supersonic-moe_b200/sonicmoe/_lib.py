@@ -50,6 +50,7 @@ SIGNATURES = {
     "smoe_gemm_dgated_fused_gather": (_I, [_P, _L, _P] + [_P] * 13 + [_L, _L, _L, _L, _P, _P]),
     "smoe_gemm_wgrad": (_I, [_P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _I, _P, _P]),
     "smoe_gemm_wgrad_mn": (_I, [_P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _I, _I, _P, _P]),
+    "smoe_gemm_wgrad_mn_pair": (_I, [_P, _P, _P, _P, _P, _L, _P, _P, _P, _P, _P, _L, _P, _L, _L, _L, _I, _I, _P, _P]),
     "smoe_glu_fwd": (_I, [_P, _L, _L, _I, _P, _P, _P, _P, _P]),
     "smoe_glu_bwd": (_I, [_P, _P, _P, _P, _L, _L, _I, _P, _P, _P, _P]),
     "smoe_combine": (_I, [_P, _P, _P, _P, _P, _L, _L, _P]),

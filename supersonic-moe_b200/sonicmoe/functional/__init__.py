@@ -96,6 +96,9 @@ FUSE_DGATED_QUANT = os.getenv("SONIC_MOE_FUSE_DGATED_QUANT", "1") == "1"
 # _DownProjection.backward (needed only if a caller differentiates with respect to w2 alone, so that the first
 # Function's backward never runs).
 _DEFER_DW2 = os.getenv("SONIC_MOE_DEFER_DW2", "1") == "1"
+# A deferred dw2 and dw1 run as ONE launch of the 256 x 384 kernel when both accumulate into main_grad and their
+# shapes allow it: the two tile counts then leave one partly filled last wave instead of one each.
+_PAIR_WGRADS = os.getenv("SONIC_MOE_PAIR_WGRADS", "1") == "1"
 
 
 def _mn_wgrad_ok(E: int, M: int, N: int) -> bool:
@@ -525,8 +528,16 @@ class _UpProjection(torch.autograd.Function):
             note_result_ready(dx)
             _log_stage_memory(link.get("stagewise", False), "backward: after dx")
         deferred_dw2 = link.pop("dw2_job", None)
+        paired = None
         if deferred_dw2 is not None:
-            deferred_dw2()
+            ops2 = getattr(deferred_dw2, "operands", None)
+            mg1, _ = _grad_target(w1, (E, N2, H)) if ctx.needs_input_grad[1] else (None, None)
+            # dw2 joins dw1's launch: both into main_grad, dz / y1s left [TKp, dim], column operands transposed
+            if (_PAIR_WGRADS and ops2 is not None and mg1 is not None and dz_t is None and ops2["a_rows"] and not ops2["b_rows"] and _wide_wgrad_ok(E, N2, H)
+                    and _wide_wgrad_ok(E, ops2["a_op"].shape[1], H)):
+                paired = ops2
+            else:
+                deferred_dw2()
         dw1 = None
         if ctx.needs_input_grad[1]:
             if ctx.x_is_fp8:     # x is e4m3 + raw scales: dequantise, then column-wise re-quantise
@@ -536,7 +547,17 @@ class _UpProjection(torch.autograd.Function):
             mg, base = _grad_target(w1, (E, N2, H))
             out = mg if mg is not None else torch.empty(E, N2, H, dtype=torch.float32, device=dz_q.device)
             # a row-major dz payload (32x32-block scales) doubles as the MN-major weight-gradient operand
-            _wgrad(dz_q if dz_t is None else dz_t, dz_csf, dz_t is None, xc, x_sf, xc_rows, efo, out, mg is not None)
+            if paired is not None and not xc_rows:
+                ops.gemm_wgrad_pair(dz_q, dz_csf, xc, x_sf, mg, paired["a_op"], paired["sf_a"], paired["b_op"],
+                                    paired["sf_b"], paired["mg"], efo, True, True)
+                _after_accumulate(paired["base"])
+                paired = None
+            else:
+                if paired is not None:
+                    deferred_dw2()
+                    paired = None
+                _wgrad(dz_q if dz_t is None else dz_t, dz_csf, dz_t is None, xc, x_sf, xc_rows, efo, out,
+                       mg is not None)
             if mg is not None:
                 _after_accumulate(base)
             else:
@@ -697,6 +718,9 @@ class _DownProjection(torch.autograd.Function):
                             base=base, efo=efo):
                     _wgrad(a_op, sf_a, a_rows, b_op, sf_b, b_rows, efo, mg, True)
                     _after_accumulate(base)
+                # the operands too, so that the first Function's backward can fold this GEMM into dw1's launch
+                dw2_job.operands = dict(a_op=a_op, a_rows=a_rows, b_op=b_op, b_rows=b_rows, sf_a=y1s_sf, sf_b=dout_sf,
+                                        mg=mg, base=base)
                 link["dw2_job"] = dw2_job
             elif mg is not None:
                 _wgrad(a_op, y1s_sf, a_rows, b_op, dout_sf, b_rows, efo, mg, True)

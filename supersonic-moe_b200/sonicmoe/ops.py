@@ -567,6 +567,26 @@ def gemm_wgrad_mn(a, a_sf, b, b_sf, efo, out, accumulate, a_rowmajor_tk, b_rowma
     return out
 
 
+@_timed
+def gemm_wgrad_pair(a1, a1_sf, b1, b1_sf, out1, a2, a2_sf, b2, b2_sf, out2, efo, accumulate, a_rowmajor_tk):
+    """Two weight gradients in one launch (256 x 384 kernel): out1 [E,M1,N] (+)= A1^T B1 and out2 [E,M2,N] (+)= A2^T B2
+    over the same expert segments.  A operands u8 [TKp, M] (a_rowmajor_tk) or [M, TKp]; B operands u8 [N, TKp];
+    N % 384 == 0, M1, M2 % 256 == 0."""
+    _cuda(a1, a1_sf, b1, b1_sf, out1, a2, a2_sf, b2, b2_sf, out2, efo)
+    E, M1, N = out1.shape
+    E2, M2, N2 = out2.shape
+    TKp = b1.shape[1]
+    assert (E2, N2) == (E, N) and tuple(b1.shape) == (N, TKp) and tuple(b2.shape) == (N, TKp)
+    assert tuple(a1.shape) == ((TKp, M1) if a_rowmajor_tk else (M1, TKp))
+    assert tuple(a2.shape) == ((TKp, M2) if a_rowmajor_tk else (M2, TKp))
+    assert out1.dtype == torch.float32 and out2.dtype == torch.float32
+    check(lib.smoe_gemm_wgrad_mn_pair(_p(a1), _p(a1_sf), _p(b1), _p(b1_sf), _p(out1), M1, _p(a2), _p(a2_sf), _p(b2),
+                                      _p(b2_sf), _p(out2), M2, _p(efo), N, TKp, E, int(accumulate),
+                                      int(bool(a_rowmajor_tk)), _p(status_word(a1.device)), _stream()),
+          "gemm_wgrad_pair")
+    return out1, out2
+
+
 # ---------------------------------------------------------------- gated activations outside the GEMMs
 @_timed
 def glu_fwd(z, act):

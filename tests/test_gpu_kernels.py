@@ -773,3 +773,36 @@ def test_payload_only_scatter_and_caller_owned_gated_outputs(ops):
     assert torch.equal(ref[2][:n], got[2][:n]) and torch.equal(ref[3][:nb], got[3][:nb])
     with pytest.raises(ValueError):
         ops.gemm_gated(full, None, isa, wq, wsf, md["efo"], TKp, out=(bufs[0], bufs[1], bufs[2], bufs[3][:-1]))
+
+
+def test_two_weight_gradients_in_one_launch_give_the_bits_of_two_launches(ops):
+    """`gemm_wgrad_pair`: dw1 and dw2 share a launch of the 256 x 384 kernel; every output element has the same single
+    writer and the same K order as in its own launch, so the results are bit-identical, overwriting or accumulating,
+    with an empty expert and with the A operands stored either way."""
+    g = torch.Generator().manual_seed(303)
+    E, N, M1, M2 = 4, 768, 512, 256
+    seg = (256, 0, 384, 128)
+    TKp = sum(seg)
+    efo = torch.tensor([0] + list(torch.tensor(seg).cumsum(0)), dtype=torch.int32, device=DEV)
+    rnd = lambda *s: torch.randint(0, 256, s, generator=g, dtype=torch.uint8).to(DEV)
+    finite = lambda t: torch.where((t & 0x7F) == 0x7F, t & 0xFE, t)          # no e4m3 NaN patterns
+    sfr = lambda n: torch.randint(118, 130, (n,), generator=g, dtype=torch.uint8).to(DEV)
+    b1, b2 = finite(rnd(N, TKp)), finite(rnd(N, TKp))
+    b1_sf, b2_sf = sfr(ops.isa_bytes(N, TKp)), sfr(ops.isa_bytes(N, TKp))
+    for a_rows_tk in (True, False):
+        a1 = finite(rnd(TKp, M1) if a_rows_tk else rnd(M1, TKp))
+        a2 = finite(rnd(TKp, M2) if a_rows_tk else rnd(M2, TKp))
+        a1_sf, a2_sf = sfr(ops.isa_bytes(M1, TKp)), sfr(ops.isa_bytes(M2, TKp))
+        for accumulate in (False, True):
+            base1 = torch.randn(E, M1, N, generator=g).to(DEV)
+            base2 = torch.randn(E, M2, N, generator=g).to(DEV)
+            r1, r2 = base1.clone(), base2.clone()
+            ops.gemm_wgrad_mn(a1, a1_sf, b1, b1_sf, efo, r1, accumulate, a_rows_tk, False)
+            ops.gemm_wgrad_mn(a2, a2_sf, b2, b2_sf, efo, r2, accumulate, a_rows_tk, False)
+            o1, o2 = base1.clone(), base2.clone()
+            ops.gemm_wgrad_pair(a1, a1_sf, b1, b1_sf, o1, a2, a2_sf, b2, b2_sf, o2, efo, accumulate, a_rows_tk)
+            torch.cuda.synchronize()
+            ops.check_status(DEV)
+            assert torch.equal(o1, r1) and torch.equal(o2, r2), (a_rows_tk, accumulate)
+            if not accumulate:
+                assert bool((o1[1] == 0).all()) and bool((o2[1] == 0).all())      # the empty expert

@@ -913,3 +913,31 @@ def test_metadata_with_scales_and_preallocated_gated_outputs(sm):
     assert torch.equal(ref["z"][1][:n], zs[:n]) and torch.equal(ref["y1"][1][:nb], ps.view(-1)[:nb])
     torch.cuda.synchronize()
     sm.ops.check_status(DEV)
+
+
+def test_paired_weight_gradient_launch_changes_no_bit(sm):
+    """dw2 folded into dw1's launch (the default when both accumulate into `main_grad` and H is a multiple of 384)
+    against the two separate launches: identical main_grad, and the op list shows the one launch."""
+    import sonicmoe.functional as Fn
+    T, H, I, E, K = 1024, 768, 256, 4, 2
+    x, dy, w1, w2, _, _ = make_layer(T, H, I, E, K, 161)
+    idx, scores = masked_routing(T, E, K, E, 162)
+
+    def run(pair):
+        prev = Fn._PAIR_WGRADS
+        Fn._PAIR_WGRADS = pair
+        rec = []
+        sm.ops.set_recorder(rec)
+        try:
+            res = _layer_run(sm, x, dy, w1, w2, idx, scores, K, E, None, main_grad=True)
+        finally:
+            sm.ops.set_recorder(None)
+            Fn._PAIR_WGRADS = prev
+        return res, [n for n, _, _ in rec]
+
+    base, names_two = run(False)
+    got, names_one = run(True)
+    assert "gemm_wgrad_pair" in names_one and "gemm_wgrad_pair" not in names_two
+    assert names_two.count("gemm_wgrad_mn") == 2 and "gemm_wgrad_mn" not in names_one
+    for name, a, b in zip(("out", "dx", "ds", "dw1", "dw2"), base, got):
+        assert torch.equal(a, b), name
