@@ -63,6 +63,7 @@ static int g_force_v1 = 0;
 static int g_force_gather4 = 0;     // A rows by index: TMA gather4 instead of the cp.async load warps
 static int g_stage_cut = 0;
 static int g_l2_prefetch = -1;     // -1: the kernel's default
+static void* g_trace = nullptr;    // timing experiment: per-tile stamps of the MMA issuer (256 x 384 kernel)
 
 // Per-device state: the SM count and the "large dynamic shared memory" function attribute belong to a device,
 // not to the process, so both are kept per device ordinal.
@@ -147,6 +148,7 @@ static int launch3(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
   GemmParams q = p;
   q.dbg_stage_cut = g_stage_cut > 2 ? 2 : g_stage_cut;      // the head / tail schedule holds two stages
   q.l2_prefetch = g_l2_prefetch;                            // this kernel reads it as "length of the head / tail", -1 = default
+  q.trace = reinterpret_cast<long long*>(g_trace);
   SecondMaps none{};
   kern<<<(unsigned)(2 * pairs), S::THREADS, S::TOTAL, stream>>>(ta, tb, tsa, tsb, tc, second ? *second : none, q);
   return cudaGetLastError() == cudaSuccess ? SMOE_OK : SMOE_ERR_LAUNCH;
@@ -354,6 +356,11 @@ static int wgrad_nothing_routed(float* c, int64_t M, int64_t N, int64_t E, int a
 using namespace smoe;
 
 extern "C" {
+
+int smoe_internal_gemm_trace(void* device_buffer) {
+  g_trace = device_buffer;
+  return SMOE_OK;
+}
 
 int smoe_internal_gemm_knobs(int bn) {
   g_force_bn = bn & 0xFFFF;

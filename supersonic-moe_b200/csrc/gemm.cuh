@@ -39,6 +39,7 @@ struct GemmParams {
   int sfb_ktiles;
   // outputs / epilogue operands
   void* c;              // PLAIN: bf16 [rows,N]; WGRAD: f32 [E,rows,N]
+  long long* trace;     // timing experiment (256x384 kernel): per-tile stamps of the MMA issuer, else null
   int rows2;            // WGRAD, 256x384 kernel: output rows per expert of a SECOND product run by the same launch
   void* c2;             //   (same N, K range and operand layouts; own A, B, scales and f32 [E,rows2,N] output); 0: none
   int accumulate;       // WGRAD: add into c instead of overwriting

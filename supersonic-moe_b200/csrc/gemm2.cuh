@@ -34,6 +34,14 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// The same without memory-ordering semantics, for hand-overs that pass no data through memory: an epilogue warp that
+// has read its accumulator columns out of TMEM (tcgen05.wait::ld + tcgen05.fence::before_thread_sync order those
+// reads) tells the MMA issuer so.  The releasing form makes the arrival wait for every earlier store of the thread
+// - the staging stores of the previous tile among them - to become visible cluster-wide: 1700 cycles in the
+// 256 x 384 kernel, at every tile boundary, with the tensor pipe idle.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
 // Loads of a CTA pair: data lands in the issuing CTA, the byte count is
 // credited to the barrier named by a shared::cluster address (the leader's).
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap, uint32_t bar_cluster, int c0,
@@ -627,7 +635,7 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * as);
+        if (lane == 0) mbar_arrive_cluster_relaxed(tempty0 + 8 * as);
         released = true;
 #pragma unroll
         for (int c = 0; c < NC; ++c) {
@@ -657,7 +665,7 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * as);
+        if (lane == 0) mbar_arrive_cluster_relaxed(tempty0 + 8 * as);
         released = true;
 #pragma unroll
         for (int c = 0; c < 2 * NC; ++c) {
@@ -696,7 +704,7 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           tmem_ld_wait();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * as);
+          if (lane == 0) mbar_arrive_cluster_relaxed(tempty0 + 8 * as);
           released = true;
         }
 #pragma unroll
@@ -988,7 +996,7 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       if (!released) {
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * as);
+        if (lane == 0) mbar_arrive_cluster_relaxed(tempty0 + 8 * as);
       }
       if (++as == S::ACC_STAGES) { as = 0; aphase ^= 1; }
     }

@@ -214,10 +214,14 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                            (k | kb) != 0);
       };
 
+      long long* trace = (pair_id == 0) ? p.trace : nullptr;      // timing experiment, null in product use
+      int trace_n = 0;
       for (int tile = pair_id; tile < n_total_u && ok; tile += n_pairs_grid) {
         const PairTile t = pair_tile<BN, MODE>(tile, 0, p, s_efo, s_pairs);
         const int nkt = __shfl_sync(0xffffffffu, t.nkt, 0);
         if (nkt == 0) continue;
+        const long long tr0 = trace ? clock64() : 0;
+        long long tr_full = 0, tr_sf = 0, tr_acc1 = 0, tr_first = 0;
         const int J = nkt >= 2 * JJ ? JJ : 0;
         int held0 = 0, held1 = 0;             // ring stages of the K tiles whose half-1 MMAs are still to come
         static_assert(kHeadTail3 == 2, "held0 / held1");
@@ -228,16 +232,25 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           if (!ok) break;
         }
         tc_fence_after();
+        const long long tr1 = trace ? clock64() : 0;
         for (int k = 0; k < nkt; ++k) {
           // first touch of K tile k: its operands and scales have landed; scales go to TMEM; half 0 always,
           // half 1 too unless the K tile belongs to the head or the tail of the tile
           const int kg = k & (S::SF_GROUP - 1);
           if (kg == 0) {
+            const long long c0 = trace ? clock64() : 0;
             ok = __all_sync(0xffffffffu, mbar_wait(bar_sffull + 8 * sfs, sfphase));
             if (!ok) break;
+            if (trace) tr_sf += clock64() - c0;
           }
+          const long long c1 = trace ? clock64() : 0;
           ok = __all_sync(0xffffffffu, mbar_wait(bar_full + 8 * stage, phase));
           if (!ok) break;
+          if (trace) {
+            const long long d = clock64() - c1;
+            tr_full += d;
+            if (k == 0) tr_first = d;
+          }
           const bool both = (k >= J && k < nkt - J);
           const bool sf_done = (kg == S::SF_GROUP - 1 || k == nkt - 1);
           const uint32_t sf_lo = sf_lo0 + ((sfs * S::SF_SLOT_BYTES + kg * 512) >> 4);
@@ -266,9 +279,11 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           // end of the head / of the tail: the half-1 MMAs of the K tiles held back
           const bool head_end = (J > 0 && k == J - 1), tail_end = (J > 0 && k == nkt - 1);
           if (head_end) {
+            const long long c2 = trace ? clock64() : 0;
             ok = __all_sync(0xffffffffu, mbar_wait(bar_tempty + 8, aphase ^ 1));
             if (!ok) break;
             tc_fence_after();
+            if (trace) tr_acc1 = clock64() - c2;
           }
           if (head_end || tail_end) {
             if (elect_one()) {
@@ -288,6 +303,20 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           if (J == 0) tc_commit_pair(bar_tfull, 3);
           tc_commit_pair(bar_tfull + 8, 3);
         }
+        if (trace) {
+          // how long the tensor pipe still works on what has been issued: wait for this tile's last commit here
+          const long long c3 = clock64();
+          long long drain0 = 0;
+          if (J > 0) { mbar_wait(bar_tfull, aphase); drain0 = clock64() - c3; }
+          mbar_wait(bar_tfull + 8, aphase);
+          const long long drain = clock64() - c3;
+          if (trace_n < 256 && lane == 0) {
+            long long* r = trace + 8 * trace_n;
+            r[0] = tr0; r[1] = tr1; r[2] = tr_full; r[3] = tr_sf; r[4] = tr_acc1; r[5] = c3; r[6] = drain0;
+            r[7] = nkt | (drain << 16);
+          }
+        }
+        ++trace_n;
         aphase ^= 1;
       }
       if (!ok && lane == 0) { *s_abort = 1; atomicCAS(p.status, 0, 202); }
@@ -352,9 +381,14 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     uint32_t aphase = 0;
     int buf = 0;
     bool ok = true;
+    // timing experiment: the first epilogue warp of the leader CTA of pair 0 stamps its side of the hand-over
+    long long* etrace = (p.trace != nullptr && pair_id == 0 && rank == 0 && warp == S::LEAD_WARPS && lane == 0)
+                            ? p.trace + 8 * 256 : nullptr;
+    int etrace_n = 0;
     for (int tile = pair_id; tile < n_total && ok; tile += n_pairs_grid) {
       const PairTile t = pair_tile<BN, MODE>(tile, rank, p, s_efo, s_pairs);
       const size_t grow = (size_t)t.m0 + row_in_tile;
+      long long es[6] = {0, 0, 0, 0, 0, 0};
       if (t.nkt == 0) {
         if (MODE == WGRAD && !p.accumulate) {
 #pragma unroll
@@ -373,9 +407,11 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         uint32_t pk[2][NC][16];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
+          if (etrace && h == 0) es[0] = clock64();
           if (lane == 0) ok = mbar_wait(bar_tfull + 8 * h, aphase);
           ok = __shfl_sync(0xffffffff, ok, 0);
           if (!ok) break;
+          if (etrace && h == 0) es[1] = clock64();
           tc_fence_after();
           if (!(p.debug_skip_store & 8)) {
             // all of this warp's columns of the half in one go (one wait), the accumulator is handed back before
@@ -384,10 +420,13 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             uint32_t r[NC][32];
 #pragma unroll
             for (int c = 0; c < NC; ++c) tmem_ld32(t_row + c * 32, r[c]);
+            if (etrace && h == 0) es[3] = clock64();            // (experiment: loads issued)
             tmem_ld_wait();
+            if (etrace && h == 0) es[4] = clock64();            // (experiment: loads complete)
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * h);
+            if (lane == 0) mbar_arrive_cluster_relaxed(tempty0 + 8 * h);
+            if (etrace && h == 0) es[2] = clock64();
 #pragma unroll
             for (int c = 0; c < NC; ++c)
 #pragma unroll
@@ -396,10 +435,15 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           } else {
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * h);
+            if (lane == 0) mbar_arrive_cluster_relaxed(tempty0 + 8 * h);
           }
         }
         if (!ok) break;
+        if (etrace && etrace_n < 256) {
+#pragma unroll
+          for (int i = 0; i < 6; ++i) etrace[8 * etrace_n + i] = es[i];
+        }
+        ++etrace_n;
         if (t.valid && !(p.debug_skip_store & 8)) {
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
@@ -439,7 +483,7 @@ gemm3_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           }
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * h);
+          if (lane == 0) mbar_arrive_cluster_relaxed(tempty0 + 8 * h);
           if (!drain) continue;
 #pragma unroll
           for (int c = 0; c < 2 * NC; ++c) {

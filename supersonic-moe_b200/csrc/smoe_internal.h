@@ -13,6 +13,12 @@ extern "C" {
  * no accumulator drain, no scale copies, ...).  0 restores the defaults. */
 int smoe_internal_gemm_knobs(int bits);
 
+/* A device buffer of 8 x 256 int64 that the MMA issuer of CTA pair 0 of the 256 x 384 kernel fills, per tile, with
+ * SM-clock stamps and the cycles it spent in each kind of wait (tile start, after the accumulator waits, cycles
+ * waiting for operands / scales / the second accumulator, tile end, wait for the first operands); null switches the
+ * stamping off (the default). */
+int smoe_internal_gemm_trace(void* device_buffer);
+
 #ifdef __cplusplus
 }
 #endif

@@ -64,6 +64,7 @@ SIGNATURES = {
 # exported for the library's own tests and timing experiments only (csrc/smoe_internal.h); not product ABI
 INTERNAL_SIGNATURES = {
     "smoe_internal_gemm_knobs": (_I, [_I]),
+    "smoe_internal_gemm_trace": (_I, [_P]),
 }
 
 ERRORS = {1: "SMOE_ERR_SHAPE", 2: "SMOE_ERR_ALIGN", 3: "SMOE_ERR_DRIVER", 4: "SMOE_ERR_TMAP", 5: "SMOE_ERR_LAUNCH",
