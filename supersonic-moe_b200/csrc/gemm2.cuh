@@ -42,6 +42,11 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
 __device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// Releasing at CTA scope (the form without qualifiers): orders this thread's earlier writes to ITS OWN shared memory
+// - which is where the data the arrival announces lies - without the cluster-wide flush.
+__device__ __forceinline__ void mbar_arrive_cluster_cta_release(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
 // Loads of a CTA pair: data lands in the issuing CTA, the byte count is
 // credited to the barrier named by a shared::cluster address (the leader's).
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap, uint32_t bar_cluster, int c0,
@@ -522,7 +527,7 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         ok = mbar_wait(bar_landed + 8 * lane, ph);
         if (!ok) break;
         fence_proxy_async_smem();
-        mbar_arrive_cluster(full0 + 8 * lane);
+        mbar_arrive_cluster_cta_release(full0 + 8 * lane);
         ph ^= 1;
       }
     }
