@@ -1,12 +1,12 @@
 // Two-CTA MXFP8 grouped GEMM with a 256 x 384 tile held as TWO accumulators of 256 x 192 (TMEM columns 0..191 and
 // 192..383) that share every A tile.
 //
-// Why: the 256 x 256 kernel is bound by the bytes its operand loads pull from L2 into shared memory, not by the
-// tensor pipe (time went up in proportion to bytes per MMA across the 128x256 / 256x192 / 256x256 tiles, did not move
-// with the depth of the shared-memory ring, and rose when L2 prefetches were added).  Per 128-wide K tile a CTA of
-// this kernel loads A (16 KB) once for two B halves (2 x 12 KB): 40 KB for 768 tensor clocks instead of 32 KB for 512
-// - 17 % fewer bytes per MMA - with no multicast load anywhere (each CTA fetches its own rows of A and of both B
-// halves with plain tiled TMA copies).
+// Why: per 128-wide K tile a CTA of this kernel loads A (16 KB) once for two B halves (2 x 12 KB): 40 KB for 768
+// tensor clocks instead of 32 KB for 512 - 17 % fewer operand bytes per MMA than the 256 x 256 tile - with no
+// multicast load anywhere (each CTA fetches its own rows of A and of both B halves with plain tiled TMA copies).
+// When it was written that bought 7-9 % on the plain and weight-gradient GEMMs; since the accumulator hand-back no
+// longer stalls (relaxed arrival, see the epilogue) the 256 x 256 kernel runs the activation-gradient GEMM in the
+// same time, and this kernel is kept for the weight gradients, which it can run two products at a time.
 //
 // The two accumulators also hide the accumulator hand-over between tiles: the last J K tiles of a tile are issued
 // half 0 first, so the epilogue drains accumulator 0 under the half-1 MMAs of those K tiles, and the next tile
