@@ -6,7 +6,8 @@
 // multicast load anywhere (each CTA fetches its own rows of A and of both B halves with plain tiled TMA copies).
 // When it was written that bought 7-9 % on the plain and weight-gradient GEMMs; since the accumulator hand-back no
 // longer stalls (relaxed arrival, see the epilogue) the 256 x 256 kernel runs the activation-gradient GEMM in the
-// same time, and this kernel is kept for the weight gradients, which it can run two products at a time.
+// same time; this kernel stays the default where N % 384 == 0 and is the one that runs the two weight gradients
+// of a layer in a single launch.
 //
 // The two accumulators also hide the accumulator hand-over between tiles: the last J K tiles of a tile are issued
 // half 0 first, so the epilogue drains accumulator 0 under the half-1 MMAs of those K tiles, and the next tile
