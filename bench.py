@@ -614,7 +614,9 @@ def _roofline(cname, world, T, K, H, I, order, breakdown, pk):
         n = k.split("#")[0]
         if n.startswith("gemm_wgrad"):
             n = "gemm_wgrad"
-        if n == "gemm_gated":
+        if k.split("#")[0] == "gemm_wgrad_pair":        # dw1 (4) and dw2 (2) in one launch
+            per_gemm_flops[k] = 6 * TKH_I
+        elif n == "gemm_gated":
             per_gemm_flops[k] = 4 * TKH_I
         elif n in ("gemm_dgated", "gemm_dgated_fused"):
             per_gemm_flops[k] = 2 * TKH_I
@@ -629,6 +631,10 @@ def _roofline(cname, world, T, K, H, I, order, breakdown, pk):
         dn = dom.split("#")[0]
         same = [k for k in gemm_keys if k.split("#")[0] == dn]
         traffic = table.get(f"{dn}#{same.index(dom)}")
+        if traffic is None and dn == "gemm_wgrad_pair":
+            # the two weight gradients were captured as separate launches; run together they move the same tiles
+            parts = [table.get("gemm_wgrad_mn#0"), table.get("gemm_wgrad_mn#1")]
+            traffic = sum(parts) if all(p is not None for p in parts) else None
     return {"bound": "tensor", "kernel": dom, "achieved": round(ach, 1), "peak": round(peak_burst, 1),
             "unit": "TFLOP/s", "frac": round(ach / peak_burst, 4),
             "frac_of_sustained_peak": round(ach / peak_sus, 4), "peak_sustained": round(peak_sus, 1),
