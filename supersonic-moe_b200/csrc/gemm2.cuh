@@ -702,10 +702,16 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const int ch0 = half * PER;
         const int nch = min(PER, CHUNKS - ch0);
         const uint32_t t_tile = tmem_base + ((uint32_t)(q * 32) << 16) + as * BN;
-        uint32_t acc[DRAIN ? PER * 2 : 1][32];
+        uint32_t acc[DRAIN ? PER * 2 * 32 : 32];
         if (DRAIN) {
+          static_assert(!DRAIN || PER * 2 * 32 == 128, "the single-accumulator tile is 256 wide: 128 columns per warp");
+          if constexpr (!CPG) {
+            tmem_ld128(t_tile + ch0 * 64, reinterpret_cast<uint32_t(&)[128]>(acc));
+          } else {      // sixteen warps per CTA leave 128 registers a thread: no room for one 128-register load
 #pragma unroll
-          for (int c = 0; c < PER * 2; ++c) tmem_ld32(t_tile + ch0 * 64 + c * 32, acc[DRAIN ? c : 0]);
+            for (int c = 0; c < PER * 2; ++c)
+              tmem_ld32(t_tile + ch0 * 64 + c * 32, reinterpret_cast<uint32_t(&)[32]>(acc[DRAIN ? c * 32 : 0]));
+          }
           tmem_ld_wait();
           tc_fence_before();
           __syncwarp();
@@ -728,7 +734,7 @@ gemm2_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
               tmem_ld32(t_tile + (ch0 + ci) * 64 + h * 32, rl);
               tmem_ld_wait();
             }
-            const uint32_t* r = DRAIN ? acc[DRAIN ? ci * 2 + h : 0] : rl;
+            const uint32_t* r = DRAIN ? &acc[DRAIN ? (ci * 2 + h) * 32 : 0] : rl;
             float amax = 0.f;
 #pragma unroll
             for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(__uint_as_float(r[i])));
