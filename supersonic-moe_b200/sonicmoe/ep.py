@@ -2,9 +2,14 @@
 group, tokens travel to the ranks that own their experts and back.
 
 The reference ships no communication code (its host framework calls DeepEP
-around `run_sonic_moe`); this module supplies the two exchanges as NCCL
-all-to-alls (`torch.distributed.all_to_all_single`, NVLink / NVSwitch on one
-node) with the payload formats the reference's entry points accept:
+around `run_sonic_moe`); this module supplies the two exchanges with the
+payload formats the reference's entry points accept.  On CUDA ranks that can
+map each other's memory they run over NVLink peer memory (the destination
+pulls its rows from the sources' quantised tokens; the forward's return is a
+pull fused with the per-token reduction; dx returns as device-to-device
+copies underneath the weight-gradient GEMMs; the forward reads no count back
+from the device); everywhere else - CPU tensors with gloo, or the switches
+below - they are `torch.distributed.all_to_all_single` calls:
 
   dispatch  a token is sent ONCE to every rank that owns at least one of its
             top-k experts, as e4m3 bytes + raw 1x32 ue8m0 scales (quantise before
@@ -17,9 +22,11 @@ node) with the payload formats the reference's entry points accept:
             down-projection backward through `Fp8CombineGradHandle`; dx and the
             score gradients return with the reverse all-to-all.
 
-Every reduction has a fixed order, so results do not depend on timing.
-The planning and exchange code is device-agnostic (CPU tensors + gloo work);
-only the FP8 payload and the expert compute need the CUDA kernels.
+Every reduction has a fixed order, so results do not depend on timing, and
+the peer-memory paths deliver rows in the order the all-to-alls would: both
+give the same bits.  The planning and the all-to-all path are device-agnostic
+(CPU tensors + gloo work); the FP8 payload, the peer-memory movers and the
+expert compute need the CUDA kernels.
 """
 from __future__ import annotations
 
