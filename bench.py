@@ -513,13 +513,18 @@ def _measure(args, cname, world, rank, dev, dist, sonicmoe, ops, strong, extra=F
             main_s.wait_stream(s_out)
 
         e2e_run(2)
-        barrier()
-        e2e_ev0, e2e_ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e2e_ev0.record()
-        e2e_run(e2e_steps)
-        e2e_ev1.record()
-        barrier()
-        e2e_ms = e2e_ev0.elapsed_time(e2e_ev1) / e2e_steps
+        # three passes of `e2e_steps` steps, the median pass is reported (the host link is shared with other
+        # tenants of the machine: single passes moved between 3.2 and 6.5 ms per step from box to box)
+        e2e_passes = []
+        for _ in range(3):
+            barrier()
+            e2e_ev0, e2e_ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e2e_ev0.record()
+            e2e_run(e2e_steps)
+            e2e_ev1.record()
+            barrier()
+            e2e_passes.append(e2e_ev0.elapsed_time(e2e_ev1) / e2e_steps)
+        e2e_ms = sorted(e2e_passes)[1]
         h2d = sum(pin[k].numel() * pin[k].element_size() for k in pin)
         d2h = 2 * T * H * 2
     clocks = sampler.stop()      # sampled over the timed steps (and the end-to-end steps that follow them)
@@ -589,7 +594,9 @@ def _measure(args, cname, world, rank, dev, dist, sonicmoe, ops, strong, extra=F
         "kernel_us": breakdown,
     }
     if e2e_ms is not None:
-        line["e2e"] = {"value": round(e2e_ms * 1e3, 1), "unit": "us/iter", "h2d_bytes_per_step": h2d,
+        line["e2e"] = {"value": round(e2e_ms * 1e3, 1), "unit": "us/iter",
+                       "passes_us": [round(v * 1e3, 1) for v in e2e_passes] if world == 1 else None,
+                       "h2d_bytes_per_step": h2d,
                        "d2h_bytes_per_step": d2h}
     line["roofline"] = _roofline(cname, world, T, K, H, I, order, breakdown, pk)
     if world == 1 and cname in ("C2", "P1") and not extra:
