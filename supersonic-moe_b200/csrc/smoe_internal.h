@@ -7,10 +7,13 @@
 extern "C" {
 #endif
 
-/* bits 0..15: force the GEMM column tile (128, 192 or 256; 0 = automatic); bit 16: epilogues skip their stores;
+/* bits 0..15: force the GEMM column tile (128, 192, 256 or 384; 0 = automatic); bit 16: epilogues skip their stores;
  * bit 17: force the single-CTA kernel; bit 18: the fused dgated epilogue is skipped whole;
- * bits 19..23: timing experiments of the two-CTA main loop (no operand loads after the first ring pass,
- * no accumulator drain, no scale copies, ...).  0 restores the defaults. */
+ * timing experiments of the two-CTA main loops: bit 19: no operand loads after the first ring pass; bit 20: the
+ * accumulators are handed back undrained (and nothing is stored); bit 21: no scale copies into TMEM;
+ * bits 24..25: ring stages left unused; bits 26..30: value + 1 of the L2 prefetch distance (256-wide kernels) or of
+ * the head / tail length (256 x 384 kernel), 0 = the kernel's default; bit 31: indexed A rows through TMA gather4
+ * instead of the cp.async load warps.  0 restores the defaults. */
 int smoe_internal_gemm_knobs(int bits);
 
 /* A device buffer of 8 x 256 int64 that the MMA issuer of CTA pair 0 of the 256 x 384 kernel fills, per tile, with
