@@ -37,13 +37,13 @@ import torch.distributed as dist
 
 # SONIC_MOE_EP_PEER: how the two bf16 return exchanges (forward combine, backward dx) travel.
 #   "fwd" (default)  the forward's return reads the partial rows straight from the owners' memory over NVLink, fused
-#                    with the per-token reduction (csrc/ep_peer.cu); the backward's (dx) is an NCCL all-to-all on the
-#                    communication stream, where it runs underneath the weight-gradient GEMMs
+#                    with the per-token reduction (csrc/ep_peer.cu); the backward's (dx) travels on the communication
+#                    stream, where it runs underneath the weight-gradient GEMMs (how: SONIC_MOE_EP_DX_RETURN below)
 #   "1"              both read peer memory (the dx return then follows the weight gradients: nothing hides it)
 #   "0"              both are NCCL all-to-alls followed by a local reduction
 # Reading peer memory needs ranks that can map each other's memory (torch symmetric memory); if that fails the
-# layer warns once and uses NCCL.  Measured on the reference-shape layer, first-10-step medians: 8 GPUs 5.37 ms
-# ("fwd") against 5.55 ("0"); 2 GPUs 3.86 ("1") against 3.92 ("0").
+# layer warns once and uses NCCL.  Measured on the reference-shape layer with NCCL dispatch and an NCCL dx return,
+# first-10-step medians: 8 GPUs 5.37 ms ("fwd") against 5.55 ("0"); 2 GPUs 3.86 ("1") against 3.92 ("0").
 _PEER_MODE = os.getenv("SONIC_MOE_EP_PEER", "fwd")
 if _PEER_MODE not in ("0", "1", "fwd"):
     raise ValueError(f"SONIC_MOE_EP_PEER={_PEER_MODE!r}: expected '0', '1' or 'fwd'")
@@ -72,7 +72,7 @@ if DX_RETURN not in ("copy", "nccl"):
 
 _COMM_STREAMS: dict = {}
 _READBACK_STREAMS: dict = {}
-_PINNED: dict = {}
+_PINNED_FREE: dict = {}      # (device index, shape) -> pinned int64 host buffers no plan owns at the moment
 
 
 def _readback_stream(device) -> "torch.cuda.Stream":
@@ -84,14 +84,22 @@ def _readback_stream(device) -> "torch.cuda.Stream":
     return st
 
 
-def _pinned_i64(shape):
-    """Pinned int64 host buffers, eight per shape used in turn (a plan reads its copy within the step it was made)."""
-    ring = _PINNED.setdefault(shape, [[], 0])
-    if len(ring[0]) < 8:
-        ring[0].append(torch.empty(shape, dtype=torch.int64).pin_memory())
-        return ring[0][-1]
-    ring[1] = (ring[1] + 1) % 8
-    return ring[0][ring[1]]
+def _alloc_pinned_i64(shape):
+    return torch.empty(shape, dtype=torch.int64).pin_memory()
+
+
+def _pinned_take(key):
+    """A pinned int64 host buffer for `key` = (device index, shape).  A plan owns its buffer from the copy of its
+    counts until it has read them (or dies unread), however many plans are in flight in between - a pipeline schedule
+    may run many forwards before the first backward looks at its counts."""
+    free = _PINNED_FREE.setdefault(key, [])
+    return free.pop() if free else _alloc_pinned_i64(key[1])
+
+
+def _pinned_give(key, buf):
+    """Back to the pool.  A copy into `buf` may still be in flight (a plan that died unread): the next owner's copy is
+    issued on the same device's read-back stream, hence after it."""
+    _PINNED_FREE.setdefault(key, []).append(buf)
 
 
 def _comm_stream(device) -> "torch.cuda.Stream":
@@ -280,13 +288,23 @@ class DispatchPlan:
     def __getattr__(self, name):
         # reached only when the attribute is missing: a host-side field of a plan whose counts are still in flight
         if name in DispatchPlan._HOST_FIELDS and self.__dict__.get("_pending") is not None:
-            host, ready = self._pending
+            host, ready, key = self._pending
             self._pending = None
             ready.synchronize()
-            self._set_counts(host.tolist())
+            counts = host.tolist()
+            _pinned_give(key, host)
+            self._set_counts(counts)
             self._finish_cuda()
             return self.__dict__[name]
         raise AttributeError(name)
+
+    def __del__(self):
+        pending = self.__dict__.get("_pending")
+        if pending is not None:                 # never looked at (a forward without a backward): the buffer is free
+            try:
+                _pinned_give(pending[2], pending[0])
+            except Exception:                   # interpreter shutdown: the pool may be gone already
+                pass
 
     def _set_counts(self, M):
         me, El, world = dist.get_rank(self.group), self.El, self.world
@@ -319,13 +337,14 @@ class DispatchPlan:
         dev = M.device
         cur, side = torch.cuda.current_stream(dev), _readback_stream(dev)
         side.wait_stream(cur)
-        host = _pinned_i64(tuple(M.shape))
+        key = (dev.index, tuple(M.shape))
+        host = _pinned_take(key)
         with torch.cuda.stream(side):
             host.copy_(M, non_blocking=True)
             ready = torch.cuda.Event()
             ready.record(side)
         M.record_stream(side)
-        self._pending = (host, ready)
+        self._pending = (host, ready, key)
 
     def _build_cuda(self, idx, world):
         """The plan is the routing-metadata problem with destination ranks in the role of experts: one call of the

@@ -149,3 +149,50 @@ def test_ep_two_ranks_matches_single_process_oracle():
         torch.testing.assert_close(results[o]["dw1"], dw1_tot[o], rtol=1e-4, atol=1e-4)
         torch.testing.assert_close(results[o]["dw2"], dw2_tot[o], rtol=1e-4, atol=1e-4)
     assert results[0]["n_recv"] == results[0]["send_counts"][0] + results[1]["send_counts"][0]
+
+
+def test_deferred_counts_buffers_are_owned_per_plan(monkeypatch):
+    """The host copy of a plan's counts lives in a pinned buffer the plan owns until it has read it: any number of
+    plans may be in flight (a pipeline schedule runs many forwards before the first backward), each resolves to its
+    own counts, and a buffer returns to the pool when its plan has read it or dies unread."""
+    import gc
+    from sonicmoe import ep
+
+    monkeypatch.setattr(ep, "_alloc_pinned_i64", lambda shape: torch.empty(shape, dtype=torch.int64))
+    monkeypatch.setattr(ep, "_PINNED_FREE", {})
+    monkeypatch.setattr(ep.dist, "get_rank", lambda group=None: 0)
+    monkeypatch.setattr(ep.DispatchPlan, "_finish_cuda", lambda self: None)
+
+    class Arrived:
+        def synchronize(self):
+            pass
+
+    world, El = 2, 2
+    key = (0, (world, world + world * El + 1))
+
+    def plan_in_flight(i):
+        p = object.__new__(ep.DispatchPlan)
+        p.El, p.world, p.group = El, world, None
+        host = ep._pinned_take(key)
+        # rows of the gathered matrix: [rows to rank 0, rows to rank 1, pairs per expert (4), tokens]
+        host.copy_(torch.tensor([[i, i + 1, 1, 2, 3, 4, 100 + i], [i + 2, i + 3, 5, 6, 7, 8, 200 + i]]))
+        p._pending = (host, Arrived(), key)
+        return p
+
+    plans = [plan_in_flight(i) for i in range(12)]
+    assert len({p._pending[0].data_ptr() for p in plans}) == 12
+    for i, p in reversed(list(enumerate(plans))):
+        assert p.send_counts == [i, i + 1]
+        assert p.recv_counts == [i, i + 2]
+        assert p.tokens_per_local_expert == [1 + 5, 2 + 6]
+        assert p.tokens_all == [100 + i, 200 + i]
+        assert p.src_seg_off == [0, 0] and p.first_row_at == [0, 0]
+        assert p._pending is None
+    assert len(ep._PINNED_FREE[key]) == 12
+    unread = plan_in_flight(99)
+    assert len(ep._PINNED_FREE[key]) == 11
+    del unread
+    gc.collect()
+    assert len(ep._PINNED_FREE[key]) == 12
+    with pytest.raises(AttributeError):
+        plans[0].no_such_field

@@ -147,3 +147,48 @@ def test_pull_entry_points_refuse_what_they_cannot_run(ops):
     assert lib.smoe_ep_dispatch_pull(one, cnt, cnt, 1, 0, 0, 0, 0, 0, 0, 512, 4, None, None, None, None, None) == 0
     assert lib.smoe_ep_tables(one, 1, 0, 0, 0, None, None) != 0
     assert lib.smoe_ep_tables_bytes() >= 4 * (17 + 16 * 3 + 1)
+
+
+def test_plans_with_counts_in_flight_resolve_to_their_own_counts(ops):
+    """A plan built without a read-back keeps its counts in a pinned host buffer of its own until something asks for
+    them.  Twelve such plans are built back to back (more than a pipeline's forwards in flight would be) and resolved
+    in reverse order: each must give exactly what a plan built with an immediate read-back gives.  One-rank group:
+    the plan's kernels, its all-gather and the side-stream copy run as on many ranks."""
+    import socket
+    import torch.distributed as dist
+    from sonicmoe import ep
+
+    if dist.is_initialized():
+        pytest.skip("a process group exists already")
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    torch.cuda.set_device(0)
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1,
+                            device_id=torch.device("cuda", 0))
+    try:
+        E, K = 8, 4
+        g = torch.Generator().manual_seed(31)
+        problems = []
+        for i in range(12):
+            T = 64 + 8 * i
+            idx = torch.randn(T, E, generator=g).topk(K, dim=-1).indices.to(torch.int32)
+            idx[torch.rand(T, K, generator=g) < 0.2] = -1          # masked slots
+            idx[i:T:7] = -1                                        # tokens that go nowhere
+            problems.append(idx.to(DEV))
+        in_flight = [ep.DispatchPlan(idx, E, dist.group.WORLD, deferred=True) for idx in problems]
+        assert all(p.deferred and p._pending is not None for p in in_flight)
+        assert len({p._pending[0].data_ptr() for p in in_flight}) == len(in_flight)
+        for idx, p in reversed(list(zip(problems, in_flight))):
+            now = ep.DispatchPlan(idx, E, dist.group.WORLD, deferred=False)
+            for name in ("send_counts", "recv_counts", "tokens_per_local_expert", "n_send", "n_recv", "tokens_all",
+                         "first_row_at", "src_seg_off", "send_off", "max_recv_rows"):
+                assert getattr(p, name) == getattr(now, name), name
+            assert p._pending is None
+            assert 0 < p.n_send < idx.shape[0]
+            for name in ("send_tok", "send_idx", "send_rank", "copy_pos", "copy_off"):
+                assert torch.equal(getattr(p, name), getattr(now, name)), name
+        torch.cuda.synchronize()
+    finally:
+        dist.destroy_process_group()
