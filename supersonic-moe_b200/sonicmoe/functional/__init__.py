@@ -8,12 +8,13 @@ argument lists (:828-847, :1617-1640), the FP8 hand-off between them
 `moe_TC_softmax_topk_layer` (call sites sonicmoe/moe.py:604-616).
 
 Dataflow (one code path, MXFP8 1x32 ue8m0 everywhere a GEMM runs):
-  forward   x --row quant--> x_fp8 ; scales gathered to expert-sorted rows
-            up-proj GEMM (row gather by TMA) + SwiGLU + z/y1 re-quant in the epilogue
+  forward   x --row quant, written in expert-sorted order--> x_fp8 [TKp,H] + ISA scales
+            up-proj GEMM + SwiGLU + z/y1 re-quant in the epilogue
             down-proj GEMM -> y2 bf16 ; top-k weighted combine -> o
-  backward  dout row quant ; GemmDGated (e4m3 z reload, dSwiGLU) -> dz, y1s, ds
-            column quantizers (transposed outputs) ; dw2, dw1 varlen-K GEMMs into fp32
+  backward  dout row quant (expert-sorted) ; GemmDGated (e4m3 z reload, dSwiGLU, dz / y1s quantizers
+            in the epilogue) -> dz, y1s as e4m3, ds
             dgrad GEMM -> dx_expanded ; unweighted combine -> dx
+            column quantizers of x / dout (transposed outputs) ; dw2 + dw1 varlen-K GEMMs into fp32
 """
 from __future__ import annotations
 
@@ -533,7 +534,8 @@ class _UpProjection(torch.autograd.Function):
             ops2 = getattr(deferred_dw2, "operands", None)
             mg1, _ = _grad_target(w1, (E, N2, H)) if ctx.needs_input_grad[1] else (None, None)
             # dw2 joins dw1's launch: both into main_grad, dz / y1s left [TKp, dim], column operands transposed
-            if (_PAIR_WGRADS and ops2 is not None and mg1 is not None and dz_t is None and ops2["a_rows"] and not ops2["b_rows"] and _wide_wgrad_ok(E, N2, H)
+            if (_PAIR_WGRADS and ops2 is not None and mg1 is not None and dz_t is None and ops2["a_rows"]
+                    and not ops2["b_rows"] and _wide_wgrad_ok(E, N2, H)
                     and _wide_wgrad_ok(E, ops2["a_op"].shape[1], H)):
                 paired = ops2
             else:
