@@ -110,7 +110,7 @@ class SonicMoEMlpNode:
         key = ("w",) + _cache_key(*w1s, *w2s)
         hit = self._w_cache.get(key)
         if hit is None:
-            for k in [k for k in self._w_cache if k[0] == "w"]:
+            for k in [k for k in self._w_cache if isinstance(k, tuple) and k[0] == "w"]:
                 del self._w_cache[k]                                # weights moved on: drop the stale stack
             w1 = stack_w1_interleaved(w1s, self._I).requires_grad_(True)
             w2 = stack_w2(w2s).requires_grad_(True)

@@ -47,3 +47,34 @@ def test_flush_turns_kernel_layout_storage_into_framework_layout_in_place():
     (w1 * dw1_native).sum().backward()
     for e in range(E):
         assert torch.equal(ws[e].grad, per_expert[e])
+
+
+def test_gradient_buffers_outlive_weight_updates_and_steps():
+    """The fp32 buffers whose slices are the experts' `main_grad` are allocated once: neither `step()` nor a weight
+    update (which replaces the stacked weight copies) may replace them - an optimizer that captured `main_grad`
+    would otherwise keep reading a dead tensor - while the stacked copies do follow the new weights."""
+    from types import SimpleNamespace
+    from sonicmoe.ernie_compat import SonicMoEMlpNode
+
+    E, H, I = 2, 8, 4
+    g = torch.Generator().manual_seed(2)
+    experts = [SimpleNamespace(up_gate_proj=SimpleNamespace(weight=torch.randn(H, 2 * I, generator=g)),
+                               down_proj=SimpleNamespace(weight=torch.randn(I, H, generator=g))) for _ in range(E)]
+    node = SonicMoEMlpNode(experts, E, H, I)
+    w1, w2 = node._stacked_weights()
+    held1 = [e.up_gate_proj.weight.main_grad for e in experts]
+    held2 = [e.down_proj.weight.main_grad for e in experts]
+    assert w1.main_grad.data_ptr() == held1[0].data_ptr() and w2.main_grad.data_ptr() == held2[0].data_ptr()
+    held1[1].fill_(3.0)
+
+    experts[0].up_gate_proj.weight.add_(1.0)                     # version counter moves: a new stack, same buffers
+    w1b, _ = node._stacked_weights()
+    assert w1b is not w1 and torch.equal(w1b[0, 0], experts[0].up_gate_proj.weight[:, 0])
+    node.step()
+    experts[1].down_proj.weight.data.copy_(torch.zeros(I, H))    # invisible to the version counter; after step()
+    w1c, w2c = node._stacked_weights()
+    assert torch.equal(w2c[1], torch.zeros(H, I))
+    for e in range(E):
+        assert experts[e].up_gate_proj.weight.main_grad.data_ptr() == held1[e].data_ptr()
+        assert experts[e].down_proj.weight.main_grad.data_ptr() == held2[e].data_ptr()
+    assert w1c.main_grad.data_ptr() == held1[0].data_ptr() and float(held1[1].min()) == 3.0
